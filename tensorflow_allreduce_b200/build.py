@@ -1,0 +1,107 @@
+"""In-tree build of the native library (C++ runtime + sm_100a CUDA kernels).
+
+`python -m tensorflow_allreduce_b200.build` compiles every source under `csrc/` and links
+`lib/libbcoll.so` next to the package, so the binary travels with the source tree. The CUDA
+runtime is linked statically and driver entry points are looked up at run time, so the library
+also loads on machines without a GPU (the CPU collectives and the control plane work there).
+
+Stands where the reference has its Bazel rule `tf_custom_op_library(mpi_collectives.so, ...)`
+(tensorflow/contrib/mpi_collectives/BUILD:38-46).
+"""
+from __future__ import annotations
+
+import concurrent.futures
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+LIBDIR = PKG / "lib"
+OBJDIR = LIBDIR / "obj"
+LIB = LIBDIR / "libbcoll.so"
+
+CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+NVCC = os.environ.get("NVCC", str(Path(CUDA_HOME) / "bin" / "nvcc"))
+CXX = os.environ.get("CXX", "g++")
+
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = ARCH_FLAGS + ["-lineinfo", "-O3", "-std=c++17", "--extended-lambda", "-Xcompiler", "-fPIC,-Wall"]
+CXX_FLAGS = ["-O2", "-g1", "-fPIC", "-std=c++17", "-Wall", "-pthread", f"-I{CUDA_HOME}/include"]
+
+
+def _sources():
+    cc = sorted(p for p in CSRC.rglob("*.cc"))
+    cu = sorted(p for p in CSRC.rglob("*.cu"))
+    return cc, cu
+
+
+def _headers_mtime() -> float:
+    hs = list(CSRC.rglob("*.h")) + list(CSRC.rglob("*.cuh"))
+    return max((h.stat().st_mtime for h in hs), default=0.0)
+
+
+def _obj_for(src: Path) -> Path:
+    rel = src.relative_to(CSRC)
+    return OBJDIR / ("_".join(rel.parts) + ".o")
+
+
+def _compile(src: Path, obj: Path, verbose: bool, extra: list[str]) -> None:
+    if src.suffix == ".cu":
+        cmd = [NVCC] + NVCC_FLAGS + extra + ["-c", str(src), "-o", str(obj)]
+    else:
+        cmd = [CXX] + CXX_FLAGS + extra + ["-c", str(src), "-o", str(obj)]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"compiling {src} failed:\n{r.stdout}\n{r.stderr}")
+    if verbose and (r.stderr.strip() or r.stdout.strip()):
+        print(r.stdout, r.stderr, flush=True)
+
+
+def needs_build() -> bool:
+    if not LIB.exists():
+        return True
+    cc, cu = _sources()
+    newest = max([p.stat().st_mtime for p in cc + cu] + [_headers_mtime()])
+    return newest > LIB.stat().st_mtime
+
+
+def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
+    """Compile what changed and link the shared library. Returns its path."""
+    if shutil.which(NVCC) is None and not Path(NVCC).exists():
+        raise RuntimeError(f"nvcc not found at {NVCC}; set CUDA_HOME or NVCC")
+    OBJDIR.mkdir(parents=True, exist_ok=True)
+    cc, cu = _sources()
+    hm = _headers_mtime()
+    todo = []
+    objs = []
+    for src in cc + cu:
+        obj = _obj_for(src)
+        objs.append(obj)
+        if force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hm):
+            todo.append((src, obj))
+    extra_cu = ["-Xptxas", "-v"] if ptxas_info else []
+    if todo:
+        with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
+            futs = [ex.submit(_compile, s, o, verbose or ptxas_info, extra_cu if s.suffix == ".cu" else []) for s, o in todo]
+            for f in futs:
+                f.result()
+    if todo or not LIB.exists() or force:
+        tmp = LIB.with_suffix(".so.tmp")
+        cmd = [NVCC] + ARCH_FLAGS + ["-shared", "-o", str(tmp)] + [str(o) for o in objs] + ["-lpthread", "-ldl", "-lrt"]
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"linking failed:\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, LIB)
+    return LIB
+
+
+if __name__ == "__main__":
+    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv, ptxas_info="--ptxas" in sys.argv)
+    print(path)

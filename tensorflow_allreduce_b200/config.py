@@ -1,0 +1,81 @@
+"""Run-time configuration: one dataclass, overridable through `BC_*` environment variables.
+
+The reference's collective package has no run-time knobs at all; its only configuration is the
+build-time MPI switch (`configure:823-897`). Everything here is new: algorithm cut-overs, bucket
+size, grid caps, deadlines, symmetric-memory sizes, NVLS on/off and the log level
+(`BC_LOG_LEVEL`, read by the native side).
+"""
+from __future__ import annotations
+
+import dataclasses
+import os
+
+_ALGOS = {"auto": 0, "one_shot": 1, "two_shot": 2, "nvls": 3}
+_SYMM = {"auto": 0, "vmm": 1, "ipc": 2}
+
+
+def _env(name, cast, default):
+    v = os.environ.get(name)
+    if v is None or v == "":
+        return default
+    return cast(v)
+
+
+def _flag(v: str) -> bool:
+    return str(v).strip().lower() not in ("0", "false", "no", "off", "")
+
+
+@dataclasses.dataclass
+class Config:
+    """Settings read at `init()`; every rank must use the same values."""
+
+    timeout_s: float = 300.0           # host-side deadline: bootstrap, negotiation, ring steps
+    device_timeout_s: float = 30.0     # bound of every device-side wait on a peer
+    staging_mb: int = 64               # symmetric staging area for tensors outside symmetric memory
+    heap_mb: int = 256                 # symmetric heap for allgather outputs and `symm_empty`
+    algo: str = "auto"                 # force one of: one_shot, two_shot, nvls
+    one_shot_max_kb: int = 256         # messages up to this size use the one-shot kernel
+    nvls_min_kb: int = 512             # messages from this size use NVLS when multicast is bound
+    nvls: bool = True                  # bind a multicast object to symmetric segments when possible
+    max_blocks: int = 0                # cap on CTAs per collective kernel (0 = heuristic)
+    symm: str = "auto"                 # symmetric memory back end: vmm (fd passing) or ipc
+    bucket_mb: float = 32.0            # DistributedOptimizer gradient bucket size
+    fault: str = ""                    # host-side fault injection, e.g. "drop_request:rank=1:name=x"
+
+    @classmethod
+    def from_env(cls, **overrides) -> "Config":
+        c = cls(
+            timeout_s=_env("BC_TIMEOUT_S", float, cls.timeout_s),
+            device_timeout_s=_env("BC_DEVICE_TIMEOUT_S", float, cls.device_timeout_s),
+            staging_mb=_env("BC_STAGING_MB", int, cls.staging_mb),
+            heap_mb=_env("BC_HEAP_MB", int, cls.heap_mb),
+            algo=_env("BC_ALGO", str, cls.algo),
+            one_shot_max_kb=_env("BC_ONE_SHOT_MAX_KB", int, cls.one_shot_max_kb),
+            nvls_min_kb=_env("BC_NVLS_MIN_KB", int, cls.nvls_min_kb),
+            nvls=_env("BC_NVLS", _flag, cls.nvls),
+            max_blocks=_env("BC_MAX_BLOCKS", int, cls.max_blocks),
+            symm=_env("BC_SYMM", str, cls.symm),
+            bucket_mb=_env("BC_BUCKET_MB", float, cls.bucket_mb),
+            fault=_env("BC_FAULT", str, cls.fault),
+        )
+        for k, v in overrides.items():
+            if v is not None:
+                setattr(c, k, v)
+        c.validate()
+        return c
+
+    def validate(self) -> None:
+        if self.algo not in _ALGOS:
+            raise ValueError(f"BC_ALGO must be one of {sorted(_ALGOS)}, got {self.algo!r}")
+        if self.symm not in _SYMM:
+            raise ValueError(f"BC_SYMM must be one of {sorted(_SYMM)}, got {self.symm!r}")
+        if self.timeout_s <= 0 or self.device_timeout_s <= 0:
+            raise ValueError("timeouts must be positive")
+
+    @property
+    def algo_code(self) -> int:
+        return _ALGOS[self.algo]
+
+    @property
+    def symm_code(self) -> int:
+        return _SYMM[self.symm]

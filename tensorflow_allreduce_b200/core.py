@@ -1,0 +1,468 @@
+"""Process group and the two collectives: the Python face of the native runtime.
+
+API parity with `tensorflow/contrib/mpi_collectives` (`__init__.py:114-164`, `mpi_ops.py:62-160`):
+`init / size / rank / local_rank`, `allreduce(tensor, average=True)` for dense and sparse tensors,
+`allgather(tensor)` with a per-rank first dimension. Collectives are keyed by name; a name given
+by only some ranks, or with mismatching dtype / shape / operation, fails on every rank with the
+reference's error wording instead of hanging. Collective results carry no autograd history
+(the reference marks the ops NotDifferentiable, `mpi_ops.py:135,163`).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import itertools
+import json
+import os
+import threading
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import _lib
+from .config import Config
+
+__all__ = [
+    "CollectiveError", "init", "shutdown", "is_initialized", "size", "rank", "local_rank", "local_size",
+    "allreduce", "allreduce_", "allreduce_async", "allgather", "allgather_async", "broadcast", "barrier",
+    "host_allgather", "stats", "clear_stats", "on_gpu", "config", "set_fault", "check_device_status",
+]
+
+
+class CollectiveError(RuntimeError):
+    """A collective failed: mismatched requests, a lost peer, a timeout, or use before `init()`.
+
+    Counterpart of the reference's `FailedPreconditionError` (mpi_ops.cc:506-507, 827-833)."""
+
+
+_DTYPES = {
+    torch.float32: 0, torch.int32: 1, torch.int64: 2, torch.bfloat16: 3, torch.float16: 4,
+    torch.float64: 5, torch.uint8: 6,
+}
+
+_state = {"config": None, "device": None}
+_counter_lock = threading.Lock()
+_counters = {"allreduce": itertools.count(), "allgather": itertools.count(), "blob": itertools.count(),
+             "broadcast": itertools.count(), "barrier": itertools.count()}
+_tokens = itertools.count(1)
+_pending_allocs = {}
+
+
+def _call(rc, what=""):
+    try:
+        return _lib.check(rc, what)
+    except _lib.NativeError as e:
+        raise CollectiveError(str(e)) from None
+
+
+def _auto_name(kind: str) -> str:
+    with _counter_lock:
+        return f"{kind}.{next(_counters[kind])}"
+
+
+def _env_rank_size():
+    """Rank / size / local rank from the launcher's environment. torchrun's names first, then the
+    Open MPI and PMI names that the reference's tests read (mpi_ops_test.py:30-62)."""
+    env = os.environ
+    for r, s, lr in (("RANK", "WORLD_SIZE", "LOCAL_RANK"),
+                     ("OMPI_COMM_WORLD_RANK", "OMPI_COMM_WORLD_SIZE", "OMPI_COMM_WORLD_LOCAL_RANK"),
+                     ("PMI_RANK", "PMI_SIZE", "MPI_LOCALRANKID")):
+        if r in env and s in env:
+            return int(env[r]), int(env[s]), (int(env[lr]) if lr in env else -1)
+    return 0, 1, -1
+
+
+def _resolve_port(rank_: int, size_: int, addr: str) -> int:
+    """Port of the control plane's rendezvous.
+
+    Under torchrun the port in MASTER_PORT belongs to the launcher's key-value store, so rank 0
+    picks a free port and publishes it through that store. Otherwise `BC_PORT` or MASTER_PORT is
+    used directly (nothing else is listening there)."""
+    if "BC_PORT" in os.environ:
+        return int(os.environ["BC_PORT"])
+    port = int(os.environ.get("MASTER_PORT", "29500"))
+    if size_ > 1 and os.environ.get("TORCHELASTIC_USE_AGENT_STORE", "") == "True":
+        import datetime
+        import socket
+
+        from torch.distributed import TCPStore
+
+        store = TCPStore(addr, port, size_, is_master=False, timeout=datetime.timedelta(seconds=300))
+        key = "bcoll/ctrl_port/" + os.environ.get("TORCHELASTIC_RUN_ID", "0") + "/" + os.environ.get("TORCHELASTIC_RESTART_COUNT", "0")
+        if rank_ == 0:
+            with socket.socket() as s:
+                s.bind(("", 0))
+                free = s.getsockname()[1]
+            store.set(key, str(free))
+            return free
+        return int(store.get(key).decode())
+    return port
+
+
+def init(device=None, config: Optional[Config] = None, rank: Optional[int] = None, size: Optional[int] = None,
+         addr: Optional[str] = None, port: Optional[int] = None) -> None:
+    """Start the runtime of this process and join the group.
+
+    `device` is a CUDA device (index, `torch.device`, or "cuda") to bind to, `"cpu"` for a
+    host-only group, or None: then `cuda:LOCAL_RANK` is used when CUDA is available, else the CPU.
+    Like the reference, the group is bound to that one device (mpi_ops.cc:900-907); CPU tensors
+    are accepted by a GPU group as well.
+    """
+    lib = _lib.lib()
+    if lib.bc_initialized():
+        raise CollectiveError("init() was already called in this process")
+    cfg = config or Config.from_env()
+    cfg.validate()
+    env_rank, env_size, env_local = _env_rank_size()
+    rank_ = env_rank if rank is None else rank
+    size_ = env_size if size is None else size
+    addr_ = addr or os.environ.get("MASTER_ADDR", "127.0.0.1")
+    port_ = port if port is not None else _resolve_port(rank_, size_, addr_)
+
+    dev_index = -1
+    if device is None:
+        if torch.cuda.is_available():
+            dev_index = env_local if env_local >= 0 else rank_ % max(torch.cuda.device_count(), 1)
+    elif isinstance(device, int):
+        dev_index = device
+    else:
+        d = torch.device(device)
+        if d.type == "cuda":
+            dev_index = d.index if d.index is not None else (env_local if env_local >= 0 else torch.cuda.current_device())
+        elif d.type != "cpu":
+            raise ValueError(f"unsupported device {device!r}")
+    if dev_index >= 0:
+        torch.cuda.set_device(dev_index)
+        torch.cuda.init()
+
+    _call(lib.bc_init(rank_, size_, env_local, addr_.encode(), port_, dev_index, cfg.timeout_s, cfg.device_timeout_s,
+                      cfg.staging_mb << 20, cfg.heap_mb << 20, cfg.algo_code, cfg.one_shot_max_kb << 10,
+                      cfg.nvls_min_kb << 10, int(cfg.nvls), cfg.max_blocks, cfg.symm_code, cfg.fault.encode()), "bc_init")
+    _state["config"] = cfg
+    _state["device"] = dev_index
+    for k in _counters:
+        _counters[k] = itertools.count()
+
+
+def shutdown() -> None:
+    """Leave the group: a last handshake with the other ranks, then stop the background thread."""
+    lib = _lib.lib()
+    if lib.bc_initialized():
+        from .ops import symmetric
+
+        symmetric._reset()
+        _call(lib.bc_shutdown(), "bc_shutdown")
+    _state["config"] = None
+    _state["device"] = None
+
+
+def is_initialized() -> bool:
+    return bool(_lib.lib().bc_initialized())
+
+
+def size() -> int:
+    """Number of ranks (reference: `mpi_ops.py:62-71`)."""
+    return _call(_lib.lib().bc_size())
+
+
+def rank() -> int:
+    """Rank of this process (reference: `mpi_ops.py:77-86`)."""
+    return _call(_lib.lib().bc_rank())
+
+
+def local_rank() -> int:
+    """Rank among the processes of this host; pick the GPU with it (reference: `mpi_ops.py:104-115`)."""
+    return _call(_lib.lib().bc_local_rank())
+
+
+def local_size() -> int:
+    return _call(_lib.lib().bc_local_size())
+
+
+def on_gpu() -> bool:
+    return bool(_call(_lib.lib().bc_on_gpu()))
+
+
+def config() -> Config:
+    if _state["config"] is None:
+        raise CollectiveError("MPI has not been initialized; use Session or init() first.")
+    return _state["config"]
+
+
+def set_fault(spec: str) -> None:
+    """Arm a host-side fault (tests): `drop_request`, `delay_ms=N`, `exit_before`, `close_ctrl`,
+    each optionally followed by `:rank=R` and `:name=NAME`."""
+    _call(_lib.lib().bc_set_fault(spec.encode()))
+
+
+def check_device_status() -> None:
+    """Raise if a device-side wait on a peer has timed out since `init()`."""
+    st = _lib.lib().bc_device_status()
+    if st:
+        raise CollectiveError(f"a device-side wait on a peer timed out (status 0x{st:08x}); the group is unusable")
+
+
+# ---- handles -----------------------------------------------------------------------------------
+
+
+class Handle:
+    """An in-flight collective. `wait()` returns the result tensor.
+
+    For CUDA tensors `wait()` blocks the host only until the kernel has been enqueued on the
+    library's private stream, then makes the caller's current stream wait for it on the device."""
+
+    def __init__(self, hid: int, keep, on_gpu_: bool, result=None, finalize=None):
+        self._hid = hid
+        self._keep = keep
+        self._gpu = on_gpu_
+        self._result = result
+        self._finalize = finalize
+        self._done = False
+        self.algo = 0
+
+    def done(self) -> bool:
+        return self._done or bool(_call(_lib.lib().bc_poll(self._hid)))
+
+    def wait(self, timeout_s: Optional[float] = None):
+        if self._done:
+            return self._result
+        lib = _lib.lib()
+        t = timeout_s if timeout_s is not None else config().timeout_s + 10.0
+        try:
+            _call(lib.bc_wait(self._hid, float(t)))
+            if self._gpu:
+                ev = lib.bc_done_event(self._hid)
+                _call(lib.bc_stream_wait_event(C.c_void_p(torch.cuda.current_stream().cuda_stream), C.c_void_p(ev)))
+            self.algo = lib.bc_result_algo(self._hid)
+            if self._finalize is not None:
+                self._result = self._finalize(self)
+        finally:
+            lib.bc_release(self._hid)
+            self._done = True
+            self._keep = None
+        return self._result
+
+
+def _prep(tensor: torch.Tensor):
+    if tensor.dtype not in _DTYPES:
+        raise CollectiveError(f"unsupported dtype {tensor.dtype}; supported: {sorted(str(k) for k in _DTYPES)}")
+    t = tensor.detach()
+    if not t.is_contiguous():
+        t = t.contiguous()
+    if t.is_cuda and t.data_ptr() % 16 != 0:
+        t = t.clone()
+    return t
+
+
+def _shape_array(shape: Sequence[int]):
+    arr = (C.c_longlong * max(len(shape), 1))(*shape)
+    return arr
+
+
+def _ready_event(t: torch.Tensor):
+    if not t.is_cuda:
+        return None
+    ev = torch.cuda.Event()
+    ev.record(torch.cuda.current_stream(t.device))
+    return ev
+
+
+def allreduce_async(tensor: torch.Tensor, average: bool = True, name: Optional[str] = None, out: Optional[torch.Tensor] = None) -> Handle:
+    """Start a sum (or average) over all ranks; returns a `Handle`."""
+    lib = _lib.lib()
+    name = name or _auto_name("allreduce")
+    t = _prep(tensor)
+    in_place = out is not None and out.data_ptr() == t.data_ptr() and out.is_contiguous()
+    if out is None or (not in_place and (not out.is_contiguous() or out.shape != t.shape or out.dtype != t.dtype
+                                         or (out.is_cuda and out.data_ptr() % 16 != 0))):
+        result = torch.empty_like(t)
+        copy_back = out
+    else:
+        result = out.detach()
+        copy_back = None
+    ev = _ready_event(t)
+    zero_copy = int(in_place and t.is_cuda)
+    hid = _call(lib.bc_allreduce_async(name.encode(), C.c_void_p(t.data_ptr()), C.c_void_p(result.data_ptr()), _DTYPES[t.dtype],
+                                       t.dim(), _shape_array(t.shape), int(t.is_cuda), int(average), zero_copy,
+                                       C.c_void_p(ev.cuda_event) if ev is not None else None), "allreduce")
+
+    def fin(_h):
+        if copy_back is not None:
+            copy_back.copy_(result)
+            return copy_back
+        return result
+
+    return Handle(hid, (t, result, ev, out), t.is_cuda, finalize=fin)
+
+
+def allreduce(tensor: torch.Tensor, average: bool = True, name: Optional[str] = None) -> torch.Tensor:
+    """Sum `tensor` over all ranks, or average it (`average=True`, the default).
+
+    Dense tensors of identical shape and dtype on every rank give a new tensor of that shape.
+    Integer tensors are averaged with truncating integer division. A sparse COO tensor is reduced
+    the way the reference reduces `IndexedSlices` (`__init__.py:148-158`): values and indices are
+    allgathered, values divided by `size()` when averaging; repeated indices are left uncoalesced
+    and sum up when the tensor is used.
+    """
+    if tensor.is_sparse:
+        base = name or _auto_name("allreduce")
+        t = tensor.detach()
+        idx = t._indices().t().contiguous()          # [nnz, ndim]
+        vals = t._values().contiguous()              # [nnz, ...]
+        g_vals = allgather(vals, name=base + ".values")
+        g_idx = allgather(idx, name=base + ".indices")
+        if average:
+            g_vals = g_vals / size() if g_vals.is_floating_point() else torch.div(g_vals, size(), rounding_mode="trunc")
+        return torch.sparse_coo_tensor(g_idx.t(), g_vals, t.shape)
+    return allreduce_async(tensor, average=average, name=name).wait()
+
+
+def allreduce_(tensor: torch.Tensor, average: bool = True, name: Optional[str] = None) -> torch.Tensor:
+    """In-place `allreduce`. A CUDA tensor that lives in symmetric memory (see `ops.symmetric`) at
+    the same place on every rank is reduced where it is, with no staging copy."""
+    if not tensor.is_contiguous():
+        raise CollectiveError("allreduce_ needs a contiguous tensor")
+    allreduce_async(tensor, average=average, name=name, out=tensor).wait()
+    return tensor
+
+
+@_lib.ALLOC_FN
+def _alloc_callback(handle, total_rows, user, is_symm):
+    # Runs on the native background thread once every rank's first dimension is known.
+    try:
+        ctx = _pending_allocs.get(int(user or 0))
+        if ctx is None:
+            return None
+        t = ctx["input"]
+        shape = (int(total_rows),) + tuple(t.shape[1:])
+        out = None
+        if t.is_cuda:
+            from .ops import symmetric
+
+            out = symmetric.try_empty(shape, t.dtype, t.device)
+            if out is not None:
+                is_symm[0] = 1
+        if out is None:
+            is_symm[0] = 0
+            out = torch.empty(shape, dtype=t.dtype, device=t.device)
+        ctx["out"] = out
+        return out.data_ptr() if out.numel() else None
+    except Exception as e:  # never let an exception cross into native code
+        ctx = _pending_allocs.get(int(user or 0))
+        if ctx is not None:
+            ctx["error"] = e
+        return None
+
+
+def allgather_async(tensor: torch.Tensor, name: Optional[str] = None) -> Handle:
+    """Start a concatenation along dimension 0 over all ranks; returns a `Handle`."""
+    lib = _lib.lib()
+    name = name or _auto_name("allgather")
+    t = _prep(tensor)
+    token = next(_tokens)
+    ctx = {"input": t, "out": None, "error": None}
+    _pending_allocs[token] = ctx
+    ev = _ready_event(t)
+    try:
+        hid = _call(lib.bc_allgather_async(name.encode(), C.c_void_p(t.data_ptr()), _DTYPES[t.dtype], t.dim(), _shape_array(t.shape),
+                                           int(t.is_cuda), _alloc_callback, C.c_void_p(token),
+                                           C.c_void_p(ev.cuda_event) if ev is not None else None), "allgather")
+    except Exception:
+        _pending_allocs.pop(token, None)
+        raise
+
+    def fin(h):
+        _pending_allocs.pop(token, None)
+        if ctx["error"] is not None:
+            raise CollectiveError(f"allgather output allocation failed: {ctx['error']}")
+        n = size()
+        dims = (C.c_longlong * n)()
+        _call(lib.bc_result_dim0(h._hid, dims, n))
+        h.sizes = [int(x) for x in dims]
+        out = ctx["out"]
+        if out is None:
+            out = torch.empty((0,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        return out
+
+    h = Handle(hid, (t, ev, ctx), t.is_cuda, finalize=fin)
+    orig_wait = h.wait
+
+    def wait(timeout_s=None):
+        try:
+            return orig_wait(timeout_s)
+        finally:
+            _pending_allocs.pop(token, None)
+
+    h.wait = wait
+    return h
+
+
+def allgather(tensor: torch.Tensor, name: Optional[str] = None) -> torch.Tensor:
+    """Concatenate `tensor` from all ranks along dimension 0, in rank order.
+
+    Ranks may differ in the first dimension (zero rows included); all other dimensions and the
+    dtype must match, and the tensor must have at least one dimension
+    (reference: `mpi_ops.py:138-160`, `ring.h:230-301`). One negotiation round carries every
+    rank's row count, so there is no separate sizing pass. On CUDA the result lives in the
+    library's symmetric heap when it fits (peers store their rows straight into it)."""
+    return allgather_async(tensor, name=name).wait()
+
+
+def broadcast(tensor: torch.Tensor, root: int = 0, name: Optional[str] = None) -> torch.Tensor:
+    """Value of `tensor` on rank `root`, delivered to every rank (same shape and dtype everywhere).
+
+    The reference has no broadcast; this is an allgather in which only `root` contributes rows."""
+    name = name or _auto_name("broadcast")
+    flat = tensor.detach().reshape(-1)
+    part = flat if rank() == root else flat[:0]
+    out = allgather(part, name=name)
+    return out.reshape(tensor.shape)
+
+
+def host_allgather(obj, name: Optional[str] = None) -> List:
+    """Allgather of one small picklable Python object per rank through the control plane."""
+    import pickle
+
+    lib = _lib.lib()
+    name = name or _auto_name("blob")
+    data = pickle.dumps(obj)
+    n = size()
+    cap = max(1 << 20, len(data) * n * 4 + 4096)
+    for _ in range(2):
+        buf = C.create_string_buffer(cap)
+        lens = (C.c_int * n)()
+        rc = lib.bc_blob_gather(name.encode(), data, len(data), buf, cap, lens)
+        if rc == 0:
+            break
+        if "too small" in _lib.last_error():
+            raise CollectiveError("host_allgather payloads are limited to about 1 MiB per rank")
+        _call(rc)
+    out, pos = [], 0
+    for r in range(n):
+        out.append(pickle.loads(buf.raw[pos:pos + lens[r]]))
+        pos += lens[r]
+    return out
+
+
+def barrier(name: Optional[str] = None) -> None:
+    """Host-side barrier over the control plane."""
+    host_allgather(None, name=name or _auto_name("barrier"))
+
+
+def stats() -> List[dict]:
+    """One record per completed collective since the last `clear_stats()`: name, operation,
+    algorithm, bytes, CTA count and host timestamps (enqueue, negotiated, done/launched)."""
+    raw = _lib.lib().bc_stats_json()
+    if not raw:
+        raise CollectiveError(_lib.last_error())
+    ops = {0: "allreduce", 1: "allgather", 2: "host_gather", 3: "shutdown"}
+    algos = {0: "cpu_ring", 1: "one_shot", 2: "two_shot", 3: "nvls"}
+    out = json.loads(raw.decode())
+    for e in out:
+        e["op"] = ops.get(e["op"], str(e["op"]))
+        e["algo"] = algos.get(e["algo"], str(e["algo"])) if e["device"] == 1 else "cpu_ring"
+        e["negotiation_us"] = (e["t_negotiated"] - e["t_enqueue"]) * 1e6
+    return out
+
+
+def clear_stats() -> None:
+    _call(_lib.lib().bc_clear_stats())

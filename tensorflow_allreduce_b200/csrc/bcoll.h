@@ -1,0 +1,101 @@
+/* Public C interface of the native collectives library.
+ *
+ * Conventions: functions return 0 or a non-negative value on success and -1 (or NULL) on failure;
+ * bc_last_error() gives the message for the calling thread. dtype codes: 0 float32, 1 int32,
+ * 2 int64, 3 bfloat16, 4 float16, 5 float64, 6 uint8. device_kind: 0 host memory, 1 CUDA memory.
+ * Algorithm codes: 1 one-shot, 2 two-shot, 3 NVLS (multimem).
+ */
+#ifndef BCOLL_H_
+#define BCOLL_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+const char* bc_last_error(void);
+
+/* Process group. `device` is a CUDA ordinal or -1 for a host-only group. Byte sizes <= 0 (or < 0
+ * where 0 is meaningful) keep the defaults. `fault` is a host-side fault-injection spec or NULL. */
+int bc_init(int rank, int size, int local_rank, const char* addr, int port, int device, double timeout_s,
+            double device_timeout_s, long long staging_bytes, long long heap_bytes, int force_algo,
+            long long one_shot_max_bytes, long long nvls_min_bytes, int use_nvls, int max_blocks, int symm_mode,
+            const char* fault);
+int bc_initialized(void);
+int bc_shutdown(void);
+int bc_rank(void);
+int bc_size(void);
+int bc_local_rank(void);
+int bc_local_size(void);
+int bc_on_gpu(void);
+int bc_broken(void);
+
+/* Negotiated, name-keyed collectives. The returned handle must be released. For CUDA tensors
+ * `ready_event` (a cudaEvent_t or NULL) is what the private stream waits on before touching the
+ * input, and bc_done_event() is what the consumer's stream must wait on after bc_wait(). */
+typedef void* (*bc_alloc_fn)(long long handle, long long total_rows, void* user, int* is_symmetric);
+long long bc_allreduce_async(const char* name, const void* in, void* out, int dtype, int ndim, const long long* shape,
+                             int device_kind, int average, int zero_copy, void* ready_event);
+long long bc_allgather_async(const char* name, const void* in, int dtype, int ndim, const long long* shape, int device_kind,
+                             bc_alloc_fn alloc, void* user, void* ready_event);
+int bc_wait(long long handle, double timeout_s);
+int bc_poll(long long handle);
+void* bc_done_event(long long handle);
+int bc_result_algo(long long handle);
+int bc_result_dim0(long long handle, long long* out, int n);
+int bc_release(long long handle);
+/* Host allgather of one small blob per rank; `out` receives them back to back, `lens[r]` their sizes. */
+int bc_blob_gather(const char* name, const void* data, int len, void* out, long long out_cap, int* lens);
+
+int bc_set_fault(const char* spec);
+const char* bc_stats_json(void);
+int bc_clear_stats(void);
+unsigned bc_device_status(void);
+int bc_set_device_timeout(double seconds);
+
+/* Symmetric memory (CUDA groups only). */
+void* bc_symm_heap(long long* bytes);
+void* bc_symm_new_segment(long long bytes, int* seg_id, int* has_multicast); /* collective */
+int bc_symm_contains(const void* p, long long bytes);
+const char* bc_symm_describe(void);
+void* bc_comm_stream(int channel);
+/* cudaStreamWaitEvent(stream, event) for raw handles (e.g. a torch stream and bc_done_event()). */
+int bc_stream_wait_event(void* stream, void* event);
+
+/* Optimizer update fused behind a gradient reduction; mirrors bc::gpu::OptHyper. */
+typedef struct bc_opt_hyper {
+  int kind; /* 1 SGD, 2 Adam */
+  float lr, weight_decay, momentum, dampening;
+  int nesterov, first_step;
+  float beta1, beta2, eps, bias_c1, bias_c2;
+  int decoupled_wd, tf_epsilon_hat, zero_grad;
+} bc_opt_hyper;
+
+/* Ordered launches on a channel's private stream, without negotiation: every rank must issue the
+ * same sequence of calls per channel. `wait_event` / `record_event` are cudaEvent_t or NULL. */
+int bc_allreduce_direct(int channel, const void* in, void* out, long long count, int dtype, int average,
+                        void* wait_event, void* record_event);
+int bc_fused_step(int channel, void* grad, long long count, int dtype, void* param, float* master, float* s1, float* s2,
+                  const bc_opt_hyper* h, float scale, void* wait_event, void* record_event);
+
+/* A group of ranks emulated on ONE GPU: each collective is a single cooperative launch. */
+void* bc_emu_create(int device, int nranks, long long bytes_per_rank);
+int bc_emu_destroy(void* g);
+void* bc_emu_buffer(void* g, int r);
+unsigned bc_emu_status(void* g);
+int bc_emu_allreduce(void* g, long long off, void* const* outs, long long count, int dtype, int algo, float scale, int idiv,
+                     int blocks, void* stream);
+int bc_emu_fused_step(void* g, long long off, long long count, int dtype, void* const* params, float* const* masters,
+                      float* const* s1, float* const* s2, const bc_opt_hyper* h, float scale, int blocks, void* stream);
+int bc_emu_allgatherv(void* g, const void* const* ins, const unsigned long long* bytes, const unsigned long long* out_offs,
+                      int blocks, void* stream);
+int bc_emu_barrier_probe(void* g, int absent, double timeout_s, void* stream);
+int bc_max_emulated_blocks(int device, int nranks);
+
+/* Coordinator validation run on synthetic requests (unit tests). Returns the response type. */
+int bc_test_validate(int nranks, const int* ops, const int* dtypes, const int* devices, const int* ndims,
+                     const long long* shapes, char* err_out, int err_cap, long long* dim0_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BCOLL_H_ */

@@ -1,0 +1,368 @@
+// C ABI of the native library (loaded from Python with ctypes; declarations in bcoll.h).
+//
+// This is the analogue of the reference's op registrations (MPIInit / MPISize / MPIRank /
+// MPILocalRank / MPIAllreduce / MPIAllgather, tensorflow/contrib/mpi_collectives/mpi_ops.cc:878-1270):
+// thin entry points over the runtime. Every function returns 0 / a non-negative value on success
+// and -1 on failure; bc_last_error() then holds the message for the calling thread.
+#include "bcoll.h"
+
+#include <cuda_runtime.h>
+#include <string.h>
+
+#include <memory>
+#include <mutex>
+
+#include "cuda/comm.h"
+#include "runtime/runtime.h"
+
+using namespace bc;
+
+namespace {
+
+std::unique_ptr<Runtime> g_rt;
+std::mutex g_mu;
+thread_local std::string t_err;
+thread_local std::string t_str;
+int64_t g_segment_seq = 0;
+
+Runtime& rt() {
+  if (!g_rt) throw Error("MPI has not been initialized; use Session or init() first.");
+  return *g_rt;
+}
+
+gpu::Comm& comm() {
+  Runtime& r = rt();
+  if (!r.comm()) throw Error("init() ran without a GPU device; GPU collectives are unavailable");
+  return *r.comm();
+}
+
+#define API_BEGIN try {
+#define API_END(fail)                      \
+  }                                        \
+  catch (const std::exception& e) {        \
+    t_err = e.what();                      \
+    return fail;                           \
+  }                                        \
+  catch (...) {                            \
+    t_err = "unknown native error";        \
+    return fail;                           \
+  }
+
+void check_cuda(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) throw Error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* bc_last_error() { return t_err.c_str(); }
+
+int bc_init(int rank, int size, int local_rank, const char* addr, int port, int device, double timeout_s,
+            double device_timeout_s, long long staging_bytes, long long heap_bytes, int force_algo,
+            long long one_shot_max_bytes, long long nvls_min_bytes, int use_nvls, int max_blocks, int symm_mode,
+            const char* fault) {
+  API_BEGIN
+  std::lock_guard<std::mutex> g(g_mu);
+  if (g_rt) throw Error("init() was already called in this process");
+  RuntimeOptions o;
+  o.rank = rank;
+  o.size = size;
+  o.local_rank_override = local_rank;
+  o.addr = addr ? addr : "127.0.0.1";
+  o.port = port;
+  o.device = device;
+  o.timeout_s = timeout_s;
+  o.device_timeout_s = device_timeout_s;
+  if (staging_bytes > 0) o.staging_bytes = (size_t)staging_bytes;
+  if (heap_bytes >= 0) o.heap_bytes = (size_t)heap_bytes;
+  o.force_algo = force_algo;
+  if (one_shot_max_bytes >= 0) o.one_shot_max_bytes = (size_t)one_shot_max_bytes;
+  if (nvls_min_bytes >= 0) o.nvls_min_bytes = (size_t)nvls_min_bytes;
+  o.use_nvls = use_nvls != 0;
+  o.max_blocks = max_blocks;
+  o.symm_mode = symm_mode;
+  o.fault = fault ? fault : "";
+  g_rt.reset(new Runtime(o));
+  return 0;
+  API_END(-1)
+}
+
+int bc_initialized() { return g_rt ? 1 : 0; }
+
+int bc_shutdown() {
+  API_BEGIN
+  std::lock_guard<std::mutex> g(g_mu);
+  if (g_rt) {
+    g_rt->shutdown();
+    g_rt.reset();
+  }
+  return 0;
+  API_END(-1)
+}
+
+int bc_rank() { API_BEGIN return rt().rank(); API_END(-1) }
+int bc_size() { API_BEGIN return rt().size(); API_END(-1) }
+int bc_local_rank() { API_BEGIN return rt().local_rank(); API_END(-1) }
+int bc_local_size() { API_BEGIN return rt().local_size(); API_END(-1) }
+int bc_on_gpu() { API_BEGIN return rt().on_gpu() ? 1 : 0; API_END(-1) }
+int bc_broken() { API_BEGIN return rt().broken() ? 1 : 0; API_END(-1) }
+
+long long bc_allreduce_async(const char* name, const void* in, void* out, int dtype, int ndim, const long long* shape,
+                             int device_kind, int average, int zero_copy, void* ready_event) {
+  API_BEGIN
+  std::unique_ptr<OpRecord> r(new OpRecord());
+  r->name = name;
+  r->op = OpType::ALLREDUCE;
+  r->dtype = (DType)dtype;
+  r->device = (DeviceKind)device_kind;
+  r->shape.assign(shape, shape + ndim);
+  r->in = in;
+  r->out = out;
+  r->average = average != 0;
+  r->zero_copy = zero_copy != 0;
+  r->ready_event = ready_event;
+  return rt().enqueue(std::move(r));
+  API_END(-1)
+}
+
+long long bc_allgather_async(const char* name, const void* in, int dtype, int ndim, const long long* shape, int device_kind,
+                             bc_alloc_fn alloc, void* user, void* ready_event) {
+  API_BEGIN
+  std::unique_ptr<OpRecord> r(new OpRecord());
+  r->name = name;
+  r->op = OpType::ALLGATHER;
+  r->dtype = (DType)dtype;
+  r->device = (DeviceKind)device_kind;
+  r->shape.assign(shape, shape + ndim);
+  r->in = in;
+  r->alloc = (AllocFn)alloc;
+  r->alloc_user = user;
+  r->ready_event = ready_event;
+  return rt().enqueue(std::move(r));
+  API_END(-1)
+}
+
+int bc_wait(long long handle, double timeout_s) {
+  API_BEGIN
+  rt().wait(handle, timeout_s);
+  return 0;
+  API_END(-1)
+}
+
+int bc_poll(long long handle) { API_BEGIN return rt().poll(handle) ? 1 : 0; API_END(-1) }
+
+void* bc_done_event(long long handle) { API_BEGIN return rt().get(handle)->done_event; API_END(nullptr) }
+
+int bc_result_algo(long long handle) { API_BEGIN return rt().get(handle)->algo; API_END(-1) }
+
+int bc_result_dim0(long long handle, long long* out, int n) {
+  API_BEGIN
+  auto r = rt().get(handle);
+  if ((int)r->dim0.size() != n) throw Error("bc_result_dim0: size mismatch");
+  for (int i = 0; i < n; i++) out[i] = r->dim0[i];
+  return 0;
+  API_END(-1)
+}
+
+int bc_release(long long handle) { API_BEGIN rt().release(handle); return 0; API_END(-1) }
+
+int bc_blob_gather(const char* name, const void* data, int len, void* out, long long out_cap, int* lens) {
+  API_BEGIN
+  std::vector<std::string> all = rt().blob_gather(name, std::string((const char*)data, (size_t)len));
+  long long pos = 0;
+  for (size_t r = 0; r < all.size(); r++) {
+    if (pos + (long long)all[r].size() > out_cap) throw Error("bc_blob_gather: output buffer too small");
+    memcpy((char*)out + pos, all[r].data(), all[r].size());
+    lens[r] = (int)all[r].size();
+    pos += (long long)all[r].size();
+  }
+  return 0;
+  API_END(-1)
+}
+
+int bc_set_fault(const char* spec) { API_BEGIN rt().set_fault(spec ? spec : ""); return 0; API_END(-1) }
+
+const char* bc_stats_json() {
+  API_BEGIN
+  t_str = rt().stats_json();
+  return t_str.c_str();
+  API_END(nullptr)
+}
+
+int bc_clear_stats() { API_BEGIN rt().clear_stats(); return 0; API_END(-1) }
+
+unsigned bc_device_status() { API_BEGIN return rt().comm() ? rt().comm()->device_status() : 0u; API_END(0u) }
+
+int bc_set_device_timeout(double s) { API_BEGIN comm().set_device_timeout(s); return 0; API_END(-1) }
+
+// ---- symmetric memory -------------------------------------------------------------------------
+
+void* bc_symm_heap(long long* bytes) {
+  API_BEGIN
+  if (bytes) *bytes = (long long)comm().heap_bytes();
+  return comm().heap_base();
+  API_END(nullptr)
+}
+
+void* bc_symm_new_segment(long long bytes, int* seg_id, int* has_multicast) {
+  API_BEGIN
+  Runtime& r = rt();
+  gpu::Comm& c = comm();
+  const int64_t seq = g_segment_seq++;
+  int64_t step = 0;
+  gpu::HostAllgather ag = [&](const std::string& mine) {
+    return r.blob_gather("__symm." + std::to_string(seq) + "." + std::to_string(step++), mine);
+  };
+  gpu::Segment* s = c.new_segment((size_t)bytes, ag);
+  if (seg_id) *seg_id = s->id;
+  if (has_multicast) *has_multicast = s->mc ? 1 : 0;
+  return s->local;
+  API_END(nullptr)
+}
+
+int bc_symm_contains(const void* p, long long bytes) {
+  API_BEGIN
+  return comm().allocator().find(p, (size_t)bytes) ? 1 : 0;
+  API_END(-1)
+}
+
+const char* bc_symm_describe() {
+  API_BEGIN
+  t_str = comm().allocator().describe();
+  return t_str.c_str();
+  API_END(nullptr)
+}
+
+void* bc_comm_stream(int channel) {
+  API_BEGIN
+  if (channel < 0 || channel >= dev::kChannels) throw Error("bad channel");
+  return comm().stream(channel);
+  API_END(nullptr)
+}
+
+int bc_stream_wait_event(void* stream, void* event) {
+  API_BEGIN
+  if (event) check_cuda(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)event, 0), "cudaStreamWaitEvent");
+  return 0;
+  API_END(-1)
+}
+
+// ---- ordered launches (no negotiation; every rank must issue the same sequence per channel) ------
+
+static void stream_prologue(cudaStream_t s, void* wait_event) {
+  if (wait_event) check_cuda(cudaStreamWaitEvent(s, (cudaEvent_t)wait_event, 0), "cudaStreamWaitEvent");
+}
+static void stream_epilogue(cudaStream_t s, void* record_event) {
+  if (record_event) check_cuda(cudaEventRecord((cudaEvent_t)record_event, s), "cudaEventRecord");
+}
+
+int bc_allreduce_direct(int channel, const void* in, void* out, long long count, int dtype, int average,
+                        void* wait_event, void* record_event) {
+  API_BEGIN
+  gpu::Comm& c = comm();
+  if (c.device_status() != 0) throw Error("an earlier device-side wait timed out; the communicator cannot be used any more");
+  cudaStream_t s = c.stream(channel);
+  stream_prologue(s, wait_event);
+  const int n = c.world();
+  gpu::Algo a = c.allreduce(channel, in, out, (size_t)count, (DType)dtype, average ? 1.f / n : 1.f, average ? n : 1, in == out);
+  stream_epilogue(s, record_event);
+  return (int)a;
+  API_END(-1)
+}
+
+int bc_fused_step(int channel, void* grad, long long count, int dtype, void* param, float* master, float* s1, float* s2,
+                  const bc_opt_hyper* h, float scale, void* wait_event, void* record_event) {
+  API_BEGIN
+  gpu::Comm& c = comm();
+  if (c.device_status() != 0) throw Error("an earlier device-side wait timed out; the communicator cannot be used any more");
+  cudaStream_t s = c.stream(channel);
+  stream_prologue(s, wait_event);
+  static_assert(sizeof(bc_opt_hyper) == sizeof(gpu::OptHyper), "bc_opt_hyper must mirror OptHyper");
+  gpu::OptHyper hh;
+  memcpy(&hh, h, sizeof(hh));
+  gpu::Algo a = c.fused_step(channel, grad, (size_t)count, (DType)dtype, param, master, s1, s2, hh, scale, nullptr);
+  stream_epilogue(s, record_event);
+  return (int)a;
+  API_END(-1)
+}
+
+// ---- single-GPU emulation of a rank group --------------------------------------------------------
+
+void* bc_emu_create(int device, int nranks, long long bytes_per_rank) {
+  API_BEGIN
+  return new gpu::EmuGroup(device, nranks, (size_t)bytes_per_rank);
+  API_END(nullptr)
+}
+
+int bc_emu_destroy(void* g) { API_BEGIN delete (gpu::EmuGroup*)g; return 0; API_END(-1) }
+
+void* bc_emu_buffer(void* g, int r) { API_BEGIN return ((gpu::EmuGroup*)g)->buffer(r); API_END(nullptr) }
+
+unsigned bc_emu_status(void* g) { API_BEGIN return ((gpu::EmuGroup*)g)->status(); API_END(0u) }
+
+int bc_emu_allreduce(void* g, long long off, void* const* outs, long long count, int dtype, int algo, float scale, int idiv,
+                     int blocks, void* stream) {
+  API_BEGIN
+  check_cuda(((gpu::EmuGroup*)g)->allreduce((size_t)off, outs, (size_t)count, (DType)dtype, (gpu::Algo)algo, scale, idiv, blocks,
+                                            (cudaStream_t)stream), "emulated allreduce launch");
+  return 0;
+  API_END(-1)
+}
+
+int bc_emu_fused_step(void* g, long long off, long long count, int dtype, void* const* params, float* const* masters,
+                      float* const* s1, float* const* s2, const bc_opt_hyper* h, float scale, int blocks, void* stream) {
+  API_BEGIN
+  gpu::OptHyper hh;
+  memcpy(&hh, h, sizeof(hh));
+  check_cuda(((gpu::EmuGroup*)g)->fused_step((size_t)off, (size_t)count, (DType)dtype, params, masters, s1, s2, hh, scale, blocks,
+                                             (cudaStream_t)stream), "emulated fused step launch");
+  return 0;
+  API_END(-1)
+}
+
+int bc_emu_allgatherv(void* g, const void* const* ins, const unsigned long long* bytes, const unsigned long long* out_offs,
+                      int blocks, void* stream) {
+  API_BEGIN
+  check_cuda(((gpu::EmuGroup*)g)->allgatherv(ins, bytes, out_offs, blocks, (cudaStream_t)stream), "emulated allgatherv launch");
+  return 0;
+  API_END(-1)
+}
+
+int bc_emu_barrier_probe(void* g, int absent, double timeout_s, void* stream) {
+  API_BEGIN
+  check_cuda(((gpu::EmuGroup*)g)->barrier_probe(absent, timeout_s, (cudaStream_t)stream), "barrier probe launch");
+  return 0;
+  API_END(-1)
+}
+
+int bc_max_emulated_blocks(int device, int nranks) { return gpu::max_emulated_blocks(device, nranks, 512); }
+
+// ---- wire-format helpers exposed for unit tests ------------------------------------------------------
+
+int bc_test_validate(int nranks, const int* ops, const int* dtypes, const int* devices, const int* ndims,
+                     const long long* shapes /* nranks x 8 */, char* err_out, int err_cap, long long* dim0_out) {
+  API_BEGIN
+  std::vector<Request> reqs(nranks);
+  for (int r = 0; r < nranks; r++) {
+    reqs[r].rank = r;
+    reqs[r].op = (OpType)ops[r];
+    reqs[r].dtype = (DType)dtypes[r];
+    reqs[r].device = (DeviceKind)devices[r];
+    reqs[r].name = "t";
+    reqs[r].shape.assign(shapes + r * 8, shapes + r * 8 + ndims[r]);
+    // round trip through the encoder, as on the wire
+    reqs[r] = decode_request(encode(reqs[r]));
+  }
+  Response resp = decode_response(encode(build_response("t", reqs)));
+  if (err_out && err_cap > 0) {
+    strncpy(err_out, resp.error.c_str(), (size_t)err_cap - 1);
+    err_out[err_cap - 1] = 0;
+  }
+  if (dim0_out)
+    for (size_t i = 0; i < resp.dim0.size(); i++) dim0_out[i] = resp.dim0[i];
+  return (int)resp.type;
+  API_END(-1)
+}
+
+}  // extern "C"

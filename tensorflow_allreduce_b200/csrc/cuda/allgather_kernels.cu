@@ -1,0 +1,134 @@
+// Variable-length allgather over peer-mapped memory (sm_100a).
+//
+// Every rank owns a slab of `bytes` bytes (its rows of the gathered tensor; the first dimension
+// may differ per rank, the other dimensions are equal). In ONE launch each rank
+//   1. publishes (bytes, offset of its output inside its symmetric segment) into every peer's
+//      signal pad and meets the peers at a flag barrier,
+//   2. computes every displacement on the device as a prefix sum of the published sizes,
+//   3. stores its slab straight into every peer's output at that displacement (P2P stores over
+//      NVLink; the local copy is one of them),
+//   4. meets the peers again, after which the whole concatenation is present everywhere.
+// The reference does this with a sizing allgather on the host followed by N-1 MPI_Sendrecv steps
+// (tensorflow/contrib/mpi_collectives/mpi_ops.py:152-160, ring.h:236-301).
+#include "collectives.h"
+#include "device_prims.cuh"
+
+namespace bc {
+namespace gpu {
+
+using namespace dev;
+
+namespace {
+
+// Copy `n` bytes from local `src` to (possibly remote) `dst`, spread over the whole grid.
+// The widest access that both addresses allow is used for the body; ragged ends go bytewise.
+__device__ __forceinline__ void push_slab(char* dst, const char* src, size_t n, size_t tid, size_t nthreads) {
+  if (n == 0) return;
+  const uintptr_t d = (uintptr_t)dst, s = (uintptr_t)src;
+  const unsigned rel = (unsigned)((d - s) & 15);
+  // Head: bytes until dst is 16-byte aligned (at most 15).
+  size_t head = (16 - (d & 15)) & 15;
+  if (head > n) head = n;
+  if (tid < head) dst[tid] = src[tid];
+  dst += head; src += head; n -= head;
+  if (n == 0) return;
+  size_t body = 0;
+  if (rel == 0) {
+    const size_t k = n / 16;
+    for (size_t i = tid; i < k; i += nthreads) st16(dst + i * 16, ld_local16(src + i * 16));
+    body = k * 16;
+  } else if ((rel & 7) == 0) {
+    const size_t k = n / 8;
+    for (size_t i = tid; i < k; i += nthreads) reinterpret_cast<uint2*>(dst)[i] = reinterpret_cast<const uint2*>(src)[i];
+    body = k * 8;
+  } else if ((rel & 3) == 0) {
+    const size_t k = n / 4;
+    for (size_t i = tid; i < k; i += nthreads) reinterpret_cast<uint32_t*>(dst)[i] = reinterpret_cast<const uint32_t*>(src)[i];
+    body = k * 4;
+  } else if ((rel & 1) == 0) {
+    const size_t k = n / 2;
+    for (size_t i = tid; i < k; i += nthreads) reinterpret_cast<uint16_t*>(dst)[i] = reinterpret_cast<const uint16_t*>(src)[i];
+    body = k * 2;
+  }
+  for (size_t i = body + tid; i < n; i += nthreads) dst[i] = src[i];
+}
+
+__global__ void __launch_bounds__(512) allgatherv_kernel(const __grid_constant__ AgArgs a) {
+  const AgRank& R = a.r[blockIdx.y];
+  const RankCtx& c = R.ctx;
+  const int P = c.world, me = c.rank;
+  __shared__ unsigned long long s_bytes[kMaxRanks];
+  __shared__ unsigned long long s_off[kMaxRanks];
+
+  uint32_t epoch = load_epoch(c);
+  // Publish my size and output offset into slot [block][me] of every peer's metadata area.
+  if ((int)threadIdx.x < P) {
+    uint64_t* slot = c.meta[threadIdx.x] + ((size_t)blockIdx.x * kMaxRanks + me) * 2;
+    slot[0] = R.bytes;
+    slot[1] = R.out_off;
+  }
+  if (P > 1) {
+    if (!peer_barrier(c, epoch)) { store_epoch(c, epoch); return; }
+  } else {
+    __syncthreads();
+  }
+  if ((int)threadIdx.x < P) {
+    const volatile uint64_t* slot = c.meta[me] + ((size_t)blockIdx.x * kMaxRanks + threadIdx.x) * 2;
+    s_bytes[threadIdx.x] = slot[0];
+    s_off[threadIdx.x] = slot[1];
+  }
+  __syncthreads();
+  unsigned long long disp = 0;
+  for (int q = 0; q < me; q++) disp += s_bytes[q];
+
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t nthreads = (size_t)gridDim.x * blockDim.x;
+  // Start with the next rank so that at any moment the P ranks write to P different targets.
+  for (int k = 0; k < P; k++) {
+    const int p = (me + 1 + k) % P;
+    push_slab(R.base[p] + s_off[p] + disp, R.in, (size_t)R.bytes, tid, nthreads);
+  }
+  if (P > 1) peer_barrier(c, epoch);
+  store_epoch(c, epoch);
+}
+
+struct ProbeArgs {
+  int n;
+  int absent;
+  RankCtx c[kMaxRanks];
+};
+
+// Barrier only. The block of rank `absent` leaves at once, so the others exercise the bounded wait.
+__global__ void barrier_probe_kernel(const __grid_constant__ ProbeArgs a) {
+  if ((int)blockIdx.y == a.absent) return;
+  const RankCtx& c = a.c[blockIdx.y];
+  uint32_t epoch = load_epoch(c);
+  peer_barrier(c, epoch);
+  store_epoch(c, epoch);
+}
+
+}  // namespace
+
+cudaError_t launch_barrier_probe(const RankCtx* ctxs, int nranks, int absent, cudaStream_t s) {
+  ProbeArgs a;
+  a.n = nranks;
+  a.absent = absent;
+  for (int r = 0; r < nranks; r++) a.c[r] = ctxs[r];
+  dim3 grid(1, nranks), block(32);
+  void* params[] = {(void*)&a};
+  return cudaLaunchCooperativeKernel((const void*)barrier_probe_kernel, grid, block, params, 0, s);
+}
+
+cudaError_t launch_allgatherv(const AgArgs& a, const LaunchCfg& cfg, cudaStream_t s) {
+  if (cfg.blocks <= 0 || cfg.blocks > kMetaBlocks || cfg.threads < 32 || cfg.threads > 512) return cudaErrorInvalidConfiguration;
+  dim3 grid(cfg.blocks, a.nranks_here), block(cfg.threads);
+  if (cfg.cooperative || a.nranks_here > 1) {
+    void* params[] = {(void*)&a};
+    return cudaLaunchCooperativeKernel((const void*)allgatherv_kernel, grid, block, params, 0, s);
+  }
+  allgatherv_kernel<<<grid, block, 0, s>>>(a);
+  return cudaGetLastError();
+}
+
+}  // namespace gpu
+}  // namespace bc

@@ -1,0 +1,421 @@
+// Sum-allreduce over peer-mapped memory for sm_100a: one-shot, two-shot and NVLS (multimem)
+// variants, with the averaging scale, the 16-bit <-> fp32 conversion and the momentum-SGD /
+// Adam(W) parameter update fused behind the reduction.
+//
+// Reference behaviour covered here: RingAllreduce + elemwise_accum
+// (tensorflow/contrib/mpi_collectives/ring.h:136-228, ring.cu.cc:48-66), the averaging divide
+// (mpi_collectives/__init__.py:160-164) and the optimizer kernels it feeds
+// (core/kernels/training_ops_gpu.cu.cc:82-145). None of the reference's structure is kept: there
+// is no ring, because through NVSwitch every peer is one hop away.
+//
+//   one-shot : barrier | every rank loads all P copies of every element, sums, writes `out` | barrier
+//   two-shot : barrier | rank r sums slice r over all P copies and stores the result into all P
+//              buffers (in place) | barrier | local epilogue over the whole buffer
+//   NVLS     : as two-shot, but the switch does the sum (multimem.ld_reduce) and the fan-out
+//              (multimem.st), so each GPU moves N/P + N bytes instead of 2N(P-1)/P.
+//
+// Block b of a rank only ever waits for block b of its peers, and touches only elements that
+// block b of the producing rank wrote, so per-block flag barriers are sufficient.
+#include "collectives.h"
+#include "device_prims.cuh"
+
+#include <type_traits>
+
+namespace bc {
+namespace gpu {
+
+using namespace dev;
+
+namespace {
+
+constexpr int ALGO_ONE = 1, ALGO_TWO = 2, ALGO_NVLS = 3;
+constexpr int OPT_NONE = 0, OPT_SGD = 1, OPT_ADAM = 2;
+
+template <typename T> struct Scalar;  // scalar load/store in the accumulator type
+template <> struct Scalar<float> { using Acc = float; __device__ static Acc ld(const float* p) { return *p; } __device__ static void st(float* p, Acc v) { *p = v; } };
+template <> struct Scalar<double> { using Acc = double; __device__ static Acc ld(const double* p) { return *p; } __device__ static void st(double* p, Acc v) { *p = v; } };
+template <> struct Scalar<int32_t> { using Acc = int32_t; __device__ static Acc ld(const int32_t* p) { return *p; } __device__ static void st(int32_t* p, Acc v) { *p = v; } };
+template <> struct Scalar<int64_t> { using Acc = long long; __device__ static Acc ld(const int64_t* p) { return *p; } __device__ static void st(int64_t* p, Acc v) { *p = v; } };
+template <> struct Scalar<uint8_t> { using Acc = uint8_t; __device__ static Acc ld(const uint8_t* p) { return *p; } __device__ static void st(uint8_t* p, Acc v) { *p = v; } };
+template <> struct Scalar<__nv_bfloat16> { using Acc = float; __device__ static Acc ld(const __nv_bfloat16* p) { return __bfloat162float(*p); } __device__ static void st(__nv_bfloat16* p, Acc v) { *p = __float2bfloat16_rn(v); } };
+template <> struct Scalar<__half> { using Acc = float; __device__ static Acc ld(const __half* p) { return __half2float(*p); } __device__ static void st(__half* p, Acc v) { *p = __float2half_rn(v); } };
+
+template <typename T> struct IsFloatGrad { static constexpr bool value = false; };
+template <> struct IsFloatGrad<float> { static constexpr bool value = true; };
+template <> struct IsFloatGrad<__nv_bfloat16> { static constexpr bool value = true; };
+template <> struct IsFloatGrad<__half> { static constexpr bool value = true; };
+
+__device__ __forceinline__ float sgd_step(float p, float g, float* buf, const OptHyper& h) {
+  if (h.weight_decay != 0.f) g = fmaf(h.weight_decay, p, g);
+  if (h.momentum != 0.f) {
+    float b = h.first_step ? g : fmaf(h.momentum, *buf, (1.f - h.dampening) * g);
+    *buf = b;
+    g = h.nesterov ? fmaf(h.momentum, b, g) : b;
+  }
+  return fmaf(-h.lr, g, p);
+}
+
+__device__ __forceinline__ float adam_step(float p, float g, float* m, float* v, const OptHyper& h) {
+  if (h.weight_decay != 0.f) {
+    if (h.decoupled_wd) p *= (1.f - h.lr * h.weight_decay);
+    else g = fmaf(h.weight_decay, p, g);
+  }
+  const float mm = fmaf(h.beta1, *m, (1.f - h.beta1) * g);
+  const float vv = fmaf(h.beta2, *v, (1.f - h.beta2) * g * g);
+  *m = mm;
+  *v = vv;
+  if (h.tf_epsilon_hat) {
+    const float step = h.lr * sqrtf(h.bias_c2) / h.bias_c1;
+    return p - step * mm / (sqrtf(vv) + h.eps);
+  }
+  const float denom = sqrtf(vv) / sqrtf(h.bias_c2) + h.eps;
+  return p - (h.lr / h.bias_c1) * mm / denom;
+}
+
+template <int OPT>
+__device__ __forceinline__ float opt_step(float p, float g, float* s1, float* s2, const OptHyper& h) {
+  if (OPT == OPT_SGD) return sgd_step(p, g, s1, h);
+  return adam_step(p, g, s1, s2, h);
+}
+
+// Sum of packs over all ranks' buffers, in rank order (identical on every rank), for the packs
+// begin + first, begin + first + stride, ... below `end`. PP is the number of ranks when known
+// at compile time (0: use the run-time P); U packs are fetched together so that U*P 16-byte
+// loads per thread are in flight across NVLink. `sink(i, acc)` consumes each reduced pack.
+template <typename T, int PP, int U, typename Sink>
+__device__ __forceinline__ void reduce_range(const ArRank& R, int P, size_t begin, size_t end, size_t first, size_t stride, Sink sink) {
+  using PK = Pack<T>;
+  constexpr int N = PP > 0 ? PP : kMaxRanks;
+  for (size_t i0 = begin + first; i0 < end; i0 += stride * U) {
+    uint4 v[U][N];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const size_t i = i0 + (size_t)u * stride;
+      if (i < end) {
+#pragma unroll
+        for (int p = 0; p < N; p++)
+          if (PP > 0 || p < P) v[u][p] = ld_stream16(R.in[p] + i * 16);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const size_t i = i0 + (size_t)u * stride;
+      if (i < end) {
+        typename PK::Acc acc[PK::kElems];
+        PK::unpack(v[u][0], acc);
+#pragma unroll
+        for (int p = 1; p < N; p++) {
+          if (PP > 0 || p < P) {
+            typename PK::Acc tmp[PK::kElems];
+            PK::unpack(v[u][p], tmp);
+#pragma unroll
+            for (int e = 0; e < PK::kElems; e++) acc[e] += tmp[e];
+          }
+        }
+        sink(i, acc);
+      }
+    }
+  }
+}
+
+template <typename T, typename Sink>
+__device__ __forceinline__ void reduce_range_any(const ArRank& R, int P, size_t begin, size_t end, size_t first, size_t stride, Sink sink) {
+  switch (P) {
+    case 2: reduce_range<T, 2, 4>(R, P, begin, end, first, stride, sink); break;
+    case 4: reduce_range<T, 4, 2>(R, P, begin, end, first, stride, sink); break;
+    case 8: reduce_range<T, 8, 1>(R, P, begin, end, first, stride, sink); break;
+    default: reduce_range<T, 0, 1>(R, P, begin, end, first, stride, sink); break;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ typename Scalar<T>::Acc reduce_scalar(const ArRank& R, int P, size_t e) {
+  typename Scalar<T>::Acc acc = Scalar<T>::ld(reinterpret_cast<const T*>(R.in[0]) + e);
+  for (int p = 1; p < P; p++) acc += Scalar<T>::ld(reinterpret_cast<const T*>(R.in[p]) + e);
+  return acc;
+}
+
+// Epilogue for one pack of already reduced (and scaled) values.
+template <typename T, int OPT>
+__device__ __forceinline__ void epilogue_pack(const ArRank& R, const ArArgs& a, size_t i, typename Pack<T>::Acc* acc, int me) {
+  using PK = Pack<T>;
+  constexpr int E = PK::kElems;
+  if constexpr (OPT == OPT_NONE) {
+    st_local16(reinterpret_cast<char*>(R.out) + i * 16, PK::pack(acc));
+  } else if constexpr (IsFloatGrad<T>::value) {
+    const OptHyper& h = a.opt;
+    const size_t e0 = i * E;
+    float p[E], s1[E], s2[E];
+    // parameters in fp32: the tensor itself (fp32 model) or the master copy (16-bit model)
+    const float* p32 = sizeof(T) == 4 ? reinterpret_cast<const float*>(R.param) : R.master;
+    if (p32) {
+#pragma unroll
+      for (int k = 0; k < E / 4; k++) Pack<float>::unpack(ld_local16(p32 + e0 + 4 * k), p + 4 * k);
+    } else {
+      PK::unpack(ld_local16(reinterpret_cast<const char*>(R.param) + i * 16), p);
+    }
+    const bool has_s1 = (OPT == OPT_ADAM) || (h.momentum != 0.f);
+    if (has_s1 && !(OPT == OPT_SGD && h.first_step)) {
+#pragma unroll
+      for (int k = 0; k < E / 4; k++) Pack<float>::unpack(ld_local16(R.state1 + e0 + 4 * k), s1 + 4 * k);
+    }
+    if (OPT == OPT_ADAM) {
+#pragma unroll
+      for (int k = 0; k < E / 4; k++) Pack<float>::unpack(ld_local16(R.state2 + e0 + 4 * k), s2 + 4 * k);
+    }
+#pragma unroll
+    for (int e = 0; e < E; e++) p[e] = opt_step<OPT>(p[e], acc[e], &s1[e], &s2[e], h);
+    if (has_s1) {
+#pragma unroll
+      for (int k = 0; k < E / 4; k++) st_local16(R.state1 + e0 + 4 * k, Pack<float>::pack(s1 + 4 * k));
+    }
+    if (OPT == OPT_ADAM) {
+#pragma unroll
+      for (int k = 0; k < E / 4; k++) st_local16(R.state2 + e0 + 4 * k, Pack<float>::pack(s2 + 4 * k));
+    }
+    if (sizeof(T) == 4) {
+      st_local16(reinterpret_cast<float*>(R.param) + e0, Pack<float>::pack(p));
+    } else {
+      if (R.master) {
+#pragma unroll
+        for (int k = 0; k < E / 4; k++) st_local16(R.master + e0 + 4 * k, Pack<float>::pack(p + 4 * k));
+      }
+      st_local16(reinterpret_cast<char*>(R.param) + i * 16, PK::pack(p));
+    }
+    if (h.zero_grad) st_local16(R.in[me] + i * 16, make_uint4(0, 0, 0, 0));
+  }
+}
+
+template <typename T, int OPT>
+__device__ __forceinline__ void epilogue_scalar(const ArRank& R, const ArArgs& a, size_t e, typename Scalar<T>::Acc g, int me) {
+  if constexpr (OPT == OPT_NONE) {
+    Scalar<T>::st(reinterpret_cast<T*>(R.out) + e, g);
+  } else if constexpr (IsFloatGrad<T>::value) {
+    const OptHyper& h = a.opt;
+    float p;
+    if (sizeof(T) == 4) p = reinterpret_cast<const float*>(R.param)[e];
+    else p = R.master ? R.master[e] : Scalar<T>::ld(reinterpret_cast<const T*>(R.param) + e);
+    float s1 = 0.f, s2 = 0.f;
+    const bool has_s1 = (OPT == OPT_ADAM) || (h.momentum != 0.f);
+    if (has_s1 && !(OPT == OPT_SGD && h.first_step)) s1 = R.state1[e];
+    if (OPT == OPT_ADAM) s2 = R.state2[e];
+    p = opt_step<OPT>(p, (float)g, &s1, &s2, h);
+    if (has_s1) R.state1[e] = s1;
+    if (OPT == OPT_ADAM) R.state2[e] = s2;
+    if (sizeof(T) == 4) reinterpret_cast<float*>(R.param)[e] = p;
+    else {
+      if (R.master) R.master[e] = p;
+      Scalar<T>::st(reinterpret_cast<T*>(R.param) + e, p);
+    }
+    if (h.zero_grad) Scalar<T>::st(reinterpret_cast<T*>(R.in[me]) + e, 0.f);
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ uint4 nvls_reduce(const char* mc) {
+  if constexpr (sizeof(T) == 4) return multimem_ld_reduce_f32(mc);
+  else if constexpr (std::is_same<T, __nv_bfloat16>::value) return multimem_ld_reduce_bf16(mc);
+  else return multimem_ld_reduce_f16(mc);
+}
+
+template <typename T, int ALGO, int OPT>
+__global__ void __launch_bounds__(512) allreduce_kernel(const __grid_constant__ ArArgs a) {
+  using PK = Pack<T>;
+  using Acc = typename PK::Acc;
+  constexpr int E = PK::kElems;
+  const ArRank& R = a.r[blockIdx.y];
+  const RankCtx& c = R.ctx;
+  const int P = c.world, me = c.rank;
+  const size_t npacks = a.count / E;
+  const size_t tail0 = npacks * E;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t first = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+
+  if (P == 1) {
+    // Single rank: the reduction is the identity; only the epilogue runs.
+    for (size_t i = first; i < npacks; i += stride) {
+      Acc acc[E];
+      PK::unpack(ld_local16(R.in[0] + i * 16), acc);
+#pragma unroll
+      for (int e = 0; e < E; e++) acc[e] = finish<Acc>(acc[e], a.scale, a.idiv);
+      epilogue_pack<T, OPT>(R, a, i, acc, 0);
+    }
+    if (blockIdx.x == 0)
+      for (size_t e = tail0 + threadIdx.x; e < a.count; e += blockDim.x)
+        epilogue_scalar<T, OPT>(R, a, e, finish<typename Scalar<T>::Acc>(Scalar<T>::ld(reinterpret_cast<const T*>(R.in[0]) + e), a.scale, a.idiv), 0);
+    return;
+  }
+
+  uint32_t epoch = load_epoch(c);
+  if (!peer_barrier(c, epoch)) { store_epoch(c, epoch); return; }
+
+  if constexpr (ALGO == ALGO_ONE) {
+    reduce_range_any<T>(R, P, 0, npacks, first, stride, [&](size_t i, Acc* acc) {
+#pragma unroll
+      for (int e = 0; e < E; e++) acc[e] = finish<Acc>(acc[e], a.scale, a.idiv);
+      epilogue_pack<T, OPT>(R, a, i, acc, me);
+    });
+    if (blockIdx.x == 0)
+      for (size_t e = tail0 + threadIdx.x; e < a.count; e += blockDim.x)
+        epilogue_scalar<T, OPT>(R, a, e, finish<typename Scalar<T>::Acc>(reduce_scalar<T>(R, P, e), a.scale, a.idiv), me);
+    // Peers may still be reading this rank's input: nobody leaves before everybody is done.
+    peer_barrier(c, epoch);
+    store_epoch(c, epoch);
+    return;
+  } else {
+    // Phase 1: reduce this rank's slice and store the result into every rank's buffer.
+    const size_t sbeg = npacks * (size_t)me / P, send = npacks * (size_t)(me + 1) / P;
+    if constexpr (ALGO == ALGO_NVLS && IsFloatGrad<T>::value) {
+      for (size_t i = sbeg + first; i < send; i += stride) {
+        uint4 r = nvls_reduce<T>(R.mc_in + i * 16);
+        if (a.scale != 1.f) {
+          Acc acc[E];
+          PK::unpack(r, acc);
+#pragma unroll
+          for (int e = 0; e < E; e++) acc[e] = finish<Acc>(acc[e], a.scale, a.idiv);
+          r = PK::pack(acc);
+        }
+        multimem_st16(R.mc_in + i * 16, r);
+      }
+    } else {
+      reduce_range_any<T>(R, P, sbeg, send, first, stride, [&](size_t i, Acc* acc) {
+#pragma unroll
+        for (int e = 0; e < E; e++) acc[e] = finish<Acc>(acc[e], a.scale, a.idiv);
+        const uint4 r = PK::pack(acc);
+#pragma unroll
+        for (int p = 0; p < kMaxRanks; p++)
+          if (p < P) st16(R.in[p] + i * 16, r);
+      });
+    }
+    // The ragged tail (fewer elements than one pack) belongs to rank 0, block 0.
+    if (me == 0 && blockIdx.x == 0) {
+      for (size_t e = tail0 + threadIdx.x; e < a.count; e += blockDim.x) {
+        typename Scalar<T>::Acc g = finish<typename Scalar<T>::Acc>(reduce_scalar<T>(R, P, e), a.scale, a.idiv);
+        for (int p = 0; p < P; p++) Scalar<T>::st(reinterpret_cast<T*>(R.in[p]) + e, g);
+      }
+    }
+    if (!peer_barrier(c, epoch)) { store_epoch(c, epoch); return; }
+    store_epoch(c, epoch);
+
+    // Phase 2: local epilogue. Block b reads, inside each slice, exactly the packs that block b
+    // of the owning rank produced.
+    const bool copy_needed = (OPT != OPT_NONE) || (R.out != (void*)R.in[me]);
+    if (copy_needed) {
+      for (int q = 0; q < P; q++) {
+        const size_t qb = npacks * (size_t)q / P, qe = npacks * (size_t)(q + 1) / P;
+        for (size_t i = qb + first; i < qe; i += stride) {
+          Acc acc[E];
+          PK::unpack(ld_local16(R.in[me] + i * 16), acc);
+          epilogue_pack<T, OPT>(R, a, i, acc, me);
+        }
+      }
+      if (blockIdx.x == 0)
+        for (size_t e = tail0 + threadIdx.x; e < a.count; e += blockDim.x)
+          epilogue_scalar<T, OPT>(R, a, e, Scalar<T>::ld(reinterpret_cast<const T*>(R.in[me]) + e), me);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(512) copy_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, size_t npacks,
+                                                    char* dtail, const char* stail, int ntail) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < npacks; i += stride) dst[i] = src[i];
+  if (blockIdx.x == 0 && (int)threadIdx.x < ntail) dtail[threadIdx.x] = stail[threadIdx.x];
+}
+
+template <typename T, int ALGO, int OPT>
+cudaError_t launch_one(const ArArgs& a, const LaunchCfg& cfg, cudaStream_t s) {
+  dim3 grid(cfg.blocks, a.nranks_here), block(cfg.threads);
+  if (cfg.cooperative || a.nranks_here > 1) {
+    void* params[] = {(void*)&a};
+    return cudaLaunchCooperativeKernel((const void*)allreduce_kernel<T, ALGO, OPT>, grid, block, params, 0, s);
+  }
+  allreduce_kernel<T, ALGO, OPT><<<grid, block, 0, s>>>(a);
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t dispatch_plain(const ArArgs& a, const LaunchCfg& cfg, cudaStream_t s) {
+  switch (a.algo) {
+    case ALGO_ONE: return launch_one<T, ALGO_ONE, OPT_NONE>(a, cfg, s);
+    case ALGO_TWO: return launch_one<T, ALGO_TWO, OPT_NONE>(a, cfg, s);
+    case ALGO_NVLS:
+      if constexpr (IsFloatGrad<T>::value) return launch_one<T, ALGO_NVLS, OPT_NONE>(a, cfg, s);
+      return cudaErrorInvalidValue;
+  }
+  return cudaErrorInvalidValue;
+}
+
+template <typename T>
+cudaError_t dispatch_fused(const ArArgs& a, const LaunchCfg& cfg, cudaStream_t s) {
+  const bool nvls = a.algo == ALGO_NVLS;
+  if (a.algo == ALGO_ONE) return cudaErrorInvalidValue;  // the fused update needs the two-phase structure
+  switch (a.opt.kind) {
+    case OPT_SGD: return nvls ? launch_one<T, ALGO_NVLS, OPT_SGD>(a, cfg, s) : launch_one<T, ALGO_TWO, OPT_SGD>(a, cfg, s);
+    case OPT_ADAM: return nvls ? launch_one<T, ALGO_NVLS, OPT_ADAM>(a, cfg, s) : launch_one<T, ALGO_TWO, OPT_ADAM>(a, cfg, s);
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+cudaError_t launch_allreduce(const ArArgs& a, DType dtype, DType param_dtype, const LaunchCfg& cfg, cudaStream_t s) {
+  if (cfg.blocks <= 0 || cfg.blocks > kMaxBlocks || cfg.threads < 32 || cfg.threads > 512) return cudaErrorInvalidConfiguration;
+  if (a.opt.kind != OPT_NONE) {
+    if (!(param_dtype == dtype)) return cudaErrorInvalidValue;
+    switch (dtype) {
+      case DType::F32: return dispatch_fused<float>(a, cfg, s);
+      case DType::BF16: return dispatch_fused<__nv_bfloat16>(a, cfg, s);
+      case DType::F16: return dispatch_fused<__half>(a, cfg, s);
+      default: return cudaErrorInvalidValue;
+    }
+  }
+  switch (dtype) {
+    case DType::F32: return dispatch_plain<float>(a, cfg, s);
+    case DType::BF16: return dispatch_plain<__nv_bfloat16>(a, cfg, s);
+    case DType::F16: return dispatch_plain<__half>(a, cfg, s);
+    case DType::I32: return dispatch_plain<int32_t>(a, cfg, s);
+    case DType::I64: return dispatch_plain<int64_t>(a, cfg, s);
+    case DType::F64: return dispatch_plain<double>(a, cfg, s);
+    case DType::U8: return dispatch_plain<uint8_t>(a, cfg, s);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+cudaError_t launch_copy(void* dst, const void* src, size_t bytes, cudaStream_t s) {
+  if (bytes == 0) return cudaSuccess;
+  if ((((uintptr_t)dst | (uintptr_t)src) & 15) != 0) return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, s);
+  const size_t npacks = bytes / 16;
+  const int ntail = (int)(bytes % 16);
+  int blocks = (int)((npacks + 512 * 8 - 1) / (512 * 8));
+  if (blocks < 1) blocks = 1;
+  if (blocks > 592) blocks = 592;
+  copy_kernel<<<blocks, 512, 0, s>>>((uint4*)dst, (const uint4*)src, npacks, (char*)dst + npacks * 16,
+                                     (const char*)src + npacks * 16, ntail);
+  return cudaGetLastError();
+}
+
+int max_emulated_blocks(int device, int nranks, int threads) {
+  int per_sm = 0, sms = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void*)allreduce_kernel<float, ALGO_TWO, OPT_ADAM>, threads, 0) != cudaSuccess) return 1;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 1;
+  int total = per_sm * sms;
+  int g = total / (nranks > 0 ? nranks : 1);
+  if (g > kMaxBlocks) g = kMaxBlocks;
+  return g < 1 ? 1 : g;
+}
+
+int choose_blocks(size_t bytes, int world, int algo, bool fused_opt, int sm_count) {
+  // One block per 64 KiB of payload, at least 1; the cap keeps SMs free for the backward pass
+  // that runs beside a gradient reduction. A fused update is HBM-bound in its second phase and
+  // gets a larger grid.
+  (void)world;
+  size_t want = (bytes + (64u << 10) - 1) / (64u << 10);
+  int cap = fused_opt ? sm_count : (algo == ALGO_NVLS ? 32 : 64);
+  if (cap > kMaxBlocks) cap = kMaxBlocks;
+  if (want < 1) want = 1;
+  return (int)(want > (size_t)cap ? (size_t)cap : want);
+}
+
+}  // namespace gpu
+}  // namespace bc

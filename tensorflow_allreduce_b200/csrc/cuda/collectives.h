@@ -1,0 +1,110 @@
+// Host-visible launch interface of the peer-memory collective kernels.
+//
+// One launch = one collective on one rank. The same kernels also run "emulated": a single
+// cooperative launch whose blockIdx.y selects one of several ranks whose buffers all live on one
+// GPU. That is how the multi-rank protocol is tested on a single device, where separate launches
+// that wait on one another must never be used.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../common.h"
+#include "layout.h"
+
+namespace bc {
+namespace gpu {
+
+enum class Algo : int { AUTO = 0, ONE_SHOT = 1, TWO_SHOT = 2, NVLS = 3 };
+inline const char* algo_name(Algo a) {
+  switch (a) {
+    case Algo::AUTO: return "auto";
+    case Algo::ONE_SHOT: return "one_shot";
+    case Algo::TWO_SHOT: return "two_shot";
+    case Algo::NVLS: return "nvls";
+  }
+  return "?";
+}
+
+enum class OptKind : int { NONE = 0, SGD = 1, ADAM = 2 };
+
+// Optimizer update fused behind the reduction. Formulas:
+//   SGD  (TF ApplyMomentum, core/kernels/training_ops_gpu.cu.cc:82-100; torch.optim.SGD):
+//        g += wd*p;  buf = first ? g : mu*buf + (1-dampening)*g;  d = nesterov ? g + mu*buf : buf;
+//        p -= lr*d        (mu == 0: p -= lr*g, no buffer)
+//   ADAM (TF ApplyAdam, training_ops_gpu.cu.cc:103-145, python/training/adam.py:50-60; torch AdamW):
+//        decoupled: p *= 1 - lr*wd      else: g += wd*p
+//        m = b1*m + (1-b1)*g;  v = b2*v + (1-b2)*g*g
+//        torch form: p -= (lr/bc1) * m / (sqrt(v)/sqrt(bc2) + eps)
+//        TF form   : p -= lr*sqrt(bc2)/bc1 * m / (sqrt(v) + eps)        ("epsilon hat")
+// bc1 = 1 - b1^t, bc2 = 1 - b2^t are computed on the host for step t.
+struct OptHyper {
+  int kind;              // OptKind
+  float lr;
+  float weight_decay;
+  float momentum;        // SGD mu
+  float dampening;
+  int nesterov;
+  int first_step;        // SGD: momentum buffer is uninitialised (torch copies g into it)
+  float beta1, beta2, eps;
+  float bias_c1, bias_c2;
+  int decoupled_wd;      // AdamW
+  int tf_epsilon_hat;
+  int zero_grad;         // write zeros over the gradient once it has been consumed
+};
+
+// Per-rank operands of a reduction launch.
+struct ArRank {
+  dev::RankCtx ctx;
+  char* in[dev::kMaxRanks];   // every rank's input buffer as mapped here (16-byte aligned)
+  char* mc_in;                // multicast mapping of the same buffer (NVLS) or null
+  void* out;                  // local result; may alias in[rank]
+  // fused optimizer operands (local, flat, same element order as the gradient)
+  void* param;                // fp32 or same 16-bit type as the gradient
+  float* master;              // fp32 master copy when param is 16-bit, else null
+  float* state1;              // momentum buffer / Adam m
+  float* state2;              // Adam v
+};
+
+struct ArArgs {
+  int nranks_here;            // 1, or the number of emulated ranks (grid.y)
+  int algo;                   // Algo (resolved, not AUTO)
+  size_t count;               // elements
+  float scale;                // applied to floating sums (1/size when averaging)
+  int idiv;                   // integer divisor when averaging integer tensors
+  OptHyper opt;
+  ArRank r[dev::kMaxRanks];
+};
+
+// Per-rank operands of a variable-length allgather launch.
+struct AgRank {
+  dev::RankCtx ctx;
+  const char* in;             // local slab
+  unsigned long long bytes;   // its size
+  char* base[dev::kMaxRanks]; // every rank's output segment base as mapped here
+  unsigned long long out_off; // where this rank's output starts inside its own segment
+};
+
+struct AgArgs {
+  int nranks_here;
+  AgRank r[dev::kMaxRanks];
+};
+
+struct LaunchCfg {
+  int blocks = 0;     // 0 = choose from size
+  int threads = 512;
+  bool cooperative = false;   // required when nranks_here > 1
+};
+
+// Launch the reduction. `param_dtype` is F32, or equal to `dtype` for 16-bit parameters.
+cudaError_t launch_allreduce(const ArArgs& a, DType dtype, DType param_dtype, const LaunchCfg& cfg, cudaStream_t s);
+cudaError_t launch_allgatherv(const AgArgs& a, const LaunchCfg& cfg, cudaStream_t s);
+// Plain device copy kernel (staging of tensors that are not in symmetric memory).
+cudaError_t launch_copy(void* dst, const void* src, size_t bytes, cudaStream_t s);
+
+// Largest grid.x for which an emulated launch of `nranks` ranks is co-resident on `device`.
+int max_emulated_blocks(int device, int nranks, int threads);
+int choose_blocks(size_t bytes, int world, int algo, bool fused_opt, int sm_count);
+
+}  // namespace gpu
+}  // namespace bc

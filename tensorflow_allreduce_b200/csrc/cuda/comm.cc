@@ -1,0 +1,353 @@
+#include "comm.h"
+
+#include <string.h>
+
+#include <algorithm>
+
+namespace bc {
+namespace gpu {
+
+using namespace dev;
+
+#define CUDA_RT(expr)                                                                            \
+  do {                                                                                           \
+    cudaError_t _e = (expr);                                                                     \
+    if (_e != cudaSuccess) throw ::bc::Error(std::string(#expr) + ": " + cudaGetErrorString(_e)); \
+  } while (0)
+
+namespace {
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+unsigned long long to_ns(double s) { return (unsigned long long)(s * 1e9); }
+}  // namespace
+
+Comm::Comm(int rank, int world, int device, uint64_t job_id, const CommConfig& cfg, const HostAllgather& ag, double host_timeout_s)
+    : rank_(rank), world_(world), device_(device), cfg_(cfg) {
+  CUDA_RT(cudaSetDevice(device));
+  CUDA_RT(cudaDeviceGetAttribute(&sm_count_, cudaDevAttrMultiProcessorCount, device));
+  int lo = 0, hi = 0;
+  CUDA_RT(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+  for (int c = 0; c < kChannels; c++) CUDA_RT(cudaStreamCreateWithPriority(&streams_[c], cudaStreamNonBlocking, hi));
+  alloc_.reset(new SymmAllocator(rank, world, device, job_id, cfg.symm_mode, cfg.use_nvls, host_timeout_s));
+  pad_off_ = 0;
+  staging_off_ = align_up(kPadBytes, 1u << 20);
+  cfg_.staging_bytes = align_up(std::max<size_t>(cfg_.staging_bytes, 1u << 20), 1u << 20);
+  heap_off_ = staging_off_ + cfg_.staging_bytes;
+  cfg_.heap_bytes = align_up(cfg_.heap_bytes, 1u << 20);
+  seg0_ = alloc_->alloc(heap_off_ + cfg_.heap_bytes, ag);
+  CUDA_RT(cudaMalloc(&epochs_, sizeof(uint32_t) * kChannels * kMaxBlocks));
+  CUDA_RT(cudaMemset(epochs_, 0, sizeof(uint32_t) * kChannels * kMaxBlocks));
+  CUDA_RT(cudaHostAlloc(&status_host_, 64, cudaHostAllocMapped));
+  memset(status_host_, 0, 64);
+  CUDA_RT(cudaHostGetDevicePointer((void**)&status_dev_, status_host_, 0));
+  CUDA_RT(cudaDeviceSynchronize());
+  ag(std::string());
+}
+
+Comm::~Comm() {
+  cudaSetDevice(device_);
+  cudaDeviceSynchronize();
+  alloc_.reset();
+  if (epochs_) cudaFree(epochs_);
+  if (status_host_) cudaFreeHost(status_host_);
+  for (int c = 0; c < kChannels; c++)
+    if (streams_[c]) cudaStreamDestroy(streams_[c]);
+}
+
+RankCtx Comm::make_ctx(int channel) const {
+  RankCtx c;
+  memset(&c, 0, sizeof(c));
+  c.rank = rank_;
+  c.world = world_;
+  for (int p = 0; p < world_; p++) {
+    char* pad = seg0_->peer[p] + pad_off_ + (size_t)channel * kChannelBytes;
+    c.flags[p] = (uint32_t*)pad;
+    c.meta[p] = (uint64_t*)(pad + kFlagBytes);
+  }
+  c.epochs = epochs_ + (size_t)channel * kMaxBlocks;
+  c.status = status_dev_;
+  c.timeout_ns = to_ns(cfg_.device_timeout_s);
+  return c;
+}
+
+Algo Comm::choose_algo(size_t bytes, DType dtype, bool in_place_or_fused, bool has_mc) const {
+  const bool is_float = dtype == DType::F32 || dtype == DType::BF16 || dtype == DType::F16;
+  Algo forced = (Algo)cfg_.force_algo;
+  if (forced == Algo::ONE_SHOT && !in_place_or_fused) return forced;
+  if (forced == Algo::TWO_SHOT) return forced;
+  if (forced == Algo::NVLS && has_mc && is_float) return forced;
+  if (forced != Algo::AUTO) return Algo::TWO_SHOT;
+  if (!in_place_or_fused && bytes <= cfg_.one_shot_max_bytes) return Algo::ONE_SHOT;
+  if (has_mc && cfg_.use_nvls && is_float && bytes >= cfg_.nvls_min_bytes) return Algo::NVLS;
+  return Algo::TWO_SHOT;
+}
+
+void Comm::fill_ar_rank(ArRank* r, int channel, Segment* seg, size_t off) const {
+  memset(r, 0, sizeof(*r));
+  r->ctx = make_ctx(channel);
+  for (int p = 0; p < world_; p++) r->in[p] = seg->peer[p] + off;
+  r->mc_in = seg->mc ? seg->mc + off : nullptr;
+}
+
+Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType dtype, float scale, int idiv,
+                     bool zero_copy_agreed) {
+  CUDA_RT(cudaSetDevice(device_));
+  cudaStream_t s = streams_[channel];
+  const size_t es = dtype_size(dtype);
+  const size_t bytes = count * es;
+  if (count == 0) return Algo::ONE_SHOT;
+  BC_CHECK((((uintptr_t)in | (uintptr_t)out) & 15) == 0, "allreduce: device pointers must be 16-byte aligned");
+  ArArgs a;
+  memset(&a, 0, sizeof(a));
+  a.nranks_here = 1;
+  a.scale = scale;
+  a.idiv = idiv;
+  LaunchCfg cfg;
+
+  if (world_ == 1) {
+    if (in == out && scale == 1.f && idiv <= 1) return Algo::ONE_SHOT;
+    a.algo = (int)Algo::ONE_SHOT;
+    a.count = count;
+    a.r[0].ctx = make_ctx(channel);
+    a.r[0].in[0] = (char*)in;
+    a.r[0].out = out;
+    cfg.blocks = choose_blocks(bytes, 1, a.algo, true, sm_count_);
+    CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, s));
+    last_blocks = cfg.blocks;
+    return Algo::ONE_SHOT;
+  }
+
+  Segment* seg = zero_copy_agreed ? alloc_->find(in, bytes) : nullptr;
+  if (seg && in == out) {
+    // In place on symmetric memory: no staging at all.
+    const size_t off = (const char*)in - seg->local;
+    Algo algo = choose_algo(bytes, dtype, true, seg->mc != nullptr);
+    fill_ar_rank(&a.r[0], channel, seg, off);
+    a.r[0].out = out;
+    a.algo = (int)algo;
+    a.count = count;
+    cfg.blocks = choose_blocks(bytes, world_, a.algo, false, sm_count_);
+    if (cfg_.max_blocks > 0) cfg.blocks = std::min(cfg.blocks, cfg_.max_blocks);
+    CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, s));
+    last_blocks = cfg.blocks;
+    return algo;
+  }
+  if (seg && bytes <= cfg_.one_shot_max_bytes && (Algo)cfg_.force_algo != Algo::TWO_SHOT && (Algo)cfg_.force_algo != Algo::NVLS) {
+    // Small registered input, separate output: one-shot reads the peers' tensors where they are.
+    const size_t off = (const char*)in - seg->local;
+    fill_ar_rank(&a.r[0], channel, seg, off);
+    a.r[0].out = out;
+    a.algo = (int)Algo::ONE_SHOT;
+    a.count = count;
+    cfg.blocks = choose_blocks(bytes, world_, a.algo, false, sm_count_);
+    if (cfg_.max_blocks > 0) cfg.blocks = std::min(cfg.blocks, cfg_.max_blocks);
+    CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, s));
+    last_blocks = cfg.blocks;
+    return Algo::ONE_SHOT;
+  }
+
+  // Staged: copy a chunk into the symmetric staging area, reduce from there into `out`.
+  const size_t chunk_elems = (cfg_.staging_bytes / 16) * (16 / es);
+  Algo used = Algo::TWO_SHOT;
+  for (size_t done = 0; done < count; done += chunk_elems) {
+    const size_t n = std::min(chunk_elems, count - done);
+    const size_t nb = n * es;
+    CUDA_RT(launch_copy(staging(), (const char*)in + done * es, nb, s));
+    Algo algo = choose_algo(nb, dtype, false, seg0_->mc != nullptr);
+    fill_ar_rank(&a.r[0], channel, seg0_, staging_off_);
+    a.r[0].out = (char*)out + done * es;
+    a.algo = (int)algo;
+    a.count = n;
+    cfg.blocks = choose_blocks(nb, world_, a.algo, false, sm_count_);
+    if (cfg_.max_blocks > 0) cfg.blocks = std::min(cfg.blocks, cfg_.max_blocks);
+    CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, s));
+    last_blocks = cfg.blocks;
+    used = algo;
+  }
+  return used;
+}
+
+void Comm::allgatherv(int channel, const void* in, size_t bytes, void* out_symm, void* out_private, size_t total_bytes) {
+  CUDA_RT(cudaSetDevice(device_));
+  cudaStream_t s = streams_[channel];
+  if (total_bytes == 0) return;
+  AgArgs a;
+  memset(&a, 0, sizeof(a));
+  a.nranks_here = 1;
+  AgRank& r = a.r[0];
+  r.ctx = make_ctx(channel);
+  r.in = (const char*)in;
+  r.bytes = bytes;
+  for (int p = 0; p < world_; p++) r.base[p] = seg0_->peer[p];
+  if (out_symm) {
+    BC_CHECK((char*)out_symm >= seg0_->local && (char*)out_symm + total_bytes <= seg0_->local + seg0_->size,
+             "allgatherv: symmetric output lies outside segment 0");
+    r.out_off = (char*)out_symm - seg0_->local;
+  } else {
+    BC_CHECK(total_bytes <= cfg_.staging_bytes, "allgatherv: result of " << total_bytes
+             << " bytes fits neither the symmetric heap nor the staging area; raise BC_HEAP_MB or BC_STAGING_MB");
+    r.out_off = staging_off_;
+  }
+  LaunchCfg cfg;
+  size_t want = (total_bytes / world_ + (128u << 10) - 1) / (128u << 10);
+  cfg.blocks = (int)std::min<size_t>(std::max<size_t>(want, 1), 32);
+  CUDA_RT(launch_allgatherv(a, cfg, s));
+  last_blocks = cfg.blocks;
+  if (!out_symm && out_private) CUDA_RT(launch_copy(out_private, staging(), total_bytes, s));
+}
+
+Algo Comm::fused_step(int channel, void* grad, size_t count, DType dtype, void* param, float* master, float* s1, float* s2,
+                      const OptHyper& h, float scale, cudaStream_t stream_override) {
+  CUDA_RT(cudaSetDevice(device_));
+  cudaStream_t s = stream_override ? stream_override : streams_[channel];
+  const size_t bytes = count * dtype_size(dtype);
+  if (count == 0) return Algo::TWO_SHOT;
+  ArArgs a;
+  memset(&a, 0, sizeof(a));
+  a.nranks_here = 1;
+  a.scale = scale;
+  a.idiv = 1;
+  a.count = count;
+  a.opt = h;
+  Algo algo = Algo::TWO_SHOT;
+  if (world_ == 1) {
+    a.r[0].ctx = make_ctx(channel);
+    a.r[0].in[0] = (char*)grad;
+  } else {
+    Segment* seg = alloc_->find(grad, bytes);
+    BC_CHECK(seg, "fused_step: the gradient bucket must live in symmetric memory");
+    fill_ar_rank(&a.r[0], channel, seg, (char*)grad - seg->local);
+    algo = choose_algo(bytes, dtype, true, seg->mc != nullptr);
+  }
+  a.algo = (int)algo;
+  a.r[0].out = grad;
+  a.r[0].param = param;
+  a.r[0].master = master;
+  a.r[0].state1 = s1;
+  a.r[0].state2 = s2;
+  LaunchCfg cfg;
+  cfg.blocks = choose_blocks(bytes, world_, a.algo, true, sm_count_);
+  if (cfg_.max_blocks > 0) cfg.blocks = std::min(cfg.blocks, cfg_.max_blocks);
+  CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, s));
+  last_blocks = cfg.blocks;
+  return algo;
+}
+
+// ---------------------------------------------------------------------------------------------
+
+EmuGroup::EmuGroup(int device, int nranks, size_t bytes_per_rank) : device_(device), n_(nranks), bytes_(align_up(bytes_per_rank, 256)) {
+  BC_CHECK(nranks >= 1 && nranks <= kMaxRanks, "emulated group size must be 1.." << kMaxRanks);
+  CUDA_RT(cudaSetDevice(device));
+  bufs_.assign(n_, nullptr);
+  pads_.assign(n_, nullptr);
+  for (int r = 0; r < n_; r++) {
+    CUDA_RT(cudaMalloc(&bufs_[r], bytes_));
+    CUDA_RT(cudaMalloc(&pads_[r], kPadBytes));
+    CUDA_RT(cudaMemset(pads_[r], 0, kPadBytes));
+  }
+  CUDA_RT(cudaMalloc(&epochs_, sizeof(uint32_t) * n_ * kChannels * kMaxBlocks));
+  CUDA_RT(cudaMemset(epochs_, 0, sizeof(uint32_t) * n_ * kChannels * kMaxBlocks));
+  CUDA_RT(cudaHostAlloc(&status_host_, 64, cudaHostAllocMapped));
+  memset(status_host_, 0, 64);
+  CUDA_RT(cudaHostGetDevicePointer((void**)&status_dev_, status_host_, 0));
+  CUDA_RT(cudaDeviceSynchronize());
+}
+
+EmuGroup::~EmuGroup() {
+  cudaSetDevice(device_);
+  cudaDeviceSynchronize();
+  for (char* p : bufs_) if (p) cudaFree(p);
+  for (char* p : pads_) if (p) cudaFree(p);
+  if (epochs_) cudaFree(epochs_);
+  if (status_host_) cudaFreeHost(status_host_);
+}
+
+RankCtx EmuGroup::ctx(int r, int channel) const {
+  RankCtx c;
+  memset(&c, 0, sizeof(c));
+  c.rank = r;
+  c.world = n_;
+  for (int p = 0; p < n_; p++) {
+    char* pad = pads_[p] + (size_t)channel * kChannelBytes;
+    c.flags[p] = (uint32_t*)pad;
+    c.meta[p] = (uint64_t*)(pad + kFlagBytes);
+  }
+  c.epochs = epochs_ + ((size_t)r * kChannels + channel) * kMaxBlocks;
+  c.status = status_dev_;
+  c.timeout_ns = to_ns(timeout_s_);
+  return c;
+}
+
+cudaError_t EmuGroup::allreduce(size_t off, void* const* outs, size_t count, DType dtype, Algo algo, float scale, int idiv,
+                                int blocks, cudaStream_t s) {
+  ArArgs a;
+  memset(&a, 0, sizeof(a));
+  a.nranks_here = n_;
+  a.algo = (int)algo;
+  a.count = count;
+  a.scale = scale;
+  a.idiv = idiv;
+  for (int r = 0; r < n_; r++) {
+    a.r[r].ctx = ctx(r, 0);
+    for (int p = 0; p < n_; p++) a.r[r].in[p] = bufs_[p] + off;
+    a.r[r].out = outs[r];
+  }
+  LaunchCfg cfg;
+  cfg.cooperative = true;
+  cfg.blocks = std::min(blocks > 0 ? blocks : 4, max_emulated_blocks(device_, n_, cfg.threads));
+  return launch_allreduce(a, dtype, dtype, cfg, s);
+}
+
+cudaError_t EmuGroup::fused_step(size_t off, size_t count, DType dtype, void* const* params, float* const* masters,
+                                 float* const* s1, float* const* s2, const OptHyper& h, float scale, int blocks, cudaStream_t s) {
+  ArArgs a;
+  memset(&a, 0, sizeof(a));
+  a.nranks_here = n_;
+  a.algo = (int)Algo::TWO_SHOT;
+  a.count = count;
+  a.scale = scale;
+  a.idiv = 1;
+  a.opt = h;
+  for (int r = 0; r < n_; r++) {
+    a.r[r].ctx = ctx(r, 0);
+    for (int p = 0; p < n_; p++) a.r[r].in[p] = bufs_[p] + off;
+    a.r[r].out = bufs_[r] + off;
+    a.r[r].param = params[r];
+    a.r[r].master = masters ? masters[r] : nullptr;
+    a.r[r].state1 = s1 ? s1[r] : nullptr;
+    a.r[r].state2 = s2 ? s2[r] : nullptr;
+  }
+  LaunchCfg cfg;
+  cfg.cooperative = true;
+  cfg.blocks = std::min(blocks > 0 ? blocks : 4, max_emulated_blocks(device_, n_, cfg.threads));
+  return launch_allreduce(a, dtype, dtype, cfg, s);
+}
+
+cudaError_t EmuGroup::allgatherv(const void* const* ins, const unsigned long long* bytes, const unsigned long long* out_offs,
+                                 int blocks, cudaStream_t s) {
+  AgArgs a;
+  memset(&a, 0, sizeof(a));
+  a.nranks_here = n_;
+  for (int r = 0; r < n_; r++) {
+    a.r[r].ctx = ctx(r, 1);
+    a.r[r].in = (const char*)ins[r];
+    a.r[r].bytes = bytes[r];
+    a.r[r].out_off = out_offs[r];
+    for (int p = 0; p < n_; p++) a.r[r].base[p] = bufs_[p];
+  }
+  LaunchCfg cfg;
+  cfg.cooperative = true;
+  cfg.blocks = std::min(std::min(blocks > 0 ? blocks : 2, (int)kMetaBlocks), max_emulated_blocks(device_, n_, cfg.threads));
+  return launch_allgatherv(a, cfg, s);
+}
+
+cudaError_t EmuGroup::barrier_probe(int absent, double timeout_s, cudaStream_t s) {
+  std::vector<RankCtx> c(n_);
+  for (int r = 0; r < n_; r++) {
+    c[r] = ctx(r, 2);
+    c[r].timeout_ns = to_ns(timeout_s);
+  }
+  return launch_barrier_probe(c.data(), n_, absent, s);
+}
+
+}  // namespace gpu
+}  // namespace bc

@@ -1,0 +1,139 @@
+// GPU communicator of one rank: symmetric segments, signal pads, private streams, the
+// algorithm selector, and the launch paths used by the runtime (negotiated collectives), by the
+// gradient-bucket fast path (ordered launches without negotiation) and by single-GPU emulation.
+//
+// Reference counterpart: the private CUDA stream plus RingAllreduce<GPU>/RingAllgather<GPU>
+// dispatch of the background thread (tensorflow/contrib/mpi_collectives/mpi_ops.cc:213-230,
+// 435-515, 873).
+#pragma once
+
+#include <atomic>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "collectives.h"
+#include "symm.h"
+
+namespace bc {
+namespace gpu {
+
+struct CommConfig {
+  size_t staging_bytes = 64u << 20;     // staging area for tensors outside symmetric memory
+  size_t heap_bytes = 256u << 20;       // general symmetric heap inside segment 0 (allgather outputs, user tensors)
+  double device_timeout_s = 30.0;       // bound of every device-side wait
+  int force_algo = 0;                   // Algo, 0 = pick from the table
+  size_t one_shot_max_bytes = 256u << 10;
+  size_t nvls_min_bytes = 512u << 10;
+  bool use_nvls = true;
+  int max_blocks = 0;                   // 0 = heuristic
+  SymmAllocator::Mode symm_mode = SymmAllocator::Mode::AUTO;
+};
+
+struct OpTiming {
+  cudaEvent_t start = nullptr, stop = nullptr;
+};
+
+class Comm {
+ public:
+  Comm(int rank, int world, int device, uint64_t job_id, const CommConfig& cfg, const HostAllgather& ag, double host_timeout_s);
+  ~Comm();
+
+  int rank() const { return rank_; }
+  int world() const { return world_; }
+  int device() const { return device_; }
+  cudaStream_t stream(int channel) const { return streams_[channel]; }
+  const CommConfig& config() const { return cfg_; }
+  SymmAllocator& allocator() { return *alloc_; }
+
+  // Status word written by kernels whose wait ran out; 0 while healthy.
+  uint32_t device_status() const { return status_host_ ? *(volatile uint32_t*)status_host_ : 0; }
+  void set_device_timeout(double s) { cfg_.device_timeout_s = s; }
+
+  // Algorithm for a reduction of `bytes` bytes (all ranks compute the same answer).
+  Algo choose_algo(size_t bytes, DType dtype, bool in_place_or_fused, bool has_mc) const;
+
+  // Sum-allreduce of `count` elements, launched on stream(channel). `in` may be anywhere on the
+  // device; data outside symmetric memory is staged. `scale`/`idiv` implement averaging.
+  // Returns the algorithm used.
+  Algo allreduce(int channel, const void* in, void* out, size_t count, DType dtype, float scale, int idiv,
+                 bool zero_copy_agreed);
+  // Variable allgather: `in` = this rank's slab, `out` must lie in segment 0's heap or be null
+  // (then the staging area is the landing zone and `out_private` receives a copy).
+  void allgatherv(int channel, const void* in, size_t bytes, void* out_symm, void* out_private, size_t total_bytes);
+
+  // Fused reduce + optimizer update on a gradient bucket that lives in symmetric memory.
+  Algo fused_step(int channel, void* grad, size_t count, DType dtype, void* param, float* master, float* s1, float* s2,
+                  const OptHyper& h, float scale, cudaStream_t stream_override);
+
+  // Segment-0 heap offsets
+  char* staging() const { return seg0_->local + staging_off_; }
+  size_t staging_bytes() const { return cfg_.staging_bytes; }
+  char* heap_base() const { return seg0_->local + heap_off_; }
+  size_t heap_bytes() const { return cfg_.heap_bytes; }
+  Segment* seg0() const { return seg0_; }
+  Segment* new_segment(size_t bytes, const HostAllgather& ag) { return alloc_->alloc(bytes, ag); }
+
+  dev::RankCtx make_ctx(int channel) const;
+  int sm_count() const { return sm_count_; }
+
+  // last launch info (for stats)
+  int last_blocks = 0;
+
+ private:
+  void fill_ar_rank(ArRank* r, int channel, Segment* seg, size_t off) const;
+
+  int rank_, world_, device_;
+  CommConfig cfg_;
+  std::unique_ptr<SymmAllocator> alloc_;
+  Segment* seg0_ = nullptr;
+  size_t pad_off_ = 0, staging_off_ = 0, heap_off_ = 0;
+  uint32_t* epochs_ = nullptr;        // device-local epoch counters [kChannels][kMaxBlocks]
+  uint32_t* status_host_ = nullptr;   // pinned, mapped
+  uint32_t* status_dev_ = nullptr;
+  cudaStream_t streams_[dev::kChannels] = {nullptr};
+  int sm_count_ = 148;
+};
+
+// ---------------------------------------------------------------------------------------------
+// Single-GPU emulation of an N-rank group: all ranks' buffers and pads live on one device and a
+// collective is ONE cooperative launch (blockIdx.y = rank). Used to test the multi-rank protocol
+// where only one GPU is available.
+class EmuGroup {
+ public:
+  EmuGroup(int device, int nranks, size_t bytes_per_rank);
+  ~EmuGroup();
+  int nranks() const { return n_; }
+  char* buffer(int r) const { return bufs_[r]; }
+  size_t bytes_per_rank() const { return bytes_; }
+  uint32_t status() const { return *(volatile uint32_t*)status_host_; }
+  void clear_status() { *(volatile uint32_t*)status_host_ = 0; }
+
+  // In-place-capable allreduce over ranks' buffers at `off`; outs[r] may equal the input.
+  cudaError_t allreduce(size_t off, void* const* outs, size_t count, DType dtype, Algo algo, float scale, int idiv,
+                        int blocks, cudaStream_t s);
+  cudaError_t fused_step(size_t off, size_t count, DType dtype, void* const* params, float* const* masters,
+                         float* const* s1, float* const* s2, const OptHyper& h, float scale, int blocks, cudaStream_t s);
+  cudaError_t allgatherv(const void* const* ins, const unsigned long long* bytes, const unsigned long long* out_offs,
+                         int blocks, cudaStream_t s);
+  // A barrier-only launch in which rank `absent` (if >= 0) does not take part, so that the
+  // others run into the bounded wait. `timeout_s` bounds it.
+  cudaError_t barrier_probe(int absent, double timeout_s, cudaStream_t s);
+
+ private:
+  dev::RankCtx ctx(int r, int channel) const;
+  int device_, n_;
+  size_t bytes_;
+  std::vector<char*> bufs_;
+  std::vector<char*> pads_;
+  uint32_t* epochs_ = nullptr;  // [n][kChannels][kMaxBlocks]
+  uint32_t* status_host_ = nullptr;
+  uint32_t* status_dev_ = nullptr;
+  double timeout_s_ = 20.0;
+};
+
+cudaError_t launch_barrier_probe(const dev::RankCtx* ctxs, int nranks, int absent, cudaStream_t s);
+
+}  // namespace gpu
+}  // namespace bc

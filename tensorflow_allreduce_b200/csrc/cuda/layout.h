@@ -1,0 +1,37 @@
+// Constants and plain structs shared by host code and kernels: signal-pad layout and the
+// per-rank synchronisation context handed to every collective kernel.
+#pragma once
+
+#include <stddef.h>
+#include <stdint.h>
+
+namespace bc {
+namespace dev {
+
+constexpr int kMaxRanks = 8;
+constexpr int kMaxBlocks = 256;     // barrier slots per channel
+constexpr int kMetaBlocks = 64;     // blocks that may exchange per-call metadata (allgatherv)
+constexpr int kChannels = 4;
+
+// Layout of one channel inside a rank's signal pad (all offsets in bytes).
+constexpr size_t kFlagBytes = (size_t)kMaxBlocks * kMaxRanks * sizeof(uint32_t);          // 8 KiB
+constexpr size_t kMetaBytes = (size_t)kMetaBlocks * kMaxRanks * 2 * sizeof(uint64_t);     // 8 KiB
+constexpr size_t kChannelBytes = kFlagBytes + kMetaBytes;
+constexpr size_t kPadBytes = kChannels * kChannelBytes;                                  // 64 KiB
+
+// Status word written by a block whose wait ran out (host-mapped memory).
+constexpr uint32_t kStatusTimeout = 0x80000000u;
+
+// What one (real or emulated) rank needs to synchronise with its peers on one channel.
+struct RankCtx {
+  int rank;
+  int world;
+  uint32_t* flags[kMaxRanks];   // flags[p] = channel flag area inside rank p's pad
+  uint64_t* meta[kMaxRanks];    // meta[p]  = channel metadata area inside rank p's pad
+  uint32_t* epochs;             // this rank's private per-block epoch counters for the channel
+  uint32_t* status;             // host-visible status word
+  unsigned long long timeout_ns;
+};
+
+}  // namespace dev
+}  // namespace bc

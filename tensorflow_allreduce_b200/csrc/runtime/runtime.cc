@@ -1,0 +1,585 @@
+#include "runtime.h"
+
+#include <cuda_runtime.h>
+#include <poll.h>
+#include <stdarg.h>
+#include <string.h>
+#include <sys/eventfd.h>
+#include <unistd.h>
+
+#include <algorithm>
+
+#include "../cpu/ring.h"
+#include "../cuda/comm.h"
+
+namespace bc {
+
+// ---- logging -------------------------------------------------------------------------------
+
+int log_level() {
+  static int lvl = [] {
+    const char* e = getenv("BC_LOG_LEVEL");
+    return e ? atoi(e) : 0;
+  }();
+  return lvl;
+}
+
+void log_line(int level, const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  const char* rank = getenv("RANK");
+  fprintf(stderr, "[bcoll %s r%s] %s\n", level <= 0 ? "E" : level == 1 ? "I" : "D", rank ? rank : "?", buf);
+}
+
+// ---- fault injection (host side only) --------------------------------------------------------
+
+FaultSpec FaultSpec::parse(const std::string& s) {
+  FaultSpec f;
+  if (s.empty()) return f;
+  size_t pos = 0;
+  bool first = true;
+  while (pos <= s.size()) {
+    size_t next = s.find(':', pos);
+    std::string tok = s.substr(pos, next == std::string::npos ? std::string::npos : next - pos);
+    if (first) {
+      first = false;
+      std::string kind = tok;
+      size_t eq = tok.find('=');
+      if (eq != std::string::npos) kind = tok.substr(0, eq);
+      if (kind == "drop_request") f.kind = DROP_REQUEST;
+      else if (kind == "delay_ms") { f.kind = DELAY_MS; if (eq != std::string::npos) f.ms = atoi(tok.c_str() + eq + 1); }
+      else if (kind == "exit_before") f.kind = EXIT_BEFORE;
+      else if (kind == "close_ctrl") f.kind = CLOSE_CTRL;
+      else throw Error("unknown fault kind '" + kind + "'");
+    } else {
+      size_t eq = tok.find('=');
+      if (eq != std::string::npos) {
+        std::string k = tok.substr(0, eq), v = tok.substr(eq + 1);
+        if (k == "rank") f.rank = atoi(v.c_str());
+        else if (k == "name") f.name = v;
+        else if (k == "ms") f.ms = atoi(v.c_str());
+      }
+    }
+    if (next == std::string::npos) break;
+    pos = next + 1;
+  }
+  return f;
+}
+
+// ---- construction / teardown ---------------------------------------------------------------
+
+Runtime::Runtime(const RuntimeOptions& o) : opt_(o) {
+  t_ = bootstrap(o.rank, o.size, o.addr, o.port, o.timeout_s);
+  local_rank_ = o.local_rank_override >= 0 ? o.local_rank_override : t_.local_rank;
+  fault_ = FaultSpec::parse(o.fault);
+  if (o.device >= 0) {
+    BC_CHECK(t_.local_size == t_.size, "GPU collectives need all ranks on one NVLink node (ranks span several hosts)");
+    gpu::CommConfig cc;
+    cc.staging_bytes = o.staging_bytes;
+    cc.heap_bytes = o.heap_bytes;
+    cc.device_timeout_s = o.device_timeout_s;
+    cc.force_algo = o.force_algo;
+    cc.one_shot_max_bytes = o.one_shot_max_bytes;
+    cc.nvls_min_bytes = o.nvls_min_bytes;
+    cc.use_nvls = o.use_nvls;
+    cc.max_blocks = o.max_blocks;
+    cc.symm_mode = o.symm_mode == 1 ? gpu::SymmAllocator::Mode::VMM
+                 : o.symm_mode == 2 ? gpu::SymmAllocator::Mode::IPC : gpu::SymmAllocator::Mode::AUTO;
+    const double dl = o.timeout_s;
+    Transport* tp = &t_;
+    gpu::HostAllgather ag = [tp, dl](const std::string& mine) { return tp->allgather(mine, now_s() + dl); };
+    comm_.reset(new gpu::Comm(t_.rank, t_.size, o.device, t_.job_id, cc, ag, o.timeout_s));
+  }
+  wake_fd_ = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
+  BC_CHECK(wake_fd_ >= 0, "eventfd failed");
+  thread_ = std::thread([this] { loop(); });
+}
+
+Runtime::~Runtime() {
+  try {
+    shutdown();
+  } catch (...) {
+  }
+  if (wake_fd_ >= 0) ::close(wake_fd_);
+}
+
+void Runtime::wake() {
+  uint64_t one = 1;
+  ssize_t k = ::write(wake_fd_, &one, 8);
+  (void)k;
+}
+
+void Runtime::shutdown() {
+  if (shutdown_done_) return;
+  shutdown_done_ = true;
+  if (!broken_.load() && thread_.joinable()) {
+    try {
+      std::unique_ptr<OpRecord> rec(new OpRecord());
+      rec->name = "__shutdown__";
+      rec->op = OpType::SHUTDOWN;
+      int64_t h = enqueue(std::move(rec));
+      wait(h, std::min(opt_.timeout_s, 30.0));
+      release(h);
+    } catch (const std::exception& e) {
+      BC_LOG(1, "shutdown handshake failed: %s", e.what());
+    }
+  }
+  stop_.store(true);
+  wake();
+  if (thread_.joinable()) thread_.join();
+  if (comm_) {
+    cudaSetDevice(opt_.device);
+    cudaDeviceSynchronize();
+    if (!broken_.load()) {
+      try {
+        t_.barrier(now_s() + std::min(opt_.timeout_s, 30.0));
+      } catch (...) {
+      }
+    }
+    comm_.reset();
+  }
+}
+
+std::string Runtime::broken_reason() {
+  std::lock_guard<std::mutex> g(mu_);
+  return broken_reason_;
+}
+
+void Runtime::set_fault(const std::string& spec) {
+  std::lock_guard<std::mutex> g(mu_);
+  fault_ = FaultSpec::parse(spec);
+}
+
+// ---- user-thread side ----------------------------------------------------------------------
+
+int64_t Runtime::enqueue(std::unique_ptr<OpRecord> rec_in) {
+  std::shared_ptr<OpRecord> rec(rec_in.release());
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    if (broken_.load()) throw CommLost("communicator is broken: " + broken_reason_);
+    BC_CHECK(!stop_.load(), "the runtime has been shut down");
+    BC_CHECK(table_.find(rec->name) == table_.end(),
+             "a collective named '" << rec->name << "' is already in flight on this rank");
+    if (rec->device == DeviceKind::GPU) {
+      BC_CHECK(comm_ != nullptr, "GPU tensor passed, but init() ran without a GPU device");
+      cudaEvent_t ev = nullptr;
+      cudaSetDevice(opt_.device);
+      cudaError_t e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+      BC_CHECK(e == cudaSuccess, "cudaEventCreate: " << cudaGetErrorString(e));
+      rec->done_event = ev;
+    }
+    rec->id = next_id_++;
+    rec->t_enqueue = now_s();
+    handles_[rec->id] = rec;
+    table_[rec->name] = rec;
+    queue_.push_back(rec);
+  }
+  wake();
+  return rec->id;
+}
+
+std::shared_ptr<OpRecord> Runtime::get(int64_t handle) {
+  std::lock_guard<std::mutex> g(mu_);
+  auto it = handles_.find(handle);
+  BC_CHECK(it != handles_.end(), "unknown handle " << handle);
+  return it->second;
+}
+
+bool Runtime::poll(int64_t handle) {
+  std::lock_guard<std::mutex> g(mu_);
+  auto it = handles_.find(handle);
+  BC_CHECK(it != handles_.end(), "unknown handle " << handle);
+  return it->second->state != OpRecord::PENDING;
+}
+
+void Runtime::wait(int64_t handle, double timeout_s) {
+  std::unique_lock<std::mutex> lk(mu_);
+  auto it = handles_.find(handle);
+  BC_CHECK(it != handles_.end(), "unknown handle " << handle);
+  std::shared_ptr<OpRecord> rec = it->second;
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::duration<double>(timeout_s);
+  while (rec->state == OpRecord::PENDING) {
+    if (cv_.wait_until(lk, deadline) == std::cv_status::timeout && rec->state == OpRecord::PENDING)
+      throw Error("timed out waiting for collective '" + rec->name + "'");
+  }
+  if (rec->state == OpRecord::FAILED) throw Error(rec->error);
+}
+
+void Runtime::release(int64_t handle) {
+  std::shared_ptr<OpRecord> rec;
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = handles_.find(handle);
+    if (it == handles_.end()) return;
+    rec = it->second;
+    handles_.erase(it);
+  }
+  if (rec->done_event) {
+    cudaEventDestroy((cudaEvent_t)rec->done_event);
+    rec->done_event = nullptr;
+  }
+}
+
+std::vector<std::string> Runtime::blob_gather(const std::string& name, const std::string& mine) {
+  std::unique_ptr<OpRecord> rec(new OpRecord());
+  rec->name = name;
+  rec->op = OpType::BLOB_GATHER;
+  rec->dtype = DType::U8;
+  rec->blob = mine;
+  int64_t h = enqueue(std::move(rec));
+  wait(h, opt_.timeout_s + 5.0);
+  std::vector<std::string> out = get(h)->blobs;
+  release(h);
+  return out;
+}
+
+// ---- background thread ---------------------------------------------------------------------
+
+void Runtime::finish(const std::shared_ptr<OpRecord>& r, bool ok, const std::string& err) {
+  r->t_done = now_s();
+  {
+    std::lock_guard<std::mutex> g(stats_mu_);
+    StatEntry e;
+    e.name = r->name;
+    e.op = (int)r->op;
+    e.algo = r->algo;
+    e.device = (int)r->device;
+    e.blocks = (comm_ && r->device == DeviceKind::GPU) ? comm_->last_blocks : 0;
+    int64_t n = 1;
+    for (int64_t d : r->shape) n *= d;
+    e.bytes = n * (int64_t)dtype_size(r->dtype);
+    e.t_enqueue = r->t_enqueue;
+    e.t_negotiated = r->t_negotiated;
+    e.t_done = r->t_done;
+    stats_.push_back(e);
+    if (stats_.size() > 4096) stats_.pop_front();
+  }
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    r->error = err;
+    r->state = ok ? OpRecord::DONE : OpRecord::FAILED;
+  }
+  cv_.notify_all();
+}
+
+void Runtime::fail_everything(const std::string& why) {
+  std::vector<std::shared_ptr<OpRecord>> victims;
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    broken_.store(true);
+    broken_reason_ = why;
+    for (auto& kv : table_) victims.push_back(kv.second);
+    table_.clear();
+    queue_.clear();
+  }
+  BC_LOG(0, "communicator failed: %s", why.c_str());
+  if (t_.rank == 0) {
+    Response abort_msg;
+    abort_msg.type = ResponseType::ABORT;
+    abort_msg.error = why;
+    const std::string frame = encode(abort_msg);
+    for (int r = 1; r < t_.size; r++) {
+      if (!t_.ctrl[r].valid()) continue;
+      try {
+        t_.ctrl[r].send_frame(frame, now_s() + 1.0);
+      } catch (...) {
+      }
+    }
+  }
+  for (auto& r : victims)
+    if (r->state == OpRecord::PENDING) finish(r, false, "collective '" + r->name + "' failed: " + why);
+}
+
+void Runtime::loop() {
+  if (comm_) cudaSetDevice(opt_.device);
+  try {
+    while (!stop_.load()) loop_body();
+  } catch (const std::exception& e) {
+    fail_everything(e.what());
+  }
+}
+
+void Runtime::send_request(const OpRecord& rec) {
+  Request q;
+  q.rank = t_.rank;
+  q.op = rec.op;
+  q.dtype = rec.dtype;
+  q.device = rec.device;
+  q.name = rec.name;
+  q.shape = rec.shape;
+  q.blob = rec.blob;
+  q.symm_off = -1;
+  if (rec.zero_copy && comm_) {
+    int64_t n = 1;
+    for (int64_t d : rec.shape) n *= d;
+    gpu::Segment* seg = comm_->allocator().find(rec.in, (size_t)n * dtype_size(rec.dtype));
+    if (seg && rec.in == rec.out) q.symm_off = ((int64_t)seg->id << 48) | (int64_t)((const char*)rec.in - seg->local);
+  }
+  FaultSpec f;
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    f = fault_;
+  }
+  if (f.matches(t_.rank, rec.name)) {
+    switch (f.kind) {
+      case FaultSpec::DROP_REQUEST:
+        BC_LOG(1, "fault injection: dropping request for '%s'", rec.name.c_str());
+        return;
+      case FaultSpec::DELAY_MS:
+        std::this_thread::sleep_for(std::chrono::milliseconds(f.ms));
+        break;
+      case FaultSpec::EXIT_BEFORE:
+        fprintf(stderr, "[bcoll] fault injection: exiting before '%s'\n", rec.name.c_str());
+        fflush(stderr);
+        _exit(41);
+      case FaultSpec::CLOSE_CTRL:
+        for (auto& s : t_.ctrl) s.close();
+        throw CommLost("fault injection: control connection closed");
+      default:
+        break;
+    }
+  }
+  if (t_.rank == 0) {
+    coordinator_handle(q);
+  } else {
+    t_.ctrl[0].send_frame(encode(q), now_s() + opt_.timeout_s);
+  }
+}
+
+void Runtime::drain_local_queue() {
+  std::deque<std::shared_ptr<OpRecord>> local;
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    local.swap(queue_);
+  }
+  for (auto& rec : local) send_request(*rec);
+}
+
+void Runtime::coordinator_handle(const Request& q) {
+  BC_CHECK(q.rank >= 0 && q.rank < t_.size, "request from out-of-range rank " << q.rank);
+  Pending& p = pending_[q.name];
+  if (p.reqs.empty()) {
+    p.reqs.resize(t_.size);
+    p.have.assign(t_.size, false);
+    p.first_seen = now_s();
+  }
+  if (p.have[q.rank]) {
+    BC_LOG(0, "rank %d asked twice for '%s' before it completed; ignoring the second request", q.rank, q.name.c_str());
+    return;
+  }
+  p.have[q.rank] = true;
+  p.reqs[q.rank] = q;
+  p.count++;
+  if (p.count < t_.size) return;
+  Response resp = build_response(q.name, p.reqs);
+  pending_.erase(q.name);
+  const std::string frame = encode(resp);
+  for (int r = 1; r < t_.size; r++) t_.ctrl[r].send_frame(frame, now_s() + opt_.timeout_s);
+  perform(resp);
+}
+
+void Runtime::coordinator_check_deadlines() {
+  if (pending_.empty()) return;
+  const double now = now_s();
+  std::vector<std::string> late;
+  for (auto& kv : pending_)
+    if (now - kv.second.first_seen > opt_.timeout_s) late.push_back(kv.first);
+  for (const auto& name : late) {
+    Pending& p = pending_[name];
+    std::string missing;
+    for (int r = 0; r < t_.size; r++)
+      if (!p.have[r]) missing += (missing.empty() ? "" : ",") + std::to_string(r);
+    Response resp;
+    resp.type = ResponseType::ERROR;
+    resp.name = name;
+    resp.error = "Timed out after " + std::to_string((int)opt_.timeout_s) + " s waiting for rank(s) " + missing +
+                 " to request collective '" + name + "'.";
+    pending_.erase(name);
+    const std::string frame = encode(resp);
+    for (int r = 1; r < t_.size; r++) t_.ctrl[r].send_frame(frame, now_s() + opt_.timeout_s);
+    perform(resp);
+  }
+}
+
+void Runtime::loop_body() {
+  std::vector<struct pollfd> fds;
+  std::vector<int> who;
+  fds.push_back({wake_fd_, POLLIN, 0});
+  who.push_back(-1);
+  if (t_.size > 1) {
+    if (t_.rank == 0) {
+      for (int r = 1; r < t_.size; r++) {
+        fds.push_back({t_.ctrl[r].fd(), POLLIN, 0});
+        who.push_back(r);
+      }
+    } else {
+      fds.push_back({t_.ctrl[0].fd(), POLLIN, 0});
+      who.push_back(0);
+    }
+  }
+  const int timeout_ms = (t_.rank == 0 && !pending_.empty()) ? 50 : 500;
+  int rc = ::poll(fds.data(), fds.size(), timeout_ms);
+  if (rc < 0) {
+    if (errno == EINTR) return;
+    throw CommLost(std::string("poll failed: ") + strerror(errno));
+  }
+  if (fds[0].revents & POLLIN) {
+    uint64_t v;
+    while (::read(wake_fd_, &v, 8) == 8) {
+    }
+    drain_local_queue();
+  }
+  for (size_t i = 1; i < fds.size(); i++) {
+    if (!(fds[i].revents & (POLLIN | POLLHUP | POLLERR))) continue;
+    if (stop_.load()) break;
+    const int r = who[i];
+    std::string frame;
+    try {
+      frame = t_.ctrl[r].recv_frame(now_s() + opt_.timeout_s);
+    } catch (const CommLost& e) {
+      throw CommLost("lost the control connection to rank " + std::to_string(r) + " (" + e.what() + ")");
+    }
+    if (t_.rank == 0) {
+      coordinator_handle(decode_request(frame));
+    } else {
+      perform(decode_response(frame));
+    }
+  }
+  if (t_.rank == 0) coordinator_check_deadlines();
+}
+
+void Runtime::perform(const Response& resp) {
+  if (resp.type == ResponseType::ABORT) throw CommLost(resp.error.empty() ? "aborted by rank 0" : resp.error);
+  std::shared_ptr<OpRecord> rec;
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    auto it = table_.find(resp.name);
+    if (it != table_.end()) {
+      rec = it->second;
+      table_.erase(it);
+    }
+  }
+  if (!rec) {
+    if (resp.type == ResponseType::ERROR) {
+      BC_LOG(1, "error for a collective this rank has not requested ('%s'): %s", resp.name.c_str(), resp.error.c_str());
+      return;
+    }
+    throw Error("received a go-ahead for unknown collective '" + resp.name + "'");
+  }
+  rec->t_negotiated = now_s();
+  try {
+    switch (resp.type) {
+      case ResponseType::ERROR:
+        finish(rec, false, resp.error);
+        return;
+      case ResponseType::ALLREDUCE:
+        rec->zero_copy = rec->zero_copy && (resp.flags & kFlagZeroCopy);
+        perform_allreduce(*rec);
+        break;
+      case ResponseType::ALLGATHER:
+        perform_allgather(*rec, resp);
+        break;
+      case ResponseType::BLOB_GATHER:
+        rec->blobs = resp.blobs;
+        break;
+      case ResponseType::SHUTDOWN:
+        stop_.store(true);
+        break;
+      default:
+        throw Error("unexpected response type");
+    }
+    finish(rec, true, "");
+  } catch (const CommLost&) {
+    finish(rec, false, "collective '" + rec->name + "' failed: connection lost");
+    throw;
+  } catch (const std::exception& e) {
+    finish(rec, false, e.what());
+  }
+}
+
+void Runtime::perform_allreduce(OpRecord& r) {
+  size_t count = 1;
+  for (int64_t d : r.shape) count *= (size_t)d;
+  const double scale = r.average ? 1.0 / t_.size : 1.0;
+  const int64_t idiv = r.average ? t_.size : 1;
+  if (r.device == DeviceKind::CPU) {
+    if (r.in != r.out && count) memcpy(r.out, r.in, count * dtype_size(r.dtype));
+    cpu_ring_allreduce(t_, r.out, count, r.dtype, scale, idiv, now_s() + opt_.timeout_s);
+    r.algo = 0;
+    return;
+  }
+  BC_CHECK(comm_, "GPU collective without a GPU communicator");
+  BC_CHECK(comm_->device_status() == 0, "an earlier device-side wait timed out (status 0x" << std::hex << comm_->device_status()
+           << "); the communicator cannot be used any more");
+  cudaStream_t s = comm_->stream(0);
+  if (r.ready_event) {
+    cudaError_t e = cudaStreamWaitEvent(s, (cudaEvent_t)r.ready_event, 0);
+    BC_CHECK(e == cudaSuccess, "cudaStreamWaitEvent: " << cudaGetErrorString(e));
+  }
+  r.algo = (int)comm_->allreduce(0, r.in, r.out, count, r.dtype, (float)scale, (int)idiv, r.zero_copy);
+  cudaError_t e = cudaEventRecord((cudaEvent_t)r.done_event, s);
+  BC_CHECK(e == cudaSuccess, "cudaEventRecord: " << cudaGetErrorString(e));
+}
+
+void Runtime::perform_allgather(OpRecord& r, const Response& resp) {
+  BC_CHECK((int)resp.dim0.size() == t_.size, "allgather response lacks the per-rank sizes");
+  r.dim0 = resp.dim0;
+  int64_t total_rows = 0;
+  for (int64_t d : r.dim0) total_rows += d;
+  size_t row_bytes = dtype_size(r.dtype);
+  for (size_t i = 1; i < r.shape.size(); i++) row_bytes *= (size_t)r.shape[i];
+  int is_symm = 0;
+  BC_CHECK(r.alloc, "allgather needs an output allocator");
+  r.out = r.alloc(r.id, total_rows, r.alloc_user, &is_symm);
+  const size_t total_bytes = (size_t)total_rows * row_bytes;
+  BC_CHECK(r.out || total_bytes == 0, "the output allocator returned no buffer");
+  if (r.device == DeviceKind::CPU) {
+    cpu_ring_allgatherv(t_, r.in, r.out, r.dim0, row_bytes, now_s() + opt_.timeout_s);
+    return;
+  }
+  BC_CHECK(comm_, "GPU collective without a GPU communicator");
+  BC_CHECK(comm_->device_status() == 0, "an earlier device-side wait timed out; the communicator cannot be used any more");
+  cudaStream_t s = comm_->stream(0);
+  if (r.ready_event) {
+    cudaError_t e = cudaStreamWaitEvent(s, (cudaEvent_t)r.ready_event, 0);
+    BC_CHECK(e == cudaSuccess, "cudaStreamWaitEvent: " << cudaGetErrorString(e));
+  }
+  comm_->allgatherv(0, r.in, (size_t)r.shape[0] * row_bytes, is_symm ? r.out : nullptr, is_symm ? nullptr : r.out, total_bytes);
+  r.algo = 0;
+  cudaError_t e = cudaEventRecord((cudaEvent_t)r.done_event, s);
+  BC_CHECK(e == cudaSuccess, "cudaEventRecord: " << cudaGetErrorString(e));
+}
+
+// ---- stats ---------------------------------------------------------------------------------
+
+std::string Runtime::stats_json() {
+  std::lock_guard<std::mutex> g(stats_mu_);
+  std::ostringstream os;
+  os << "[";
+  bool first = true;
+  for (const auto& e : stats_) {
+    if (!first) os << ",";
+    first = false;
+    os << "{\"name\":\"";
+    for (char ch : e.name) {
+      if (ch == '"' || ch == '\\') os << '\\';
+      os << ch;
+    }
+    os.precision(9);
+    os << "\",\"op\":" << e.op << ",\"algo\":" << e.algo << ",\"device\":" << e.device << ",\"blocks\":" << e.blocks
+       << ",\"bytes\":" << e.bytes << std::fixed << ",\"t_enqueue\":" << e.t_enqueue << ",\"t_negotiated\":" << e.t_negotiated
+       << ",\"t_done\":" << e.t_done << "}";
+  }
+  os << "]";
+  return os.str();
+}
+
+void Runtime::clear_stats() {
+  std::lock_guard<std::mutex> g(stats_mu_);
+  stats_.clear();
+}
+
+}  // namespace bc

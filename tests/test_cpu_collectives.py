@@ -1,0 +1,206 @@
+"""CPU group, world size 2 and 3 over local sockets: the plumbing configuration (fp32 tensors of
+shapes [17], [1000,10], [3,5,7] filled with N(0,1)+rank, sum and average; allgather of
+[rank+2, 4]) and the cases of the reference's unit tests
+(tensorflow/contrib/mpi_collectives/mpi_ops_test.py:70-263)."""
+import pytest
+
+from _util import run
+
+
+def test_rank_size_single_process():
+    # Without a launcher the library falls back to rank 0 / size 1 (mpi_ops_test.py:61-62).
+    res = run("""
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"): os.environ.pop(k, None)
+    bc.init(device="cpu")
+    emit(rank=bc.rank(), size=bc.size(), local_rank=bc.local_rank())
+    bc.shutdown()
+    """, nranks=1)
+    assert res[0][1] == {"rank": 0, "size": 1, "local_rank": 0}
+
+
+@pytest.mark.parametrize("n", [2, 3])
+def test_rank_size_env(n):
+    res = run("""
+    with bc.Session(device="cpu"):
+        emit(rank=bc.rank(), size=bc.size(), local_rank=bc.local_rank(), local_size=bc.local_size())
+    """, nranks=n)
+    for i, (_, rec) in enumerate(res):
+        assert rec == {"rank": i, "size": n, "local_rank": i, "local_size": n}
+
+
+def test_ompi_env_names():
+    res = run("""
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        v = os.environ.pop(k)
+        os.environ["OMPI_COMM_WORLD_" + {"RANK": "RANK", "WORLD_SIZE": "SIZE", "LOCAL_RANK": "LOCAL_RANK"}[k]] = v
+    bc.init(device="cpu")
+    emit(rank=bc.rank(), size=bc.size())
+    bc.shutdown()
+    """, nranks=2)
+    assert [r[1]["rank"] for r in res] == [0, 1]
+    assert all(r[1]["size"] == 2 for r in res)
+
+
+def test_plumbing_config_world2():
+    res = run("""
+    bc.init(device="cpu")
+    ok = True; worst = 0.0
+    for shape in ([17], [1000, 10], [3, 5, 7]):
+        per_rank = []
+        for r in range(SIZE):
+            g = torch.Generator().manual_seed(0)
+            per_rank.append(torch.randn(shape, generator=g) + r)
+        mine = per_rank[RANK]
+        want = sum(per_rank)
+        s = bc.allreduce(mine, average=False)
+        a = bc.allreduce(mine, average=True)
+        worst = max(worst, (s - want).abs().max().item(), (a - want / SIZE).abs().max().item())
+        ok = ok and s.shape == mine.shape and s.dtype == mine.dtype
+    t = (RANK * 100 + torch.arange((RANK + 2) * 4, dtype=torch.float32)).reshape(RANK + 2, 4)
+    g = bc.allgather(t)
+    want = torch.cat([(r * 100 + torch.arange((r + 2) * 4, dtype=torch.float32)).reshape(r + 2, 4) for r in range(SIZE)])
+    emit(ok=bool(ok), worst=worst, gshape=list(g.shape), gather_ok=bool(torch.equal(g, want)))
+    bc.shutdown()
+    """, nranks=2)
+    for _, rec in res:
+        assert rec["ok"] and rec["worst"] <= 1e-6
+        assert rec["gshape"] == [5, 4] and rec["gather_ok"]
+
+
+@pytest.mark.parametrize("n", [2, 3])
+def test_allreduce_cpu_like_reference(n):
+    # int32 + float32, 1/2/3-D [17]*dim, same tensor on every rank => expected = tensor * size,
+    # exact for size <= 3 (mpi_ops_test.py:84-112).
+    res = run("""
+    bc.init(device="cpu")
+    bad = []
+    for dtype in (torch.int32, torch.float32, torch.int64, torch.float64, torch.bfloat16, torch.float16, torch.uint8):
+        for dim in (1, 2, 3):
+            g = torch.Generator().manual_seed(1234)
+            if dtype.is_floating_point:
+                t = (torch.rand([17] * dim, generator=g) * 200 - 100).to(dtype)
+            elif dtype == torch.uint8:
+                t = torch.randint(0, 40, [17] * dim, generator=g, dtype=dtype)
+            else:
+                t = torch.randint(-100, 100, [17] * dim, generator=g, dtype=dtype)
+            s = bc.allreduce(t, average=False)
+            want = (t.float() * SIZE).to(dtype) if dtype in (torch.bfloat16, torch.float16) else t * SIZE
+            if not torch.equal(s, want):
+                bad.append([str(dtype), dim, "sum"])
+            a = bc.allreduce(t, average=True)
+            if dtype.is_floating_point:
+                tol = 1e-2 if dtype in (torch.bfloat16, torch.float16) else 1e-6
+                if not torch.allclose(a.float(), t.float(), rtol=tol, atol=tol):
+                    bad.append([str(dtype), dim, "avg"])
+            elif not torch.equal(a, t):
+                bad.append([str(dtype), dim, "avg"])
+    emit(bad=bad)
+    bc.shutdown()
+    """, nranks=n)
+    for _, rec in res:
+        assert rec["bad"] == []
+
+
+def test_integer_average_truncates():
+    res = run("""
+    bc.init(device="cpu")
+    t = torch.tensor([RANK * 3 + 1, -(RANK * 3 + 1), 7], dtype=torch.int32)
+    emit(avg=bc.allreduce(t, average=True).tolist())
+    bc.shutdown()
+    """, nranks=2)
+    # sums: [5, -5, 14] -> truncating division by 2
+    for _, rec in res:
+        assert rec["avg"] == [2, -2, 7]
+
+
+@pytest.mark.parametrize("n", [2, 3])
+def test_allgather_fixed_and_variable(n):
+    res = run("""
+    bc.init(device="cpu")
+    bad = []
+    sizes = ([17, 32, 81, 12, 15, 23, 22] * 5)[:SIZE]
+    for dtype in (torch.int32, torch.float32):
+        for dim in (1, 2, 3):
+            t = torch.ones([17] * dim, dtype=dtype) * RANK
+            g = bc.allgather(t)
+            if list(g.shape) != [17 * SIZE] + [17] * (dim - 1): bad.append(["fixed-shape", dim])
+            for i in range(SIZE):
+                if not bool((g[i * 17:(i + 1) * 17] == i).all()): bad.append(["fixed", dim, i])
+            t = torch.ones([sizes[RANK]] + [17] * (dim - 1), dtype=dtype) * RANK
+            g = bc.allgather(t)
+            if list(g.shape) != [sum(sizes)] + [17] * (dim - 1): bad.append(["var-shape", dim])
+            for i in range(SIZE):
+                lo = sum(sizes[:i])
+                if not bool((g[lo:lo + sizes[i]] == i).all()): bad.append(["var", dim, i])
+    # zero rows on one rank, and everywhere
+    t = torch.full((0 if RANK == 0 else 3, 2), float(RANK))
+    g = bc.allgather(t)
+    if g.shape[0] != 3 * (SIZE - 1): bad.append(["zero-rows", list(g.shape)])
+    g = bc.allgather(torch.zeros(0, 5))
+    if list(g.shape) != [0, 5]: bad.append(["all-empty", list(g.shape)])
+    # zero-sized allreduce
+    z = bc.allreduce(torch.zeros(0, 3))
+    if list(z.shape) != [0, 3]: bad.append(["empty-allreduce"])
+    emit(bad=bad)
+    bc.shutdown()
+    """, nranks=n)
+    for _, rec in res:
+        assert rec["bad"] == []
+
+
+def test_sparse_allreduce_matches_dense():
+    res = run("""
+    bc.init(device="cpu")
+    idx = torch.tensor([[RANK, 2, 2], [0, 1, RANK]])
+    val = torch.tensor([1.0 + RANK, 2.0, 3.0])
+    sp = torch.sparse_coo_tensor(idx, val, (4, 3))
+    dense_avg = bc.allreduce(sp.to_dense(), average=True)
+    sp_avg = bc.allreduce(sp, average=True)
+    sp_sum = bc.allreduce(sp, average=False)
+    emit(is_sparse=bool(sp_avg.is_sparse), avg_ok=bool(torch.allclose(sp_avg.to_dense(), dense_avg)),
+         sum_ok=bool(torch.allclose(sp_sum.to_dense(), dense_avg * SIZE)), nnz=int(sp_sum._nnz()))
+    bc.shutdown()
+    """, nranks=2)
+    for _, rec in res:
+        assert rec == {"is_sparse": True, "avg_ok": True, "sum_ok": True, "nnz": 6}
+
+
+def test_broadcast_and_named_out_of_order():
+    res = run("""
+    bc.init(device="cpu")
+    t = torch.arange(6.).reshape(2, 3) + 10 * RANK
+    b = bc.broadcast(t, root=1)
+    # names decide what is matched with what, not the call order (mpi_ops.cc:255-269)
+    x = torch.full((4,), 1.0 + RANK); y = torch.full((5,), 10.0 + RANK)
+    if RANK == 0:
+        hx = bc.allreduce_async(x, average=False, name="x"); hy = bc.allreduce_async(y, average=False, name="y")
+    else:
+        hy = bc.allreduce_async(y, average=False, name="y"); hx = bc.allreduce_async(x, average=False, name="x")
+    emit(b=b.tolist(), x=hx.wait().tolist(), y=hy.wait().tolist(), objs=bc.host_allgather({"r": RANK}))
+    bc.shutdown()
+    """, nranks=2)
+    for _, rec in res:
+        assert rec["b"] == [[10.0, 11.0, 12.0], [13.0, 14.0, 15.0]]
+        assert rec["x"] == [3.0] * 4 and rec["y"] == [21.0] * 5
+        assert rec["objs"] == [{"r": 0}, {"r": 1}]
+
+
+def test_dependent_allreduce_chain():
+    # Chained add -> allreduce stages with a closed-form result, as the reference's stress test
+    # (mpi_allreduce_test.py:35-128), shortened for the CPU path.
+    res = run("""
+    bc.init(device="cpu")
+    stages, n = 6, 121
+    ok = True
+    for it in range(20):
+        x = torch.ones(n, n) + RANK * 100
+        for i in range(stages):
+            x = bc.allreduce(x + 2.0 ** (i + 1), average=False)
+        want = 1.0
+        for i in range(stages):
+            want = (want + 2.0 ** (i + 1)) * SIZE + (100 * SIZE * (SIZE - 1) / 2 if i == 0 else 0)
+        ok = ok and bool(torch.allclose(x, torch.full_like(x, want)))
+    emit(ok=ok)
+    bc.shutdown()
+    """, nranks=2)
+    assert all(rec["ok"] for _, rec in res)
