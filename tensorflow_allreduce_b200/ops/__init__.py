@@ -1,2 +1,2 @@
 """Kernel-level operations: symmetric memory, fused reduce+update launches, single-GPU emulation."""
-from . import symmetric  # noqa: F401
+from . import emulated, fused_optim, symmetric  # noqa: F401

@@ -1,0 +1,113 @@
+"""A group of ranks emulated on ONE GPU.
+
+All ranks' buffers and signal pads live on the same device and each collective is a single
+cooperative launch of the production kernels (grid.y = rank). This exercises the complete
+multi-rank protocol (flag barriers, peer loads and stores, slice ownership, fused epilogues) on a
+machine with one GPU, where separate launches that wait on one another must never be used. The
+reference's closest analogue is its NCCL test that maps several "devices" onto one GPU
+(tensorflow/contrib/nccl/python/ops/nccl_ops_test.py:46).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import torch
+
+from .. import _lib
+from ..core import _DTYPES
+from .symmetric import tensor_from_ptr
+
+ALGOS = {"one_shot": 1, "two_shot": 2}
+
+
+def _check(rc, what):
+    if rc is None or rc < 0:
+        raise RuntimeError(f"{what}: {_lib.last_error()}")
+
+
+class EmulatedGroup:
+    def __init__(self, nranks: int, bytes_per_rank: int, device: Optional[int] = None):
+        self.lib = _lib.lib()
+        self.device = torch.cuda.current_device() if device is None else device
+        self.nranks = nranks
+        self.bytes_per_rank = int(bytes_per_rank)
+        self._g = self.lib.bc_emu_create(self.device, nranks, self.bytes_per_rank)
+        if not self._g:
+            raise RuntimeError(_lib.last_error())
+
+    def close(self):
+        if self._g:
+            torch.cuda.synchronize(self.device)
+            self.lib.bc_emu_destroy(self._g)
+            self._g = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def buffer(self, r: int, dtype: torch.dtype, numel: int, offset_bytes: int = 0) -> torch.Tensor:
+        """View of rank r's symmetric buffer."""
+        ptr = self.lib.bc_emu_buffer(self._g, r)
+        return tensor_from_ptr(int(ptr) + offset_bytes, (numel,), dtype, torch.device("cuda", self.device))
+
+    @property
+    def status(self) -> int:
+        return int(self.lib.bc_emu_status(self._g))
+
+    def max_blocks(self) -> int:
+        return int(self.lib.bc_max_emulated_blocks(self.device, self.nranks))
+
+    def allreduce(self, count: int, dtype: torch.dtype, algo: str = "two_shot", outs: Optional[Sequence[torch.Tensor]] = None,
+                  scale: float = 1.0, idiv: int = 1, blocks: int = 4, offset_bytes: int = 0):
+        """Reduce the first `count` elements (at `offset_bytes`) of all ranks' buffers. `outs`
+        defaults to in place (two-shot only)."""
+        n = self.nranks
+        arr = (C.c_void_p * n)()
+        for r in range(n):
+            if outs is None:
+                arr[r] = int(self.lib.bc_emu_buffer(self._g, r)) + offset_bytes
+            else:
+                arr[r] = outs[r].data_ptr()
+        s = torch.cuda.current_stream(self.device).cuda_stream
+        _check(self.lib.bc_emu_allreduce(self._g, offset_bytes, arr, count, _DTYPES[dtype], ALGOS[algo], float(scale), int(idiv),
+                                         blocks, C.c_void_p(s)), "emulated allreduce")
+
+    def fused_step(self, count: int, dtype: torch.dtype, params: Sequence[torch.Tensor], hyper: "_lib.OptHyper",
+                   masters: Optional[Sequence[torch.Tensor]] = None, state1: Optional[Sequence[torch.Tensor]] = None,
+                   state2: Optional[Sequence[torch.Tensor]] = None, scale: float = 1.0, blocks: int = 4, offset_bytes: int = 0):
+        n = self.nranks
+
+        def ptrs(ts):
+            if ts is None:
+                return None
+            a = (C.c_void_p * n)()
+            for r in range(n):
+                a[r] = ts[r].data_ptr()
+            return a
+
+        s = torch.cuda.current_stream(self.device).cuda_stream
+        _check(self.lib.bc_emu_fused_step(self._g, offset_bytes, count, _DTYPES[dtype], ptrs(params), ptrs(masters), ptrs(state1),
+                                          ptrs(state2), C.byref(hyper), float(scale), blocks, C.c_void_p(s)), "emulated fused step")
+
+    def allgatherv(self, ins: Sequence[torch.Tensor], out_offsets: Sequence[int], blocks: int = 2):
+        """Each rank r pushes `ins[r]` into every rank's buffer at `out_offsets[that rank]` plus
+        the displacement of r's slab (computed on the device)."""
+        n = self.nranks
+        ip = (C.c_void_p * n)()
+        nb = (C.c_ulonglong * n)()
+        oo = (C.c_ulonglong * n)()
+        for r in range(n):
+            ip[r] = ins[r].data_ptr() if ins[r].numel() else 0
+            nb[r] = ins[r].numel() * ins[r].element_size()
+            oo[r] = int(out_offsets[r])
+        s = torch.cuda.current_stream(self.device).cuda_stream
+        _check(self.lib.bc_emu_allgatherv(self._g, ip, nb, oo, blocks, C.c_void_p(s)), "emulated allgatherv")
+
+    def barrier_probe(self, absent: int = -1, timeout_s: float = 0.5):
+        """Barrier-only launch; rank `absent` does not take part, so the others run into the
+        bounded wait, record a status word and return."""
+        s = torch.cuda.current_stream(self.device).cuda_stream
+        _check(self.lib.bc_emu_barrier_probe(self._g, absent, float(timeout_s), C.c_void_p(s)), "barrier probe")

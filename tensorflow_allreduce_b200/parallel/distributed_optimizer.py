@@ -130,6 +130,7 @@ class DistributedOptimizer(torch.optim.Optimizer):
         self._buckets: List[_Bucket] = []
         self._next_bucket = 0
         self._launched_any = False
+        self.launch_count = 0   # collective kernels launched by this optimizer so far
         if self._gpu:
             cfg = core.config()
             self._bucket_bytes = int((bucket_mb if bucket_mb is not None else cfg.bucket_mb) * (1 << 20))
@@ -347,6 +348,7 @@ class DistributedOptimizer(torch.optim.Optimizer):
         core._call(rc, "bucket launch")
         b.launched = True
         self._launched_any = True
+        self.launch_count += 1
 
     # ---- optimizer interface -----------------------------------------------------------------
 

@@ -1,0 +1,222 @@
+"""The production kernels on ONE GPU with 2/4/8 emulated ranks, against plain PyTorch fp32
+references. Counterpart of the reference's GPU allreduce/allgather tests
+(tensorflow/contrib/mpi_collectives/mpi_ops_test.py:114-156, 204-263), which need one GPU per rank."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16, torch.float16, torch.int32, torch.int64, torch.float64, torch.uint8]
+PACK = {torch.float32: 4, torch.bfloat16: 8, torch.float16: 8, torch.int32: 4, torch.int64: 2, torch.float64: 2, torch.uint8: 16}
+
+
+def _fill(dtype, n, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    if dtype.is_floating_point:
+        return (torch.rand(n, generator=g, device="cuda") * 2 - 1).to(dtype)
+    if dtype == torch.uint8:
+        return torch.randint(0, 16, (n,), generator=g, device="cuda", dtype=torch.int32).to(dtype)
+    return torch.randint(-1000, 1000, (n,), generator=g, device="cuda", dtype=dtype)
+
+
+def _reference_sum(xs, dtype, scale=1.0, idiv=1):
+    """Sum in rank order; 16-bit floats accumulate in fp32 and round once (as the kernels do)."""
+    if dtype in (torch.bfloat16, torch.float16):
+        acc = xs[0].float()
+        for x in xs[1:]:
+            acc = acc + x.float()
+        return (acc * scale).to(dtype)
+    acc = xs[0].clone()
+    for x in xs[1:]:
+        acc = acc + x
+    if dtype.is_floating_point:
+        return acc * torch.tensor(scale, dtype=dtype, device=acc.device) if dtype == torch.float64 else acc * scale
+    if idiv > 1:
+        return torch.div(acc, idiv, rounding_mode="trunc").to(dtype)
+    return acc
+
+
+@pytest.fixture(scope="module")
+def emu():
+    from tensorflow_allreduce_b200.ops.emulated import EmulatedGroup
+
+    groups = {}
+
+    def get(n, nbytes=8 << 20):
+        key = (n, nbytes)
+        if key not in groups:
+            groups[key] = EmulatedGroup(n, nbytes)
+        return groups[key]
+
+    yield get
+    for g in groups.values():
+        g.close()
+
+
+@pytest.mark.parametrize("nranks", [2, 4, 8])
+@pytest.mark.parametrize("algo", ["one_shot", "two_shot"])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_allreduce_matches_reference(emu, nranks, algo, dtype):
+    g = emu(nranks)
+    e = PACK[dtype]
+    sizes = [0, 1, e - 1, e, e + 1, 3 * e * nranks + 5, 4096 + 3, (1 << 18) + 7]
+    for n in sizes:
+        bufs = [g.buffer(r, dtype, max(n, 1)) for r in range(nranks)]
+        xs = [_fill(dtype, n, 100 * r + 7) for r in range(nranks)]
+        for r in range(nranks):
+            bufs[r][:n].copy_(xs[r])
+        want = _reference_sum(xs, dtype)
+        if algo == "one_shot":
+            outs = [torch.empty(max(n, 1), dtype=dtype, device="cuda") for _ in range(nranks)]
+            g.allreduce(n, dtype, "one_shot", outs=outs, blocks=3)
+            got = [o[:n] for o in outs]
+            # one-shot must leave the inputs untouched
+            for r in range(nranks):
+                assert torch.equal(bufs[r][:n], xs[r])
+        else:
+            g.allreduce(n, dtype, "two_shot", blocks=3)
+            got = [b[:n] for b in bufs]
+        torch.cuda.synchronize()
+        assert g.status == 0
+        for r in range(nranks):
+            assert torch.equal(got[r], want), f"rank {r} n={n} {dtype} {algo}"
+
+
+@pytest.mark.parametrize("nranks", [2, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_allreduce_exhaustive_small_sizes(emu, nranks, dtype):
+    g = emu(nranks)
+    e = PACK[dtype]
+    for n in range(0, 4 * nranks * e + 1):
+        xs = [_fill(dtype, n, 31 * r + n) for r in range(nranks)]
+        bufs = [g.buffer(r, dtype, max(n, 1)) for r in range(nranks)]
+        for r in range(nranks):
+            bufs[r][:n].copy_(xs[r])
+        g.allreduce(n, dtype, "two_shot", blocks=2, scale=1.0 / nranks)
+        want = _reference_sum(xs, dtype, scale=1.0 / nranks)
+        for r in range(nranks):
+            assert torch.equal(bufs[r][:n], want), f"n={n} rank={r}"
+    assert g.status == 0
+
+
+def test_allreduce_average_and_separate_output(emu):
+    g = emu(4)
+    n = 10007
+    for dtype, idiv in ((torch.float32, 1), (torch.int32, 4)):
+        xs = [_fill(dtype, n, r) for r in range(4)]
+        for r in range(4):
+            g.buffer(r, dtype, n).copy_(xs[r])
+        outs = [torch.empty(n, dtype=dtype, device="cuda") for _ in range(4)]
+        g.allreduce(n, dtype, "two_shot", outs=outs, scale=0.25, idiv=idiv, blocks=5)
+        want = _reference_sum(xs, dtype, scale=0.25, idiv=idiv)
+        for r in range(4):
+            assert torch.equal(outs[r], want)
+
+
+def test_allreduce_many_blocks_and_reuse(emu):
+    # Back-to-back launches on the same pads: epochs must keep the barriers apart.
+    g = emu(8, 16 << 20)
+    n = (1 << 20) + 13
+    blocks = min(16, g.max_blocks())
+    for it in range(20):
+        xs = [_fill(torch.float32, n, it * 10 + r) for r in range(8)]
+        for r in range(8):
+            g.buffer(r, torch.float32, n).copy_(xs[r])
+        g.allreduce(n, torch.float32, "two_shot", blocks=blocks)
+        want = _reference_sum(xs, torch.float32)
+        assert torch.equal(g.buffer(3, torch.float32, n), want)
+    assert g.status == 0
+
+
+@pytest.mark.parametrize("nranks", [2, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("opt", ["sgd", "sgd_nesterov_wd", "adamw", "adam_l2", "adam_tf"])
+def test_fused_update_matches_reference(emu, nranks, dtype, opt):
+    from tensorflow_allreduce_b200.ops import fused_optim as fo
+
+    g = emu(nranks)
+    n = 5003
+    torch.manual_seed(0)
+    p0 = torch.randn(n, device="cuda")
+    m0 = torch.randn(n, device="cuda") * 0.1
+    v0 = torch.rand(n, device="cuda") * 0.01
+    grads = [_fill(dtype, n, 5 + r) for r in range(nranks)]
+    for r in range(nranks):
+        g.buffer(r, dtype, n).copy_(grads[r])
+    gavg = _reference_sum(grads, dtype, scale=1.0 / nranks).float()
+    if dtype == torch.float32:
+        params = [p0.clone() for _ in range(nranks)]
+        masters = None
+    else:
+        params = [p0.to(dtype) for _ in range(nranks)]
+        masters = [p0.clone() for _ in range(nranks)]
+    s1 = [m0.clone() for _ in range(nranks)]
+    s2 = [v0.clone() for _ in range(nranks)]
+    if opt.startswith("sgd"):
+        kw = dict(lr=0.1, momentum=0.9) if opt == "sgd" else dict(lr=0.05, momentum=0.8, weight_decay=0.01, nesterov=True)
+        h = fo.sgd_hyper(zero_grad=True, **kw)
+        want_p, want_m = fo.sgd_reference(p0, gavg, m0, **kw)
+        want_v = v0
+    else:
+        kw = dict(lr=1e-2, step=3, weight_decay=0.1, decoupled=(opt != "adam_l2"), tf_epsilon_hat=(opt == "adam_tf"))
+        h = fo.adam_hyper(zero_grad=True, **kw)
+        want_p, want_m, want_v = fo.adam_reference(p0, gavg, m0, v0, **kw)
+    g.fused_step(n, dtype, params, h, masters=masters, state1=s1, state2=s2, scale=1.0 / nranks, blocks=3)
+    torch.cuda.synchronize()
+    assert g.status == 0
+    for r in range(nranks):
+        fp32_p = params[r] if dtype == torch.float32 else masters[r]
+        torch.testing.assert_close(fp32_p, want_p, rtol=2e-6, atol=2e-6)
+        torch.testing.assert_close(s1[r], want_m, rtol=2e-6, atol=2e-6)
+        if not opt.startswith("sgd"):
+            torch.testing.assert_close(s2[r], want_v, rtol=2e-6, atol=1e-8)
+        if dtype != torch.float32:
+            assert torch.equal(params[r], masters[r].to(dtype))
+        # every rank must hold bit-identical parameters, and the gradient must be zeroed
+        assert torch.equal(fp32_p, params[0] if dtype == torch.float32 else masters[0])
+        assert int(g.buffer(r, dtype, n).count_nonzero()) == 0
+
+
+@pytest.mark.parametrize("nranks", [2, 4, 8])
+def test_allgatherv_device_displacements(emu, nranks):
+    g = emu(nranks)
+    sizes = [17, 32, 81, 12, 15, 23, 22, 0][:nranks]
+    for dtype, cols in ((torch.float32, 17), (torch.uint8, 3), (torch.int64, 1), (torch.bfloat16, 5)):
+        ins = [(_fill(dtype, sizes[r] * cols, r + 1)) for r in range(nranks)]
+        total = sum(sizes) * cols
+        # every rank places its output at a different offset of its buffer (not symmetric on purpose)
+        esize = ins[0].element_size()
+        offs = [256 * (r + 1) + (esize * r if dtype == torch.uint8 else 0) for r in range(nranks)]
+        for r in range(nranks):
+            g.buffer(r, torch.uint8, g.bytes_per_rank).zero_()
+        g.allgatherv(ins, offs, blocks=2)
+        torch.cuda.synchronize()
+        assert g.status == 0
+        want = torch.cat(ins)
+        for r in range(nranks):
+            got = g.buffer(r, torch.uint8, total * esize, offset_bytes=offs[r]).clone().view(dtype)
+            assert torch.equal(got, want), f"rank {r} {dtype}"
+
+
+def test_bounded_wait_reports_status_and_returns():
+    # One rank never arrives: the others give up after the limit, record a status word and the
+    # kernel returns; the context stays usable.
+    from tensorflow_allreduce_b200.ops.emulated import EmulatedGroup
+
+    g = EmulatedGroup(4, 1 << 20)
+    g.barrier_probe(absent=-1, timeout_s=5.0)
+    torch.cuda.synchronize()
+    assert g.status == 0
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    g.barrier_probe(absent=2, timeout_s=0.3)
+    t1.record()
+    torch.cuda.synchronize()
+    st = g.status
+    assert st & 0x80000000, hex(st)
+    assert st & (1 << 2), hex(st)          # the missing peer is named
+    assert 200 < t0.elapsed_time(t1) < 5000
+    x = torch.ones(10, device="cuda") * 2  # the device still works
+    assert float(x.sum()) == 20.0
+    g.close()
