@@ -1,2 +1,2 @@
-"""Kernel-level operations: symmetric memory, fused reduce+update launches, single-GPU emulation."""
-from . import emulated, fused_optim, symmetric  # noqa: F401
+"""Kernel-level operations: symmetric memory, ordered launches, fused reduce+update, single-GPU emulation."""
+from . import direct, emulated, fused_optim, symmetric  # noqa: F401
