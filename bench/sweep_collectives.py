@@ -72,6 +72,9 @@ def ref_ring_allreduce(buf, tmp, rank, world):
 
 
 def main():
+    if os.environ.get("BC_SWEEP_WATCHDOG_S"):
+        import faulthandler
+        faulthandler.dump_traceback_later(float(os.environ["BC_SWEEP_WATCHDOG_S"]), exit=True)
     ap = argparse.ArgumentParser()
     ap.add_argument("--max-mb", type=int, default=1024)
     ap.add_argument("--min-kb", type=int, default=1)
@@ -79,6 +82,7 @@ def main():
     ap.add_argument("--arms", default="ours_direct,ours_symm,ours_staged,nccl,ref_ring")
     ap.add_argument("--dtypes", default="fp32,bf16")
     ap.add_argument("--no-allgather", action="store_true")
+    ap.add_argument("--no-allreduce", action="store_true")
     a = ap.parse_args()
     arms = a.arms.split(",")
     rank = int(os.environ.get("RANK", 0))
@@ -100,7 +104,7 @@ def main():
     for dname in a.dtypes.split(","):
         dtype = {"fp32": torch.float32, "bf16": torch.bfloat16}[dname]
         es = 4 if dtype == torch.float32 else 2
-        for nbytes in sizes:
+        for nbytes in ([] if a.no_allreduce else sizes):
             n = nbytes // es
             iters = 50 if nbytes <= (1 << 20) else (20 if nbytes <= (64 << 20) else 5)
             g = torch.Generator(device="cuda").manual_seed(rank)

@@ -86,7 +86,7 @@ def _resolve_port(rank_: int, size_: int, addr: str) -> int:
 
         from torch.distributed import TCPStore
 
-        store = TCPStore(addr, port, size_, is_master=False, timeout=datetime.timedelta(seconds=300))
+        store = TCPStore(addr, port, None, False, timeout=datetime.timedelta(seconds=120), wait_for_workers=False)
         key = "bcoll/ctrl_port/" + os.environ.get("TORCHELASTIC_RUN_ID", "0") + "/" + os.environ.get("TORCHELASTIC_RESTART_COUNT", "0")
         if rank_ == 0:
             with socket.socket() as s:

@@ -355,7 +355,10 @@ void Runtime::drain_local_queue() {
     std::lock_guard<std::mutex> g(mu_);
     local.swap(queue_);
   }
-  for (auto& rec : local) send_request(*rec);
+  for (auto& rec : local) {
+    BC_LOG(2, "request '%s'", rec->name.c_str());
+    send_request(*rec);
+  }
 }
 
 void Runtime::coordinator_handle(const Request& q) {
@@ -470,6 +473,7 @@ void Runtime::perform(const Response& resp) {
     throw Error("received a go-ahead for unknown collective '" + resp.name + "'");
   }
   rec->t_negotiated = now_s();
+  BC_LOG(2, "perform '%s' type=%d", rec->name.c_str(), (int)resp.type);
   try {
     switch (resp.type) {
       case ResponseType::ERROR:
@@ -492,6 +496,7 @@ void Runtime::perform(const Response& resp) {
         throw Error("unexpected response type");
     }
     finish(rec, true, "");
+    BC_LOG(2, "performed '%s'", rec->name.c_str());
   } catch (const CommLost&) {
     finish(rec, false, "collective '" + rec->name + "' failed: connection lost");
     throw;
@@ -533,7 +538,9 @@ void Runtime::perform_allgather(OpRecord& r, const Response& resp) {
   for (size_t i = 1; i < r.shape.size(); i++) row_bytes *= (size_t)r.shape[i];
   int is_symm = 0;
   BC_CHECK(r.alloc, "allgather needs an output allocator");
+  BC_LOG(2, "allgather '%s': asking for %lld rows", r.name.c_str(), (long long)total_rows);
   r.out = r.alloc(r.id, total_rows, r.alloc_user, &is_symm);
+  BC_LOG(2, "allgather '%s': output %p symmetric=%d", r.name.c_str(), r.out, is_symm);
   const size_t total_bytes = (size_t)total_rows * row_bytes;
   BC_CHECK(r.out || total_bytes == 0, "the output allocator returned no buffer");
   if (r.device == DeviceKind::CPU) {

@@ -13,6 +13,7 @@ work queued on the freeing stream has finished.
 """
 from __future__ import annotations
 
+import collections
 import ctypes as C
 import threading
 from typing import Optional, Sequence, Tuple
@@ -72,8 +73,11 @@ class _Heap:
     def __init__(self, base: int, size: int, device: torch.device):
         self.base, self.size, self.device = base, size, device
         self.free = [(0, size)]          # (offset, length), sorted, coalesced
-        self.limbo = []                  # (event, offset, length)
-        self.lock = threading.Lock()
+        # Freed blocks wait here. A block's finalizer can run at any point of any thread (even in
+        # the middle of alloc() below, when the garbage collector kicks in), so it must not take
+        # the lock: deque.append is atomic.
+        self.limbo = collections.deque()  # (event, offset, length)
+        self.lock = threading.RLock()
 
     def _release(self, off: int, length: int):
         self.free.append((off, length))
@@ -87,13 +91,15 @@ class _Heap:
         self.free = merged
 
     def _reap(self):
-        still = []
-        for ev, off, length in self.limbo:
+        for _ in range(len(self.limbo)):
+            try:
+                ev, off, length = self.limbo.popleft()
+            except IndexError:
+                break
             if ev is None or ev.query():
                 self._release(off, length)
             else:
-                still.append((ev, off, length))
-        self.limbo = still
+                self.limbo.append((ev, off, length))
 
     def alloc(self, nbytes: int) -> Optional[int]:
         need = (max(nbytes, 1) + _ALIGN - 1) // _ALIGN * _ALIGN
@@ -116,8 +122,7 @@ class _Heap:
             ev.record(torch.cuda.current_stream(self.device))
         except Exception:
             ev = None
-        with self.lock:
-            self.limbo.append((ev, off, need))
+        self.limbo.append((ev, off, need))
 
 
 _heap: Optional[_Heap] = None

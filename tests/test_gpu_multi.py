@@ -37,17 +37,24 @@ def ref_sum(xs, dtype):
     acc = xs[0].clone()
     for x in xs[1:]: acc = acc + x
     return acc
+def same(got, want, dtype):
+    # The in-switch (NVLS) reduction of 16-bit floats may round differently from "sum in fp32,
+    # round once": allow one unit in the last place there. Everything else must be bit-exact.
+    if dtype in (torch.bfloat16, torch.float16) and bc.stats()[-1]["algo"] == "nvls":
+        ulp = 2.0 ** (-7 if dtype == torch.bfloat16 else -10)
+        return bool(((got.float() - want.float()).abs() <= ulp * want.float().abs().clamp_min(2.0 ** -14)).all())
+    return bool(torch.equal(got, want))
 for dtype in (torch.float32, torch.bfloat16, torch.float16, torch.int32, torch.int64):
     for n in (1, 17, 4913, (1 << 16) + 3, (1 << 21) + 11):
         xs = [fill(dtype, n, 1000 * r + n % 97) for r in range(SIZE)]
         want = ref_sum(xs, dtype)
         got = bc.allreduce(xs[RANK], average=False)
-        if not torch.equal(got, want): bad.append(["staged", str(dtype), n, bc.stats()[-1]["algo"]])
+        if not same(got, want, dtype): bad.append(["staged", str(dtype), n, bc.stats()[-1]["algo"], (got.float() - want.float()).abs().max().item()])
         # in place on symmetric memory (zero-copy)
         s = symmetric.empty((n,), dtype)
         s.copy_(xs[RANK])
         bc.allreduce_(s, average=False)
-        if not torch.equal(s, want): bad.append(["symmetric", str(dtype), n, bc.stats()[-1]["algo"]])
+        if not same(s, want, dtype): bad.append(["symmetric", str(dtype), n, bc.stats()[-1]["algo"], (s.float() - want.float()).abs().max().item()])
 algos = sorted({e["algo"] for e in bc.stats() if e["device"] == 1})
 # variable allgather: (rank+1)*k rows
 for k, cols, dtype in ((1, 4, torch.float32), (3, 17, torch.int32), (64, 256, torch.bfloat16), (5, 1, torch.uint8)):
