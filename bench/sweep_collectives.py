@@ -89,7 +89,7 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
-    cfg = bc.Config.from_env(heap_mb=max(2 * a.max_mb + 64, 256), staging_mb=64)
+    cfg = bc.Config.from_env(heap_mb=max(6 * a.max_mb + 64, 256), staging_mb=64)
     bc.init(device=local, config=cfg)
     use_nccl = ("nccl" in arms or "ref_ring" in arms) and world > 1
     if use_nccl:
@@ -193,6 +193,20 @@ def main():
             factor = (P - 1) / P if P > 1 else 1.0
             row["ours_ms"] = ms
             row["ours_busbw"] = total / (ms * 1e-3) * factor / 1e9
+            from tensorflow_allreduce_b200.ops.direct import allgatherv_direct
+            sym_out = symmetric.empty((total // (es * cols), cols), dtype)
+            szs = torch.zeros(P, dtype=torch.int64, device="cuda")
+            sym_out.zero_()
+            allgatherv_direct(t, sym_out, szs)
+            lo, ok = 0, True
+            for r in range(P):
+                ok = ok and bool((sym_out[lo:lo + (r + 1) * k] == r).all()) and int(szs[r]) == (r + 1) * k * cols * es
+                lo += (r + 1) * k
+            row["direct_correct"] = ok
+            ms = timed(lambda: allgatherv_direct(t, sym_out, szs), iters)
+            row["ours_direct_ms"] = ms
+            row["ours_direct_busbw"] = total / (ms * 1e-3) * factor / 1e9
+            del sym_out
             if use_nccl and "nccl" in arms:
                 # the usual workaround for a variable first dimension: pad to the largest slab
                 pad = torch.zeros(P * k, cols, dtype=dtype, device="cuda")

@@ -79,6 +79,7 @@ def _declare(lib):
         "bc_stream_wait_event": (i, [vp, vp]),
         "bc_allreduce_direct": (i, [i, vp, vp, ll, i, i, vp, vp]),
         "bc_fused_step": (i, [i, vp, ll, i, vp, vp, vp, vp, P(OptHyper), f, vp, vp]),
+        "bc_allgatherv_direct": (i, [i, vp, ll, vp, ll, vp, vp, vp]),
         "bc_emu_create": (vp, [i, i, ll]),
         "bc_emu_destroy": (i, [vp]),
         "bc_emu_buffer": (vp, [vp, i]),

@@ -77,6 +77,12 @@ int bc_allreduce_direct(int channel, const void* in, void* out, long long count,
 int bc_fused_step(int channel, void* grad, long long count, int dtype, void* param, float* master, float* s1, float* s2,
                   const bc_opt_hyper* h, float scale, void* wait_event, void* record_event);
 
+/* Variable allgather into `out_symm`, a buffer of `capacity_bytes` (equal on all ranks) inside the
+ * symmetric heap. Row counts are exchanged on the device; `sizes_out` (device memory, one entry per
+ * rank, or NULL) receives every rank's slab size in bytes. */
+int bc_allgatherv_direct(int channel, const void* in, long long bytes, void* out_symm, long long capacity_bytes,
+                         unsigned long long* sizes_out, void* wait_event, void* record_event);
+
 /* A group of ranks emulated on ONE GPU: each collective is a single cooperative launch. */
 void* bc_emu_create(int device, int nranks, long long bytes_per_rank);
 int bc_emu_destroy(void* g);

@@ -287,6 +287,19 @@ int bc_fused_step(int channel, void* grad, long long count, int dtype, void* par
   API_END(-1)
 }
 
+int bc_allgatherv_direct(int channel, const void* in, long long bytes, void* out_symm, long long capacity_bytes,
+                         unsigned long long* sizes_out, void* wait_event, void* record_event) {
+  API_BEGIN
+  gpu::Comm& c = comm();
+  if (c.device_status() != 0) throw Error("an earlier device-side wait timed out; the communicator cannot be used any more");
+  cudaStream_t s = c.stream(channel);
+  stream_prologue(s, wait_event);
+  c.allgatherv(channel, in, (size_t)bytes, out_symm, nullptr, (size_t)capacity_bytes, sizes_out);
+  stream_epilogue(s, record_event);
+  return 0;
+  API_END(-1)
+}
+
 // ---- single-GPU emulation of a rank group --------------------------------------------------------
 
 void* bc_emu_create(int device, int nranks, long long bytes_per_rank) {

@@ -35,7 +35,17 @@ __device__ __forceinline__ void push_slab(char* dst, const char* src, size_t n, 
   size_t body = 0;
   if (rel == 0) {
     const size_t k = n / 16;
-    for (size_t i = tid; i < k; i += nthreads) st16(dst + i * 16, ld_local16(src + i * 16));
+    // four independent 16-byte loads per thread before the first store
+    size_t i = tid;
+    for (; i + 3 * nthreads < k; i += 4 * nthreads) {
+      const uint4 v0 = ld_local16(src + i * 16), v1 = ld_local16(src + (i + nthreads) * 16);
+      const uint4 v2 = ld_local16(src + (i + 2 * nthreads) * 16), v3 = ld_local16(src + (i + 3 * nthreads) * 16);
+      st16(dst + i * 16, v0);
+      st16(dst + (i + nthreads) * 16, v1);
+      st16(dst + (i + 2 * nthreads) * 16, v2);
+      st16(dst + (i + 3 * nthreads) * 16, v3);
+    }
+    for (; i < k; i += nthreads) st16(dst + i * 16, ld_local16(src + i * 16));
     body = k * 16;
   } else if ((rel & 7) == 0) {
     const size_t k = n / 8;
@@ -80,6 +90,7 @@ __global__ void __launch_bounds__(512) allgatherv_kernel(const __grid_constant__
   __syncthreads();
   unsigned long long disp = 0;
   for (int q = 0; q < me; q++) disp += s_bytes[q];
+  if (R.sizes_out && blockIdx.x == 0 && (int)threadIdx.x < P) R.sizes_out[threadIdx.x] = s_bytes[threadIdx.x];
 
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t nthreads = (size_t)gridDim.x * blockDim.x;

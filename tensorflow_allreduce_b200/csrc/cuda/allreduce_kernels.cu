@@ -30,6 +30,7 @@ namespace {
 
 constexpr int ALGO_ONE = 1, ALGO_TWO = 2, ALGO_NVLS = 3;
 constexpr int OPT_NONE = 0, OPT_SGD = 1, OPT_ADAM = 2;
+constexpr int kNvlsUnroll = 8;
 
 template <typename T> struct Scalar;  // scalar load/store in the accumulator type
 template <> struct Scalar<float> { using Acc = float; __device__ static Acc ld(const float* p) { return *p; } __device__ static void st(float* p, Acc v) { *p = v; } };
@@ -266,16 +267,29 @@ __global__ void __launch_bounds__(512) allreduce_kernel(const __grid_constant__ 
     // Phase 1: reduce this rank's slice and store the result into every rank's buffer.
     const size_t sbeg = npacks * (size_t)me / P, send = npacks * (size_t)(me + 1) / P;
     if constexpr (ALGO == ALGO_NVLS && IsFloatGrad<T>::value) {
-      for (size_t i = sbeg + first; i < send; i += stride) {
-        uint4 r = nvls_reduce<T>(R.mc_in + i * 16);
-        if (a.scale != 1.f) {
-          Acc acc[E];
-          PK::unpack(r, acc);
+      // kNvlsUnroll switch-side reductions are in flight per thread before the first result is
+      // used; a single one per thread leaves the links mostly idle.
+      for (size_t i0 = sbeg + first; i0 < send; i0 += stride * kNvlsUnroll) {
+        uint4 r[kNvlsUnroll];
 #pragma unroll
-          for (int e = 0; e < E; e++) acc[e] = finish<Acc>(acc[e], a.scale, a.idiv);
-          r = PK::pack(acc);
+        for (int u = 0; u < kNvlsUnroll; u++) {
+          const size_t i = i0 + (size_t)u * stride;
+          if (i < send) r[u] = nvls_reduce<T>(R.mc_in + i * 16);
         }
-        multimem_st16(R.mc_in + i * 16, r);
+#pragma unroll
+        for (int u = 0; u < kNvlsUnroll; u++) {
+          const size_t i = i0 + (size_t)u * stride;
+          if (i < send) {
+            if (a.scale != 1.f) {
+              Acc acc[E];
+              PK::unpack(r[u], acc);
+#pragma unroll
+              for (int e = 0; e < E; e++) acc[e] = finish<Acc>(acc[e], a.scale, a.idiv);
+              r[u] = PK::pack(acc);
+            }
+            multimem_st16(R.mc_in + i * 16, r[u]);
+          }
+        }
       }
     } else {
       reduce_range_any<T>(R, P, sbeg, send, first, stride, [&](size_t i, Acc* acc) {
@@ -405,13 +419,14 @@ int max_emulated_blocks(int device, int nranks, int threads) {
   return g < 1 ? 1 : g;
 }
 
-int choose_blocks(size_t bytes, int world, int algo, bool fused_opt, int sm_count) {
-  // One block per 64 KiB of payload, at least 1; the cap keeps SMs free for the backward pass
-  // that runs beside a gradient reduction. A fused update is HBM-bound in its second phase and
-  // gets a larger grid.
+int choose_blocks(size_t bytes, int world, int algo, bool fused_opt, int sm_count, int cap_override) {
+  // One block per 32 KiB of payload, at least 1. The default cap keeps SMs free for the backward
+  // pass that runs beside a gradient reduction; a fused update is HBM-bound in its second phase
+  // and gets one block per SM.
   (void)world;
-  size_t want = (bytes + (64u << 10) - 1) / (64u << 10);
-  int cap = fused_opt ? sm_count : (algo == ALGO_NVLS ? 32 : 64);
+  (void)algo;
+  size_t want = (bytes + (32u << 10) - 1) / (32u << 10);
+  int cap = cap_override > 0 ? cap_override : (fused_opt ? sm_count : 128);
   if (cap > kMaxBlocks) cap = kMaxBlocks;
   if (want < 1) want = 1;
   return (int)(want > (size_t)cap ? (size_t)cap : want);

@@ -83,6 +83,7 @@ struct AgRank {
   unsigned long long bytes;   // its size
   char* base[dev::kMaxRanks]; // every rank's output segment base as mapped here
   unsigned long long out_off; // where this rank's output starts inside its own segment
+  unsigned long long* sizes_out;  // optional local array [world]: every rank's slab size in bytes
 };
 
 struct AgArgs {
@@ -104,7 +105,7 @@ cudaError_t launch_copy(void* dst, const void* src, size_t bytes, cudaStream_t s
 
 // Largest grid.x for which an emulated launch of `nranks` ranks is co-resident on `device`.
 int max_emulated_blocks(int device, int nranks, int threads);
-int choose_blocks(size_t bytes, int world, int algo, bool fused_opt, int sm_count);
+int choose_blocks(size_t bytes, int world, int algo, bool fused_opt, int sm_count, int cap_override);
 
 }  // namespace gpu
 }  // namespace bc

@@ -77,7 +77,9 @@ Algo Comm::choose_algo(size_t bytes, DType dtype, bool in_place_or_fused, bool h
   if (forced == Algo::NVLS && has_mc && is_float) return forced;
   if (forced != Algo::AUTO) return Algo::TWO_SHOT;
   if (!in_place_or_fused && bytes <= cfg_.one_shot_max_bytes) return Algo::ONE_SHOT;
-  if (has_mc && cfg_.use_nvls && is_float && bytes >= cfg_.nvls_min_bytes) return Algo::NVLS;
+  // With two ranks the switch-side reduction saves no traffic (each GPU moves N/2 either way)
+  // and measured slower than plain peer loads and stores; it pays from four ranks on.
+  if (has_mc && cfg_.use_nvls && is_float && world_ >= 4 && bytes >= cfg_.nvls_min_bytes) return Algo::NVLS;
   return Algo::TWO_SHOT;
 }
 
@@ -110,7 +112,7 @@ Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType
     a.r[0].ctx = make_ctx(channel);
     a.r[0].in[0] = (char*)in;
     a.r[0].out = out;
-    cfg.blocks = choose_blocks(bytes, 1, a.algo, true, sm_count_);
+    cfg.blocks = choose_blocks(bytes, 1, a.algo, true, sm_count_, cfg_.max_blocks);
     CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, s));
     last_blocks = cfg.blocks;
     return Algo::ONE_SHOT;
@@ -125,8 +127,7 @@ Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType
     a.r[0].out = out;
     a.algo = (int)algo;
     a.count = count;
-    cfg.blocks = choose_blocks(bytes, world_, a.algo, false, sm_count_);
-    if (cfg_.max_blocks > 0) cfg.blocks = std::min(cfg.blocks, cfg_.max_blocks);
+    cfg.blocks = choose_blocks(bytes, world_, a.algo, false, sm_count_, cfg_.max_blocks);
     CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, s));
     last_blocks = cfg.blocks;
     return algo;
@@ -138,8 +139,7 @@ Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType
     a.r[0].out = out;
     a.algo = (int)Algo::ONE_SHOT;
     a.count = count;
-    cfg.blocks = choose_blocks(bytes, world_, a.algo, false, sm_count_);
-    if (cfg_.max_blocks > 0) cfg.blocks = std::min(cfg.blocks, cfg_.max_blocks);
+    cfg.blocks = choose_blocks(bytes, world_, a.algo, false, sm_count_, cfg_.max_blocks);
     CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, s));
     last_blocks = cfg.blocks;
     return Algo::ONE_SHOT;
@@ -157,8 +157,7 @@ Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType
     a.r[0].out = (char*)out + done * es;
     a.algo = (int)algo;
     a.count = n;
-    cfg.blocks = choose_blocks(nb, world_, a.algo, false, sm_count_);
-    if (cfg_.max_blocks > 0) cfg.blocks = std::min(cfg.blocks, cfg_.max_blocks);
+    cfg.blocks = choose_blocks(nb, world_, a.algo, false, sm_count_, cfg_.max_blocks);
     CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, s));
     last_blocks = cfg.blocks;
     used = algo;
@@ -166,7 +165,8 @@ Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType
   return used;
 }
 
-void Comm::allgatherv(int channel, const void* in, size_t bytes, void* out_symm, void* out_private, size_t total_bytes) {
+void Comm::allgatherv(int channel, const void* in, size_t bytes, void* out_symm, void* out_private, size_t total_bytes,
+                      unsigned long long* sizes_out) {
   CUDA_RT(cudaSetDevice(device_));
   cudaStream_t s = streams_[channel];
   if (total_bytes == 0) return;
@@ -177,6 +177,7 @@ void Comm::allgatherv(int channel, const void* in, size_t bytes, void* out_symm,
   r.ctx = make_ctx(channel);
   r.in = (const char*)in;
   r.bytes = bytes;
+  r.sizes_out = sizes_out;
   for (int p = 0; p < world_; p++) r.base[p] = seg0_->peer[p];
   if (out_symm) {
     BC_CHECK((char*)out_symm >= seg0_->local && (char*)out_symm + total_bytes <= seg0_->local + seg0_->size,
@@ -188,8 +189,11 @@ void Comm::allgatherv(int channel, const void* in, size_t bytes, void* out_symm,
     r.out_off = staging_off_;
   }
   LaunchCfg cfg;
-  size_t want = (total_bytes / world_ + (128u << 10) - 1) / (128u << 10);
-  cfg.blocks = (int)std::min<size_t>(std::max<size_t>(want, 1), 32);
+  // The grid must be the same on every rank, so it is derived from the total, not from this
+  // rank's slab.
+  size_t want = (total_bytes / world_ + (32u << 10) - 1) / (32u << 10);
+  const size_t cap = cfg_.max_blocks > 0 ? std::min<size_t>(cfg_.max_blocks, kMetaBlocks) : 48;
+  cfg.blocks = (int)std::min<size_t>(std::max<size_t>(want, 1), cap);
   CUDA_RT(launch_allgatherv(a, cfg, s));
   last_blocks = cfg.blocks;
   if (!out_symm && out_private) CUDA_RT(launch_copy(out_private, staging(), total_bytes, s));
@@ -225,8 +229,7 @@ Algo Comm::fused_step(int channel, void* grad, size_t count, DType dtype, void* 
   a.r[0].state1 = s1;
   a.r[0].state2 = s2;
   LaunchCfg cfg;
-  cfg.blocks = choose_blocks(bytes, world_, a.algo, true, sm_count_);
-  if (cfg_.max_blocks > 0) cfg.blocks = std::min(cfg.blocks, cfg_.max_blocks);
+  cfg.blocks = choose_blocks(bytes, world_, a.algo, true, sm_count_, cfg_.max_blocks);
   CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, s));
   last_blocks = cfg.blocks;
   return algo;

@@ -61,7 +61,8 @@ class Comm {
                  bool zero_copy_agreed);
   // Variable allgather: `in` = this rank's slab, `out` must lie in segment 0's heap or be null
   // (then the staging area is the landing zone and `out_private` receives a copy).
-  void allgatherv(int channel, const void* in, size_t bytes, void* out_symm, void* out_private, size_t total_bytes);
+  void allgatherv(int channel, const void* in, size_t bytes, void* out_symm, void* out_private, size_t total_bytes,
+                  unsigned long long* sizes_out = nullptr);
 
   // Fused reduce + optimizer update on a gradient bucket that lives in symmetric memory.
   Algo fused_step(int channel, void* grad, size_t count, DType dtype, void* param, float* master, float* s1, float* s2,

@@ -41,3 +41,25 @@ def allreduce_direct_(tensor: torch.Tensor, average: bool = False, channel: int 
         raise CollectiveError(_lib.last_error())
     cur.wait_event(done)
     return tensor
+
+
+def allgatherv_direct(tensor: torch.Tensor, out: torch.Tensor, sizes_out: torch.Tensor = None, channel: int = 2) -> torch.Tensor:
+    """Concatenate every rank's `tensor` (rows may differ per rank) into `out`, a tensor of equal
+    capacity on all ranks that lives in the symmetric heap (`ops.symmetric.empty`). Nothing about
+    the sizes passes through the host: each rank publishes its byte count on the device and the
+    kernel computes the displacements there. `sizes_out` (int64 CUDA tensor, one entry per rank)
+    receives the byte counts; rows beyond their sum are left untouched."""
+    if not (tensor.is_cuda and tensor.is_contiguous() and out.is_contiguous()):
+        raise CollectiveError("allgatherv_direct needs contiguous CUDA tensors")
+    lib = _lib.lib()
+    ready, done = _pair(channel)
+    cur = torch.cuda.current_stream()
+    ready.record(cur)
+    rc = lib.bc_allgatherv_direct(channel, C.c_void_p(tensor.data_ptr() if tensor.numel() else 0), tensor.numel() * tensor.element_size(),
+                                  C.c_void_p(out.data_ptr()), out.numel() * out.element_size(),
+                                  C.c_void_p(sizes_out.data_ptr()) if sizes_out is not None else None,
+                                  C.c_void_p(ready.cuda_event), C.c_void_p(done.cuda_event))
+    if rc < 0:
+        raise CollectiveError(_lib.last_error())
+    cur.wait_event(done)
+    return out
