@@ -1,0 +1,79 @@
+"""Failure detection, exercised on the host only (CPU ranks, no GPU involved): a request that is
+never sent, a late rank, a rank that exits, a control connection that closes. The reference has
+none of this: a missing rank blocks everyone in MPI_Probe for ever
+(tensorflow/contrib/mpi_collectives/mpi_ops.cc:684,763)."""
+import time
+
+from _util import run
+
+
+def test_dropped_request_times_out_on_every_rank():
+    res = run("""
+    bc.init(device="cpu")
+    import time
+    t0 = time.time()
+    try:
+        bc.allreduce(torch.ones(4), name="lost")
+        err = None
+    except bc.CollectiveError as e:
+        err = str(e)
+    dt = time.time() - t0
+    ok = bc.allreduce(torch.ones(2), average=False, name="after").tolist()   # group survives a timeout
+    emit(err=err, dt=dt, ok=ok)
+    bc.shutdown()
+    """, nranks=2, env={"BC_TIMEOUT_S": "2", "BC_FAULT": "drop_request:rank=1:name=lost"}, timeout=60)
+    for _, rec in res:
+        assert rec["err"] is not None and "Timed out" in rec["err"] and "rank(s) 1" in rec["err"]
+        assert rec["dt"] < 15
+        assert rec["ok"] == [2.0, 2.0]
+
+
+def test_late_rank_within_deadline_is_fine():
+    res = run("""
+    bc.init(device="cpu")
+    out = bc.allreduce(torch.ones(4) * (RANK + 1), average=False, name="slow")
+    emit(out=out.tolist())
+    bc.shutdown()
+    """, nranks=2, env={"BC_TIMEOUT_S": "20", "BC_FAULT": "delay_ms=700:rank=1:name=slow"}, timeout=60)
+    for _, rec in res:
+        assert rec["out"] == [3.0] * 4
+
+
+def test_rank_exit_fails_the_others_quickly():
+    t0 = time.time()
+    res = run("""
+    bc.init(device="cpu")
+    bc.allreduce(torch.ones(4), name="warm")
+    try:
+        bc.allreduce(torch.ones(4), name="doomed")
+        err = None
+    except bc.CollectiveError as e:
+        err = str(e)
+    later = None
+    try:
+        bc.allreduce(torch.ones(4), name="later")
+    except bc.CollectiveError as e:
+        later = str(e)
+    emit(err=err, later=later)
+    """, nranks=3, env={"BC_TIMEOUT_S": "30", "BC_FAULT": "exit_before:rank=2:name=doomed"}, timeout=90, expect_ok=False)
+    assert time.time() - t0 < 60
+    assert res[2][0].returncode == 41            # the injected exit
+    for r in (0, 1):
+        rec = res[r][1]
+        assert rec is not None, res[r][0].stderr[-2000:]
+        assert rec["err"] is not None and ("lost" in rec["err"] or "closed" in rec["err"] or "failed" in rec["err"])
+        assert rec["later"] is not None and "broken" in rec["later"]
+
+
+def test_closed_control_connection_is_detected():
+    res = run("""
+    bc.init(device="cpu")
+    try:
+        bc.allreduce(torch.ones(4), name="x")
+        err = None
+    except bc.CollectiveError as e:
+        err = str(e)
+    emit(err=err)
+    """, nranks=2, env={"BC_TIMEOUT_S": "10", "BC_FAULT": "close_ctrl:rank=1:name=x"}, timeout=60, expect_ok=False)
+    for r, rec in res:
+        assert rec is not None and rec["err"] is not None
