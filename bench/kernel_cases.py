@@ -1,0 +1,126 @@
+"""Small, self-contained cases of the library's own kernels, for timing and for profiler captures.
+
+    python bench/kernel_cases.py --case fused_sgd        [--mb 256] [--iters 10]
+    python bench/kernel_cases.py --case fused_adamw_bf16
+    python bench/kernel_cases.py --case emu_allreduce    (8 emulated ranks on one GPU, two-shot, fp32)
+    python bench/kernel_cases.py --case emu_allgatherv
+
+Each case prints one JSON line with the CUDA-event time per launch, the algorithmic bytes moved and
+the resulting GB/s next to the measured copy bandwidth (`MEASURED_PEAKS.json` when present).
+Inputs are larger than the 126 MB L2.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+
+
+def peak_hbm():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    try:
+        return json.load(open(p))["hbm_gbs"], "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def timed(fn, iters):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", required=True, choices=["fused_sgd", "fused_adamw_bf16", "emu_allreduce", "emu_allgatherv"])
+    ap.add_argument("--mb", type=int, default=256, help="gradient / message size in MiB")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--blocks", type=int, default=0)
+    a = ap.parse_args()
+    torch.cuda.set_device(0)
+    hbm, src = peak_hbm()
+    out = {"case": a.case, "mb": a.mb}
+
+    if a.case.startswith("fused"):
+        import tensorflow_allreduce_b200 as bc
+        from tensorflow_allreduce_b200 import _lib
+        from tensorflow_allreduce_b200.ops import fused_optim as fo
+
+        for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+            os.environ.pop(k, None)
+        if a.blocks:
+            os.environ["BC_MAX_BLOCKS"] = str(a.blocks)
+        bc.init(device=0)
+        lib = _lib.lib()
+        bf16 = a.case == "fused_adamw_bf16"
+        dtype = torch.bfloat16 if bf16 else torch.float32
+        n = (a.mb << 20) // (2 if bf16 else 4)
+        grad = torch.randn(n, device="cuda").to(dtype)
+        param = torch.randn(n, device="cuda").to(dtype)
+        master = param.float() if bf16 else None
+        s1 = torch.zeros(n, device="cuda")
+        s2 = torch.zeros(n, device="cuda") if bf16 else None
+        h = fo.adam_hyper(1e-3, 3, weight_decay=0.01, zero_grad=True) if bf16 else fo.sgd_hyper(3e-4, momentum=0.9, zero_grad=True)
+        stream = torch.cuda.current_stream()
+        ev0, ev1 = torch.cuda.Event(), torch.cuda.Event()
+        ev0.record(); ev1.record()
+
+        def fn():
+            ev0.record(stream)
+            rc = lib.bc_fused_step(1, C.c_void_p(grad.data_ptr()), n, 3 if bf16 else 0, C.c_void_p(param.data_ptr()),
+                                   C.c_void_p(master.data_ptr()) if bf16 else None, C.c_void_p(s1.data_ptr()),
+                                   C.c_void_p(s2.data_ptr()) if bf16 else None, C.byref(h), 1.0, C.c_void_p(ev0.cuda_event),
+                                   C.c_void_p(ev1.cuda_event))
+            assert rc >= 0, _lib.last_error()
+            stream.wait_event(ev1)
+
+        ms = timed(fn, a.iters)
+        # bytes: grad read + grad zeroed, param (and master) read+write, state read+write
+        es = 2 if bf16 else 4
+        nbytes = n * (es + es) + (n * (2 + 4 + 4) if bf16 else n * 8) + n * 8 * (2 if bf16 else 1)
+        out.update(ms=ms, bytes=nbytes, gbs=nbytes / ms / 1e6)
+        bc.shutdown()
+    else:
+        from tensorflow_allreduce_b200.ops.emulated import EmulatedGroup
+
+        P = 8
+        per_rank = max(a.mb, 8) << 20
+        g = EmulatedGroup(P, per_rank)
+        blocks = a.blocks or g.max_blocks()
+        if a.case == "emu_allreduce":
+            n = (a.mb << 20) // 4
+            for r in range(P):
+                g.buffer(r, torch.float32, n).fill_(float(r))
+            ms = timed(lambda: g.allreduce(n, torch.float32, "two_shot", blocks=blocks, scale=1.0 / P), a.iters)
+            # per rank: reads P slices of n/P and writes P copies of n/P; in total over the GPU:
+            nbytes = P * (n * 4 + n * 4)
+            out.update(ms=ms, bytes=nbytes, gbs=nbytes / ms / 1e6, blocks=blocks, ok=bool(g.status == 0))
+        else:
+            rows = (a.mb << 20) // (4 * 256) // (P * (P + 1) // 2)
+            ins = [torch.full(((r + 1) * rows, 256), float(r), device="cuda") for r in range(P)]
+            total = sum(t.numel() for t in ins) * 4
+            blocks = min(blocks, 48)
+            ms = timed(lambda: g.allgatherv(ins, [0] * P, blocks=blocks), a.iters)
+            nbytes = total + P * total      # every slab read once, written into P outputs
+            out.update(ms=ms, bytes=nbytes, gbs=nbytes / ms / 1e6, blocks=blocks, ok=bool(g.status == 0))
+        g.close()
+    out["hbm_peak_gbs"] = hbm
+    out["frac_of_hbm_copy_" + src] = out["gbs"] / hbm
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

