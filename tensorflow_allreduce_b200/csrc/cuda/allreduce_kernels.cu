@@ -220,7 +220,7 @@ __device__ __forceinline__ uint4 nvls_reduce(const char* mc) {
 }
 
 template <typename T, int ALGO, int OPT>
-__global__ void __launch_bounds__(512) allreduce_kernel(const __grid_constant__ ArArgs a) {
+__global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant__ ArArgs a) {
   using PK = Pack<T>;
   using Acc = typename PK::Acc;
   constexpr int E = PK::kElems;
@@ -426,7 +426,7 @@ int choose_blocks(size_t bytes, int world, int algo, bool fused_opt, int sm_coun
   (void)world;
   (void)algo;
   size_t want = (bytes + (32u << 10) - 1) / (32u << 10);
-  int cap = cap_override > 0 ? cap_override : (fused_opt ? sm_count : 128);
+  int cap = cap_override > 0 ? cap_override : (fused_opt ? 2 * sm_count : 128);
   if (cap > kMaxBlocks) cap = kMaxBlocks;
   if (want < 1) want = 1;
   return (int)(want > (size_t)cap ? (size_t)cap : want);

@@ -9,13 +9,13 @@ namespace bc {
 namespace dev {
 
 constexpr int kMaxRanks = 8;
-constexpr int kMaxBlocks = 256;     // barrier slots per channel
+constexpr int kMaxBlocks = 512;     // barrier slots per channel
 constexpr int kMetaBlocks = 64;     // blocks that may exchange per-call metadata (allgatherv)
 constexpr int kChannels = 4;
 
 // Layout of one channel inside a rank's signal pad (all offsets in bytes).
-constexpr size_t kFlagBytes = (size_t)kMaxBlocks * kMaxRanks * sizeof(uint32_t);          // 8 KiB
-constexpr size_t kMetaBytes = (size_t)kMetaBlocks * kMaxRanks * 2 * sizeof(uint64_t);     // 8 KiB
+constexpr size_t kFlagBytes = (size_t)kMaxBlocks * kMaxRanks * sizeof(uint32_t);          // 16 KiB
+constexpr size_t kMetaBytes = (size_t)kMetaBlocks * kMaxRanks * 2 * sizeof(uint64_t);     // 16 KiB
 constexpr size_t kChannelBytes = kFlagBytes + kMetaBytes;
 constexpr size_t kPadBytes = kChannels * kChannelBytes;                                  // 64 KiB
 
