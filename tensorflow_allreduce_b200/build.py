@@ -33,7 +33,7 @@ CXX_FLAGS = ["-O2", "-g1", "-fPIC", "-std=c++17", "-Wall", "-pthread", f"-I{CUDA
 
 
 def _sources():
-    cc = sorted(p for p in CSRC.rglob("*.cc"))
+    cc = sorted(p for p in CSRC.rglob("*.cc") if "selftest" not in p.parts)
     cu = sorted(p for p in CSRC.rglob("*.cu"))
     return cc, cu
 
@@ -100,6 +100,58 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
             raise RuntimeError(f"linking failed:\n{r.stdout}\n{r.stderr}")
         os.replace(tmp, LIB)
     return LIB
+
+
+def _sanitizer_cxx(sanitizer: str) -> str:
+    """First C++ compiler that can link a program with -fsanitize=<sanitizer> (a toolchain may
+    ship without the sanitizer run-time libraries)."""
+    import tempfile
+
+    with tempfile.TemporaryDirectory() as tmp:
+        src = Path(tmp) / "probe.cc"
+        src.write_text("int main() { return 0; }\n")
+        for cxx in dict.fromkeys([CXX, "/usr/bin/g++", "g++", "clang++"]):
+            try:
+                r = subprocess.run([cxx, f"-fsanitize={sanitizer}", str(src), "-o", str(Path(tmp) / "probe")], capture_output=True)
+            except OSError:
+                continue
+            if r.returncode == 0:
+                return cxx
+    raise RuntimeError(f"no C++ compiler here can link with -fsanitize={sanitizer}")
+
+
+def build_selftest(sanitizer: str = "thread", verbose: bool = False) -> Path:
+    """Build `csrc/selftest/host_selftest.cc` with the host sources compiled under
+    `-fsanitize=<sanitizer>` ("thread" or "address"); CUDA objects are reused from the normal build.
+    Returns the executable."""
+    build()
+    cxx = _sanitizer_cxx(sanitizer)
+    outdir = LIBDIR / f"selftest_{sanitizer}"
+    outdir.mkdir(parents=True, exist_ok=True)
+    cc, cu = _sources()
+    cc = [p for p in cc if p.name != "capi.cc"] + [CSRC / "selftest" / "host_selftest.cc"]
+    flags = [f"-fsanitize={sanitizer}", "-fno-omit-frame-pointer", "-O1", "-g"]
+    objs = []
+
+    def one(src):
+        obj = outdir / ("_".join(src.relative_to(CSRC).parts) + ".o")
+        cmd = [cxx] + [f for f in CXX_FLAGS if f not in ("-O2", "-g1")] + flags + ["-c", str(src), "-o", str(obj)]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"compiling {src} failed:\n{r.stderr}")
+        return obj
+
+    with concurrent.futures.ThreadPoolExecutor(max_workers=8) as ex:
+        objs = list(ex.map(one, cc))
+    exe = outdir / "host_selftest"
+    cmd = [cxx, f"-fsanitize={sanitizer}", "-o", str(exe)] + [str(o) for o in objs] + [str(_obj_for(s)) for s in cu] + [
+        f"-L{CUDA_HOME}/lib64", "-lcudart_static", "-lpthread", "-ldl", "-lrt"]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"linking the self-test failed:\n{r.stderr}")
+    return exe
 
 
 if __name__ == "__main__":

@@ -5,8 +5,10 @@
 //   1. publishes (bytes, offset of its output inside its symmetric segment) into every peer's
 //      signal pad and meets the peers at a flag barrier,
 //   2. computes every displacement on the device as a prefix sum of the published sizes,
-//   3. stores its slab straight into every peer's output at that displacement (P2P stores over
-//      NVLink; the local copy is one of them),
+//   3. stores its slab into every rank's output at that displacement: with one multimem.st per
+//      16 bytes when the outputs sit at the same segment offset on all ranks and the segment has
+//      an NVLS multicast mapping (the slab then leaves this GPU once and the switch replicates
+//      it), otherwise with P2P stores to each peer in turn (the local copy is one of them),
 //   4. meets the peers again, after which the whole concatenation is present everywhere.
 // The reference does this with a sizing allgather on the host followed by N-1 MPI_Sendrecv steps
 // (tensorflow/contrib/mpi_collectives/mpi_ops.py:152-160, ring.h:236-301).
@@ -63,6 +65,51 @@ __device__ __forceinline__ void push_slab(char* dst, const char* src, size_t n, 
   for (size_t i = body + tid; i < n; i += nthreads) dst[i] = src[i];
 }
 
+// Multicast variant: `dst` is an address in the multicast mapping, so every store lands in every
+// rank's segment. multimem stores are at least 4 bytes wide; the caller guarantees that dst, src
+// and n are multiples of 4.
+__device__ __forceinline__ void mc_st4(void* p, uint32_t v) {
+  asm volatile("multimem.st.relaxed.sys.global.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void mc_st8(void* p, uint2 v) {
+  unsigned long long w = ((unsigned long long)v.y << 32) | v.x;
+  asm volatile("multimem.st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+
+__device__ __forceinline__ void push_slab_mc(char* dst, const char* src, size_t n, size_t tid, size_t nthreads) {
+  if (n == 0) return;
+  const uintptr_t d = (uintptr_t)dst, s = (uintptr_t)src;
+  const unsigned rel = (unsigned)((d - s) & 15);
+  const unsigned width = rel == 0 ? 16 : ((rel & 7) == 0 ? 8 : 4);
+  // Head: 4-byte words until dst is aligned to the body's access width.
+  size_t head = (width - (d & (width - 1))) & (width - 1);
+  if (head > n) head = n;
+  if (tid < head / 4) mc_st4(dst + tid * 4, reinterpret_cast<const uint32_t*>(src)[tid]);
+  dst += head; src += head; n -= head;
+  if (n == 0) return;
+  size_t body = 0;
+  if (width == 16) {
+    const size_t k = n / 16;
+    size_t i = tid;
+    for (; i + 3 * nthreads < k; i += 4 * nthreads) {
+      const uint4 v0 = ld_local16(src + i * 16), v1 = ld_local16(src + (i + nthreads) * 16);
+      const uint4 v2 = ld_local16(src + (i + 2 * nthreads) * 16), v3 = ld_local16(src + (i + 3 * nthreads) * 16);
+      multimem_st16(dst + i * 16, v0);
+      multimem_st16(dst + (i + nthreads) * 16, v1);
+      multimem_st16(dst + (i + 2 * nthreads) * 16, v2);
+      multimem_st16(dst + (i + 3 * nthreads) * 16, v3);
+    }
+    for (; i < k; i += nthreads) multimem_st16(dst + i * 16, ld_local16(src + i * 16));
+    body = k * 16;
+  } else if (width == 8) {
+    const size_t k = n / 8;
+    for (size_t i = tid; i < k; i += nthreads) mc_st8(dst + i * 8, reinterpret_cast<const uint2*>(src)[i]);
+    body = k * 8;
+  }
+  const size_t words = (n - body) / 4;
+  for (size_t i = tid; i < words; i += nthreads) mc_st4(dst + body + i * 4, reinterpret_cast<const uint32_t*>(src + body)[i]);
+}
+
 __global__ void __launch_bounds__(512) allgatherv_kernel(const __grid_constant__ AgArgs a) {
   const AgRank& R = a.r[blockIdx.y];
   const RankCtx& c = R.ctx;
@@ -94,10 +141,18 @@ __global__ void __launch_bounds__(512) allgatherv_kernel(const __grid_constant__
 
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t nthreads = (size_t)gridDim.x * blockDim.x;
-  // Start with the next rank so that at any moment the P ranks write to P different targets.
-  for (int k = 0; k < P; k++) {
-    const int p = (me + 1 + k) % P;
-    push_slab(R.base[p] + s_off[p] + disp, R.in, (size_t)R.bytes, tid, nthreads);
+  bool multicast = R.mc_base != nullptr;
+  for (int q = 1; q < P; q++) multicast = multicast && s_off[q] == s_off[0];
+  multicast = multicast && ((((uintptr_t)R.in) | (s_off[0] + disp) | R.bytes) & 3) == 0;
+  if (multicast) {
+    // One store per 16 bytes; the switch delivers it to every rank, this one included.
+    push_slab_mc(R.mc_base + s_off[0] + disp, R.in, (size_t)R.bytes, tid, nthreads);
+  } else {
+    // Start with the next rank so that at any moment the P ranks write to P different targets.
+    for (int k = 0; k < P; k++) {
+      const int p = (me + 1 + k) % P;
+      push_slab(R.base[p] + s_off[p] + disp, R.in, (size_t)R.bytes, tid, nthreads);
+    }
   }
   if (P > 1) peer_barrier(c, epoch);
   store_epoch(c, epoch);

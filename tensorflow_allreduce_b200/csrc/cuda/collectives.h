@@ -82,6 +82,7 @@ struct AgRank {
   const char* in;             // local slab
   unsigned long long bytes;   // its size
   char* base[dev::kMaxRanks]; // every rank's output segment base as mapped here
+  char* mc_base;              // multicast mapping of the same segment (NVLS), or null: P2P stores only
   unsigned long long out_off; // where this rank's output starts inside its own segment
   unsigned long long* sizes_out;  // optional local array [world]: every rank's slab size in bytes
 };

@@ -59,10 +59,12 @@ class Comm {
   // Returns the algorithm used.
   Algo allreduce(int channel, const void* in, void* out, size_t count, DType dtype, float scale, int idiv,
                  bool zero_copy_agreed);
-  // Variable allgather: `in` = this rank's slab, `out` must lie in segment 0's heap or be null
-  // (then the staging area is the landing zone and `out_private` receives a copy).
+  // Variable allgather: `in` = this rank's slab, `out_symm` must lie in segment 0's heap or be null
+  // (then the staging area is the landing zone and `out_private` receives a copy; a result larger
+  // than the staging area is gathered in rounds, for which `all_bytes` = every rank's slab size
+  // must be given).
   void allgatherv(int channel, const void* in, size_t bytes, void* out_symm, void* out_private, size_t total_bytes,
-                  unsigned long long* sizes_out = nullptr);
+                  unsigned long long* sizes_out = nullptr, const unsigned long long* all_bytes = nullptr);
 
   // Fused reduce + optimizer update on a gradient bucket that lives in symmetric memory.
   Algo fused_step(int channel, void* grad, size_t count, DType dtype, void* param, float* master, float* s1, float* s2,

@@ -554,7 +554,10 @@ void Runtime::perform_allgather(OpRecord& r, const Response& resp) {
     cudaError_t e = cudaStreamWaitEvent(s, (cudaEvent_t)r.ready_event, 0);
     BC_CHECK(e == cudaSuccess, "cudaStreamWaitEvent: " << cudaGetErrorString(e));
   }
-  comm_->allgatherv(0, r.in, (size_t)r.shape[0] * row_bytes, is_symm ? r.out : nullptr, is_symm ? nullptr : r.out, total_bytes);
+  std::vector<unsigned long long> slab_bytes(r.dim0.size());
+  for (size_t i = 0; i < r.dim0.size(); i++) slab_bytes[i] = (unsigned long long)r.dim0[i] * row_bytes;
+  comm_->allgatherv(0, r.in, (size_t)r.shape[0] * row_bytes, is_symm ? r.out : nullptr, is_symm ? nullptr : r.out, total_bytes,
+                    nullptr, slab_bytes.data());
   r.algo = 0;
   cudaError_t e = cudaEventRecord((cudaEvent_t)r.done_event, s);
   BC_CHECK(e == cudaSuccess, "cudaEventRecord: " << cudaGetErrorString(e));

@@ -1,0 +1,131 @@
+// Host-side self-test of the control plane, the CPU ring and the runtime, meant to be built with
+// -fsanitize=thread or -fsanitize=address: N ranks run as threads of ONE process, each with its
+// own Runtime (own sockets, own background thread), on a CPU-only group. The reference has no
+// sanitizer configuration at all and its global state has real data races
+// (tensorflow/contrib/mpi_collectives/mpi_ops.cc:593,621,816-821).
+//
+//   host_selftest <nranks> <port>        exit code 0 = all checks passed
+#include <stdio.h>
+#include <string.h>
+
+#include <atomic>
+#include <thread>
+#include <vector>
+
+#include "../runtime/runtime.h"
+
+using namespace bc;
+
+static std::atomic<int> g_failures{0};
+#define EXPECT(cond, ...)                                   \
+  do {                                                      \
+    if (!(cond)) {                                          \
+      fprintf(stderr, "FAIL %s:%d: ", __FILE__, __LINE__);  \
+      fprintf(stderr, __VA_ARGS__);                         \
+      fprintf(stderr, "\n");                                \
+      g_failures++;                                         \
+    }                                                       \
+  } while (0)
+
+static void* alloc_cb(int64_t, int64_t rows, void* user, int* is_symm) {
+  auto* v = (std::vector<float>*)user;
+  v->assign((size_t)rows * 3, -1.f);
+  *is_symm = 0;
+  return v->data();
+}
+
+static int64_t enqueue_allreduce(Runtime& rt, const std::string& name, const float* in, float* out, std::vector<int64_t> shape,
+                                 bool average, DType dt = DType::F32) {
+  std::unique_ptr<OpRecord> r(new OpRecord());
+  r->name = name;
+  r->op = OpType::ALLREDUCE;
+  r->dtype = dt;
+  r->shape = shape;
+  r->in = in;
+  r->out = out;
+  r->average = average;
+  return rt.enqueue(std::move(r));
+}
+
+static void rank_main(int rank, int size, int port) {
+  try {
+    RuntimeOptions o;
+    o.rank = rank;
+    o.size = size;
+    o.port = port;
+    o.device = -1;
+    o.timeout_s = 20;
+    Runtime rt(o);
+    EXPECT(rt.rank() == rank && rt.size() == size, "rank/size");
+
+    // many named allreduces in flight at once, enqueued in a rank-dependent order
+    const int K = 16, n = 1000;
+    std::vector<std::vector<float>> in(K, std::vector<float>(n)), out(K, std::vector<float>(n));
+    std::vector<int64_t> h(K);
+    for (int k = 0; k < K; k++)
+      for (int i = 0; i < n; i++) in[k][i] = (float)(rank + k + i % 7);
+    for (int j = 0; j < K; j++) {
+      int k = (j * 5 + rank * 3) % K;
+      h[k] = enqueue_allreduce(rt, "t" + std::to_string(k), in[k].data(), out[k].data(), {n}, false);
+    }
+    for (int k = 0; k < K; k++) {
+      rt.wait(h[k], 30);
+      rt.release(h[k]);
+      float want = 0;
+      for (int r = 0; r < size; r++) want += (float)(r + k + 3);
+      EXPECT(out[k][3] == want, "allreduce t%d: got %f want %f", k, out[k][3], want);
+    }
+
+    // variable allgather: rank r contributes r+1 rows of 3
+    std::vector<float> mine((size_t)(rank + 1) * 3, (float)rank), gathered;
+    {
+      std::unique_ptr<OpRecord> r(new OpRecord());
+      r->name = "gather";
+      r->op = OpType::ALLGATHER;
+      r->dtype = DType::F32;
+      r->shape = {rank + 1, 3};
+      r->in = mine.data();
+      r->alloc = alloc_cb;
+      r->alloc_user = &gathered;
+      int64_t id = rt.enqueue(std::move(r));
+      rt.wait(id, 30);
+      auto rec = rt.get(id);
+      EXPECT((int)rec->dim0.size() == size, "dim0 size");
+      rt.release(id);
+      size_t pos = 0;
+      for (int r2 = 0; r2 < size; r2++)
+        for (int i = 0; i < (r2 + 1) * 3; i++) EXPECT(gathered[pos++] == (float)r2, "allgather slab of rank %d", r2);
+    }
+
+    // a mismatch must fail on every rank and leave the runtime usable
+    {
+      std::vector<float> a(10 + rank), b(10 + rank);
+      int64_t id = enqueue_allreduce(rt, "bad", a.data(), b.data(), {10 + rank}, false);
+      bool threw = false;
+      try {
+        rt.wait(id, 30);
+      } catch (const Error& e) {
+        threw = strstr(e.what(), "Mismatched allreduce tensor shapes") != nullptr;
+      }
+      rt.release(id);
+      EXPECT(threw || size == 1, "mismatch not reported");
+    }
+    auto blobs = rt.blob_gather("blob", std::string(1, (char)('a' + rank)));
+    for (int r2 = 0; r2 < size; r2++) EXPECT(blobs[r2] == std::string(1, (char)('a' + r2)), "blob of rank %d", r2);
+    (void)rt.stats_json();
+    rt.shutdown();
+  } catch (const std::exception& e) {
+    fprintf(stderr, "rank %d: exception: %s\n", rank, e.what());
+    g_failures++;
+  }
+}
+
+int main(int argc, char** argv) {
+  int n = argc > 1 ? atoi(argv[1]) : 3;
+  int port = argc > 2 ? atoi(argv[2]) : 29650;
+  std::vector<std::thread> ts;
+  for (int r = 0; r < n; r++) ts.emplace_back(rank_main, r, n, port);
+  for (auto& t : ts) t.join();
+  if (g_failures.load() == 0) printf("host_selftest ok (%d ranks)\n", n);
+  return g_failures.load() == 0 ? 0 : 1;
+}

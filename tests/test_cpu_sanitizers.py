@@ -1,0 +1,30 @@
+"""The control plane, the CPU ring and the runtime under ThreadSanitizer and AddressSanitizer:
+three ranks run as threads of one process (csrc/selftest/host_selftest.cc). The reference
+configures no sanitizer and its coordinator state has data races
+(tensorflow/contrib/mpi_collectives/mpi_ops.cc:593,621,816-821)."""
+import socket
+import subprocess
+
+import pytest
+
+from tensorflow_allreduce_b200 import build
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("sanitizer", ["thread", "address"])
+def test_host_runtime_is_clean_under_sanitizer(sanitizer):
+    try:
+        exe = build.build_selftest(sanitizer)
+    except RuntimeError as e:
+        if "no C++ compiler" in str(e):
+            pytest.skip(str(e))
+        raise
+    r = subprocess.run([str(exe), "3", str(_free_port())], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-6000:]
+    assert "host_selftest ok" in r.stdout
+    assert "WARNING: ThreadSanitizer" not in r.stderr and "ERROR: AddressSanitizer" not in r.stderr

@@ -37,25 +37,26 @@ def ref_sum(xs, dtype):
     acc = xs[0].clone()
     for x in xs[1:]: acc = acc + x
     return acc
-def same(got, want, dtype):
-    # The in-switch (NVLS) reduction of 16-bit floats may round differently from "sum in fp32,
-    # round once": allow one unit in the last place there. Everything else must be bit-exact.
-    # and the switch sums fp32 in its own order.
+def same(got, want, dtype, mag):
+    # The in-switch (NVLS) reduction sums in its own order and, for 16-bit floats, may round
+    # differently from "sum in fp32, round once": allow one unit in the last place of the largest
+    # partial sum that can occur (the sum of magnitudes). Everything else must be bit-exact.
     if dtype.is_floating_point and bc.stats()[-1]["algo"] == "nvls":
         ulp = {torch.bfloat16: 2.0 ** -7, torch.float16: 2.0 ** -10, torch.float32: 2.0 ** -21}[dtype]
-        return bool(((got.float() - want.float()).abs() <= ulp * want.float().abs().clamp_min(2.0 ** -10)).all())
+        return bool(((got.float() - want.float()).abs() <= ulp * mag.clamp_min(2.0 ** -10)).all())
     return bool(torch.equal(got, want))
 for dtype in (torch.float32, torch.bfloat16, torch.float16, torch.int32, torch.int64):
     for n in (1, 17, 4913, (1 << 16) + 3, (1 << 21) + 11):
         xs = [fill(dtype, n, 1000 * r + n % 97) for r in range(SIZE)]
         want = ref_sum(xs, dtype)
+        mag = sum(x.float().abs() for x in xs)
         got = bc.allreduce(xs[RANK], average=False)
-        if not same(got, want, dtype): bad.append(["staged", str(dtype), n, bc.stats()[-1]["algo"], (got.float() - want.float()).abs().max().item()])
+        if not same(got, want, dtype, mag): bad.append(["staged", str(dtype), n, bc.stats()[-1]["algo"], (got.float() - want.float()).abs().max().item()])
         # in place on symmetric memory (zero-copy)
         s = symmetric.empty((n,), dtype)
         s.copy_(xs[RANK])
         bc.allreduce_(s, average=False)
-        if not same(s, want, dtype): bad.append(["symmetric", str(dtype), n, bc.stats()[-1]["algo"], (s.float() - want.float()).abs().max().item()])
+        if not same(s, want, dtype, mag): bad.append(["symmetric", str(dtype), n, bc.stats()[-1]["algo"], (s.float() - want.float()).abs().max().item()])
 algos = sorted({e["algo"] for e in bc.stats() if e["device"] == 1})
 # variable allgather: (rank+1)*k rows
 for k, cols, dtype in ((1, 4, torch.float32), (3, 17, torch.int32), (64, 256, torch.bfloat16), (5, 1, torch.uint8)):
@@ -87,6 +88,32 @@ def test_collectives_across_gpus(world, env):
         assert rec["bad"] == [], rec
     if not env:
         assert "one_shot" in res[0][1]["algos"]
+
+
+@pytest.mark.parametrize("world", _worlds()[:1] + _worlds()[-1:] if len(_worlds()) > 1 else _worlds())
+def test_allgather_larger_than_staging_goes_in_rounds(world):
+    # Heap and staging area of 1 MiB each: a 6 MiB result can only be gathered piecewise.
+    res = run("""
+    bc.init()
+    bad = []
+    for k, cols, dtype in ((20000, 13, torch.float32), (7001, 3, torch.bfloat16), (100000, 1, torch.uint8)):
+        rows = (RANK + 1) * k
+        t = (torch.arange(rows * cols, device="cuda") % 251 + RANK).reshape(rows, cols).to(dtype)
+        g = bc.allgather(t)
+        lo = 0
+        for r in range(SIZE):
+            n = (r + 1) * k
+            want = (torch.arange(n * cols, device="cuda") % 251 + r).reshape(n, cols).to(dtype)
+            if not torch.equal(g[lo:lo + n], want): bad.append([k, r])
+            lo += n
+        if g.shape[0] != lo: bad.append(["shape", k])
+    torch.cuda.synchronize()
+    bc.check_device_status()
+    emit(bad=bad)
+    bc.shutdown()
+    """, nranks=world, gpus=True, timeout=300, env={"BC_STAGING_MB": "1", "BC_HEAP_MB": "1"})
+    for _, rec in res:
+        assert rec["bad"] == [], rec
 
 
 def test_error_paths_on_gpu_group():
