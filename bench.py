@@ -37,6 +37,8 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "ddp"])
     ap.add_argument("--model", default="ds2", choices=["ds2", "gpt2", "resnet50"])
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (0 = the configuration's value)")
+    ap.add_argument("--rnn", default="auto", choices=["auto", "persistent", "cudnn"],
+                    help="ds2: GRU stack on the library's persistent tcgen05 kernels (auto: ours yes, ddp no) or on cuDNN")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
 
@@ -50,13 +52,13 @@ def reference_unavailable():
     return 0
 
 
-def build_model(name: str, device, batch: int):
+def build_model(name: str, device, batch: int, persistent_rnn: bool = True):
     import torch
 
     if name == "ds2":
         from tensorflow_allreduce_b200.models import ds2
 
-        cfg = ds2.DS2Config()
+        cfg = ds2.DS2Config(persistent_rnn=persistent_rnn)
         model = ds2.DeepSpeech2(cfg).to(device)
         model.rnn.flatten_parameters()
         b = batch or 32
@@ -146,7 +148,9 @@ def main():
     from tensorflow_allreduce_b200.utils.clocks import ClockSampler
 
     bc.init(device=local)
-    model, base_opt, make, loss_fn, per_gpu_batch, meta = build_model(a.model, device, a.batch)
+    persistent = a.rnn == "persistent" or (a.rnn == "auto" and a.impl == "ours")
+    model, base_opt, make, loss_fn, per_gpu_batch, meta = build_model(a.model, device, a.batch, persistent)
+    from tensorflow_allreduce_b200.ops import persistent_gru
 
     ddp = None
     fwd = model
@@ -183,7 +187,7 @@ def main():
     for _ in range(a.warmup):
         step(dev_batch)
     torch.cuda.synchronize()
-    launches0 = getattr(opt, "launch_count", 0)
+    launches0 = getattr(opt, "launch_count", 0) + persistent_gru.launch_count
     bc.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clk:
@@ -195,7 +199,8 @@ def main():
         torch.cuda.synchronize()
     bc.barrier()
     ms = max_over_ranks(e0.elapsed_time(e1))
-    launches = getattr(opt, "launch_count", 0) - launches0
+    launches = getattr(opt, "launch_count", 0) + persistent_gru.launch_count - launches0
+    persistent_gru.check_status()
     final_loss = float(loss)
     clocks = clk.summary()
     bc.check_device_status()
@@ -235,7 +240,8 @@ def main():
             "config": {"model": meta["model"], "global_batch": world * per_gpu_batch, "seq_len": meta["seq_len"],
                        "parallelism": f"dp{world}", "optimizer": meta["optimizer"], "params_m": round(n_params / 1e6, 2),
                        "l2": "256 MB buffer written between steps (L2 flush); working set exceeds L2 anyway",
-                       "grad_buckets": len(getattr(opt, "buckets", [])), "fused_update": bool(getattr(opt, "fused", False))},
+                       "grad_buckets": len(getattr(opt, "buckets", [])), "fused_update": bool(getattr(opt, "fused", False)),
+                       "rnn": ("persistent tcgen05 kernels" if persistent else "cudnn") if a.model == "ds2" else None},
             "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"), "reasons": clocks.get("reasons", []),
                        "power_w_max": clocks.get("power_w_max"), "samples": clocks.get("samples")},
             "gpu_launches": launches,

@@ -21,6 +21,7 @@ Arms:
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import sys
@@ -194,7 +195,15 @@ def main():
             row["ours_ms"] = ms
             row["ours_busbw"] = total / (ms * 1e-3) * factor / 1e9
             from tensorflow_allreduce_b200.ops.direct import allgatherv_direct
-            sym_out = symmetric.empty((total // (es * cols), cols), dtype)
+            # results of the timed calls above live in the symmetric heap until they are collected
+            torch.cuda.synchronize()
+            gc.collect()
+            sym_out = symmetric.try_empty((total // (es * cols), cols), dtype, torch.device("cuda", local))
+            if not all(bc.host_allgather(sym_out is not None)):
+                rows.append(row)
+                if rank == 0:
+                    print(json.dumps(row), flush=True)
+                continue
             szs = torch.zeros(P, dtype=torch.int64, device="cuda")
             sym_out.zero_()
             allgatherv_direct(t, sym_out, szs)

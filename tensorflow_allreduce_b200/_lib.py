@@ -89,6 +89,11 @@ def _declare(lib):
         "bc_emu_allgatherv": (i, [vp, P(vp), P(C.c_ulonglong), P(C.c_ulonglong), i, vp]),
         "bc_emu_barrier_probe": (i, [vp, i, d, vp]),
         "bc_max_emulated_blocks": (i, [i, i]),
+        "bc_gru_supported": (i, [i, i, i, i, i]),
+        "bc_gru_set_profile": (i, [vp]),
+        "bc_gru_set_debug": (i, [i]),
+        "bc_gru_forward": (i, [i, i, i, i, vp, vp, vp, vp, vp, vp, vp, d, vp]),
+        "bc_gru_backward": (i, [i, i, i, i, vp, vp, vp, vp, vp, vp, vp, vp, d, vp]),
         "bc_test_validate": (i, [i, P(i), P(i), P(i), P(i), P(ll), cp, i, P(ll)]),
     }
     for name, (res, args) in sig.items():

@@ -13,6 +13,7 @@
 #include <mutex>
 
 #include "cuda/comm.h"
+#include "cuda/gru_persistent.h"
 #include "runtime/runtime.h"
 
 using namespace bc;
@@ -350,6 +351,45 @@ int bc_emu_barrier_probe(void* g, int absent, double timeout_s, void* stream) {
 }
 
 int bc_max_emulated_blocks(int device, int nranks) { return gpu::max_emulated_blocks(device, nranks, 512); }
+
+// ---- persistent GRU layer -----------------------------------------------------------------------
+
+int bc_gru_supported(int device, int T, int B, int H, int ndir) {
+  API_BEGIN
+  gpu::GruDims d{T, B, H, ndir};
+  return gpu::gru_persistent_supported(d, device) ? 1 : 0;
+  API_END(-1)
+}
+
+int bc_gru_set_profile(void* stamps) {
+  gpu::gru_persistent_set_profile((unsigned long long*)stamps);
+  return 0;
+}
+
+int bc_gru_set_debug(int flags) {
+  gpu::gru_persistent_set_debug(flags);
+  return 0;
+}
+
+int bc_gru_forward(int T, int B, int H, int ndir, const float* w_hh, const float* b_hh, const float* gx, float* y, float* rsv,
+                   unsigned* sync, unsigned* status, double timeout_s, void* stream) {
+  API_BEGIN
+  gpu::GruDims d{T, B, H, ndir};
+  check_cuda(gpu::gru_persistent_forward(d, w_hh, b_hh, gx, y, rsv, sync, status, timeout_s, (cudaStream_t)stream),
+             "persistent GRU forward launch");
+  return 0;
+  API_END(-1)
+}
+
+int bc_gru_backward(int T, int B, int H, int ndir, const float* w_hh_t, const float* y, const float* rsv, const float* dy,
+                    float* dgx, float* dgh, unsigned* sync, unsigned* status, double timeout_s, void* stream) {
+  API_BEGIN
+  gpu::GruDims d{T, B, H, ndir};
+  check_cuda(gpu::gru_persistent_backward(d, w_hh_t, y, rsv, dy, dgx, dgh, sync, status, timeout_s, (cudaStream_t)stream),
+             "persistent GRU backward launch");
+  return 0;
+  API_END(-1)
+}
 
 // ---- wire-format helpers exposed for unit tests ------------------------------------------------------
 

@@ -4,8 +4,11 @@ Two 2-D convolutions over (frequency, time) with batch norm and clipped ReLU, a 
 bidirectional GRU layers, a linear layer to the character classes and CTC loss. The reference
 ships no such model; its pieces there are Conv2D/cuDNN, FusedBatchNorm, Relu6-style clipping,
 GRU cells (tensorflow/contrib/rnn/kernels/gru_ops.h:69-119) or CudnnRNN, and a CPU-only CTC loss
-(tensorflow/core/kernels/ctc_loss_op.cc:167). Here every piece is a plain torch.nn module running
-on cuDNN/cuBLAS; the library under test is the gradient reduction and update around it.
+(tensorflow/core/kernels/ctc_loss_op.cc:167). Here the convolutions, batch norms, the output layer
+and the loss are plain torch.nn modules on cuDNN/cuBLAS; the GRU stack keeps its `nn.GRU` module
+and parameters but, on a GPU that supports them, is evaluated by the library's persistent
+tcgen05 kernels (`ops/persistent_gru.py`); the gradient reduction and update around the model are
+the library's fused collectives.
 """
 from __future__ import annotations
 
@@ -25,6 +28,7 @@ class DS2Config:
     rnn_layers: int = 5
     n_classes: int = 29          # blank + 28 characters
     label_len: int = 100
+    persistent_rnn: bool = True  # run the GRU stack on the library's persistent tcgen05 kernels when they support the shape
 
 
 class DeepSpeech2(nn.Module):
@@ -46,6 +50,13 @@ class DeepSpeech2(nn.Module):
         self.rnn = nn.GRU(self.rnn_input, cfg.rnn_hidden, num_layers=cfg.rnn_layers, bidirectional=True)
         self.fc = nn.Linear(2 * cfg.rnn_hidden, cfg.n_classes)
 
+    def _use_persistent(self, x: torch.Tensor) -> bool:
+        if not (self.cfg.persistent_rnn and x.is_cuda and x.dtype == torch.float32):
+            return False
+        from ..ops import persistent_gru
+
+        return persistent_gru.supported(x.shape[0], x.shape[1], self.cfg.rnn_hidden, 2, x.device)
+
     def out_frames(self, n_frames: int) -> int:
         return (n_frames + 2 * 5 - 11) // 2 + 1
 
@@ -55,7 +66,12 @@ class DeepSpeech2(nn.Module):
         x = self.conv(spect.unsqueeze(1))                 # [B, C, F', T']
         b, c, f, t = x.shape
         x = x.view(b, c * f, t).permute(2, 0, 1).contiguous()   # [T', B, C*F']
-        x, _ = self.rnn(x)
+        if self._use_persistent(x):
+            from ..ops import persistent_gru
+
+            x = persistent_gru.gru_forward(self.rnn, x)
+        else:
+            x, _ = self.rnn(x)
         return F.log_softmax(self.fc(x), dim=-1)
 
     def loss(self, spect: torch.Tensor, labels: torch.Tensor, label_lengths: torch.Tensor) -> torch.Tensor:
