@@ -92,8 +92,9 @@ def _declare(lib):
         "bc_gru_supported": (i, [i, i, i, i, i]),
         "bc_gru_set_profile": (i, [vp]),
         "bc_gru_set_debug": (i, [i]),
-        "bc_gru_forward": (i, [i, i, i, i, vp, vp, vp, vp, vp, vp, vp, d, vp]),
-        "bc_gru_backward": (i, [i, i, i, i, vp, vp, vp, vp, vp, vp, vp, vp, d, vp]),
+        "bc_gru_workspace_bytes": (ll, [i, i, i, i]),
+        "bc_gru_forward": (i, [i, i, i, i, vp, vp, vp, vp, vp, vp, vp, vp, d, vp]),
+        "bc_gru_backward": (i, [i, i, i, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, d, vp]),
         "bc_test_validate": (i, [i, P(i), P(i), P(i), P(i), P(ll), cp, i, P(ll)]),
     }
     for name, (res, args) in sig.items():

@@ -98,18 +98,19 @@ int bc_emu_barrier_probe(void* g, int absent, double timeout_s, void* stream);
 int bc_max_emulated_blocks(int device, int nranks);
 
 /* Persistent bidirectional GRU layer (tcgen05 / TMA kernels, csrc/cuda/gru_persistent.h). These
- * need no initialised group. All tensors fp32 on the current device; `sync` = 2*ndir zeroed
- * uint32, `status` = 1 uint32 that receives a non-zero code if a bounded wait ran out.
- * `stream` is a cudaStream_t. */
+ * need no initialised group. All tensors fp32 on the current device; `workspace` =
+ * bc_gru_workspace_bytes() bytes of scratch, `sync` = 256 zeroed uint32, `status` = 1 uint32 that
+ * receives a non-zero code if a bounded wait ran out. `stream` is a cudaStream_t. */
+long long bc_gru_workspace_bytes(int T, int B, int H, int ndir);
 int bc_gru_supported(int device, int T, int B, int H, int ndir);
 /* Tuning aid: device buffer of 8 x T uint64 that block (0,0) of later launches fills with time stamps; NULL = off. */
 int bc_gru_set_profile(void* stamps);
 /* Tuning only: 1 = no MMAs, 2 = no operand copies (results wrong). */
 int bc_gru_set_debug(int flags);
 int bc_gru_forward(int T, int B, int H, int ndir, const float* w_hh, const float* b_hh, const float* gx, float* y, float* rsv,
-                   unsigned* sync, unsigned* status, double timeout_s, void* stream);
+                   float* workspace, unsigned* sync, unsigned* status, double timeout_s, void* stream);
 int bc_gru_backward(int T, int B, int H, int ndir, const float* w_hh_t, const float* y, const float* rsv, const float* dy,
-                    float* dgx, float* dgh, unsigned* sync, unsigned* status, double timeout_s, void* stream);
+                    float* dgx, float* dgh, float* workspace, unsigned* sync, unsigned* status, double timeout_s, void* stream);
 
 /* Coordinator validation run on synthetic requests (unit tests). Returns the response type. */
 int bc_test_validate(int nranks, const int* ops, const int* dtypes, const int* devices, const int* ndims,

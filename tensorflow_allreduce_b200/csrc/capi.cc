@@ -371,21 +371,26 @@ int bc_gru_set_debug(int flags) {
   return 0;
 }
 
+long long bc_gru_workspace_bytes(int T, int B, int H, int ndir) {
+  gpu::GruDims d{T, B, H, ndir};
+  return (long long)gpu::gru_persistent_workspace_bytes(d);
+}
+
 int bc_gru_forward(int T, int B, int H, int ndir, const float* w_hh, const float* b_hh, const float* gx, float* y, float* rsv,
-                   unsigned* sync, unsigned* status, double timeout_s, void* stream) {
+                   float* workspace, unsigned* sync, unsigned* status, double timeout_s, void* stream) {
   API_BEGIN
   gpu::GruDims d{T, B, H, ndir};
-  check_cuda(gpu::gru_persistent_forward(d, w_hh, b_hh, gx, y, rsv, sync, status, timeout_s, (cudaStream_t)stream),
+  check_cuda(gpu::gru_persistent_forward(d, w_hh, b_hh, gx, y, rsv, workspace, sync, status, timeout_s, (cudaStream_t)stream),
              "persistent GRU forward launch");
   return 0;
   API_END(-1)
 }
 
 int bc_gru_backward(int T, int B, int H, int ndir, const float* w_hh_t, const float* y, const float* rsv, const float* dy,
-                    float* dgx, float* dgh, unsigned* sync, unsigned* status, double timeout_s, void* stream) {
+                    float* dgx, float* dgh, float* workspace, unsigned* sync, unsigned* status, double timeout_s, void* stream) {
   API_BEGIN
   gpu::GruDims d{T, B, H, ndir};
-  check_cuda(gpu::gru_persistent_backward(d, w_hh_t, y, rsv, dy, dgx, dgh, sync, status, timeout_s, (cudaStream_t)stream),
+  check_cuda(gpu::gru_persistent_backward(d, w_hh_t, y, rsv, dy, dgx, dgh, workspace, sync, status, timeout_s, (cudaStream_t)stream),
              "persistent GRU backward launch");
   return 0;
   API_END(-1)

@@ -1,25 +1,31 @@
 // Persistent bidirectional GRU layer for sm_100a (see gru_persistent.h for the interface).
 //
 // Work split. Direction d of a layer is run by H/16 blocks (grid.y = direction); block c owns
-// the hidden units [16c, 16c+16). Forward, it keeps the 48 rows of W_hh that produce the r, z and
-// n pre-activations of its units (48 x H fp32 = 192 KiB at H = 1024) in shared memory for the
-// whole sequence. Each time step it
-//   1. waits until every block of its direction has published h_{t-1} (a counter in global
-//      memory, release/acquire at gpu scope, bounded wait),
-//   2. streams h_{t-1} (B x H) through two 16 KiB shared-memory stages with TMA
+// the hidden units [16c, 16c+16) and produces their outputs. For the recurrent product the blocks
+// work in groups of C (4 forward, 8 backward at H = 1024) that split the reduction length K among
+// themselves: block q of a group keeps, for ALL units of its group, the weight columns of its K
+// range in shared memory for the whole sequence (forward 48C rows x H/C columns, backward 16C
+// rows x 3H/C columns: 192 KiB of fp32 at H = 1024 either way). Each time step it
+//   1. waits until every block of its direction has published the operand of this step (h_{t-1}
+//      forward, the pre-activation gradients backward; a counter in global memory,
+//      release/acquire at gpu scope, bounded wait),
+//   2. brings its K range of that operand (32 batch rows x K/C) into shared memory with TMA
 //      (cp.async.bulk.tensor, 128-byte swizzle) while one thread issues tcgen05.mma (TF32
-//      operands, M = 128 rows of which 48 are weights, N = 32 batch columns, K = 8 per
-//      instruction) into a 32-column accumulator in tensor memory,
-//   3. reads the accumulator back (tcgen05.ld), applies the gate non-linearities for its 16 units,
-//      writes h_t into the layer output and the saved activations, and signals the counter.
-// Backward, the block holds the 16 rows of W_hh^T that belong to its units (16 x 3H) and each
-// step first turns dh_t into the pre-activation gradients of its units, publishes them, and then
-// multiplies the full (B x 3H) pre-activation gradient by its weight rows to obtain the recurrent
-// part of dh_{t-1} for its units.
+//      operands, M = 64 accumulator rows of which 32 are the batch, N = the group's weight rows,
+//      K = 8 per instruction) into an accumulator in tensor memory,
+//   3. reads the accumulator back (tcgen05.ld), sends every other member of the group the partial
+//      sums of that member's units through global memory, meets the group (a second counter),
+//      adds up the C partial sums of its own units,
+//   4. applies the gate non-linearities (forward) or forms the next pre-activation gradients
+//      (backward) for its 16 units, writes the results and signals the direction's counter.
+// Why the split: one tcgen05.mma costs about 55-60 ns here almost regardless of its shape
+// (measured: M x N = 128 x 32, 64 x 32 and 64 x 192 all take the same time), and a step needs K/8
+// of them in a row. Splitting K over C blocks divides that chain by C; the price is the exchange
+// of C - 1 small partial-sum tiles per step.
 //
-// The MMA always reads 128 operand rows starting at a tile's base; rows past the block's own
-// weight rows alias whatever follows in shared memory and only produce accumulator rows that
-// are never read. All shared-memory offsets keep those reads inside the allocation.
+// The MMA reads 64 operand rows starting at a tile's base while a tile of the streamed operand
+// has 32; the rest aliases what follows in shared memory (the next tile, finally the weight
+// area) and only produces accumulator rows that are never read.
 //
 // Every wait (mbarrier, step counter) is bounded by %globaltimer. When a wait runs out the block
 // records a status bit, waits (bounded) for its own copies and MMAs in flight, frees its tensor
@@ -29,6 +35,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <atomic>
 #include <mutex>
 
 namespace bc {
@@ -43,10 +50,9 @@ constexpr int kTilesPerStage = 4;     // K tiles per pipeline stage (K = 128)
 constexpr int kStageBytes = kTilesPerStage * kBatchTile * 128;   // 16 KiB
 constexpr int kXTileBytes = kBatchTile * 128;                    // 4 KiB
 constexpr int kThreads = 128;
-constexpr int kAccumulators = 4;     // independent accumulators, summed in the epilogue (see drive_product)
-constexpr int kTmemCols = kAccumulators * kBatchTile;
+constexpr int kMaxBlocksPerDir = 64;   // H / 16 at H = 1024
 constexpr int kGStride = 33;          // padded row of the accumulator copy in shared memory
-constexpr int kMmaM = 128;
+constexpr int kMmaM = 64;            // the tensor core spends about one clock per accumulator row whatever N is (measured)
 
 struct Params {
   GruDims d;
@@ -57,6 +63,8 @@ struct Params {
   const float* dy;      // backward
   float* dgx;           // backward
   float* dgh;           // backward
+  float* xchg;          // partial sums exchanged inside a group
+  int split;            // blocks per group: each holds 1/split of the reduction length
   uint32_t* sync;
   uint32_t* status;
   unsigned long long timeout_ns;
@@ -143,9 +151,6 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
   for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
 }
 
-// Sum of the kAccumulators accumulators (32 columns each) for this thread's lane.
-__device__ __forceinline__ void tc_ld32_sum(uint32_t taddr, float* v);
-
 // Shared-memory matrix descriptor of a K-major operand tile stored as rows of 128 bytes with the
 // 128-byte swizzle (what TMA writes for a box that is 32 fp32 wide): groups of 8 rows are 1024
 // bytes apart; the leading-dimension offset is unused because a tile is one swizzle atom wide.
@@ -156,20 +161,6 @@ __device__ __forceinline__ uint64_t operand_desc(uint32_t smem_addr) {
   d |= (uint64_t)1 << 46;                         // descriptor version of sm_100
   d |= (uint64_t)2 << 61;                         // 128-byte swizzle
   return d;
-}
-
-// kind::tf32, fp32 accumulator, both operands K-major, M x N = 128 x 32.
-constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kBatchTile >> 3) << 17) | ((uint32_t)(kMmaM >> 4) << 24);
-
-__device__ __forceinline__ void tc_ld32_sum(uint32_t taddr, float* v) {
-  tc_ld32(taddr, v);
-#pragma unroll
-  for (int a = 1; a < kAccumulators; a++) {
-    float w[32];
-    tc_ld32(taddr + a * kBatchTile, w);
-#pragma unroll
-    for (int i = 0; i < 32; i++) v[i] += w[i];
-  }
 }
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
@@ -195,77 +186,63 @@ struct Driver {
   bool pending[2];
 };
 
-// One recurrent product: wait for the peers' data of this step, stream the (32 x K) operand
-// through the two stages and accumulate D = W_rows x X^T in tensor memory. Thread 0 only.
-// `row0` is the first row of the streamed operand in its tensor map, `col0` its first column.
-__device__ __forceinline__ uint32_t drive_product(Driver& dr, const CUtensorMap* tm_x, int row0, int col0, int nchunks, uint32_t w_addr,
-                                                  int w_tile_bytes, uint32_t x_addr, uint32_t bars, uint32_t tmem, const uint32_t* ctr,
-                                                  uint32_t target, unsigned long long timeout_ns, unsigned long long* stamp, int debug) {
+// One recurrent product of this block: wait until the peers have published the operand of this
+// step, stream the block's K range of it (32 rows x kq columns) through the two stages with TMA,
+// and accumulate D[batch, n] += X[batch, k] * W[n, k] in tensor memory (M = 64 rows of which the
+// first 32 are the batch, N = the group's weight rows). Thread 0 only.
+//   row0 / col0: first row and first column of the block's operand part in the tensor map
+//   ntiles: K tiles (32 columns each) of the block's K range
+__device__ __forceinline__ uint32_t drive_product(Driver& dr, const CUtensorMap* tm_x, int row0, int col0, int ntiles, uint32_t w_addr,
+                                                  int w_tile_bytes, uint32_t x_addr, uint32_t bars, uint32_t tmem, uint32_t idesc,
+                                                  const uint32_t* ctr, uint32_t target, unsigned long long timeout_ns,
+                                                  unsigned long long* stamp, int debug) {
   const uint32_t full0 = bars, empty0 = bars + 16, done = bars + 32;
-  const int rot = (int)(blockIdx.x % (unsigned)nchunks);
-  const uint64_t a_desc0 = operand_desc(w_addr), b_desc0 = operand_desc(x_addr);
   if (!wait_counter(ctr, target, timeout_ns)) return kGruTimeoutGrid;
   if (stamp) stamp[1] = gtimer();
   fence_proxy_async();   // peers wrote the operand with ordinary stores; TMA reads it through the async proxy
-  // Every block of a direction streams the same operand. Each starts at a different K chunk
-  // (`rot`) and wraps around, so that at any moment the blocks read different lines of L2
-  // instead of all asking the same few slices for the same lines.
-  auto load_chunk = [&](int c) {
+  const int nstages = (ntiles + kTilesPerStage - 1) / kTilesPerStage;
+  auto load_stage = [&](int sg) {
     if (debug & 2) return;
-    const int st = c & 1;
-    int kc = c + rot;
-    if (kc >= nchunks) kc -= nchunks;
-    mbar_expect_tx(full0 + 8 * st, kStageBytes);
+    const int st = sg & 1, t0 = sg * kTilesPerStage, nt = min(kTilesPerStage, ntiles - t0);
+    mbar_expect_tx(full0 + 8 * st, (uint32_t)(nt * kXTileBytes));
     dr.pending[st] = true;
-#pragma unroll
-    for (int i = 0; i < kTilesPerStage; i++)
-      tma_load_2d(x_addr + st * kStageBytes + i * kXTileBytes, tm_x, col0 + (kc * kTilesPerStage + i) * kKTile, row0, full0 + 8 * st);
+    for (int i = 0; i < nt; i++)
+      tma_load_2d(x_addr + st * kStageBytes + i * kXTileBytes, tm_x, col0 + (t0 + i) * kKTile, row0, full0 + 8 * st);
   };
-  load_chunk(0);
-  if (nchunks > 1) load_chunk(1);
-  for (int c = 0; c < nchunks; c++) {
-    const int st = c & 1;
-    int kc = c + rot;
-    if (kc >= nchunks) kc -= nchunks;
+  load_stage(0);
+  if (nstages > 1) load_stage(1);
+  // Descriptors differ from tile to tile only in their address field (bits 0-13, units of 16
+  // bytes), which cannot carry into the next field: all addresses lie below 256 KiB.
+  const uint64_t a_desc0 = operand_desc(x_addr), b_desc0 = operand_desc(w_addr);
+  for (int sg = 0; sg < nstages; sg++) {
+    const int st = sg & 1, t0 = sg * kTilesPerStage, nt = min(kTilesPerStage, ntiles - t0);
     if (!(debug & 2)) {
       if (!mbar_wait(full0 + 8 * st, dr.full_phase[st], timeout_ns, nullptr)) return kGruTimeoutCopy;
       dr.full_phase[st] ^= 1;
       dr.pending[st] = false;
     }
-    if (stamp && c == 0) stamp[2] = gtimer();
+    if (stamp && sg == 0) stamp[2] = gtimer();
     tc_fence_after();
-    // One thread issues every MMA of the step and each MMA is small (N = 32), so the issue path is
-    // kept to a few instructions: descriptors differ from a per-chunk base only in their address
-    // field (bits 0-13, in units of 16 bytes), which cannot carry into the next field because all
-    // addresses lie below 256 KiB.
-    // Consecutive MMAs into one accumulator form a dependent chain whose per-link latency (about
-    // 120 clocks, measured) is far above the work of one N = 32 MMA, so the four K steps of a tile
-    // go to four different accumulators; the epilogue adds them up.
     if (!(debug & 1)) {
-    const uint64_t a_base = a_desc0 + (uint64_t)(((uint32_t)kc * kTilesPerStage * (uint32_t)w_tile_bytes) >> 4);
-    const uint64_t b_base = b_desc0 + (uint64_t)((st * kStageBytes) >> 4);
-    if (c == 0) {
+      for (int i = 0; i < nt; i++) {
+        const uint64_t a_i = a_desc0 + (uint64_t)((st * kStageBytes + i * kXTileBytes) >> 4);
+        const uint64_t b_i = b_desc0 + (uint64_t)(((uint32_t)(t0 + i) * (uint32_t)w_tile_bytes) >> 4);
+        if (t0 + i == 0) {
+          tc_mma_tf32(tmem, a_i, b_i, idesc, 0u);
 #pragma unroll
-      for (int ks = 0; ks < 4; ks++) tc_mma_tf32(tmem + ks * kBatchTile, a_base + 2 * ks, b_base + 2 * ks, kInstrDesc, 0u);
-    } else {
+          for (int ks = 1; ks < 4; ks++) tc_mma_tf32_acc(tmem, a_i + 2 * ks, b_i + 2 * ks, idesc);
+        } else {
 #pragma unroll
-      for (int ks = 0; ks < 4; ks++) tc_mma_tf32_acc(tmem + ks * kBatchTile, a_base + 2 * ks, b_base + 2 * ks, kInstrDesc);
+          for (int ks = 0; ks < 4; ks++) tc_mma_tf32_acc(tmem, a_i + 2 * ks, b_i + 2 * ks, idesc);
+        }
+      }
     }
-#pragma unroll
-    for (int i = 1; i < kTilesPerStage; i++) {
-      const uint64_t a_i = a_base + (uint64_t)((i * w_tile_bytes) >> 4);
-      const uint64_t b_i = b_base + (uint64_t)((i * kXTileBytes) >> 4);
-#pragma unroll
-      for (int ks = 0; ks < 4; ks++) tc_mma_tf32_acc(tmem + ks * kBatchTile, a_i + 2 * ks, b_i + 2 * ks, kInstrDesc);
-    }
-    }
-    if (c + 2 < nchunks) {
-      // Refill this stage as soon as its MMAs have read it, so that two copies are always in
-      // flight: the stream is bound by copy latency, not by the tensor core.
+    if (sg + 2 < nstages) {
+      // Longer K ranges than two stages: refill this stage as soon as its MMAs have read it.
       tc_commit(empty0 + 8 * st);
       if (!mbar_wait(empty0 + 8 * st, dr.empty_phase[st], timeout_ns, nullptr)) return kGruTimeoutMma;
       dr.empty_phase[st] ^= 1;
-      load_chunk(c + 2);
+      load_stage(sg + 2);
     }
   }
   tc_commit(done);
@@ -305,20 +282,26 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
   const int dir = blockIdx.y, u0 = blockIdx.x * kUnits;
   const int T = p.d.T, B = p.d.B, H = p.d.H, ND = p.d.ndir;
   const int nblocks = gridDim.x;
+  constexpr int kRows = BWD ? kUnits : 3 * kUnits;     // weight rows per owner: its units (x 3 gates forward)
+  const int C = p.split;                               // blocks per group = K split
+  const int grp = blockIdx.x / C, q = blockIdx.x % C;  // group and this block's K range / member index
   const int kdim = BWD ? 3 * H : H;
-  constexpr int kRows = BWD ? kUnits : 3 * kUnits;
-  constexpr int kWTile = kRows * 128;
-  const int nkt = kdim / kKTile;
-  const int nchunks = kdim / (kKTile * kTilesPerStage);
+  const int kq = kdim / C;                             // this block's K range is [q * kq, (q + 1) * kq)
+  const int ntiles = kq / kKTile;
+  const int nrows = kRows * C;                         // MMA N: weight rows of the whole group
+  const int w_tile = nrows * 128;
 
-  uint8_t* w_s = smem;
-  uint8_t* x_s = smem + (size_t)nkt * kWTile;
-  float* g_s = reinterpret_cast<float*>(x_s);   // accumulator copy; aliases stage 0 between products
-  uint64_t* bar_s = reinterpret_cast<uint64_t*>(x_s + 2 * kStageBytes);   // full[2], empty[2], done, weights
+  // Stages first: the MMA reads 64 operand rows from a 32-row tile, and what follows the last
+  // tile must still be inside the allocation (it is the weight area).
+  uint8_t* x_s = smem;
+  uint8_t* w_s = smem + 2 * kStageBytes;
+  float* g_s = reinterpret_cast<float*>(x_s) + nrows * 32;   // summed partial sums of the block's rows; with t_s below it aliases the stages between products
+  uint64_t* bar_s = reinterpret_cast<uint64_t*>(w_s + (size_t)ntiles * w_tile);   // full[2], -, -, done, weights
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_s + 6);
   volatile int* abort_s = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t bars = smem_u32(bar_s);
   const uint32_t done_bar = bars + 32, w_bar = bars + 40;
+  const uint32_t tmem_cols = nrows <= 32 ? 32u : nrows <= 64 ? 64u : nrows <= 128 ? 128u : 256u;
 
   if (tid == 0) {
     for (int i = 0; i < 6; i++) mbar_init(bars + 8 * i, 1);
@@ -327,7 +310,7 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
   }
   __syncthreads();
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -335,15 +318,20 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  // The block's weight rows: loaded once, resident for the whole sequence.
+  // The group's weight rows for this block's K range: loaded once, resident for the whole
+  // sequence. Row order inside a tile: owner (member of the group), then gate, then unit.
   if (tid == 0) {
-    mbar_expect_tx(w_bar, (uint32_t)(nkt * kWTile));
-    for (int kt = 0; kt < nkt; kt++) {
-      if (BWD) {
-        tma_load_2d(smem_u32(w_s) + kt * kWTile, &tm_w, kt * kKTile, dir * H + u0, w_bar);
-      } else {
-        for (int g = 0; g < 3; g++)
-          tma_load_2d(smem_u32(w_s) + kt * kWTile + g * (kUnits * 128), &tm_w, kt * kKTile, dir * 3 * H + g * H + u0, w_bar);
+    mbar_expect_tx(w_bar, (uint32_t)(ntiles * w_tile));
+    for (int kt = 0; kt < ntiles; kt++) {
+      for (int m = 0; m < C; m++) {
+        const int unit0 = (grp * C + m) * kUnits;
+        if (BWD) {
+          tma_load_2d(smem_u32(w_s) + kt * w_tile + m * (kUnits * 128), &tm_w, q * kq + kt * kKTile, dir * H + unit0, w_bar);
+        } else {
+          for (int g = 0; g < 3; g++)
+            tma_load_2d(smem_u32(w_s) + kt * w_tile + (m * 3 + g) * (kUnits * 128), &tm_w, q * kq + kt * kKTile,
+                        dir * 3 * H + g * H + unit0, w_bar);
+        }
       }
     }
   }
@@ -356,6 +344,7 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
   dr.pending[0] = dr.pending[1] = false;
   uint32_t done_phase = 0;
   bool mma_in_flight = false;
+  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(nrows >> 3) << 17) | ((uint32_t)(kMmaM >> 4) << 24);
 
   // Thread (u, bq) handles unit u0 + u for the batch entries bq, bq + 8, bq + 16, bq + 24.
   const int u = tid & 15, bq = tid >> 4;
@@ -366,8 +355,76 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
     bias_z = p.b_hh[dir * 3 * H + H + u0 + u];
     bias_n = p.b_hh[dir * 3 * H + 2 * H + u0 + u];
   }
-  uint32_t* ctr = p.sync + dir;
+  uint32_t* dir_ctr = p.sync + dir;                                 // one arrival per block and published step
+  // Partial sums travel through global memory: xchg[dir][group][owner][source][kRows][batch 32].
+  // A tile is rewritten only after the direction's step barrier, which every reader passes after
+  // it has consumed the previous contents.
+  float* xg = p.xchg + ((size_t)(dir * (nblocks / C) + grp) * C) * C * (32 * kRows);
+  uint32_t* grp_ctr = p.sync + 8 + dir * kMaxBlocksPerDir + grp;   // one arrival per member and product
   BwdInputs pre;
+  uint32_t products = 0;
+  constexpr int kMaxC = BWD ? 8 : 4;
+  constexpr int kTile4 = kRows * 8;                    // float4 words of one owner's tile (kRows x 32)
+  float* t_s = reinterpret_cast<float*>(x_s);          // the block's whole accumulator, [nrows][32]
+  // g_s: the C partial sums of the block's own rows added up, [kRows][kGStride]
+
+  // Exchange after a product. (1) The accumulator goes to shared memory: rows 16w .. 16w+15 of the
+  // M = 64 accumulator live in lanes 0-15 of the TMEM quarter that warp w may read, so threads
+  // (w < 2, lane < 16) hold batch entry 16w + lane. (2) Every member's tile is copied to that
+  // member's place in global memory with coalesced 16-byte stores. (3) The group meets (fence,
+  // counter). (4) The block adds the tiles it received to its own and leaves the sum in g_s.
+  // Returns false if the group did not arrive in time.
+  auto exchange = [&]() {
+    if (warp < 2) {
+      const int b = warp * 16 + lane;
+      for (int c0 = 0; c0 < nrows; c0 += 32) {
+        float v[32];
+        tc_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+        if (lane < 16) {
+#pragma unroll
+          for (int i = 0; i < 32; i++)
+            if (c0 + i < nrows) t_s[(c0 + i) * 32 + b] = v[i];
+        }
+      }
+    }
+    tc_fence_before();
+    __syncthreads();
+    const float4* t4 = reinterpret_cast<const float4*>(t_s);
+    for (int idx = tid; idx < C * kTile4; idx += kThreads) {
+      const int owner = idx / kTile4, w4 = idx - owner * kTile4;
+      if (owner != q) __stcg(reinterpret_cast<float4*>(xg + (size_t)(owner * C + q) * (32 * kRows)) + w4, t4[idx]);
+    }
+    products += 1;
+    bool good = true;
+    if (C > 1) {
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) {
+        signal_counter(grp_ctr);
+        good = wait_counter(grp_ctr, (uint32_t)C * products, p.timeout_ns);
+        if (!good) { atomicOr(p.status, kGruTimeoutGrid); *abort_s = 1; }
+      }
+      good = __syncthreads_and(good) != 0;
+    }
+    if (good) {
+      for (int w4 = tid; w4 < kTile4; w4 += kThreads) {
+        float4 part[kMaxC];
+#pragma unroll
+        for (int m = 0; m < kMaxC; m++) {
+          part[m] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (m < C && m != q) part[m] = __ldcg(reinterpret_cast<const float4*>(xg + (size_t)(q * C + m) * (32 * kRows)) + w4);
+        }
+        float4 acc = t4[q * kTile4 + w4];
+#pragma unroll
+        for (int m = 0; m < kMaxC; m++) { acc.x += part[m].x; acc.y += part[m].y; acc.z += part[m].z; acc.w += part[m].w; }
+        const int j = w4 >> 3, b0 = (w4 & 7) * 4;
+        float* g = g_s + j * kGStride + b0;
+        g[0] = acc.x; g[1] = acc.y; g[2] = acc.z; g[3] = acc.w;
+      }
+    }
+    __syncthreads();
+    return good;
+  };
 
   for (int s = 0; ok && s < T; s++) {
     uint32_t fail = 0;
@@ -388,8 +445,8 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
       }
       if (s > 0) {
         if (tid == 0) {
-          fail = drive_product(dr, &tm_x, tprev * B, dir * H, nchunks, smem_u32(w_s), kWTile, smem_u32(x_s), bars, tmem, ctr,
-                               (uint32_t)nblocks * (uint32_t)s, p.timeout_ns, stamp, p.debug);
+          fail = drive_product(dr, &tm_x, tprev * B, dir * H + q * kq, ntiles, smem_u32(w_s), w_tile, smem_u32(x_s), bars, tmem, idesc,
+                               dir_ctr, (uint32_t)nblocks * (uint32_t)s, p.timeout_ns, stamp, p.debug);
           if (fail) { atomicOr(p.status, fail); *abort_s = 1; }
         }
         __syncwarp();
@@ -398,19 +455,13 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
         if (got) done_phase ^= 1;
         if (stamp) stamp[4] = gtimer();
         tc_fence_after();
-        if (got && warp < 2) {
-          float v[32];
-          tc_ld32_sum(tmem + ((uint32_t)(warp * 32) << 16), v);
-          const int row = warp * 32 + lane;
-          if (row < kRows) {
-#pragma unroll
-            for (int c = 0; c < 32; c++) g_s[row * kGStride + c] = v[c];
-          }
-        }
-        tc_fence_before();
+        if (!got || fail) tc_fence_before();
         ok = __syncthreads_and(got && !fail) != 0;
         if (!ok) { mma_in_flight = true; break; }
+        ok = exchange();
+        if (!ok) break;
       }
+      float rsv_r[4], rsv_z[4], rsv_n[4], rsv_hn[4];
 #pragma unroll
       for (int j = 0; j < 4; j++) {
         const int b = bq + 8 * j;
@@ -427,8 +478,7 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
           const float h = n + z * (carry[j] - n);
           carry[j] = h;
           p.y[((size_t)t * B + b) * (ND * H) + dir * H + u0 + u] = h;
-          float* rs = p.rsv + (((size_t)(dir * T + t) * B + b) * 4) * H + u0 + u;
-          rs[0] = r; rs[H] = z; rs[2 * H] = n; rs[3 * H] = hn;
+          rsv_r[j] = r; rsv_z[j] = z; rsv_n[j] = n; rsv_hn[j] = hn;
         }
       }
       if (stamp) stamp[5] = gtimer();
@@ -436,14 +486,23 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
         __threadfence();
         fence_proxy_async();
         __syncthreads();
-        if (tid == 0) signal_counter(ctr);
+        if (tid == 0) signal_counter(dir_ctr);
       }
       if (stamp) stamp[6] = gtimer();
+      // The saved activations are not needed by the peers: written after the step is published.
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int b = bq + 8 * j;
+        if (b < B) {
+          float* rs = p.rsv + (((size_t)(dir * T + t) * B + b) * 4) * H + u0 + u;
+          rs[0] = rsv_r[j]; rs[H] = rsv_z[j]; rs[2 * H] = rsv_n[j]; rs[3 * H] = rsv_hn[j];
+        }
+      }
     } else {
       // ---------------- backward step ----------------
       const int t = dir ? s : T - 1 - s;
       if (s == 0) load_bwd_inputs(p, pre, t, dir, u0 + u, bq);
-      float keep[4];
+      float keep[4], g_r[4], g_z[4], g_n[4];
 #pragma unroll
       for (int j = 0; j < 4; j++) {
         const int b = bq + 8 * j;
@@ -455,8 +514,8 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
           const float dz = dh * (hp - n) * z * (1.f - z);
           const float drr = dn * hn * r * (1.f - r);
           const size_t o = (((size_t)t * B + b) * ND + dir) * 3 * H + u0 + u;
-          p.dgx[o] = drr; p.dgx[o + H] = dz; p.dgx[o + 2 * H] = dn;
           p.dgh[o] = drr; p.dgh[o + H] = dz; p.dgh[o + 2 * H] = dn * r;
+          g_r[j] = drr; g_z[j] = dz; g_n[j] = dn;
           keep[j] = dh * z;
         }
       }
@@ -465,13 +524,24 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
         __threadfence();
         fence_proxy_async();
         __syncthreads();
+        if (tid == 0) signal_counter(dir_ctr);
+      }
+      if (stamp) stamp[6] = gtimer();
+      // dgx is only read after the kernel: written after the step is published.
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int b = bq + 8 * j;
+        if (b < B) {
+          const size_t o = (((size_t)t * B + b) * ND + dir) * 3 * H + u0 + u;
+          p.dgx[o] = g_r[j]; p.dgx[o + H] = g_z[j]; p.dgx[o + 2 * H] = g_n[j];
+        }
+      }
+      if (s + 1 < T) {
         // Next step's saved activations and output gradient: in flight while the product runs.
         load_bwd_inputs(p, pre, dir ? s + 1 : T - 2 - s, dir, u0 + u, bq);
         if (tid == 0) {
-          signal_counter(ctr);
-          if (stamp) stamp[6] = gtimer();
-          fail = drive_product(dr, &tm_x, t * B, dir * 3 * H, nchunks, smem_u32(w_s), kWTile, smem_u32(x_s), bars, tmem, ctr,
-                               (uint32_t)nblocks * (uint32_t)(s + 1), p.timeout_ns, stamp, p.debug);
+          fail = drive_product(dr, &tm_x, t * B, dir * 3 * H + q * kq, ntiles, smem_u32(w_s), w_tile, smem_u32(x_s), bars, tmem, idesc,
+                               dir_ctr, (uint32_t)nblocks * (uint32_t)(s + 1), p.timeout_ns, stamp, p.debug);
           if (fail) { atomicOr(p.status, fail); *abort_s = 1; }
         }
         __syncwarp();
@@ -480,23 +550,16 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
         if (got) done_phase ^= 1;
         if (stamp) stamp[4] = gtimer();
         tc_fence_after();
-        if (got && warp == 0) {
-          float v[32];
-          tc_ld32_sum(tmem, v);
-          if (lane < kRows) {
-#pragma unroll
-            for (int c = 0; c < 32; c++) g_s[lane * kGStride + c] = v[c];
-          }
-        }
-        tc_fence_before();
+        if (!got || fail) tc_fence_before();
         ok = __syncthreads_and(got && !fail) != 0;
         if (!ok) { mma_in_flight = true; break; }
+        ok = exchange();
+        if (!ok) break;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
           const int b = bq + 8 * j;
           carry[j] = b < B ? keep[j] + g_s[u * kGStride + b] : 0.f;
         }
-        tc_fence_before();
         __syncthreads();   // g_s (stage 0) is overwritten by the next product's first copy
       }
     }
@@ -513,7 +576,7 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
   __syncthreads();
   if (warp == 0) {
     __syncwarp();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
   }
 }
 
@@ -559,10 +622,27 @@ size_t smem_bytes(const GruDims& d, bool bwd) {
 }
 
 bool dims_ok(const GruDims& d) {
-  return d.T >= 1 && d.B >= 1 && d.B <= kBatchTile && d.H >= 128 && d.H <= 1024 && d.H % 128 == 0 && (d.ndir == 1 || d.ndir == 2);
+  return d.T >= 1 && d.T < 4096 && d.B >= 1 && d.B <= kBatchTile && d.H >= 128 && d.H <= 1024 && d.H % 128 == 0 && (d.ndir == 1 || d.ndir == 2);
 }
 
 bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+// Blocks per group (= K split): the largest supported value for which the group's weight rows fit
+// one MMA (N <= 256), every block gets whole K tiles, and groups tile the direction's blocks.
+int choose_split(const GruDims& d, bool bwd) {
+  const int blocks = d.H / kUnits, kdim = bwd ? 3 * d.H : d.H, rows = bwd ? kUnits : 3 * kUnits;
+  for (int c : {16, 8, 4, 2, 1}) {
+    if (c > (bwd ? 8 : 4)) continue;
+    if (rows * c > 256 || blocks % c != 0 || kdim % (c * kKTile) != 0) continue;
+    return c;
+  }
+  return 1;
+}
+
+size_t xchg_floats(const GruDims& d, bool bwd) {
+  const size_t rows = bwd ? kUnits : 3 * kUnits;
+  return (size_t)d.ndir * (d.H / kUnits) * choose_split(d, bwd) * 32 * rows;
+}
 
 template <bool BWD>
 cudaError_t launch(const GruDims& d, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const Params& p, cudaStream_t stream) {
@@ -575,6 +655,7 @@ cudaError_t launch(const GruDims& d, const CUtensorMap& tm_w, const CUtensorMap&
   if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
   if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem)) != cudaSuccess) return e;
   dim3 grid(d.H / kUnits, d.ndir), block(kThreads);
+  if (grid.x > (unsigned)kMaxBlocksPerDir) return cudaErrorInvalidValue;
   if ((int)(grid.x * grid.y) > per_sm * sms) return cudaErrorCooperativeLaunchTooLarge;
   void* args[] = {(void*)&tm_w, (void*)&tm_x, (void*)&p};
   return cudaLaunchCooperativeKernel((const void*)kernel, grid, block, args, smem, stream);
@@ -595,9 +676,14 @@ bool gru_persistent_supported(const GruDims& d, int device) {
   return d.H / kUnits * d.ndir <= sms;
 }
 
+size_t gru_persistent_workspace_bytes(const GruDims& d) {
+  if (!dims_ok(d)) return 0;
+  return std::max(xchg_floats(d, false), xchg_floats(d, true)) * sizeof(float);
+}
+
 cudaError_t gru_persistent_forward(const GruDims& d, const float* w_hh, const float* b_hh, const float* gx, float* y, float* rsv,
-                                   uint32_t* sync, uint32_t* status, double timeout_s, cudaStream_t stream) {
-  if (!dims_ok(d) || !aligned16(w_hh) || !aligned16(y)) return cudaErrorInvalidValue;
+                                   float* workspace, uint32_t* sync, uint32_t* status, double timeout_s, cudaStream_t stream) {
+  if (!dims_ok(d) || !aligned16(w_hh) || !aligned16(y) || !aligned16(workspace)) return cudaErrorInvalidValue;
   CUtensorMap tm_w, tm_x;
   if (!make_map(&tm_w, w_hh, (uint64_t)d.ndir * 3 * d.H, (uint64_t)d.H, kUnits)) return cudaErrorInvalidValue;
   if (!make_map(&tm_x, y, (uint64_t)d.T * d.B, (uint64_t)d.ndir * d.H, kBatchTile)) return cudaErrorInvalidValue;
@@ -607,6 +693,8 @@ cudaError_t gru_persistent_forward(const GruDims& d, const float* w_hh, const fl
   p.gx = gx;
   p.y = y;
   p.rsv = rsv;
+  p.xchg = workspace;
+  p.split = choose_split(d, false);
   p.sync = sync;
   p.status = status;
   p.timeout_ns = (unsigned long long)(timeout_s * 1e9);
@@ -616,9 +704,9 @@ cudaError_t gru_persistent_forward(const GruDims& d, const float* w_hh, const fl
 }
 
 cudaError_t gru_persistent_backward(const GruDims& d, const float* w_hh_t, const float* y, const float* rsv, const float* dy,
-                                    float* dgx, float* dgh, uint32_t* sync, uint32_t* status, double timeout_s,
+                                    float* dgx, float* dgh, float* workspace, uint32_t* sync, uint32_t* status, double timeout_s,
                                     cudaStream_t stream) {
-  if (!dims_ok(d) || !aligned16(w_hh_t) || !aligned16(dgh)) return cudaErrorInvalidValue;
+  if (!dims_ok(d) || !aligned16(w_hh_t) || !aligned16(dgh) || !aligned16(workspace)) return cudaErrorInvalidValue;
   CUtensorMap tm_w, tm_x;
   if (!make_map(&tm_w, w_hh_t, (uint64_t)d.ndir * d.H, (uint64_t)3 * d.H, kUnits)) return cudaErrorInvalidValue;
   if (!make_map(&tm_x, dgh, (uint64_t)d.T * d.B, (uint64_t)d.ndir * 3 * d.H, kBatchTile)) return cudaErrorInvalidValue;
@@ -629,6 +717,8 @@ cudaError_t gru_persistent_backward(const GruDims& d, const float* w_hh_t, const
   p.dy = dy;
   p.dgx = dgx;
   p.dgh = dgh;
+  p.xchg = workspace;
+  p.split = choose_split(d, true);
   p.sync = sync;
   p.status = status;
   p.timeout_ns = (unsigned long long)(timeout_s * 1e9);

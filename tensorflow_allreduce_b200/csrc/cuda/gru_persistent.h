@@ -1,7 +1,8 @@
 // Persistent bidirectional GRU layer for sm_100a: the recurrent weights of a layer stay in shared
 // memory for all time steps, the per-step recurrent product runs on the 5th-generation tensor
 // cores (tcgen05.mma, TF32 operands, fp32 accumulator in tensor memory), operands arrive by TMA,
-// and the two directions run side by side in one cooperative launch.
+// groups of blocks split the reduction length of the product among themselves, and the two
+// directions run side by side in one cooperative launch.
 //
 // The reference's speech-model pieces are GRU cells that launch one GEMM plus elementwise
 // kernels per time step (tensorflow/contrib/rnn/kernels/gru_ops.h:69-119, gru_ops_gpu.cu.cc) or
@@ -39,12 +40,14 @@ constexpr uint32_t kGruTimeoutMma = 4u;       // waiting for the tensor core to 
 //   gx    [T, B, ndir, 3H]     input projections including b_ih
 //   y     [T, B, ndir*H]       output (also read back as h_{t-1} by the next step)
 //   rsv   [ndir, T, B, 4, H]   r, z, n and (W_hn h + b_hn) of every step, for the backward pass
-//   sync  [2 * ndir] uint32    zero on entry; scratch for the per-direction step barrier
+//   workspace                  gru_persistent_workspace_bytes(d) bytes of scratch, zeroed once when it is
+//                              allocated and then reused as it is by every later call on the stream
+//   sync  [256] uint32         zero on entry; counters of the step and group barriers
 //   status[1] uint32           ORed with kGruTimeout* on failure
 // `timeout_s` bounds every wait inside the kernel. Returns cudaErrorInvalidValue for unsupported
 // dimensions and cudaErrorCooperativeLaunchTooLarge if the grid cannot be co-resident.
 cudaError_t gru_persistent_forward(const GruDims& d, const float* w_hh, const float* b_hh, const float* gx, float* y, float* rsv,
-                                   uint32_t* sync, uint32_t* status, double timeout_s, cudaStream_t stream);
+                                   float* workspace, uint32_t* sync, uint32_t* status, double timeout_s, cudaStream_t stream);
 
 // Backward through time.
 //   w_hh_t [ndir, H, 3H]       transposed recurrent weights
@@ -54,8 +57,11 @@ cudaError_t gru_persistent_forward(const GruDims& d, const float* w_hh, const fl
 //   dgh    [T, B, ndir, 3H]    out: gradient of (W_h h + b_h)     = (dr, dz, dn * r)
 // The caller forms dW_ih, dx, dW_hh and the bias gradients from dgx / dgh with library GEMMs.
 cudaError_t gru_persistent_backward(const GruDims& d, const float* w_hh_t, const float* y, const float* rsv, const float* dy,
-                                    float* dgx, float* dgh, uint32_t* sync, uint32_t* status, double timeout_s,
+                                    float* dgx, float* dgh, float* workspace, uint32_t* sync, uint32_t* status, double timeout_s,
                                     cudaStream_t stream);
+
+// Bytes of scratch memory that a forward or backward call needs for these dimensions.
+size_t gru_persistent_workspace_bytes(const GruDims& d);
 
 // Tuning aid: when `stamps` (device memory, 8 x T uint64) is non-null, block (0, 0) of every later
 // launch records %globaltimer at fixed points of each step: [0] step start, [1] peers' data

@@ -35,6 +35,22 @@ def _status_word(device: torch.device) -> torch.Tensor:
     return t
 
 
+_work: Dict[int, torch.Tensor] = {}
+
+
+def _workspace(device: torch.device, T: int, B: int, H: int, nd: int) -> torch.Tensor:
+    """Scratch for the flagged partial sums that the blocks of a group exchange. It starts zeroed
+    (no launch uses flag 0) and is reused by every launch; kernels on one stream use it one after
+    the other, so one buffer per device is enough."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    need = int(_lib.lib().bc_gru_workspace_bytes(T, B, H, nd))
+    t = _work.get(idx)
+    if t is None or t.numel() * 4 < need:
+        t = torch.zeros(max(need // 4, 4), dtype=torch.float32, device=device)
+        _work[idx] = t
+    return t
+
+
 def check_status(device=None) -> None:
     """Raise if a persistent GRU kernel on `device` gave up on a bounded wait since the last
     check (this synchronises with the device)."""
@@ -74,10 +90,11 @@ class _GRULayer(torch.autograd.Function):
         gx = torch.addmm(b_ih.reshape(-1), x2, w_ih.reshape(nd * H3, I).t())
         y = torch.empty(T, B, nd * H, dtype=torch.float32, device=x.device)
         rsv = torch.empty(nd, T, B, 4, H, dtype=torch.float32, device=x.device)
-        sync = torch.zeros(2 * nd, dtype=torch.int32, device=x.device)
+        sync = torch.zeros(256, dtype=torch.int32, device=x.device)
+        work = _workspace(x.device, T, B, H, nd)
         status = _status_word(x.device)
         w_hh_c = w_hh.contiguous()
-        rc = lib.bc_gru_forward(T, B, H, nd, _ptr(w_hh_c), _ptr(b_hh.contiguous()), _ptr(gx), _ptr(y), _ptr(rsv), _ptr(sync),
+        rc = lib.bc_gru_forward(T, B, H, nd, _ptr(w_hh_c), _ptr(b_hh.contiguous()), _ptr(gx), _ptr(y), _ptr(rsv), _ptr(work), _ptr(sync),
                                 _ptr(status), _TIMEOUT_S, C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream))
         _lib.check(rc, "bc_gru_forward")
         global launch_count
@@ -94,9 +111,10 @@ class _GRULayer(torch.autograd.Function):
         dy = dy.contiguous()
         dgx = torch.empty(T, B, nd, H3, dtype=torch.float32, device=x.device)
         dgh = torch.empty(T, B, nd, H3, dtype=torch.float32, device=x.device)
-        sync = torch.zeros(2 * nd, dtype=torch.int32, device=x.device)
+        sync = torch.zeros(256, dtype=torch.int32, device=x.device)
+        work = _workspace(x.device, T, B, H, nd)
         w_hh_t = w_hh.transpose(1, 2).contiguous()            # [nd, H, 3H]
-        rc = lib.bc_gru_backward(T, B, H, nd, _ptr(w_hh_t), _ptr(y), _ptr(rsv), _ptr(dy), _ptr(dgx), _ptr(dgh), _ptr(sync),
+        rc = lib.bc_gru_backward(T, B, H, nd, _ptr(w_hh_t), _ptr(y), _ptr(rsv), _ptr(dy), _ptr(dgx), _ptr(dgh), _ptr(work), _ptr(sync),
                                  _ptr(_status_word(x.device)), _TIMEOUT_S, C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream))
         _lib.check(rc, "bc_gru_backward")
         global launch_count
