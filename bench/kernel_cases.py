@@ -4,6 +4,7 @@
     python bench/kernel_cases.py --case fused_adamw_bf16
     python bench/kernel_cases.py --case emu_allreduce    (8 emulated ranks on one GPU, two-shot, fp32)
     python bench/kernel_cases.py --case emu_allgatherv
+    python bench/kernel_cases.py --case gru [--T 350]    (one bidirectional GRU layer 2048 -> 1024, batch 32: persistent kernels vs cuDNN)
 
 Each case prints one JSON line with the CUDA-event time per launch, the algorithmic bytes moved and
 the resulting GB/s next to the measured copy bandwidth (`MEASURED_PEAKS.json` when present).
@@ -45,15 +46,43 @@ def timed(fn, iters):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", required=True, choices=["fused_sgd", "fused_adamw_bf16", "emu_allreduce", "emu_allgatherv"])
+    ap.add_argument("--case", required=True, choices=["fused_sgd", "fused_adamw_bf16", "emu_allreduce", "emu_allgatherv", "gru"])
     ap.add_argument("--mb", type=int, default=256, help="gradient / message size in MiB")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--blocks", type=int, default=0)
+    ap.add_argument("--T", type=int, default=350, help="gru: time steps")
     a = ap.parse_args()
     torch.cuda.set_device(0)
     hbm, src = peak_hbm()
     out = {"case": a.case, "mb": a.mb}
 
+    if a.case == "gru":
+        from tensorflow_allreduce_b200.ops import persistent_gru as pg
+
+        torch.backends.cuda.matmul.allow_tf32 = True
+        torch.backends.cudnn.allow_tf32 = True
+        T, B, I, H = a.T, 32, 2048, 1024
+        torch.manual_seed(0)
+        rnn = torch.nn.GRU(I, H, num_layers=1, bidirectional=True).cuda()
+        x = torch.randn(T, B, I, device="cuda", requires_grad=True)
+        res = {}
+        for name, fn in (("persistent", lambda: pg.gru_forward(rnn, x)), ("cudnn", lambda: rnn(x)[0])):
+            f, b = [], []
+            for it in range(a.iters + 2):
+                e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+                torch.cuda.synchronize()
+                e0.record(); y = fn(); e1.record(); y.sum().backward(); e2.record()
+                torch.cuda.synchronize()
+                if it >= 2:
+                    f.append(e0.elapsed_time(e1)); b.append(e1.elapsed_time(e2))
+            res[name] = {"fwd_ms": sum(f) / len(f), "bwd_ms": sum(b) / len(b)}
+        pg.check_status()
+        # recurrent work of one layer: 2 directions x T steps x (B x H x 3H) MACs forward, the same again backward
+        flop = 2 * 2 * T * B * H * 3 * H
+        out.update(T=T, batch=B, hidden=H, **{k + "_" + kk: round(vv, 3) for k, v in res.items() for kk, vv in v.items()},
+                   recurrent_gflop_per_pass=flop / 1e9)
+        print(json.dumps(out))
+        return
     if a.case.startswith("fused"):
         import tensorflow_allreduce_b200 as bc
         from tensorflow_allreduce_b200 import _lib
