@@ -8,12 +8,14 @@ Public API, matching `tensorflow/contrib/mpi_collectives` (`__init__.py:114-131`
     Session                              context manager that joins the group on entry
     DistributedOptimizer(optimizer)      averages gradients across ranks before the update
 
-plus what the reference lacks: `broadcast`, `broadcast_parameters`, in-place and asynchronous
+plus the reductions of the reference's NCCL ops (`contrib/nccl/python/ops/nccl_ops.py`): `all_sum`,
+`all_prod`, `all_min`, `all_max` (`allreduce(..., op=...)`), `broadcast`;
+plus what the reference lacks: `broadcast_parameters`, in-place and asynchronous
 variants, symmetric-memory tensors, statistics and a launcher (`python -m
 tensorflow_allreduce_b200.launch`).
 """
 from .config import Config
-from .core import (CollectiveError, allgather, allgather_async, allreduce, allreduce_, allreduce_async, barrier,
+from .core import (CollectiveError, all_max, all_min, all_prod, all_sum, allgather, allgather_async, allreduce, allreduce_, allreduce_async, barrier,
                    broadcast, check_device_status, clear_stats, config, host_allgather, init, is_initialized,
                    local_rank, local_size, on_gpu, rank, set_fault, shutdown, size, stats)
 from .session import Session
@@ -22,7 +24,8 @@ from .parallel.broadcast import broadcast_optimizer_state, broadcast_parameters
 
 __all__ = [
     "Config", "CollectiveError", "Session", "DistributedOptimizer", "init", "shutdown", "is_initialized", "size",
-    "rank", "local_rank", "local_size", "allreduce", "allreduce_", "allreduce_async", "allgather", "allgather_async",
+    "rank", "local_rank", "local_size", "allreduce", "allreduce_", "allreduce_async", "all_sum", "all_prod", "all_min",
+    "all_max", "allgather", "allgather_async",
     "broadcast", "broadcast_parameters", "broadcast_optimizer_state", "barrier", "host_allgather", "stats",
     "clear_stats", "on_gpu", "config", "set_fault", "check_device_status",
 ]

@@ -57,7 +57,7 @@ def _declare(lib):
         "bc_local_size": (i, []),
         "bc_on_gpu": (i, []),
         "bc_broken": (i, []),
-        "bc_allreduce_async": (ll, [cp, vp, vp, i, i, P(ll), i, i, i, vp]),
+        "bc_allreduce_async": (ll, [cp, vp, vp, i, i, P(ll), i, i, i, vp, i]),
         "bc_allgather_async": (ll, [cp, vp, i, i, P(ll), i, ALLOC_FN, vp, vp]),
         "bc_wait": (i, [ll, d]),
         "bc_poll": (i, [ll]),
@@ -84,7 +84,7 @@ def _declare(lib):
         "bc_emu_destroy": (i, [vp]),
         "bc_emu_buffer": (vp, [vp, i]),
         "bc_emu_status": (C.c_uint, [vp]),
-        "bc_emu_allreduce": (i, [vp, ll, P(vp), ll, i, i, f, i, i, vp]),
+        "bc_emu_allreduce": (i, [vp, ll, P(vp), ll, i, i, f, i, i, vp, i]),
         "bc_emu_fused_step": (i, [vp, ll, ll, i, P(vp), P(vp), P(vp), P(vp), P(OptHyper), f, i, vp]),
         "bc_emu_allgatherv": (i, [vp, P(vp), P(C.c_ulonglong), P(C.c_ulonglong), i, vp]),
         "bc_emu_barrier_probe": (i, [vp, i, d, vp]),

@@ -23,7 +23,8 @@ from .config import Config
 
 __all__ = [
     "CollectiveError", "init", "shutdown", "is_initialized", "size", "rank", "local_rank", "local_size",
-    "allreduce", "allreduce_", "allreduce_async", "allgather", "allgather_async", "broadcast", "barrier",
+    "allreduce", "allreduce_", "allreduce_async", "all_sum", "all_prod", "all_min", "all_max", "allgather",
+    "allgather_async", "broadcast", "barrier",
     "host_allgather", "stats", "clear_stats", "on_gpu", "config", "set_fault", "check_device_status",
 ]
 
@@ -266,9 +267,25 @@ def _ready_event(t: torch.Tensor):
     return ev
 
 
-def allreduce_async(tensor: torch.Tensor, average: bool = True, name: Optional[str] = None, out: Optional[torch.Tensor] = None) -> Handle:
-    """Start a sum (or average) over all ranks; returns a `Handle`."""
+_REDUCTIONS = {"sum": 0, "prod": 1, "min": 2, "max": 3}
+
+
+def _resolve_reduction(op: str, average: Optional[bool]):
+    if op not in _REDUCTIONS:
+        raise ValueError(f"op must be one of {sorted(_REDUCTIONS)}, got {op!r}")
+    if average is None:
+        average = op == "sum"
+    if average and op != "sum":
+        raise ValueError("average=True goes with op='sum' only")
+    return _REDUCTIONS[op], bool(average)
+
+
+def allreduce_async(tensor: torch.Tensor, average: Optional[bool] = None, name: Optional[str] = None,
+                    out: Optional[torch.Tensor] = None, op: str = "sum") -> Handle:
+    """Start a reduction over all ranks; returns a `Handle`. `op` is "sum" (averaged unless
+    `average=False`), "prod", "min" or "max"."""
     lib = _lib.lib()
+    red, average = _resolve_reduction(op, average)
     name = name or _auto_name("allreduce")
     t = _prep(tensor)
     in_place = out is not None and out.data_ptr() == t.data_ptr() and out.is_contiguous()
@@ -283,7 +300,7 @@ def allreduce_async(tensor: torch.Tensor, average: bool = True, name: Optional[s
     zero_copy = int(in_place and t.is_cuda)
     hid = _call(lib.bc_allreduce_async(name.encode(), C.c_void_p(t.data_ptr()), C.c_void_p(result.data_ptr()), _DTYPES[t.dtype],
                                        t.dim(), _shape_array(t.shape), int(t.is_cuda), int(average), zero_copy,
-                                       C.c_void_p(ev.cuda_event) if ev is not None else None), "allreduce")
+                                       C.c_void_p(ev.cuda_event) if ev is not None else None, red), "allreduce")
 
     def fin(_h):
         if copy_back is not None:
@@ -294,8 +311,12 @@ def allreduce_async(tensor: torch.Tensor, average: bool = True, name: Optional[s
     return Handle(hid, (t, result, ev, out), t.is_cuda, finalize=fin)
 
 
-def allreduce(tensor: torch.Tensor, average: bool = True, name: Optional[str] = None) -> torch.Tensor:
-    """Sum `tensor` over all ranks, or average it (`average=True`, the default).
+def allreduce(tensor: torch.Tensor, average: Optional[bool] = None, name: Optional[str] = None, op: str = "sum") -> torch.Tensor:
+    """Sum `tensor` over all ranks, or average it (`average=True`, the default for sums).
+
+    `op` selects the element-wise reduction: "sum" (the reference's only one,
+    `mpi_collectives/ring.cc:42-50`), or "prod" / "min" / "max" as in the reference's NCCL ops
+    (`contrib/nccl/python/ops/nccl_ops.py:34-137`); those are never averaged.
 
     Dense tensors of identical shape and dtype on every rank give a new tensor of that shape.
     Integer tensors are averaged with truncating integer division. A sparse COO tensor is reduced
@@ -304,6 +325,9 @@ def allreduce(tensor: torch.Tensor, average: bool = True, name: Optional[str] = 
     and sum up when the tensor is used.
     """
     if tensor.is_sparse:
+        if op != "sum":
+            raise ValueError("sparse tensors can only be summed or averaged")
+        average = True if average is None else average
         base = name or _auto_name("allreduce")
         t = tensor.detach()
         idx = t._indices().t().contiguous()          # [nnz, ndim]
@@ -313,15 +337,35 @@ def allreduce(tensor: torch.Tensor, average: bool = True, name: Optional[str] = 
         if average:
             g_vals = g_vals / size() if g_vals.is_floating_point() else torch.div(g_vals, size(), rounding_mode="trunc")
         return torch.sparse_coo_tensor(g_idx.t(), g_vals, t.shape)
-    return allreduce_async(tensor, average=average, name=name).wait()
+    return allreduce_async(tensor, average=average, name=name, op=op).wait()
 
 
-def allreduce_(tensor: torch.Tensor, average: bool = True, name: Optional[str] = None) -> torch.Tensor:
+def all_sum(tensor: torch.Tensor, name: Optional[str] = None) -> torch.Tensor:
+    """Element-wise sum over all ranks (`nccl_ops.all_sum`, contrib/nccl/python/ops/nccl_ops.py:34-51)."""
+    return allreduce(tensor, average=False, name=name, op="sum")
+
+
+def all_prod(tensor: torch.Tensor, name: Optional[str] = None) -> torch.Tensor:
+    """Element-wise product over all ranks (`nccl_ops.all_prod`, nccl_ops.py:54-71)."""
+    return allreduce(tensor, name=name, op="prod")
+
+
+def all_min(tensor: torch.Tensor, name: Optional[str] = None) -> torch.Tensor:
+    """Element-wise minimum over all ranks (`nccl_ops.all_min`, nccl_ops.py:74-91)."""
+    return allreduce(tensor, name=name, op="min")
+
+
+def all_max(tensor: torch.Tensor, name: Optional[str] = None) -> torch.Tensor:
+    """Element-wise maximum over all ranks (`nccl_ops.all_max`, nccl_ops.py:94-111)."""
+    return allreduce(tensor, name=name, op="max")
+
+
+def allreduce_(tensor: torch.Tensor, average: Optional[bool] = None, name: Optional[str] = None, op: str = "sum") -> torch.Tensor:
     """In-place `allreduce`. A CUDA tensor that lives in symmetric memory (see `ops.symmetric`) at
     the same place on every rank is reduced where it is, with no staging copy."""
     if not tensor.is_contiguous():
         raise CollectiveError("allreduce_ needs a contiguous tensor")
-    allreduce_async(tensor, average=average, name=name, out=tensor).wait()
+    allreduce_async(tensor, average=average, name=name, out=tensor, op=op).wait()
     return tensor
 
 

@@ -34,7 +34,8 @@ int bc_broken(void);
  * input, and bc_done_event() is what the consumer's stream must wait on after bc_wait(). */
 typedef void* (*bc_alloc_fn)(long long handle, long long total_rows, void* user, int* is_symmetric);
 long long bc_allreduce_async(const char* name, const void* in, void* out, int dtype, int ndim, const long long* shape,
-                             int device_kind, int average, int zero_copy, void* ready_event);
+                             int device_kind, int average, int zero_copy, void* ready_event, int reduce_op);
+/* reduce_op: 0 sum, 1 prod, 2 min, 3 max (averaging goes with the sum only). */
 long long bc_allgather_async(const char* name, const void* in, int dtype, int ndim, const long long* shape, int device_kind,
                              bc_alloc_fn alloc, void* user, void* ready_event);
 int bc_wait(long long handle, double timeout_s);
@@ -89,7 +90,7 @@ int bc_emu_destroy(void* g);
 void* bc_emu_buffer(void* g, int r);
 unsigned bc_emu_status(void* g);
 int bc_emu_allreduce(void* g, long long off, void* const* outs, long long count, int dtype, int algo, float scale, int idiv,
-                     int blocks, void* stream);
+                     int blocks, void* stream, int reduce_op);
 int bc_emu_fused_step(void* g, long long off, long long count, int dtype, void* const* params, float* const* masters,
                       float* const* s1, float* const* s2, const bc_opt_hyper* h, float scale, int blocks, void* stream);
 int bc_emu_allgatherv(void* g, const void* const* ins, const unsigned long long* bytes, const unsigned long long* out_offs,

@@ -110,7 +110,7 @@ int bc_on_gpu() { API_BEGIN return rt().on_gpu() ? 1 : 0; API_END(-1) }
 int bc_broken() { API_BEGIN return rt().broken() ? 1 : 0; API_END(-1) }
 
 long long bc_allreduce_async(const char* name, const void* in, void* out, int dtype, int ndim, const long long* shape,
-                             int device_kind, int average, int zero_copy, void* ready_event) {
+                             int device_kind, int average, int zero_copy, void* ready_event, int reduce_op) {
   API_BEGIN
   std::unique_ptr<OpRecord> r(new OpRecord());
   r->name = name;
@@ -121,6 +121,8 @@ long long bc_allreduce_async(const char* name, const void* in, void* out, int dt
   r->in = in;
   r->out = out;
   r->average = average != 0;
+  if (reduce_op < 0 || reduce_op > (int)ReduceOp::MAX) throw Error("allreduce: unknown reduction");
+  r->red = (ReduceOp)reduce_op;
   r->zero_copy = zero_copy != 0;
   r->ready_event = ready_event;
   return rt().enqueue(std::move(r));
@@ -316,10 +318,11 @@ void* bc_emu_buffer(void* g, int r) { API_BEGIN return ((gpu::EmuGroup*)g)->buff
 unsigned bc_emu_status(void* g) { API_BEGIN return ((gpu::EmuGroup*)g)->status(); API_END(0u) }
 
 int bc_emu_allreduce(void* g, long long off, void* const* outs, long long count, int dtype, int algo, float scale, int idiv,
-                     int blocks, void* stream) {
+                     int blocks, void* stream, int reduce_op) {
   API_BEGIN
+  if (reduce_op < 0 || reduce_op > (int)ReduceOp::MAX) throw Error("unknown reduction");
   check_cuda(((gpu::EmuGroup*)g)->allreduce((size_t)off, outs, (size_t)count, (DType)dtype, (gpu::Algo)algo, scale, idiv, blocks,
-                                            (cudaStream_t)stream), "emulated allreduce launch");
+                                            (cudaStream_t)stream, (ReduceOp)reduce_op), "emulated allreduce launch");
   return 0;
   API_END(-1)
 }

@@ -40,6 +40,21 @@ inline const char* dtype_name(DType t) {
   }
 }
 
+// Element-wise reduction of an allreduce. The reference's MPI collectives only sum
+// (tensorflow/contrib/mpi_collectives/ring.cc:42-50); its single-process NCCL ops also offer
+// prod / min / max (tensorflow/contrib/nccl/kernels/nccl_ops.cc:68-79).
+enum class ReduceOp : uint8_t { SUM = 0, PROD = 1, MIN = 2, MAX = 3 };
+
+inline const char* reduce_name(ReduceOp r) {
+  switch (r) {
+    case ReduceOp::SUM: return "sum";
+    case ReduceOp::PROD: return "prod";
+    case ReduceOp::MIN: return "min";
+    case ReduceOp::MAX: return "max";
+  }
+  return "?";
+}
+
 enum class OpType : uint8_t { ALLREDUCE = 0, ALLGATHER = 1, BLOB_GATHER = 2, SHUTDOWN = 3 };
 
 inline const char* op_name(OpType t) {

@@ -44,6 +44,7 @@ std::string encode(const Request& r) {
   for (int64_t d : r.shape) w.i64(d);
   w.str(r.blob);
   w.i64(r.symm_off);
+  w.u8((uint8_t)r.red);
   return w.s;
 }
 
@@ -62,6 +63,8 @@ Request decode_request(const std::string& s) {
   for (uint32_t i = 0; i < nd; i++) r.shape[i] = rd.i64();
   r.blob = rd.str();
   r.symm_off = rd.i64();
+  r.red = (ReduceOp)rd.u8();
+  BC_CHECK((uint8_t)r.red <= (uint8_t)ReduceOp::MAX, "bad reduction in request");
   return r;
 }
 
@@ -139,6 +142,13 @@ Response build_response(const std::string& name, const std::vector<Request>& req
   }
 
   if (!bad && first.op == OpType::ALLREDUCE) {
+    for (size_t i = 1; i < reqs.size() && !bad; i++) {
+      if (reqs[i].red != first.red) {
+        bad = true;
+        err << "Mismatched reductions: One rank asked for " << reduce_name(first.red) << ", but another rank asked for "
+            << reduce_name(reqs[i].red) << ".";
+      }
+    }
     for (size_t i = 1; i < reqs.size() && !bad; i++) {
       if (reqs[i].shape != first.shape) {
         bad = true;

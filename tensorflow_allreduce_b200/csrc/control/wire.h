@@ -29,6 +29,7 @@ struct Request {
   // GPU allreduce in place on symmetric memory: (segment id << 48) | offset of the tensor inside
   // that segment, or -1. The zero-copy path is taken only if all ranks report the same value.
   int64_t symm_off = -1;
+  ReduceOp red = ReduceOp::SUM;   // allreduce only
 };
 
 enum class ResponseType : uint8_t { ALLREDUCE = 0, ALLGATHER = 1, BLOB_GATHER = 2, ERROR = 3, SHUTDOWN = 4, ABORT = 5 };

@@ -35,12 +35,17 @@ struct Slices {
 };
 
 template <typename T>
-void add_into(T* dst, const T* src, size_t n) {
-  for (size_t i = 0; i < n; i++) dst[i] += src[i];
+void add_into(T* dst, const T* src, size_t n, ReduceOp red) {
+  switch (red) {
+    case ReduceOp::SUM: for (size_t i = 0; i < n; i++) dst[i] += src[i]; break;
+    case ReduceOp::PROD: for (size_t i = 0; i < n; i++) dst[i] *= src[i]; break;
+    case ReduceOp::MIN: for (size_t i = 0; i < n; i++) dst[i] = src[i] < dst[i] ? src[i] : dst[i]; break;
+    case ReduceOp::MAX: for (size_t i = 0; i < n; i++) dst[i] = src[i] > dst[i] ? src[i] : dst[i]; break;
+  }
 }
 
 template <typename T>
-void ring_sum(Transport& t, T* buf, size_t count, double deadline) {
+void ring_sum(Transport& t, T* buf, size_t count, double deadline, ReduceOp red) {
   const int n = t.size, r = t.rank;
   if (n == 1 || count == 0) return;
   Slices sl(count, n);
@@ -51,7 +56,7 @@ void ring_sum(Transport& t, T* buf, size_t count, double deadline) {
     const int in_i = ((r - k - 1) % n + n) % n;
     send_recv(t.ring_next, buf + sl.begin(out_i), sl.len(out_i) * sizeof(T),
               t.ring_prev, incoming.data(), sl.len(in_i) * sizeof(T), deadline);
-    add_into(buf + sl.begin(in_i), incoming.data(), sl.len(in_i));
+    add_into(buf + sl.begin(in_i), incoming.data(), sl.len(in_i), red);
   }
   // Allgather: the fully reduced slice (r + 1) travels round; received slices land in place.
   for (int k = 0; k < n - 1; k++) {
@@ -102,33 +107,33 @@ void narrow_from_f32(const float* src, void* dst, size_t n, DType dtype) {
 }
 
 void cpu_ring_allreduce(Transport& t, void* data, size_t count, DType dtype, double scale,
-                        int64_t int_divisor, double deadline) {
+                        int64_t int_divisor, double deadline, ReduceOp red) {
   switch (dtype) {
     case DType::F32:
-      ring_sum(t, (float*)data, count, deadline);
+      ring_sum(t, (float*)data, count, deadline, red);
       scale_float((float*)data, count, scale);
       break;
     case DType::F64:
-      ring_sum(t, (double*)data, count, deadline);
+      ring_sum(t, (double*)data, count, deadline, red);
       scale_float((double*)data, count, scale);
       break;
     case DType::I32:
-      ring_sum(t, (int32_t*)data, count, deadline);
+      ring_sum(t, (int32_t*)data, count, deadline, red);
       divide_int((int32_t*)data, count, int_divisor);
       break;
     case DType::I64:
-      ring_sum(t, (int64_t*)data, count, deadline);
+      ring_sum(t, (int64_t*)data, count, deadline, red);
       divide_int((int64_t*)data, count, int_divisor);
       break;
     case DType::U8:
-      ring_sum(t, (uint8_t*)data, count, deadline);
+      ring_sum(t, (uint8_t*)data, count, deadline, red);
       divide_int((uint8_t*)data, count, int_divisor);
       break;
     case DType::BF16:
     case DType::F16: {
       std::vector<float> wide(count);
       widen_to_f32(data, wide.data(), count, dtype);
-      ring_sum(t, wide.data(), count, deadline);
+      ring_sum(t, wide.data(), count, deadline, red);
       scale_float(wide.data(), count, scale);
       narrow_from_f32(wide.data(), data, count, dtype);
       break;

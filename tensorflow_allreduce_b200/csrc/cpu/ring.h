@@ -19,8 +19,9 @@ namespace bc {
 // In place: on return `data` holds the element-wise sum over all ranks (times `scale` for
 // floating types when scale != 1; integer types divide by `int_divisor` when it is > 1, using
 // C++ truncating division).
+// `red` selects sum / prod / min / max; scale and divisor apply to sums.
 void cpu_ring_allreduce(Transport& t, void* data, size_t count, DType dtype, double scale,
-                        int64_t int_divisor, double deadline);
+                        int64_t int_divisor, double deadline, ReduceOp red = ReduceOp::SUM);
 
 // `rows[r]` rows of `row_bytes` bytes come from rank r; `out` receives all slabs in rank order.
 void cpu_ring_allgatherv(Transport& t, const void* in, void* out, const std::vector<int64_t>& rows,

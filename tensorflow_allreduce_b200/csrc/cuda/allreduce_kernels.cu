@@ -29,7 +29,17 @@ using namespace dev;
 namespace {
 
 constexpr int ALGO_ONE = 1, ALGO_TWO = 2, ALGO_NVLS = 3;
-constexpr int OPT_NONE = 0, OPT_SGD = 1, OPT_ADAM = 2;
+constexpr int OPT_NONE = 0, OPT_SGD = 1, OPT_ADAM = 2, OPT_RED = 3;   // OPT_RED: no update, reduction chosen at run time
+
+template <typename A>
+__device__ __forceinline__ A combine(A a, A b, int red) {
+  switch (red) {
+    case 1: return a * b;
+    case 2: return b < a ? b : a;
+    case 3: return b > a ? b : a;
+    default: return a + b;
+  }
+}
 constexpr int kNvlsUnroll = 8;
 
 template <typename T> struct Scalar;  // scalar load/store in the accumulator type
@@ -83,8 +93,8 @@ __device__ __forceinline__ float opt_step(float p, float g, float* s1, float* s2
 // begin + first, begin + first + stride, ... below `end`. PP is the number of ranks when known
 // at compile time (0: use the run-time P); U packs are fetched together so that U*P 16-byte
 // loads per thread are in flight across NVLink. `sink(i, acc)` consumes each reduced pack.
-template <typename T, int PP, int U, typename Sink>
-__device__ __forceinline__ void reduce_range(const ArRank& R, int P, size_t begin, size_t end, size_t first, size_t stride, Sink sink) {
+template <typename T, int PP, int U, bool GEN, typename Sink>
+__device__ __forceinline__ void reduce_range(const ArRank& R, int P, size_t begin, size_t end, size_t first, size_t stride, int red, Sink sink) {
   using PK = Pack<T>;
   constexpr int N = PP > 0 ? PP : kMaxRanks;
   for (size_t i0 = begin + first; i0 < end; i0 += stride * U) {
@@ -110,7 +120,7 @@ __device__ __forceinline__ void reduce_range(const ArRank& R, int P, size_t begi
             typename PK::Acc tmp[PK::kElems];
             PK::unpack(v[u][p], tmp);
 #pragma unroll
-            for (int e = 0; e < PK::kElems; e++) acc[e] += tmp[e];
+            for (int e = 0; e < PK::kElems; e++) acc[e] = GEN ? combine(acc[e], tmp[e], red) : acc[e] + tmp[e];
           }
         }
         sink(i, acc);
@@ -119,20 +129,20 @@ __device__ __forceinline__ void reduce_range(const ArRank& R, int P, size_t begi
   }
 }
 
-template <typename T, typename Sink>
-__device__ __forceinline__ void reduce_range_any(const ArRank& R, int P, size_t begin, size_t end, size_t first, size_t stride, Sink sink) {
+template <typename T, bool GEN, typename Sink>
+__device__ __forceinline__ void reduce_range_any(const ArRank& R, int P, size_t begin, size_t end, size_t first, size_t stride, int red, Sink sink) {
   switch (P) {
-    case 2: reduce_range<T, 2, 4>(R, P, begin, end, first, stride, sink); break;
-    case 4: reduce_range<T, 4, 2>(R, P, begin, end, first, stride, sink); break;
-    case 8: reduce_range<T, 8, 1>(R, P, begin, end, first, stride, sink); break;
-    default: reduce_range<T, 0, 1>(R, P, begin, end, first, stride, sink); break;
+    case 2: reduce_range<T, 2, 4, GEN>(R, P, begin, end, first, stride, red, sink); break;
+    case 4: reduce_range<T, 4, 2, GEN>(R, P, begin, end, first, stride, red, sink); break;
+    case 8: reduce_range<T, 8, 1, GEN>(R, P, begin, end, first, stride, red, sink); break;
+    default: reduce_range<T, 0, 1, GEN>(R, P, begin, end, first, stride, red, sink); break;
   }
 }
 
 template <typename T>
-__device__ __forceinline__ typename Scalar<T>::Acc reduce_scalar(const ArRank& R, int P, size_t e) {
+__device__ __forceinline__ typename Scalar<T>::Acc reduce_scalar(const ArRank& R, int P, size_t e, int red) {
   typename Scalar<T>::Acc acc = Scalar<T>::ld(reinterpret_cast<const T*>(R.in[0]) + e);
-  for (int p = 1; p < P; p++) acc += Scalar<T>::ld(reinterpret_cast<const T*>(R.in[p]) + e);
+  for (int p = 1; p < P; p++) acc = combine(acc, Scalar<T>::ld(reinterpret_cast<const T*>(R.in[p]) + e), red);
   return acc;
 }
 
@@ -141,7 +151,7 @@ template <typename T, int OPT>
 __device__ __forceinline__ void epilogue_pack(const ArRank& R, const ArArgs& a, size_t i, typename Pack<T>::Acc* acc, int me) {
   using PK = Pack<T>;
   constexpr int E = PK::kElems;
-  if constexpr (OPT == OPT_NONE) {
+  if constexpr (OPT == OPT_NONE || OPT == OPT_RED) {
     st_local16(reinterpret_cast<char*>(R.out) + i * 16, PK::pack(acc));
   } else if constexpr (IsFloatGrad<T>::value) {
     const OptHyper& h = a.opt;
@@ -189,7 +199,7 @@ __device__ __forceinline__ void epilogue_pack(const ArRank& R, const ArArgs& a, 
 
 template <typename T, int OPT>
 __device__ __forceinline__ void epilogue_scalar(const ArRank& R, const ArArgs& a, size_t e, typename Scalar<T>::Acc g, int me) {
-  if constexpr (OPT == OPT_NONE) {
+  if constexpr (OPT == OPT_NONE || OPT == OPT_RED) {
     Scalar<T>::st(reinterpret_cast<T*>(R.out) + e, g);
   } else if constexpr (IsFloatGrad<T>::value) {
     const OptHyper& h = a.opt;
@@ -251,14 +261,14 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
   if (!peer_barrier(c, epoch)) { store_epoch(c, epoch); return; }
 
   if constexpr (ALGO == ALGO_ONE) {
-    reduce_range_any<T>(R, P, 0, npacks, first, stride, [&](size_t i, Acc* acc) {
+    reduce_range_any<T, OPT == OPT_RED>(R, P, 0, npacks, first, stride, a.red, [&](size_t i, Acc* acc) {
 #pragma unroll
       for (int e = 0; e < E; e++) acc[e] = finish<Acc>(acc[e], a.scale, a.idiv);
       epilogue_pack<T, OPT>(R, a, i, acc, me);
     });
     if (blockIdx.x == 0)
       for (size_t e = tail0 + threadIdx.x; e < a.count; e += blockDim.x)
-        epilogue_scalar<T, OPT>(R, a, e, finish<typename Scalar<T>::Acc>(reduce_scalar<T>(R, P, e), a.scale, a.idiv), me);
+        epilogue_scalar<T, OPT>(R, a, e, finish<typename Scalar<T>::Acc>(reduce_scalar<T>(R, P, e, a.red), a.scale, a.idiv), me);
     // Peers may still be reading this rank's input: nobody leaves before everybody is done.
     peer_barrier(c, epoch);
     store_epoch(c, epoch);
@@ -292,7 +302,7 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
         }
       }
     } else {
-      reduce_range_any<T>(R, P, sbeg, send, first, stride, [&](size_t i, Acc* acc) {
+      reduce_range_any<T, OPT == OPT_RED>(R, P, sbeg, send, first, stride, a.red, [&](size_t i, Acc* acc) {
 #pragma unroll
         for (int e = 0; e < E; e++) acc[e] = finish<Acc>(acc[e], a.scale, a.idiv);
         const uint4 r = PK::pack(acc);
@@ -304,7 +314,7 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
     // The ragged tail (fewer elements than one pack) belongs to rank 0, block 0.
     if (me == 0 && blockIdx.x == 0) {
       for (size_t e = tail0 + threadIdx.x; e < a.count; e += blockDim.x) {
-        typename Scalar<T>::Acc g = finish<typename Scalar<T>::Acc>(reduce_scalar<T>(R, P, e), a.scale, a.idiv);
+        typename Scalar<T>::Acc g = finish<typename Scalar<T>::Acc>(reduce_scalar<T>(R, P, e, a.red), a.scale, a.idiv);
         for (int p = 0; p < P; p++) Scalar<T>::st(reinterpret_cast<T*>(R.in[p]) + e, g);
       }
     }
@@ -313,7 +323,7 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
 
     // Phase 2: local epilogue. Block b reads, inside each slice, exactly the packs that block b
     // of the owning rank produced.
-    const bool copy_needed = (OPT != OPT_NONE) || (R.out != (void*)R.in[me]);
+    const bool copy_needed = (OPT != OPT_NONE && OPT != OPT_RED) || (R.out != (void*)R.in[me]);
     if (copy_needed) {
       for (int q = 0; q < P; q++) {
         const size_t qb = npacks * (size_t)q / P, qe = npacks * (size_t)(q + 1) / P;
@@ -350,6 +360,13 @@ cudaError_t launch_one(const ArArgs& a, const LaunchCfg& cfg, cudaStream_t s) {
 
 template <typename T>
 cudaError_t dispatch_plain(const ArArgs& a, const LaunchCfg& cfg, cudaStream_t s) {
+  if (a.red != 0) {
+    switch (a.algo) {
+      case ALGO_ONE: return launch_one<T, ALGO_ONE, OPT_RED>(a, cfg, s);
+      case ALGO_TWO: return launch_one<T, ALGO_TWO, OPT_RED>(a, cfg, s);
+    }
+    return cudaErrorInvalidValue;
+  }
   switch (a.algo) {
     case ALGO_ONE: return launch_one<T, ALGO_ONE, OPT_NONE>(a, cfg, s);
     case ALGO_TWO: return launch_one<T, ALGO_TWO, OPT_NONE>(a, cfg, s);

@@ -72,6 +72,7 @@ struct ArArgs {
   size_t count;               // elements
   float scale;                // applied to floating sums (1/size when averaging)
   int idiv;                   // integer divisor when averaging integer tensors
+  int red;                    // ReduceOp; anything but SUM goes with no scale, no update and no NVLS
   OptHyper opt;
   ArRank r[dev::kMaxRanks];
 };

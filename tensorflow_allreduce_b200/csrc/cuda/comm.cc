@@ -92,7 +92,7 @@ void Comm::fill_ar_rank(ArRank* r, int channel, Segment* seg, size_t off) const 
 }
 
 Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType dtype, float scale, int idiv,
-                     bool zero_copy_agreed) {
+                     bool zero_copy_agreed, ReduceOp red) {
   CUDA_RT(cudaSetDevice(device_));
   cudaStream_t s = streams_[channel];
   const size_t es = dtype_size(dtype);
@@ -104,7 +104,13 @@ Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType
   a.nranks_here = 1;
   a.scale = scale;
   a.idiv = idiv;
+  a.red = (int)red;
   LaunchCfg cfg;
+  // The switch only adds; other reductions use the peer-load kernels.
+  auto pick = [&](size_t nbytes, bool in_place, bool has_mc) {
+    Algo g = choose_algo(nbytes, dtype, in_place, has_mc);
+    return (red != ReduceOp::SUM && g == Algo::NVLS) ? Algo::TWO_SHOT : g;
+  };
 
   if (world_ == 1) {
     if (in == out && scale == 1.f && idiv <= 1) return Algo::ONE_SHOT;
@@ -123,7 +129,7 @@ Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType
   if (seg && in == out) {
     // In place on symmetric memory: no staging at all.
     const size_t off = (const char*)in - seg->local;
-    Algo algo = choose_algo(bytes, dtype, true, seg->mc != nullptr);
+    Algo algo = pick(bytes, true, seg->mc != nullptr);
     a.algo = (int)algo;
     // Very large tensors go in pieces of kMaxLaunchBytes: measured on 8 GPUs, one 1 GiB launch
     // ran at 630 GB/s bus bandwidth where 512 MiB launches reach 790.
@@ -158,7 +164,7 @@ Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType
     const size_t n = std::min(chunk_elems, count - done);
     const size_t nb = n * es;
     CUDA_RT(launch_copy(staging(), (const char*)in + done * es, nb, s));
-    Algo algo = choose_algo(nb, dtype, false, seg0_->mc != nullptr);
+    Algo algo = pick(nb, false, seg0_->mc != nullptr);
     fill_ar_rank(&a.r[0], channel, seg0_, staging_off_);
     a.r[0].out = (char*)out + done * es;
     a.algo = (int)algo;
@@ -324,7 +330,7 @@ RankCtx EmuGroup::ctx(int r, int channel) const {
 }
 
 cudaError_t EmuGroup::allreduce(size_t off, void* const* outs, size_t count, DType dtype, Algo algo, float scale, int idiv,
-                                int blocks, cudaStream_t s) {
+                                int blocks, cudaStream_t s, ReduceOp red) {
   ArArgs a;
   memset(&a, 0, sizeof(a));
   a.nranks_here = n_;
@@ -332,6 +338,7 @@ cudaError_t EmuGroup::allreduce(size_t off, void* const* outs, size_t count, DTy
   a.count = count;
   a.scale = scale;
   a.idiv = idiv;
+  a.red = (int)red;
   for (int r = 0; r < n_; r++) {
     a.r[r].ctx = ctx(r, 0);
     for (int p = 0; p < n_; p++) a.r[r].in[p] = bufs_[p] + off;

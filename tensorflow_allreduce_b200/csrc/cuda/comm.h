@@ -58,7 +58,7 @@ class Comm {
   // device; data outside symmetric memory is staged. `scale`/`idiv` implement averaging.
   // Returns the algorithm used.
   Algo allreduce(int channel, const void* in, void* out, size_t count, DType dtype, float scale, int idiv,
-                 bool zero_copy_agreed);
+                 bool zero_copy_agreed, ReduceOp red = ReduceOp::SUM);
   // Variable allgather: `in` = this rank's slab, `out_symm` must lie in segment 0's heap or be null
   // (then the staging area is the landing zone and `out_private` receives a copy; a result larger
   // than the staging area is gathered in rounds, for which `all_bytes` = every rank's slab size
@@ -115,7 +115,7 @@ class EmuGroup {
 
   // In-place-capable allreduce over ranks' buffers at `off`; outs[r] may equal the input.
   cudaError_t allreduce(size_t off, void* const* outs, size_t count, DType dtype, Algo algo, float scale, int idiv,
-                        int blocks, cudaStream_t s);
+                        int blocks, cudaStream_t s, ReduceOp red = ReduceOp::SUM);
   cudaError_t fused_step(size_t off, size_t count, DType dtype, void* const* params, float* const* masters,
                          float* const* s1, float* const* s2, const OptHyper& h, float scale, int blocks, cudaStream_t s);
   cudaError_t allgatherv(const void* const* ins, const unsigned long long* bytes, const unsigned long long* out_offs,

@@ -312,6 +312,7 @@ void Runtime::send_request(const OpRecord& rec) {
   q.shape = rec.shape;
   q.blob = rec.blob;
   q.symm_off = -1;
+  q.red = rec.red;
   if (rec.zero_copy && comm_) {
     int64_t n = 1;
     for (int64_t d : rec.shape) n *= d;
@@ -508,11 +509,12 @@ void Runtime::perform(const Response& resp) {
 void Runtime::perform_allreduce(OpRecord& r) {
   size_t count = 1;
   for (int64_t d : r.shape) count *= (size_t)d;
+  BC_CHECK(!(r.average && r.red != ReduceOp::SUM), "allreduce: averaging goes with the sum only");
   const double scale = r.average ? 1.0 / t_.size : 1.0;
   const int64_t idiv = r.average ? t_.size : 1;
   if (r.device == DeviceKind::CPU) {
     if (r.in != r.out && count) memcpy(r.out, r.in, count * dtype_size(r.dtype));
-    cpu_ring_allreduce(t_, r.out, count, r.dtype, scale, idiv, now_s() + opt_.timeout_s);
+    cpu_ring_allreduce(t_, r.out, count, r.dtype, scale, idiv, now_s() + opt_.timeout_s, r.red);
     r.algo = 0;
     return;
   }
@@ -524,7 +526,7 @@ void Runtime::perform_allreduce(OpRecord& r) {
     cudaError_t e = cudaStreamWaitEvent(s, (cudaEvent_t)r.ready_event, 0);
     BC_CHECK(e == cudaSuccess, "cudaStreamWaitEvent: " << cudaGetErrorString(e));
   }
-  r.algo = (int)comm_->allreduce(0, r.in, r.out, count, r.dtype, (float)scale, (int)idiv, r.zero_copy);
+  r.algo = (int)comm_->allreduce(0, r.in, r.out, count, r.dtype, (float)scale, (int)idiv, r.zero_copy, r.red);
   cudaError_t e = cudaEventRecord((cudaEvent_t)r.done_event, s);
   BC_CHECK(e == cudaSuccess, "cudaEventRecord: " << cudaGetErrorString(e));
 }

@@ -46,6 +46,7 @@ struct OpRecord {
   const void* in = nullptr;
   void* out = nullptr;
   bool average = false;
+  ReduceOp red = ReduceOp::SUM;
   bool zero_copy = false;        // GPU: input and output are the same symmetric tensor on every rank
   void* ready_event = nullptr;   // cudaEvent_t recorded by the producer stream, or null
   void* done_event = nullptr;    // cudaEvent_t recorded on the private stream after the launch

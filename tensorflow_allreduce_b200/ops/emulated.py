@@ -61,9 +61,9 @@ class EmulatedGroup:
         return int(self.lib.bc_max_emulated_blocks(self.device, self.nranks))
 
     def allreduce(self, count: int, dtype: torch.dtype, algo: str = "two_shot", outs: Optional[Sequence[torch.Tensor]] = None,
-                  scale: float = 1.0, idiv: int = 1, blocks: int = 4, offset_bytes: int = 0):
+                  scale: float = 1.0, idiv: int = 1, blocks: int = 4, offset_bytes: int = 0, op: str = "sum"):
         """Reduce the first `count` elements (at `offset_bytes`) of all ranks' buffers. `outs`
-        defaults to in place (two-shot only)."""
+        defaults to in place (two-shot only). `op`: sum, prod, min or max."""
         n = self.nranks
         arr = (C.c_void_p * n)()
         for r in range(n):
@@ -73,7 +73,7 @@ class EmulatedGroup:
                 arr[r] = outs[r].data_ptr()
         s = torch.cuda.current_stream(self.device).cuda_stream
         _check(self.lib.bc_emu_allreduce(self._g, offset_bytes, arr, count, _DTYPES[dtype], ALGOS[algo], float(scale), int(idiv),
-                                         blocks, C.c_void_p(s)), "emulated allreduce")
+                                         blocks, C.c_void_p(s), {"sum": 0, "prod": 1, "min": 2, "max": 3}[op]), "emulated allreduce")
 
     def fused_step(self, count: int, dtype: torch.dtype, params: Sequence[torch.Tensor], hyper: "_lib.OptHyper",
                    masters: Optional[Sequence[torch.Tensor]] = None, state1: Optional[Sequence[torch.Tensor]] = None,

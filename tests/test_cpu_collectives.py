@@ -101,6 +101,43 @@ def test_allreduce_cpu_like_reference(n):
         assert rec["bad"] == []
 
 
+def test_prod_min_max_reductions():
+    # The reductions of the reference's NCCL ops (contrib/nccl/python/ops/nccl_ops.py:34-137) on a
+    # CPU group of three ranks; a mismatch in the reduction fails on every rank.
+    res = run("""
+    bc.init(device="cpu")
+    bad = []
+    for dtype in (torch.float32, torch.int32, torch.int64, torch.float64, torch.bfloat16):
+        xs = [((torch.arange(23) % 5) - 2 + r).to(dtype) for r in range(SIZE)]
+        for op, fn in (("prod", lambda a, b: a * b), ("min", torch.minimum), ("max", torch.maximum), ("sum", lambda a, b: a + b)):
+            want = xs[0]
+            for x in xs[1:]:
+                want = fn(want.float(), x.float()).to(dtype) if dtype == torch.bfloat16 else fn(want, x)
+            got = bc.allreduce(xs[RANK], op=op, average=False)
+            if not torch.equal(got, want):
+                bad.append([str(dtype), op])
+    helpers = [bc.all_sum(torch.tensor([1.0 + RANK])).item(), bc.all_prod(torch.tensor([2.0 + RANK])).item(),
+               bc.all_min(torch.tensor([5 - RANK])).item(), bc.all_max(torch.tensor([5 - RANK])).item()]
+    err = None
+    try:
+        bc.allreduce(torch.ones(4), op="max" if RANK == 0 else "min", name="mixed")
+    except bc.CollectiveError as e:
+        err = str(e)
+    try:
+        bc.allreduce(torch.ones(4), op="max", average=True)
+        refused = False
+    except ValueError:
+        refused = True
+    emit(bad=bad, helpers=helpers, err=err, refused=refused)
+    bc.shutdown()
+    """, nranks=3)
+    for _, rec in res:
+        assert rec["bad"] == []
+        assert rec["helpers"] == [6.0, 24.0, 3, 5]
+        assert "Mismatched reductions" in rec["err"]
+        assert rec["refused"]
+
+
 def test_integer_average_truncates():
     res = run("""
     bc.init(device="cpu")

@@ -82,6 +82,43 @@ def test_allreduce_matches_reference(emu, nranks, algo, dtype):
             assert torch.equal(got[r], want), f"rank {r} n={n} {dtype} {algo}"
 
 
+@pytest.mark.parametrize("nranks", [2, 3, 8])
+@pytest.mark.parametrize("algo", ["one_shot", "two_shot"])
+@pytest.mark.parametrize("op", ["prod", "min", "max"])
+def test_prod_min_max_match_reference(emu, nranks, algo, op):
+    g = emu(nranks)
+    fn = {"prod": lambda a, b: a * b, "min": torch.minimum, "max": torch.maximum}[op]
+    for dtype in (torch.float32, torch.bfloat16, torch.int32, torch.int64, torch.float64):
+        e = PACK[dtype]
+        for n in (1, e + 1, 3 * e * nranks + 5, (1 << 16) + 3):
+            xs = [_fill(dtype, n, 100 * r + 11) for r in range(nranks)]
+            if op == "prod" and not dtype.is_floating_point:
+                xs = [x % 3 for x in xs]      # keep integer products small
+            bufs = [g.buffer(r, dtype, n) for r in range(nranks)]
+            for r in range(nranks):
+                bufs[r][:n].copy_(xs[r])
+            if dtype == torch.bfloat16:       # the kernels combine in fp32 and round once
+                want = xs[0].float()
+                for x in xs[1:]:
+                    want = fn(want, x.float())
+                want = want.to(dtype)
+            else:
+                want = xs[0].clone()
+                for x in xs[1:]:
+                    want = fn(want, x)
+            if algo == "one_shot":
+                outs = [torch.empty(n, dtype=dtype, device="cuda") for _ in range(nranks)]
+                g.allreduce(n, dtype, "one_shot", outs=outs, blocks=3, op=op)
+                got = outs
+            else:
+                g.allreduce(n, dtype, "two_shot", blocks=3, op=op)
+                got = [b[:n] for b in bufs]
+            torch.cuda.synchronize()
+            assert g.status == 0
+            for r in range(nranks):
+                assert torch.equal(got[r], want), f"rank {r} n={n} {dtype} {algo} {op}"
+
+
 @pytest.mark.parametrize("nranks", [2, 8])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_allreduce_exhaustive_small_sizes(emu, nranks, dtype):
