@@ -49,7 +49,8 @@ constexpr int kKTile = 32;            // fp32 elements in one 128-byte swizzle r
 constexpr int kTilesPerStage = 4;     // K tiles per pipeline stage (K = 128)
 constexpr int kStageBytes = kTilesPerStage * kBatchTile * 128;   // 16 KiB
 constexpr int kXTileBytes = kBatchTile * 128;                    // 4 KiB
-constexpr int kThreads = 128;
+constexpr int kComputeThreads = 128;   // four warps: accumulator read-back, exchange, gate math
+constexpr int kThreads = 160;          // plus one warp whose first thread issues copies and MMAs
 constexpr int kMaxBlocksPerDir = 64;   // H / 16 at H = 1024
 constexpr int kGStride = 33;          // padded row of the accumulator copy in shared memory
 constexpr int kMmaM = 64;            // the tensor core spends about one clock per accumulator row whatever N is (measured)
@@ -279,6 +280,7 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool driver = tid == kComputeThreads;   // does nothing but wait for peers, issue TMA copies and MMAs
   const int dir = blockIdx.y, u0 = blockIdx.x * kUnits;
   const int T = p.d.T, B = p.d.B, H = p.d.H, ND = p.d.ndir;
   const int nblocks = gridDim.x;
@@ -320,7 +322,7 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
 
   // The group's weight rows for this block's K range: loaded once, resident for the whole
   // sequence. Row order inside a tile: owner (member of the group), then gate, then unit.
-  if (tid == 0) {
+  if (driver) {
     mbar_expect_tx(w_bar, (uint32_t)(ntiles * w_tile));
     for (int kt = 0; kt < ntiles; kt++) {
       for (int m = 0; m < C; m++) {
@@ -346,8 +348,9 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
   bool mma_in_flight = false;
   const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(nrows >> 3) << 17) | ((uint32_t)(kMmaM >> 4) << 24);
 
-  // Thread (u, bq) handles unit u0 + u for the batch entries bq, bq + 8, bq + 16, bq + 24.
-  const int u = tid & 15, bq = tid >> 4;
+  // Compute thread (u, bq) handles unit u0 + u for the batch entries bq, bq + 8, bq + 16, bq + 24.
+  // The driver's warp gets bq = 32, which fails every `b < B` test below.
+  const int u = tid & 15, bq = tid < kComputeThreads ? tid >> 4 : 32;
   float carry[4] = {0.f, 0.f, 0.f, 0.f};   // forward: h_{t-1}; backward: recurrent part of dh_t
   float bias_r = 0.f, bias_z = 0.f, bias_n = 0.f;
   if (!BWD) {
@@ -428,8 +431,8 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
 
   for (int s = 0; ok && s < T; s++) {
     uint32_t fail = 0;
-    unsigned long long* stamp = (p.prof && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) ? p.prof + (size_t)s * 8 : nullptr;
-    if (stamp) stamp[0] = gtimer();
+    unsigned long long* stamp = (p.prof && (tid == 0 || driver) && blockIdx.x == 0 && blockIdx.y == 0) ? p.prof + (size_t)s * 8 : nullptr;
+    if (stamp && tid == 0) stamp[0] = gtimer();
     if (!BWD) {
       // ---------------- forward step ----------------
       const int t = dir ? T - 1 - s : s;
@@ -444,7 +447,7 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
         }
       }
       if (s > 0) {
-        if (tid == 0) {
+        if (driver) {
           fail = drive_product(dr, &tm_x, tprev * B, dir * H + q * kq, ntiles, smem_u32(w_s), w_tile, smem_u32(x_s), bars, tmem, idesc,
                                dir_ctr, (uint32_t)nblocks * (uint32_t)s, p.timeout_ns, stamp, p.debug);
           if (fail) { atomicOr(p.status, fail); *abort_s = 1; }
@@ -453,7 +456,7 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
         bool got = mbar_wait(done_bar, done_phase, 4 * p.timeout_ns, abort_s);
         got = __all_sync(0xffffffffu, got) != 0;
         if (got) done_phase ^= 1;
-        if (stamp) stamp[4] = gtimer();
+        if (stamp && tid == 0) stamp[4] = gtimer();
         tc_fence_after();
         if (!got || fail) tc_fence_before();
         ok = __syncthreads_and(got && !fail) != 0;
@@ -481,14 +484,14 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
           rsv_r[j] = r; rsv_z[j] = z; rsv_n[j] = n; rsv_hn[j] = hn;
         }
       }
-      if (stamp) stamp[5] = gtimer();
+      if (stamp && tid == 0) stamp[5] = gtimer();
       if (s + 1 < T) {
         __threadfence();
         fence_proxy_async();
         __syncthreads();
         if (tid == 0) signal_counter(dir_ctr);
       }
-      if (stamp) stamp[6] = gtimer();
+      if (stamp && tid == 0) stamp[6] = gtimer();
       // The saved activations are not needed by the peers: written after the step is published.
 #pragma unroll
       for (int j = 0; j < 4; j++) {
@@ -519,14 +522,14 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
           keep[j] = dh * z;
         }
       }
-      if (stamp) stamp[5] = gtimer();
+      if (stamp && tid == 0) stamp[5] = gtimer();
       if (s + 1 < T) {
         __threadfence();
         fence_proxy_async();
         __syncthreads();
         if (tid == 0) signal_counter(dir_ctr);
       }
-      if (stamp) stamp[6] = gtimer();
+      if (stamp && tid == 0) stamp[6] = gtimer();
       // dgx is only read after the kernel: written after the step is published.
 #pragma unroll
       for (int j = 0; j < 4; j++) {
@@ -539,7 +542,7 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
       if (s + 1 < T) {
         // Next step's saved activations and output gradient: in flight while the product runs.
         load_bwd_inputs(p, pre, dir ? s + 1 : T - 2 - s, dir, u0 + u, bq);
-        if (tid == 0) {
+        if (driver) {
           fail = drive_product(dr, &tm_x, t * B, dir * 3 * H + q * kq, ntiles, smem_u32(w_s), w_tile, smem_u32(x_s), bars, tmem, idesc,
                                dir_ctr, (uint32_t)nblocks * (uint32_t)(s + 1), p.timeout_ns, stamp, p.debug);
           if (fail) { atomicOr(p.status, fail); *abort_s = 1; }
@@ -548,7 +551,7 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
         bool got = mbar_wait(done_bar, done_phase, 4 * p.timeout_ns, abort_s);
         got = __all_sync(0xffffffffu, got) != 0;
         if (got) done_phase ^= 1;
-        if (stamp) stamp[4] = gtimer();
+        if (stamp && tid == 0) stamp[4] = gtimer();
         tc_fence_after();
         if (!got || fail) tc_fence_before();
         ok = __syncthreads_and(got && !fail) != 0;
@@ -566,7 +569,7 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
   }
 
   // Leave cleanly: nothing of this block may still be in flight when tensor memory is freed.
-  if (tid == 0 && (mma_in_flight || !ok)) {
+  if (driver && (mma_in_flight || !ok)) {
     for (int st = 0; st < 2; st++)
       if (dr.pending[st]) mbar_wait(bars + 8 * st, dr.full_phase[st], p.timeout_ns, nullptr);
     tc_commit(done_bar);
