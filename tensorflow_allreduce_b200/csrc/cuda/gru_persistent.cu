@@ -136,8 +136,10 @@ __device__ __forceinline__ void tc_mma_tf32_acc(uint32_t tmem_d, uint64_t adesc,
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc) : "memory");
 }
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
-  uint32_t r[32];
+// 32 consecutive accumulator columns of this thread's TMEM lane; tc_ld_wait() before the values are used,
+// so that several loads can be in flight.
+__device__ __forceinline__ void tc_ld32_issue(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -147,10 +149,8 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
         "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor of a K-major operand tile stored as rows of 128 bytes with the
 // 128-byte swizzle (what TMA writes for a box that is 32 fp32 wide): groups of 8 rows are 1024
@@ -380,13 +380,23 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
   auto exchange = [&]() {
     if (warp < 2) {
       const int b = warp * 16 + lane;
-      for (int c0 = 0; c0 < nrows; c0 += 32) {
-        float v[32];
-        tc_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+      // Two loads in flight. Columns past nrows that a load touches are still inside the
+      // allocation (nrows rounded up to a power of two, at least 32) and are not stored.
+      for (int c0 = 0; c0 < nrows; c0 += 64) {
+        float v[32], w[32];
+        const bool two = c0 + 32 < nrows;
+        tc_ld32_issue(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+        if (two) tc_ld32_issue(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c0 + 32), w);
+        tc_ld_wait();
         if (lane < 16) {
 #pragma unroll
           for (int i = 0; i < 32; i++)
             if (c0 + i < nrows) t_s[(c0 + i) * 32 + b] = v[i];
+          if (two) {
+#pragma unroll
+            for (int i = 0; i < 32; i++)
+              if (c0 + 32 + i < nrows) t_s[(c0 + 32 + i) * 32 + b] = w[i];
+          }
         }
       }
     }
@@ -400,7 +410,8 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
     products += 1;
     bool good = true;
     if (C > 1) {
-      __threadfence();
+      // The barrier orders every thread's stores before thread 0's release (cumulativity), so one
+      // release at gpu scope publishes the whole tile.
       __syncthreads();
       if (tid == 0) {
         signal_counter(grp_ctr);
@@ -486,10 +497,9 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
       }
       if (stamp && tid == 0) stamp[5] = gtimer();
       if (s + 1 < T) {
-        __threadfence();
-        fence_proxy_async();
+        fence_proxy_async();   // the peers read these stores through TMA
         __syncthreads();
-        if (tid == 0) signal_counter(dir_ctr);
+        if (tid == 0) signal_counter(dir_ctr);   // release at gpu scope, cumulative over the barrier
       }
       if (stamp && tid == 0) stamp[6] = gtimer();
       // The saved activations are not needed by the peers: written after the step is published.
@@ -524,10 +534,9 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
       }
       if (stamp && tid == 0) stamp[5] = gtimer();
       if (s + 1 < T) {
-        __threadfence();
-        fence_proxy_async();
+        fence_proxy_async();   // the peers read these stores through TMA
         __syncthreads();
-        if (tid == 0) signal_counter(dir_ctr);
+        if (tid == 0) signal_counter(dir_ctr);   // release at gpu scope, cumulative over the barrier
       }
       if (stamp && tid == 0) stamp[6] = gtimer();
       // dgx is only read after the kernel: written after the step is published.
