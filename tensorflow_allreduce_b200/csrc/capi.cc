@@ -277,6 +277,7 @@ int bc_allreduce_direct(int channel, const void* in, void* out, long long count,
 int bc_fused_step(int channel, void* grad, long long count, int dtype, void* param, float* master, float* s1, float* s2,
                   const bc_opt_hyper* h, float scale, void* wait_event, void* record_event) {
   API_BEGIN
+  NvtxRange range("bcoll.fused_step");
   gpu::Comm& c = comm();
   if (c.device_status() != 0) throw Error("an earlier device-side wait timed out; the communicator cannot be used any more");
   cudaStream_t s = c.stream(channel);
@@ -382,6 +383,7 @@ long long bc_gru_workspace_bytes(int T, int B, int H, int ndir) {
 int bc_gru_forward(int T, int B, int H, int ndir, const float* w_hh, const float* b_hh, const float* gx, float* y, float* rsv,
                    float* workspace, unsigned* sync, unsigned* status, double timeout_s, void* stream) {
   API_BEGIN
+  NvtxRange range("bcoll.gru_forward");
   gpu::GruDims d{T, B, H, ndir};
   check_cuda(gpu::gru_persistent_forward(d, w_hh, b_hh, gx, y, rsv, workspace, sync, status, timeout_s, (cudaStream_t)stream),
              "persistent GRU forward launch");
@@ -392,6 +394,7 @@ int bc_gru_forward(int T, int B, int H, int ndir, const float* w_hh, const float
 int bc_gru_backward(int T, int B, int H, int ndir, const float* w_hh_t, const float* y, const float* rsv, const float* dy,
                     float* dgx, float* dgh, float* workspace, unsigned* sync, unsigned* status, double timeout_s, void* stream) {
   API_BEGIN
+  NvtxRange range("bcoll.gru_backward");
   gpu::GruDims d{T, B, H, ndir};
   check_cuda(gpu::gru_persistent_backward(d, w_hh_t, y, rsv, dy, dgx, dgh, workspace, sync, status, timeout_s, (cudaStream_t)stream),
              "persistent GRU backward launch");

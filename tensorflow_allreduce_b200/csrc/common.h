@@ -94,6 +94,16 @@ inline double now_s() {
 int log_level();
 void log_line(int level, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
 
+// NVTX range for profilers (header-only NVTX 3: without an attached tool a push/pop is a load and
+// a branch). The reference relies on TensorFlow's tracing (direct_session.cc:538-566); here the
+// runtime marks negotiation, launches and the ring itself.
+struct NvtxRange {
+  explicit NvtxRange(const char* name);
+  ~NvtxRange();
+  NvtxRange(const NvtxRange&) = delete;
+  NvtxRange& operator=(const NvtxRange&) = delete;
+};
+
 #define BC_LOG(level, ...)                                   \
   do {                                                       \
     if (::bc::log_level() >= (level)) ::bc::log_line((level), __VA_ARGS__); \

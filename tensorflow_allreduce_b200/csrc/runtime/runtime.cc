@@ -475,6 +475,7 @@ void Runtime::perform(const Response& resp) {
   }
   rec->t_negotiated = now_s();
   BC_LOG(2, "perform '%s' type=%d", rec->name.c_str(), (int)resp.type);
+  NvtxRange range(resp.type == ResponseType::ALLGATHER ? "bcoll.allgather" : resp.type == ResponseType::ALLREDUCE ? "bcoll.allreduce" : "bcoll.control");
   try {
     switch (resp.type) {
       case ResponseType::ERROR:
