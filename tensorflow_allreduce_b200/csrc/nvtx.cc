@@ -12,7 +12,14 @@ namespace {
 bool enabled() {
   static const bool on = [] {
     const char* v = getenv("BC_NVTX");
-    return !(v && strcmp(v, "0") == 0);
+    const bool use = !(v && strcmp(v, "0") == 0);
+    if (use) {
+      // NVTX binds its entry points on first use; do that here, once, under the static
+      // initialiser's lock, instead of from whichever threads call first.
+      nvtxRangePushA("bcoll.init");
+      nvtxRangePop();
+    }
+    return use;
   }();
   return on;
 }
