@@ -89,6 +89,8 @@ void* bc_emu_create(int device, int nranks, long long bytes_per_rank);
 int bc_emu_destroy(void* g);
 void* bc_emu_buffer(void* g, int r);
 unsigned bc_emu_status(void* g);
+/* Guard regions surround every buffer and pad of the group; number of guard bytes overwritten. */
+long long bc_emu_damaged_guard_bytes(void* g);
 int bc_emu_allreduce(void* g, long long off, void* const* outs, long long count, int dtype, int algo, float scale, int idiv,
                      int blocks, void* stream, int reduce_op);
 int bc_emu_fused_step(void* g, long long off, long long count, int dtype, void* const* params, float* const* masters,

@@ -316,6 +316,12 @@ int bc_emu_destroy(void* g) { API_BEGIN delete (gpu::EmuGroup*)g; return 0; API_
 
 void* bc_emu_buffer(void* g, int r) { API_BEGIN return ((gpu::EmuGroup*)g)->buffer(r); API_END(nullptr) }
 
+long long bc_emu_damaged_guard_bytes(void* g) {
+  API_BEGIN
+  return (long long)((gpu::EmuGroup*)g)->damaged_guard_bytes();
+  API_END(-1)
+}
+
 unsigned bc_emu_status(void* g) { API_BEGIN return ((gpu::EmuGroup*)g)->status(); API_END(0u) }
 
 int bc_emu_allreduce(void* g, long long off, void* const* outs, long long count, int dtype, int algo, float scale, int idiv,

@@ -18,6 +18,8 @@ using namespace dev;
 namespace {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 constexpr size_t kMaxLaunchBytes = 512u << 20;
+constexpr size_t kGuardBytes = 4096;   // before and after every buffer of an emulated group
+constexpr int kGuardPattern = 0xA5;
 unsigned long long to_ns(double s) { return (unsigned long long)(s * 1e9); }
 }  // namespace
 
@@ -292,8 +294,13 @@ EmuGroup::EmuGroup(int device, int nranks, size_t bytes_per_rank) : device_(devi
   bufs_.assign(n_, nullptr);
   pads_.assign(n_, nullptr);
   for (int r = 0; r < n_; r++) {
-    CUDA_RT(cudaMalloc(&bufs_[r], bytes_));
-    CUDA_RT(cudaMalloc(&pads_[r], kPadBytes));
+    char* raw = nullptr;
+    CUDA_RT(cudaMalloc(&raw, bytes_ + 2 * kGuardBytes));
+    CUDA_RT(cudaMemset(raw, kGuardPattern, bytes_ + 2 * kGuardBytes));
+    bufs_[r] = raw + kGuardBytes;
+    CUDA_RT(cudaMalloc(&raw, kPadBytes + 2 * kGuardBytes));
+    CUDA_RT(cudaMemset(raw, kGuardPattern, kPadBytes + 2 * kGuardBytes));
+    pads_[r] = raw + kGuardBytes;
     CUDA_RT(cudaMemset(pads_[r], 0, kPadBytes));
   }
   CUDA_RT(cudaMalloc(&epochs_, sizeof(uint32_t) * n_ * kChannels * kMaxBlocks));
@@ -307,10 +314,28 @@ EmuGroup::EmuGroup(int device, int nranks, size_t bytes_per_rank) : device_(devi
 EmuGroup::~EmuGroup() {
   cudaSetDevice(device_);
   cudaDeviceSynchronize();
-  for (char* p : bufs_) if (p) cudaFree(p);
-  for (char* p : pads_) if (p) cudaFree(p);
+  for (char* p : bufs_) if (p) cudaFree(p - kGuardBytes);
+  for (char* p : pads_) if (p) cudaFree(p - kGuardBytes);
   if (epochs_) cudaFree(epochs_);
   if (status_host_) cudaFreeHost(status_host_);
+}
+
+size_t EmuGroup::damaged_guard_bytes() {
+  CUDA_RT(cudaSetDevice(device_));
+  CUDA_RT(cudaDeviceSynchronize());
+  std::vector<unsigned char> host(kGuardBytes);
+  size_t bad = 0;
+  auto check = [&](const char* dev) {
+    CUDA_RT(cudaMemcpy(host.data(), dev, kGuardBytes, cudaMemcpyDeviceToHost));
+    for (unsigned char c : host) bad += c != (unsigned char)kGuardPattern;
+  };
+  for (int r = 0; r < n_; r++) {
+    check(bufs_[r] - kGuardBytes);
+    check(bufs_[r] + bytes_);
+    check(pads_[r] - kGuardBytes);
+    check(pads_[r] + kPadBytes);
+  }
+  return bad;
 }
 
 RankCtx EmuGroup::ctx(int r, int channel) const {

@@ -112,6 +112,10 @@ class EmuGroup {
   size_t bytes_per_rank() const { return bytes_; }
   uint32_t status() const { return *(volatile uint32_t*)status_host_; }
   void clear_status() { *(volatile uint32_t*)status_host_ = 0; }
+  // Every buffer and signal pad sits between two guard regions filled with a byte pattern.
+  // Returns the number of guard bytes that no longer hold the pattern (0 = nothing wrote out of
+  // bounds). Synchronises the device.
+  size_t damaged_guard_bytes();
 
   // In-place-capable allreduce over ranks' buffers at `off`; outs[r] may equal the input.
   cudaError_t allreduce(size_t off, void* const* outs, size_t count, DType dtype, Algo algo, float scale, int idiv,
@@ -128,7 +132,7 @@ class EmuGroup {
   dev::RankCtx ctx(int r, int channel) const;
   int device_, n_;
   size_t bytes_;
-  std::vector<char*> bufs_;
+  std::vector<char*> bufs_;   // user-visible starts (allocation start + kGuardBytes)
   std::vector<char*> pads_;
   uint32_t* epochs_ = nullptr;  // [n][kChannels][kMaxBlocks]
   uint32_t* status_host_ = nullptr;

@@ -24,6 +24,7 @@ ALGOS = {"one_shot": 1, "two_shot": 2}
 def _check(rc, what):
     if rc is None or rc < 0:
         raise RuntimeError(f"{what}: {_lib.last_error()}")
+    return rc
 
 
 class EmulatedGroup:
@@ -56,6 +57,11 @@ class EmulatedGroup:
     @property
     def status(self) -> int:
         return int(self.lib.bc_emu_status(self._g))
+
+    def damaged_guard_bytes(self) -> int:
+        """Every rank's buffer and signal pad lies between guard regions; this counts guard bytes
+        that a kernel overwrote (0 = no out-of-bounds store). Synchronises the device."""
+        return int(_check(self.lib.bc_emu_damaged_guard_bytes(self._g), "guard check"))
 
     def max_blocks(self) -> int:
         return int(self.lib.bc_max_emulated_blocks(self.device, self.nranks))

@@ -49,8 +49,12 @@ def emu():
         return groups[key]
 
     yield get
+    # Guard regions around every emulated buffer and signal pad: no kernel of this module may
+    # have stored out of bounds (sizes 0 .. a few packs, odd tails, every dtype and algorithm).
+    damaged = {k: g.damaged_guard_bytes() for k, g in groups.items()}
     for g in groups.values():
         g.close()
+    assert all(v == 0 for v in damaged.values()), damaged
 
 
 @pytest.mark.parametrize("nranks", [2, 4, 8])
