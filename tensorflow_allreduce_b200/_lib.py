@@ -114,7 +114,10 @@ def lib():
             return _lib
         from . import build as _build
 
-        if os.environ.get("BC_NO_BUILD", "0") != "1" and _build.needs_build():
+        # BC_DEBUG_KERNELS=1 loads the bounds-checked build of the same sources.
+        debug = os.environ.get("BC_DEBUG_KERNELS", "0") == "1"
+        target = _build.LIB_DEBUG if debug else _build.LIB
+        if os.environ.get("BC_NO_BUILD", "0") != "1" and _build.needs_build(debug):
             # Several ranks may start at once: serialise the build through a lock file.
             import fcntl
 
@@ -122,13 +125,13 @@ def lib():
             with open(_build.LIBDIR / ".build.lock", "w") as lk:
                 fcntl.flock(lk, fcntl.LOCK_EX)
                 try:
-                    if _build.needs_build():
-                        _build.build()
+                    if _build.needs_build(debug):
+                        _build.build(debug=debug)
                 finally:
                     fcntl.flock(lk, fcntl.LOCK_UN)
-        if not _build.LIB.exists():
-            raise NativeError(f"native library missing: {_build.LIB}")
-        loaded = C.CDLL(str(_build.LIB), mode=C.RTLD_GLOBAL)
+        if not target.exists():
+            raise NativeError(f"native library missing: {target}")
+        loaded = C.CDLL(str(target), mode=C.RTLD_GLOBAL)
         _declare(loaded)
         _lib = loaded
     return _lib

@@ -22,6 +22,7 @@ CSRC = PKG / "csrc"
 LIBDIR = PKG / "lib"
 OBJDIR = LIBDIR / "obj"
 LIB = LIBDIR / "libbcoll.so"
+LIB_DEBUG = LIBDIR / "libbcoll_debug.so"   # same sources with -DBC_DEBUG: bounds-checked kernels
 
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 NVCC = os.environ.get("NVCC", str(Path(CUDA_HOME) / "bin" / "nvcc"))
@@ -43,9 +44,9 @@ def _headers_mtime() -> float:
     return max((h.stat().st_mtime for h in hs), default=0.0)
 
 
-def _obj_for(src: Path) -> Path:
+def _obj_for(src: Path, debug: bool = False) -> Path:
     rel = src.relative_to(CSRC)
-    return OBJDIR / ("_".join(rel.parts) + ".o")
+    return (LIBDIR / "obj_debug" if debug else OBJDIR) / ("_".join(rel.parts) + ".o")
 
 
 def _compile(src: Path, obj: Path, verbose: bool, extra: list[str]) -> None:
@@ -62,32 +63,36 @@ def _compile(src: Path, obj: Path, verbose: bool, extra: list[str]) -> None:
         print(r.stdout, r.stderr, flush=True)
 
 
-def needs_build() -> bool:
-    if not LIB.exists():
+def needs_build(debug: bool = False) -> bool:
+    lib = LIB_DEBUG if debug else LIB
+    if not lib.exists():
         return True
     cc, cu = _sources()
     newest = max([p.stat().st_mtime for p in cc + cu] + [_headers_mtime()])
-    return newest > LIB.stat().st_mtime
+    return newest > lib.stat().st_mtime
 
 
-def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
-    """Compile what changed and link the shared library. Returns its path."""
+def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, debug: bool = False) -> Path:
+    """Compile what changed and link the shared library. Returns its path. `debug=True` builds the
+    bounds-checked variant (`-DBC_DEBUG`, `lib/libbcoll_debug.so`) instead."""
     if shutil.which(NVCC) is None and not Path(NVCC).exists():
         raise RuntimeError(f"nvcc not found at {NVCC}; set CUDA_HOME or NVCC")
-    OBJDIR.mkdir(parents=True, exist_ok=True)
+    LIB = LIB_DEBUG if debug else globals()["LIB"]
+    (LIBDIR / "obj_debug" if debug else OBJDIR).mkdir(parents=True, exist_ok=True)
     cc, cu = _sources()
     hm = _headers_mtime()
     todo = []
     objs = []
     for src in cc + cu:
-        obj = _obj_for(src)
+        obj = _obj_for(src, debug)
         objs.append(obj)
         if force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hm):
             todo.append((src, obj))
-    extra_cu = ["-Xptxas", "-v"] if ptxas_info else []
+    extra_cu = (["-Xptxas", "-v"] if ptxas_info else []) + (["-DBC_DEBUG"] if debug else [])
+    extra_cc = ["-DBC_DEBUG"] if debug else []
     if todo:
         with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
-            futs = [ex.submit(_compile, s, o, verbose or ptxas_info, extra_cu if s.suffix == ".cu" else []) for s, o in todo]
+            futs = [ex.submit(_compile, s, o, verbose or ptxas_info, extra_cu if s.suffix == ".cu" else extra_cc) for s, o in todo]
             for f in futs:
                 f.result()
     if todo or not LIB.exists() or force:
@@ -155,5 +160,5 @@ def build_selftest(sanitizer: str = "thread", verbose: bool = False) -> Path:
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv, ptxas_info="--ptxas" in sys.argv)
+    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv, ptxas_info="--ptxas" in sys.argv, debug="--debug" in sys.argv)
     print(path)

@@ -141,6 +141,17 @@ __global__ void __launch_bounds__(512) allgatherv_kernel(const __grid_constant__
 
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t nthreads = (size_t)gridDim.x * blockDim.x;
+  {
+    unsigned long long total = 0;
+    for (int q = 0; q < P; q++) total += s_bytes[q];
+    bool fits = true;
+    for (int q = 0; q < P; q++) fits = fits && (R.capacity == 0 || s_off[q] + total <= R.capacity);
+    if (!in_bounds(c, fits)) {   // bounds-checked builds: refuse to store past a segment
+      if (P > 1) peer_barrier(c, epoch);
+      store_epoch(c, epoch);
+      return;
+    }
+  }
   bool multicast = R.mc_base != nullptr;
   for (int q = 1; q < P; q++) multicast = multicast && s_off[q] == s_off[0];
   multicast = multicast && ((((uintptr_t)R.in) | (s_off[0] + disp) | R.bytes) & 3) == 0;

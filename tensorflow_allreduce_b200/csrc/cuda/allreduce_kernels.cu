@@ -94,7 +94,7 @@ __device__ __forceinline__ float opt_step(float p, float g, float* s1, float* s2
 // at compile time (0: use the run-time P); U packs are fetched together so that U*P 16-byte
 // loads per thread are in flight across NVLink. `sink(i, acc)` consumes each reduced pack.
 template <typename T, int PP, int U, bool GEN, typename Sink>
-__device__ __forceinline__ void reduce_range(const ArRank& R, int P, size_t begin, size_t end, size_t first, size_t stride, int red, Sink sink) {
+__device__ __forceinline__ void reduce_range(const ArRank& R, int P, size_t begin, size_t end, size_t first, size_t stride, size_t limit, int red, Sink sink) {
   using PK = Pack<T>;
   constexpr int N = PP > 0 ? PP : kMaxRanks;
   for (size_t i0 = begin + first; i0 < end; i0 += stride * U) {
@@ -102,7 +102,7 @@ __device__ __forceinline__ void reduce_range(const ArRank& R, int P, size_t begi
 #pragma unroll
     for (int u = 0; u < U; u++) {
       const size_t i = i0 + (size_t)u * stride;
-      if (i < end) {
+      if (i < end && in_bounds(R.ctx, i < limit)) {
 #pragma unroll
         for (int p = 0; p < N; p++)
           if (PP > 0 || p < P) v[u][p] = ld_stream16(R.in[p] + i * 16);
@@ -111,7 +111,7 @@ __device__ __forceinline__ void reduce_range(const ArRank& R, int P, size_t begi
 #pragma unroll
     for (int u = 0; u < U; u++) {
       const size_t i = i0 + (size_t)u * stride;
-      if (i < end) {
+      if (i < end && in_bounds(R.ctx, i < limit)) {
         typename PK::Acc acc[PK::kElems];
         PK::unpack(v[u][0], acc);
 #pragma unroll
@@ -130,12 +130,12 @@ __device__ __forceinline__ void reduce_range(const ArRank& R, int P, size_t begi
 }
 
 template <typename T, bool GEN, typename Sink>
-__device__ __forceinline__ void reduce_range_any(const ArRank& R, int P, size_t begin, size_t end, size_t first, size_t stride, int red, Sink sink) {
+__device__ __forceinline__ void reduce_range_any(const ArRank& R, int P, size_t begin, size_t end, size_t first, size_t stride, size_t limit, int red, Sink sink) {
   switch (P) {
-    case 2: reduce_range<T, 2, 4, GEN>(R, P, begin, end, first, stride, red, sink); break;
-    case 4: reduce_range<T, 4, 2, GEN>(R, P, begin, end, first, stride, red, sink); break;
-    case 8: reduce_range<T, 8, 1, GEN>(R, P, begin, end, first, stride, red, sink); break;
-    default: reduce_range<T, 0, 1, GEN>(R, P, begin, end, first, stride, red, sink); break;
+    case 2: reduce_range<T, 2, 4, GEN>(R, P, begin, end, first, stride, limit, red, sink); break;
+    case 4: reduce_range<T, 4, 2, GEN>(R, P, begin, end, first, stride, limit, red, sink); break;
+    case 8: reduce_range<T, 8, 1, GEN>(R, P, begin, end, first, stride, limit, red, sink); break;
+    default: reduce_range<T, 0, 1, GEN>(R, P, begin, end, first, stride, limit, red, sink); break;
   }
 }
 
@@ -261,7 +261,7 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
   if (!peer_barrier(c, epoch)) { store_epoch(c, epoch); return; }
 
   if constexpr (ALGO == ALGO_ONE) {
-    reduce_range_any<T, OPT == OPT_RED>(R, P, 0, npacks, first, stride, a.red, [&](size_t i, Acc* acc) {
+    reduce_range_any<T, OPT == OPT_RED>(R, P, 0, npacks, first, stride, npacks, a.red, [&](size_t i, Acc* acc) {
 #pragma unroll
       for (int e = 0; e < E; e++) acc[e] = finish<Acc>(acc[e], a.scale, a.idiv);
       epilogue_pack<T, OPT>(R, a, i, acc, me);
@@ -284,12 +284,12 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
 #pragma unroll
         for (int u = 0; u < kNvlsUnroll; u++) {
           const size_t i = i0 + (size_t)u * stride;
-          if (i < send) r[u] = nvls_reduce<T>(R.mc_in + i * 16);
+          if (i < send && in_bounds(c, i < npacks)) r[u] = nvls_reduce<T>(R.mc_in + i * 16);
         }
 #pragma unroll
         for (int u = 0; u < kNvlsUnroll; u++) {
           const size_t i = i0 + (size_t)u * stride;
-          if (i < send) {
+          if (i < send && in_bounds(c, i < npacks)) {
             if (a.scale != 1.f) {
               Acc acc[E];
               PK::unpack(r[u], acc);
@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
         }
       }
     } else {
-      reduce_range_any<T, OPT == OPT_RED>(R, P, sbeg, send, first, stride, a.red, [&](size_t i, Acc* acc) {
+      reduce_range_any<T, OPT == OPT_RED>(R, P, sbeg, send, first, stride, npacks, a.red, [&](size_t i, Acc* acc) {
 #pragma unroll
         for (int e = 0; e < E; e++) acc[e] = finish<Acc>(acc[e], a.scale, a.idiv);
         const uint4 r = PK::pack(acc);
@@ -328,6 +328,7 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
       for (int q = 0; q < P; q++) {
         const size_t qb = npacks * (size_t)q / P, qe = npacks * (size_t)(q + 1) / P;
         for (size_t i = qb + first; i < qe; i += stride) {
+          if (!in_bounds(c, i < npacks)) continue;
           Acc acc[E];
           PK::unpack(ld_local16(R.in[me] + i * 16), acc);
           epilogue_pack<T, OPT>(R, a, i, acc, me);

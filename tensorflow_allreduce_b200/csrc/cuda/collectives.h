@@ -86,6 +86,7 @@ struct AgRank {
   char* mc_base;              // multicast mapping of the same segment (NVLS), or null: P2P stores only
   unsigned long long out_off; // where this rank's output starts inside its own segment
   unsigned long long* sizes_out;  // optional local array [world]: every rank's slab size in bytes
+  unsigned long long capacity;    // bytes available from every rank's segment base (0 = unknown); bounds-checked builds only
 };
 
 struct AgArgs {

@@ -191,6 +191,7 @@ void Comm::allgatherv(int channel, const void* in, size_t bytes, void* out_symm,
   r.ctx = make_ctx(channel);
   r.sizes_out = sizes_out;
   for (int p = 0; p < world_; p++) r.base[p] = seg0_->peer[p];
+  r.capacity = seg0_->size;
   // With two ranks the multicast store saves nothing (one peer either way).
   r.mc_base = (cfg_.use_nvls && seg0_->mc && world_ >= 3) ? seg0_->mc : nullptr;
   LaunchCfg cfg;
@@ -410,6 +411,7 @@ cudaError_t EmuGroup::allgatherv(const void* const* ins, const unsigned long lon
     a.r[r].in = (const char*)ins[r];
     a.r[r].bytes = bytes[r];
     a.r[r].out_off = out_offs[r];
+    a.r[r].capacity = bytes_;
     for (int p = 0; p < n_; p++) a.r[r].base[p] = bufs_[p];
   }
   LaunchCfg cfg;

@@ -109,6 +109,21 @@ __device__ __forceinline__ bool peer_barrier(const RankCtx& c, uint32_t& epoch) 
   return __syncthreads_and(ok) != 0;
 }
 
+// Bounds-checked builds (-DBC_DEBUG, `build.build(debug=True)` -> lib/libbcoll_debug.so, loaded
+// when BC_DEBUG_KERNELS=1): every pack index and every allgather destination range is tested
+// before the access; a violation sets kStatusBounds in the status word and the access is
+// skipped. In normal builds the test folds to `true`.
+__device__ __forceinline__ bool in_bounds(const RankCtx& c, bool ok) {
+#ifdef BC_DEBUG
+  if (!ok) atomicOr(c.status, kStatusBounds | ((uint32_t)c.rank << 8));
+  return ok;
+#else
+  (void)c;
+  (void)ok;
+  return true;
+#endif
+}
+
 __device__ __forceinline__ uint32_t load_epoch(const RankCtx& c) { return c.epochs[blockIdx.x]; }
 __device__ __forceinline__ void store_epoch(const RankCtx& c, uint32_t epoch) {
   if (threadIdx.x == 0) c.epochs[blockIdx.x] = epoch;

@@ -21,6 +21,9 @@ constexpr size_t kPadBytes = kChannels * kChannelBytes;                         
 
 // Status word written by a block whose wait ran out (host-mapped memory).
 constexpr uint32_t kStatusTimeout = 0x80000000u;
+// Status bit written by a bounds-checked build (-DBC_DEBUG) when an index left its tensor; the
+// access is skipped, nothing traps.
+constexpr uint32_t kStatusBounds = 0x40000000u;
 
 // What one (real or emulated) rank needs to synchronise with its peers on one channel.
 struct RankCtx {
