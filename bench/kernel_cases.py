@@ -3,6 +3,7 @@
     python bench/kernel_cases.py --case fused_sgd        [--mb 256] [--iters 10]
     python bench/kernel_cases.py --case fused_adamw_bf16
     python bench/kernel_cases.py --case emu_allreduce    (8 emulated ranks on one GPU, two-shot, fp32)
+    python bench/kernel_cases.py --case emu_one_shot --kb 256   (8 emulated ranks, one-shot, small message)
     python bench/kernel_cases.py --case emu_allgatherv
     python bench/kernel_cases.py --case gru [--T 350]    (one bidirectional GRU layer 2048 -> 1024, batch 32: persistent kernels vs cuDNN)
 
@@ -46,11 +47,12 @@ def timed(fn, iters):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", required=True, choices=["fused_sgd", "fused_adamw_bf16", "emu_allreduce", "emu_allgatherv", "gru"])
+    ap.add_argument("--case", required=True, choices=["fused_sgd", "fused_adamw_bf16", "emu_allreduce", "emu_one_shot", "emu_allgatherv", "gru"])
     ap.add_argument("--mb", type=int, default=256, help="gradient / message size in MiB")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--blocks", type=int, default=0)
     ap.add_argument("--T", type=int, default=350, help="gru: time steps")
+    ap.add_argument("--kb", type=int, default=256, help="emu_one_shot: message size in KiB")
     a = ap.parse_args()
     torch.cuda.set_device(0)
     hbm, src = peak_hbm()
@@ -129,7 +131,16 @@ def main():
         per_rank = max(a.mb, 8) << 20
         g = EmulatedGroup(P, per_rank)
         blocks = a.blocks or g.max_blocks()
-        if a.case == "emu_allreduce":
+        if a.case == "emu_one_shot":
+            n = (a.kb << 10) // 4
+            for r in range(P):
+                g.buffer(r, torch.float32, n).fill_(float(r))
+            outs = [torch.empty(n, device="cuda") for _ in range(P)]
+            blocks = a.blocks or max(1, min(blocks, (a.kb + 31) // 32))
+            ms = timed(lambda: g.allreduce(n, torch.float32, "one_shot", outs=outs, blocks=blocks, scale=1.0 / P), a.iters)
+            nbytes = P * (P * n * 4 + n * 4)     # every rank reads all P copies and writes one result
+            out.update(ms=ms, bytes=nbytes, gbs=nbytes / ms / 1e6, blocks=blocks, ok=bool(g.status == 0 and float(outs[3][5]) == 3.5))
+        elif a.case == "emu_allreduce":
             n = (a.mb << 20) // 4
             for r in range(P):
                 g.buffer(r, torch.float32, n).fill_(float(r))
