@@ -52,7 +52,7 @@ constexpr int kXTileBytes = kBatchTile * 128;                    // 4 KiB
 constexpr int kComputeThreads = 128;   // four warps: accumulator read-back, exchange, gate math
 constexpr int kThreads = 160;          // plus one warp whose first thread issues copies and MMAs
 constexpr int kMaxBlocksPerDir = 64;   // H / 16 at H = 1024
-constexpr int kGStride = 33;          // padded row of the accumulator copy in shared memory
+constexpr int kGStride = 33;          // forward: padded row of the summed partial sums in shared memory
 constexpr int kMmaM = 64;            // the tensor core spends about one clock per accumulator row whatever N is (measured)
 
 struct Params {
@@ -297,7 +297,11 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
   // tile must still be inside the allocation (it is the weight area).
   uint8_t* x_s = smem;
   uint8_t* w_s = smem + 2 * kStageBytes;
-  float* g_s = reinterpret_cast<float*>(x_s) + nrows * 32;   // summed partial sums of the block's rows; with t_s below it aliases the stages between products
+  // Summed partial sums of the block's own rows. Forward: a padded tile behind t_s. Backward: in
+  // place over the block's own tile inside t_s (the accumulator of a group of 16 fills the whole
+  // stage area; the few reads of it tolerate the bank conflicts of the unpadded rows).
+  constexpr int kGs = BWD ? 32 : kGStride;
+  float* g_s = BWD ? reinterpret_cast<float*>(x_s) + q * (kRows * 32) : reinterpret_cast<float*>(x_s) + nrows * 32;
   uint64_t* bar_s = reinterpret_cast<uint64_t*>(w_s + (size_t)ntiles * w_tile);   // full[2], -, -, done, weights
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_s + 6);
   volatile int* abort_s = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -366,10 +370,9 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
   uint32_t* grp_ctr = p.sync + 8 + dir * kMaxBlocksPerDir + grp;   // one arrival per member and product
   BwdInputs pre;
   uint32_t products = 0;
-  constexpr int kMaxC = BWD ? 8 : 4;
+  constexpr int kMaxC = BWD ? 16 : 4;
   constexpr int kTile4 = kRows * 8;                    // float4 words of one owner's tile (kRows x 32)
   float* t_s = reinterpret_cast<float*>(x_s);          // the block's whole accumulator, [nrows][32]
-  // g_s: the C partial sums of the block's own rows added up, [kRows][kGStride]
 
   // Exchange after a product. (1) The accumulator goes to shared memory: rows 16w .. 16w+15 of the
   // M = 64 accumulator live in lanes 0-15 of the TMEM quarter that warp w may read, so threads
@@ -432,7 +435,7 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
 #pragma unroll
         for (int m = 0; m < kMaxC; m++) { acc.x += part[m].x; acc.y += part[m].y; acc.z += part[m].z; acc.w += part[m].w; }
         const int j = w4 >> 3, b0 = (w4 & 7) * 4;
-        float* g = g_s + j * kGStride + b0;
+        float* g = g_s + j * kGs + b0;
         g[0] = acc.x; g[1] = acc.y; g[2] = acc.z; g[3] = acc.w;
       }
     }
@@ -482,9 +485,9 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
         if (b < B) {
           float hr = bias_r, hz = bias_z, hn = bias_n;
           if (s > 0) {
-            hr += g_s[u * kGStride + b];
-            hz += g_s[(kUnits + u) * kGStride + b];
-            hn += g_s[(2 * kUnits + u) * kGStride + b];
+            hr += g_s[u * kGs + b];
+            hz += g_s[(kUnits + u) * kGs + b];
+            hn += g_s[(2 * kUnits + u) * kGs + b];
           }
           const float r = sigmoidf_(gxr[j] + hr);
           const float z = sigmoidf_(gxz[j] + hz);
@@ -570,7 +573,7 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
 #pragma unroll
         for (int j = 0; j < 4; j++) {
           const int b = bq + 8 * j;
-          carry[j] = b < B ? keep[j] + g_s[u * kGStride + b] : 0.f;
+          carry[j] = b < B ? keep[j] + g_s[u * kGs + b] : 0.f;
         }
         __syncthreads();   // g_s (stage 0) is overwritten by the next product's first copy
       }
@@ -644,7 +647,7 @@ bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 int choose_split(const GruDims& d, bool bwd) {
   const int blocks = d.H / kUnits, kdim = bwd ? 3 * d.H : d.H, rows = bwd ? kUnits : 3 * kUnits;
   for (int c : {16, 8, 4, 2, 1}) {
-    if (c > (bwd ? 8 : 4)) continue;
+    if (c > (bwd ? 16 : 4)) continue;
     if (rows * c > 256 || blocks % c != 0 || kdim % (c * kKTile) != 0) continue;
     return c;
   }
