@@ -2,7 +2,7 @@
 //
 // Work split. Direction d of a layer is run by H/16 blocks (grid.y = direction); block c owns
 // the hidden units [16c, 16c+16) and produces their outputs. For the recurrent product the blocks
-// work in groups of C (4 forward, 8 backward at H = 1024) that split the reduction length K among
+// work in groups of C (4 forward, 16 backward at H = 1024) that split the reduction length K among
 // themselves: block q of a group keeps, for ALL units of its group, the weight columns of its K
 // range in shared memory for the whole sequence (forward 48C rows x H/C columns, backward 16C
 // rows x 3H/C columns: 192 KiB of fp32 at H = 1024 either way). Each time step it
@@ -52,7 +52,6 @@ constexpr int kXTileBytes = kBatchTile * 128;                    // 4 KiB
 constexpr int kComputeThreads = 128;   // four warps: accumulator read-back, exchange, gate math
 constexpr int kThreads = 160;          // plus one warp whose first thread issues copies and MMAs
 constexpr int kMaxBlocksPerDir = 64;   // H / 16 at H = 1024
-constexpr int kGStride = 33;          // forward: padded row of the summed partial sums in shared memory
 constexpr int kMmaM = 64;            // the tensor core spends about one clock per accumulator row whatever N is (measured)
 
 struct Params {
@@ -297,11 +296,6 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
   // tile must still be inside the allocation (it is the weight area).
   uint8_t* x_s = smem;
   uint8_t* w_s = smem + 2 * kStageBytes;
-  // Summed partial sums of the block's own rows. Forward: a padded tile behind t_s. Backward: in
-  // place over the block's own tile inside t_s (the accumulator of a group of 16 fills the whole
-  // stage area; the few reads of it tolerate the bank conflicts of the unpadded rows).
-  constexpr int kGs = BWD ? 32 : kGStride;
-  float* g_s = BWD ? reinterpret_cast<float*>(x_s) + q * (kRows * 32) : reinterpret_cast<float*>(x_s) + nrows * 32;
   uint64_t* bar_s = reinterpret_cast<uint64_t*>(w_s + (size_t)ntiles * w_tile);   // full[2], -, -, done, weights
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_s + 6);
   volatile int* abort_s = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -363,7 +357,7 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
     bias_n = p.b_hh[dir * 3 * H + 2 * H + u0 + u];
   }
   uint32_t* dir_ctr = p.sync + dir;                                 // one arrival per block and published step
-  // Partial sums travel through global memory: xchg[dir][group][owner][source][kRows][batch 32].
+  // Partial sums travel through global memory: xchg[dir][group][owner][source][batch 32][kRows].
   // A tile is rewritten only after the direction's step barrier, which every reader passes after
   // it has consumed the previous contents.
   float* xg = p.xchg + ((size_t)(dir * (nblocks / C) + grp) * C) * C * (32 * kRows);
@@ -371,14 +365,21 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
   BwdInputs pre;
   uint32_t products = 0;
   constexpr int kMaxC = BWD ? 16 : 4;
-  constexpr int kTile4 = kRows * 8;                    // float4 words of one owner's tile (kRows x 32)
-  float* t_s = reinterpret_cast<float*>(x_s);          // the block's whole accumulator, [nrows][32]
+  // The block's whole accumulator in shared memory, one row of nrows floats per batch entry (it
+  // aliases the stages between products). 16-byte slot n/4 of row b sits at slot (n/4) ^ (b & swz),
+  // so that the 16 threads that write one slot of 16 different rows at a time hit all banks.
+  float* t_s = reinterpret_cast<float*>(x_s);
+  float4* t4 = reinterpret_cast<float4*>(x_s);
+  const int row4 = nrows / 4;                          // 16-byte slots per row
+  const int swz = (nrows % 32 == 0) ? 7 : 0;
+  constexpr int kRows4 = kRows / 4;
 
   // Exchange after a product. (1) The accumulator goes to shared memory: rows 16w .. 16w+15 of the
   // M = 64 accumulator live in lanes 0-15 of the TMEM quarter that warp w may read, so threads
-  // (w < 2, lane < 16) hold batch entry 16w + lane. (2) Every member's tile is copied to that
-  // member's place in global memory with coalesced 16-byte stores. (3) The group meets (fence,
-  // counter). (4) The block adds the tiles it received to its own and leaves the sum in g_s.
+  // (w < 2, lane < 16) hold batch entry 16w + lane and write 32 consecutive columns as eight
+  // 16-byte stores. (2) Every member's columns are copied, as a [32][kRows] tile, to that member's
+  // place in global memory with coalesced 16-byte stores. (3) The group meets (one release,
+  // counter). (4) The block adds the tiles it received to its own columns, in place.
   // Returns false if the group did not arrive in time.
   auto exchange = [&]() {
     if (warp < 2) {
@@ -392,23 +393,27 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
         if (two) tc_ld32_issue(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c0 + 32), w);
         tc_ld_wait();
         if (lane < 16) {
+          float4* row = t4 + b * row4;
 #pragma unroll
-          for (int i = 0; i < 32; i++)
-            if (c0 + i < nrows) t_s[(c0 + i) * 32 + b] = v[i];
+          for (int k = 0; k < 8; k++)
+            if (c0 + 4 * k < nrows) row[((c0 >> 2) + k) ^ (b & swz)] = make_float4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
           if (two) {
 #pragma unroll
-            for (int i = 0; i < 32; i++)
-              if (c0 + 32 + i < nrows) t_s[(c0 + 32 + i) * 32 + b] = w[i];
+            for (int k = 0; k < 8; k++)
+              if (c0 + 32 + 4 * k < nrows) row[((c0 >> 2) + 8 + k) ^ (b & swz)] = make_float4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
           }
         }
       }
     }
     tc_fence_before();
     __syncthreads();
-    const float4* t4 = reinterpret_cast<const float4*>(t_s);
+    constexpr int kTile4 = 32 * kRows4;                // 16-byte words of one member's tile
     for (int idx = tid; idx < C * kTile4; idx += kThreads) {
       const int owner = idx / kTile4, w4 = idx - owner * kTile4;
-      if (owner != q) __stcg(reinterpret_cast<float4*>(xg + (size_t)(owner * C + q) * (32 * kRows)) + w4, t4[idx]);
+      if (owner != q) {
+        const int b = w4 / kRows4, j4 = w4 - b * kRows4;
+        __stcg(reinterpret_cast<float4*>(xg + (size_t)(owner * C + q) * (32 * kRows)) + w4, t4[b * row4 + ((owner * kRows4 + j4) ^ (b & swz))]);
+      }
     }
     products += 1;
     bool good = true;
@@ -431,16 +436,21 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
           part[m] = make_float4(0.f, 0.f, 0.f, 0.f);
           if (m < C && m != q) part[m] = __ldcg(reinterpret_cast<const float4*>(xg + (size_t)(q * C + m) * (32 * kRows)) + w4);
         }
-        float4 acc = t4[q * kTile4 + w4];
+        const int b = w4 / kRows4, j4 = w4 - b * kRows4;
+        float4* own = t4 + b * row4 + ((q * kRows4 + j4) ^ (b & swz));
+        float4 acc = *own;
 #pragma unroll
         for (int m = 0; m < kMaxC; m++) { acc.x += part[m].x; acc.y += part[m].y; acc.z += part[m].z; acc.w += part[m].w; }
-        const int j = w4 >> 3, b0 = (w4 & 7) * 4;
-        float* g = g_s + j * kGs + b0;
-        g[0] = acc.x; g[1] = acc.y; g[2] = acc.z; g[3] = acc.w;
+        *own = acc;
       }
     }
     __syncthreads();
     return good;
+  };
+  // Summed pre-activation (forward: gate g) of unit u0 + u for batch entry b, after exchange().
+  auto summed = [&](int g, int b) {
+    const int n = q * kRows + g * kUnits + u;
+    return t_s[(b * row4 + ((n >> 2) ^ (b & swz))) * 4 + (n & 3)];
   };
 
   for (int s = 0; ok && s < T; s++) {
@@ -485,9 +495,9 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
         if (b < B) {
           float hr = bias_r, hz = bias_z, hn = bias_n;
           if (s > 0) {
-            hr += g_s[u * kGs + b];
-            hz += g_s[(kUnits + u) * kGs + b];
-            hn += g_s[(2 * kUnits + u) * kGs + b];
+            hr += summed(0, b);
+            hz += summed(1, b);
+            hn += summed(2, b);
           }
           const float r = sigmoidf_(gxr[j] + hr);
           const float z = sigmoidf_(gxz[j] + hz);
@@ -573,9 +583,9 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
 #pragma unroll
         for (int j = 0; j < 4; j++) {
           const int b = bq + 8 * j;
-          carry[j] = b < B ? keep[j] + g_s[u * kGs + b] : 0.f;
+          carry[j] = b < B ? keep[j] + summed(0, b) : 0.f;
         }
-        __syncthreads();   // g_s (stage 0) is overwritten by the next product's first copy
+        __syncthreads();   // the summed tile lives in the stage area, which the next product's first copy overwrites
       }
     }
   }
