@@ -40,7 +40,7 @@ __device__ __forceinline__ A combine(A a, A b, int red) {
     default: return a + b;
   }
 }
-constexpr int kNvlsUnroll = 8;
+constexpr int kNvlsUnroll = 4;   // packs per batch; two batches are in flight per thread
 
 template <typename T> struct Scalar;  // scalar load/store in the accumulator type
 template <> struct Scalar<float> { using Acc = float; __device__ static Acc ld(const float* p) { return *p; } __device__ static void st(float* p, Acc v) { *p = v; } };
@@ -277,15 +277,20 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
     // Phase 1: reduce this rank's slice and store the result into every rank's buffer.
     const size_t sbeg = npacks * (size_t)me / P, send = npacks * (size_t)(me + 1) / P;
     if constexpr (ALGO == ALGO_NVLS && IsFloatGrad<T>::value) {
-      // kNvlsUnroll switch-side reductions are in flight per thread before the first result is
-      // used; a single one per thread leaves the links mostly idle.
-      for (size_t i0 = sbeg + first; i0 < send; i0 += stride * kNvlsUnroll) {
-        uint4 r[kNvlsUnroll];
+      // Software pipeline of batches of kNvlsUnroll packs: the reductions of batch k+1 are issued
+      // before the stores of batch k. The reduction keeps this GPU's outbound links busy (every
+      // peer's share of the slice travels to the switch), the multicast store its inbound links;
+      // issued back to back by all threads, the two directions would take turns instead of
+      // running together, which halves the speed of messages with only one or two batches per
+      // thread (tens of MiB).
+      auto load_batch = [&](size_t i0, uint4* r) {
 #pragma unroll
         for (int u = 0; u < kNvlsUnroll; u++) {
           const size_t i = i0 + (size_t)u * stride;
           if (i < send && in_bounds(c, i < npacks)) r[u] = nvls_reduce<T>(R.mc_in + i * 16);
         }
+      };
+      auto store_batch = [&](size_t i0, uint4* r) {
 #pragma unroll
         for (int u = 0; u < kNvlsUnroll; u++) {
           const size_t i = i0 + (size_t)u * stride;
@@ -300,6 +305,20 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
             multimem_st16(R.mc_in + i * 16, r[u]);
           }
         }
+      };
+      const size_t step = stride * kNvlsUnroll;
+      uint4 ra[kNvlsUnroll], rb[kNvlsUnroll];
+      size_t i0 = sbeg + first;
+      if (i0 < send) load_batch(i0, ra);
+      while (i0 < send) {
+        const size_t i1 = i0 + step;
+        if (i1 < send) load_batch(i1, rb);
+        store_batch(i0, ra);
+        if (i1 >= send) break;
+        const size_t i2 = i1 + step;
+        if (i2 < send) load_batch(i2, ra);
+        store_batch(i1, rb);
+        i0 = i2;
       }
     } else {
       reduce_range_any<T, OPT == OPT_RED>(R, P, sbeg, send, first, stride, npacks, a.red, [&](size_t i, Acc* acc) {

@@ -81,7 +81,7 @@ bc.shutdown()
 
 
 @pytest.mark.parametrize("world", _worlds())
-@pytest.mark.parametrize("env", [{}, {"BC_ALGO": "two_shot"}, {"BC_NVLS": "0"}, {"BC_SYMM": "ipc"}])
+@pytest.mark.parametrize("env", [{}, {"BC_ALGO": "two_shot"}, {"BC_NVLS": "0"}, {"BC_SYMM": "ipc"}, {"BC_ALGO": "nvls"}])
 def test_collectives_across_gpus(world, env):
     res = run(COLLECTIVES, nranks=world, gpus=True, timeout=300, env=env)
     for _, rec in res:
@@ -186,6 +186,17 @@ def test_data_parallel_equals_large_batch(world, opt):
         assert rec["identical"], "ranks diverged"
         assert rec["fused"] == (opt != "rmsprop")
         assert rec["buckets"] > 1
+
+
+@pytest.mark.parametrize("opt", ["sgd", "adamw"])
+def test_fused_update_over_nvls(opt):
+    # The switch-side reduction forced for every bucket (it is the default only from 4 ranks and
+    # 512 KiB on): same equivalence with the single-process large-batch run.
+    res = run(TRAIN, nranks=2, gpus=True, timeout=300, env={"TEST_OPT": opt, "BC_ALGO": "nvls"})
+    for _, rec in res:
+        assert rec["worst"] < 2e-5, rec
+        assert rec["identical"], "ranks diverged"
+        assert rec["fused"]
 
 
 def test_dependent_allreduce_stress():
