@@ -243,7 +243,7 @@ def main():
                        "grad_buckets": len(getattr(opt, "buckets", [])), "fused_update": bool(getattr(opt, "fused", False)),
                        "rnn": ("persistent tcgen05 kernels" if persistent else "cudnn") if a.model == "ds2" else None},
             "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"), "reasons": clocks.get("reasons", []),
-                       "power_w_max": clocks.get("power_w_max"), "samples": clocks.get("samples")},
+                       "power_w_max": clocks.get("power_w_max"), "samples": clocks.get("samples"), "source": clocks.get("source")},
             "gpu_launches": launches,
             "final_loss": final_loss,
         }

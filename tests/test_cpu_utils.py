@@ -1,0 +1,46 @@
+"""Utilities that need no GPU: the clock sampler against a fake NVML, the timeline export."""
+import sys
+import time
+import types
+
+
+def test_clock_sampler_reads_nvml(monkeypatch):
+    fake = types.ModuleType("pynvml")
+    fake.NVML_CLOCK_SM = 1
+    calls = {"n": 0}
+    fake.nvmlInit = lambda: None
+    fake.nvmlDeviceGetHandleByIndex = lambda i: ("handle", i)
+    fake.nvmlDeviceGetMaxClockInfo = lambda h, k: 1965
+
+    def clock(h, k):
+        calls["n"] += 1
+        return 1200 + 10 * (calls["n"] % 3)
+
+    fake.nvmlDeviceGetClockInfo = clock
+    fake.nvmlDeviceGetPowerUsage = lambda h: 950000
+    fake.nvmlDeviceGetCurrentClocksEventReasons = lambda h: 0x4        # sw_power_cap only
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "3,5")
+    from tensorflow_allreduce_b200.utils.clocks import ClockSampler
+
+    with ClockSampler(1, nvml_period_ms=5) as c:
+        time.sleep(0.1)
+    s = c.summary()
+    assert c.source == "nvml" and s["source"] == "nvml"
+    assert s["samples"] >= 5 and s["sm_max_mhz"] == 1965 and 1200 <= s["sm_mhz"] <= 1220
+    assert s["reasons"] == ["sw_power_cap"] and abs(s["power_w_max"] - 950.0) < 1e-6
+    assert c.samples[0][0] == "5"                                       # CUDA ordinal 1 -> NVML index 5
+
+
+def test_timeline_export():
+    from tensorflow_allreduce_b200.utils import timeline
+
+    recs = [{"name": "a", "op": "allreduce", "algo": "nvls", "blocks": 64, "bytes": 1 << 20, "device": 1,
+             "t_enqueue": 1.0, "t_negotiated": 1.0002, "t_done": 1.0003},
+            {"name": "b", "op": "allgather", "algo": "cpu_ring", "blocks": 0, "bytes": 100, "device": 0,
+             "t_enqueue": 1.001, "t_negotiated": 1.0012, "t_done": 1.002}]
+    ev = timeline.chrome_trace(recs, pid=0)
+    assert len(ev) == 4 and ev[0]["cat"] == "allreduce.negotiate" and ev[1]["cat"] == "allreduce.launch" and ev[3]["cat"] == "allgather.run"
+    assert abs(ev[0]["dur"] - 200.0) < 1e-3
+    s = timeline.summary(recs)
+    assert s["allreduce/nvls"]["calls"] == 1 and s["allgather/cpu_ring"]["bytes"] == 100
