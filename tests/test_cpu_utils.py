@@ -44,3 +44,27 @@ def test_timeline_export():
     assert abs(ev[0]["dur"] - 200.0) < 1e-3
     s = timeline.summary(recs)
     assert s["allreduce/nvls"]["calls"] == 1 and s["allgather/cpu_ring"]["bytes"] == 100
+
+
+def test_launcher_starts_ranks_and_propagates_failure(tmp_path):
+    import os
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "job.py"
+    script.write_text(
+        "import os, sys\n"
+        f"sys.path.insert(0, {root!r})\n"
+        "import torch, tensorflow_allreduce_b200 as bc\n"
+        "with bc.Session(device='cpu'):\n"
+        "    s = bc.allreduce(torch.tensor([float(bc.rank() + 1)]), average=False)\n"
+        "    me = bc.rank()\n"
+        "    print('SUM', me, bc.size(), bc.local_rank(), s.item(), flush=True)\n"
+        "sys.exit(int(sys.argv[1]) if me == 1 else 0)\n")
+    cmd = [sys.executable, "-m", "tensorflow_allreduce_b200.launch", "--nproc", "3", "--cpu", str(script)]
+    ok = subprocess.run(cmd + ["0"], cwd=root, capture_output=True, text=True, timeout=120)
+    assert ok.returncode == 0, ok.stderr[-2000:]
+    lines = sorted(l for l in ok.stdout.splitlines() if l.startswith("SUM"))
+    assert lines == [f"SUM {r} 3 {r} 6.0" for r in range(3)]
+    bad = subprocess.run(cmd + ["7"], cwd=root, capture_output=True, text=True, timeout=120)
+    assert bad.returncode == 7
