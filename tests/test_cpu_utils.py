@@ -59,7 +59,7 @@ def test_launcher_starts_ranks_and_propagates_failure(tmp_path):
         "with bc.Session(device='cpu'):\n"
         "    s = bc.allreduce(torch.tensor([float(bc.rank() + 1)]), average=False)\n"
         "    me = bc.rank()\n"
-        "    print('SUM', me, bc.size(), bc.local_rank(), s.item(), flush=True)\n"
+        "    sys.stdout.write(f'SUM {me} {bc.size()} {bc.local_rank()} {s.item()}\\n'); sys.stdout.flush()\n"
         "sys.exit(int(sys.argv[1]) if me == 1 else 0)\n")
     cmd = [sys.executable, "-m", "tensorflow_allreduce_b200.launch", "--nproc", "3", "--cpu", str(script)]
     ok = subprocess.run(cmd + ["0"], cwd=root, capture_output=True, text=True, timeout=120)
