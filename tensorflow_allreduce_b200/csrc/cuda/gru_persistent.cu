@@ -44,7 +44,7 @@ namespace gpu {
 namespace {
 
 constexpr int kUnits = 16;            // hidden units per block
-constexpr int kBatchTile = 32;        // MMA N and rows of one TMA box of the streamed operand
+constexpr int kBatchTile = 32;        // batch entries: rows of one TMA box of the streamed operand, the valid rows of the MMA's M
 constexpr int kKTile = 32;            // fp32 elements in one 128-byte swizzle row
 constexpr int kTilesPerStage = 4;     // K tiles per pipeline stage (K = 128)
 constexpr int kStageBytes = kTilesPerStage * kBatchTile * 128;   // 16 KiB
@@ -52,7 +52,7 @@ constexpr int kXTileBytes = kBatchTile * 128;                    // 4 KiB
 constexpr int kComputeThreads = 128;   // four warps: accumulator read-back, exchange, gate math
 constexpr int kThreads = 160;          // plus one warp whose first thread issues copies and MMAs
 constexpr int kMaxBlocksPerDir = 64;   // H / 16 at H = 1024
-constexpr int kMmaM = 64;            // the tensor core spends about one clock per accumulator row whatever N is (measured)
+constexpr int kMmaM = 64;            // smallest M of tcgen05.mma; the batch fills 32 of its rows (an MMA costs the same for M = 128)
 
 struct Params {
   GruDims d;
