@@ -46,8 +46,8 @@ def parse():
 def reference_unavailable():
     print(json.dumps({
         "impl": "reference",
-        "unavailable": "the reference is a TensorFlow 1.3 fork: pip reports '/root/reference is not installable "
-                       "(neither setup.py nor pyproject.toml)'; its build needs Bazel, an MPI install and CUDA 8/cuDNN 6, none present offline",
+        "unavailable": "the reference is a TensorFlow 1.3 fork: pip reports that its tree is not installable "
+                       "(neither setup.py nor pyproject.toml); its build needs Bazel, an MPI install and CUDA 8/cuDNN 6, none present offline",
     }))
     return 0
 
