@@ -7,7 +7,6 @@ reference. `torchrun` works as well; the library reads the same variables.
 from __future__ import annotations
 
 import argparse
-import os
 import signal
 import subprocess
 import sys

@@ -10,7 +10,7 @@ reference's closest analogue is its NCCL test that maps several "devices" onto o
 from __future__ import annotations
 
 import ctypes as C
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import torch
 

@@ -23,7 +23,6 @@ from __future__ import annotations
 
 import contextlib
 import ctypes as C
-import math
 from typing import List, Optional
 
 import torch
