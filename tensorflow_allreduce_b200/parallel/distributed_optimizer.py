@@ -114,6 +114,7 @@ class DistributedOptimizer(torch.optim.Optimizer):
         self.state = optimizer.state
         self._world = core.size()
         self._sync = True
+        self._synced = False     # synchronize() has already averaged this iteration's gradients
         self._tf_adam = tf_adam
         self._fused_zero_grad = fused_zero_grad
         self._master_weights = master_weights
@@ -352,15 +353,8 @@ class DistributedOptimizer(torch.optim.Optimizer):
     # ---- optimizer interface -----------------------------------------------------------------
 
     @torch.no_grad()
-    def step(self, closure=None):
-        """Finish the gradient averaging of this iteration and apply the update."""
-        loss = None
-        if closure is not None:
-            with torch.enable_grad():
-                loss = closure()
-        if not self._gpu:
-            self._step_cpu()
-            return loss
+    def _finish_reduction(self):
+        """Launch the buckets that have not gone yet and make the current stream wait for all."""
         # Buckets whose parameters received no gradient in this pass are reduced now (zeros).
         for b in self._buckets[self._next_bucket:]:
             self._launch(b)
@@ -369,6 +363,40 @@ class DistributedOptimizer(torch.optim.Optimizer):
         for b in self._buckets:
             if b.launched:
                 cur.wait_event(b.done_event)
+
+    @torch.no_grad()
+    def synchronize(self):
+        """Finish the gradient averaging of this iteration WITHOUT applying the update: afterwards
+        every `p.grad` holds the average over all ranks, so gradients can be inspected or clipped
+        before `step()`. Needs the unfused path (`fused=False`): a fused update consumes the
+        gradients inside the reduction kernel."""
+        if self._kind:
+            raise RuntimeError("synchronize() needs DistributedOptimizer(..., fused=False): with a fused update the "
+                               "gradients are consumed inside the reduction kernel")
+        if self._synced:
+            return
+        if self._gpu:
+            self._finish_reduction()
+        else:
+            self._reduce_cpu()
+        self._synced = True
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        """Finish the gradient averaging of this iteration and apply the update."""
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        if not self._gpu:
+            if not self._synced:
+                self._reduce_cpu()
+            self._synced = False
+            self._optimizer.step()
+            return loss
+        if not self._synced:
+            self._finish_reduction()
+        self._synced = False
         if self._kind:
             for gi, g in enumerate(self.param_groups):
                 self._step_count[gi] += 1
@@ -385,7 +413,7 @@ class DistributedOptimizer(torch.optim.Optimizer):
         self._next_bucket = 0
         return loss
 
-    def _step_cpu(self):
+    def _reduce_cpu(self):
         handles = []
         idx = 0
         for g in self.param_groups:
@@ -398,7 +426,6 @@ class DistributedOptimizer(torch.optim.Optimizer):
                 idx += 1
         for h in handles:
             h.wait()
-        self._optimizer.step()
 
     def zero_grad(self, set_to_none: bool = True):
         """Reset gradients. On a CUDA group the flat buckets stay in place (they are zeroed, never

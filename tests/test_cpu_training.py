@@ -58,6 +58,43 @@ def test_distributed_optimizer_cpu_equals_large_batch_and_round_trips_state():
         assert rec["keys"] == ["param_groups", "state"]
 
 
+CLIP = """
+bc.init(%s)
+DEV = "%s"
+def make():
+    torch.manual_seed(0)
+    return torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.Tanh(), torch.nn.Linear(32, 4)).to(DEV)
+mine, ref = make(), make()
+o_mine = bc.DistributedOptimizer(torch.optim.SGD(mine.parameters(), lr=0.5, momentum=0.9), fused=False)
+o_ref = torch.optim.SGD(ref.parameters(), lr=0.5, momentum=0.9)
+g = torch.Generator().manual_seed(5)
+X = (torch.randn(4, 8 * SIZE, 16, generator=g) * 3).to(DEV); Y = (torch.randn(4, 8 * SIZE, 4, generator=g) * 3).to(DEV)
+norms = []
+for it in range(4):
+    o_ref.zero_grad(); torch.nn.functional.mse_loss(ref(X[it]), Y[it]).backward()
+    torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.1); o_ref.step()
+    sl = slice(RANK * 8, (RANK + 1) * 8)
+    o_mine.zero_grad(); torch.nn.functional.mse_loss(mine(X[it][sl]), Y[it][sl]).backward()
+    o_mine.synchronize()                                   # p.grad now holds the average over the ranks
+    norms.append(float(torch.nn.utils.clip_grad_norm_(mine.parameters(), 0.1)))
+    o_mine.step()
+worst = max((a - b).abs().max().item() for a, b in zip(ref.parameters(), mine.parameters()))
+fused_refuses = False
+try:
+    bc.DistributedOptimizer(torch.optim.SGD(make().parameters(), lr=0.1)).synchronize()
+except RuntimeError:
+    fused_refuses = True
+emit(worst=worst, clipped=all(n > 0.1 for n in norms), fused_refuses=fused_refuses)
+bc.shutdown()
+"""
+
+
+def test_synchronize_allows_clipping_before_step():
+    res = run(CLIP % ('device="cpu"', "cpu"), nranks=2)
+    for _, rec in res:
+        assert rec["worst"] < 1e-6 and rec["clipped"]
+
+
 def test_models_run_on_cpu():
     from tensorflow_allreduce_b200.models import ds2, gpt2
     from tensorflow_allreduce_b200.ops import persistent_gru

@@ -199,6 +199,14 @@ def test_fused_update_over_nvls(opt):
         assert rec["fused"]
 
 
+def test_synchronize_allows_clipping_before_step():
+    from test_cpu_training import CLIP
+
+    res = run(CLIP % ("", "cuda"), nranks=2, gpus=True, timeout=300)
+    for _, rec in res:
+        assert rec["worst"] < 2e-5 and rec["clipped"] and rec["fused_refuses"]
+
+
 def test_dependent_allreduce_stress():
     # 13 chained add -> allreduce stages on 1331 x 1331 fp32, closed-form check, many iterations:
     # catches buffer-reuse and epoch bugs.
