@@ -3,7 +3,9 @@
 The reference's collective package has no run-time knobs at all; its only configuration is the
 build-time MPI switch (`configure:823-897`). Everything here is new: algorithm cut-overs, bucket
 size, grid caps, deadlines, symmetric-memory sizes, NVLS on/off and the log level
-(`BC_LOG_LEVEL`, read by the native side).
+(`BC_LOG_LEVEL`, read by the native side). Read elsewhere: `BC_STATS_JSONL` (per-collective records
+appended at shutdown, `core.py`), `BC_NVTX` (`csrc/nvtx.cc`), `BC_DEBUG_KERNELS` (bounds-checked
+build, `_lib.py`), `BC_GRU_TIMEOUT_S` (`ops/persistent_gru.py`).
 """
 from __future__ import annotations
 

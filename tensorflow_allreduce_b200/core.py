@@ -150,10 +150,31 @@ def shutdown() -> None:
     if lib.bc_initialized():
         from .ops import symmetric
 
+        _dump_stats_jsonl()
         symmetric._reset()
         _call(lib.bc_shutdown(), "bc_shutdown")
     _state["config"] = None
     _state["device"] = None
+
+
+def _dump_stats_jsonl() -> None:
+    """`BC_STATS_JSONL=path`: on shutdown every rank appends one JSON line per completed collective
+    (rank, name, operation, algorithm, bytes, CTAs, negotiation and launch/run microseconds) to
+    `path` (a `{rank}` in the path is replaced by the rank)."""
+    path = os.environ.get("BC_STATS_JSONL", "")
+    if not path:
+        return
+    try:
+        r = rank()
+        recs = stats()
+        with open(path.replace("{rank}", str(r)), "a") as f:
+            for e in recs:
+                f.write(json.dumps({"rank": r, "name": e["name"], "op": e["op"], "algo": e["algo"], "bytes": e["bytes"],
+                                    "blocks": e["blocks"], "device": "cuda" if e["device"] else "cpu",
+                                    "negotiation_us": round(e["negotiation_us"], 1),
+                                    "run_us": round((e["t_done"] - e["t_negotiated"]) * 1e6, 1)}) + "\n")
+    except Exception:      # observability must never break a shutdown
+        pass
 
 
 def is_initialized() -> bool:

@@ -68,3 +68,23 @@ def test_launcher_starts_ranks_and_propagates_failure(tmp_path):
     assert lines == [f"SUM {r} 3 {r} 6.0" for r in range(3)]
     bad = subprocess.run(cmd + ["7"], cwd=root, capture_output=True, text=True, timeout=120)
     assert bad.returncode == 7
+
+
+def test_stats_jsonl_is_written_at_shutdown(tmp_path):
+    import json
+
+    from _util import run
+
+    path = str(tmp_path / "stats.{rank}.jsonl")
+    run("""
+    bc.init(device="cpu")
+    bc.allreduce(torch.ones(100), name="x")
+    bc.allgather(torch.ones(RANK + 1, 2), name="y")
+    bc.shutdown()
+    emit(ok=True)
+    """, nranks=2, env={"BC_STATS_JSONL": path})
+    for r in range(2):
+        recs = [json.loads(l) for l in open(path.replace("{rank}", str(r)))]
+        names = {e["name"]: e for e in recs}
+        assert names["x"]["op"] == "allreduce" and names["x"]["bytes"] == 400 and names["x"]["rank"] == r
+        assert names["y"]["op"] == "allgather" and names["y"]["algo"] == "cpu_ring" and names["y"]["device"] == "cpu"
