@@ -28,6 +28,22 @@ def test_rank_size_env(n):
         assert rec == {"rank": i, "size": n, "local_rank": i, "local_size": n}
 
 
+def test_ranks_of_several_hosts_get_per_host_local_ranks():
+    # Two "hosts" on one machine (the reported host name is overridden per rank): local_rank counts
+    # the lower ranks of the same host, as MPI_Comm_split_type(SHARED) does in the reference
+    # (mpi_ops.cc:609-613); collectives span both hosts.
+    res = run("""
+    bc.init(device="cpu")
+    s = bc.allreduce(torch.tensor([float(RANK)]), average=False)
+    g = bc.allgather(torch.full((1, 1), float(bc.local_rank())))
+    emit(local_rank=bc.local_rank(), local_size=bc.local_size(), s=s.item(), g=g.flatten().tolist())
+    bc.shutdown()
+    """, nranks=4, per_rank_env={r: {"BC_HOSTNAME": "hostA" if r % 2 == 0 else "hostB", "LOCAL_RANK": "-1"} for r in range(4)})   # -1: no launcher-given local rank
+    assert [rec["local_rank"] for _, rec in res] == [0, 0, 1, 1]
+    for _, rec in res:
+        assert rec["local_size"] == 2 and rec["s"] == 6.0 and rec["g"] == [0.0, 0.0, 1.0, 1.0]
+
+
 def test_ompi_env_names():
     res = run("""
     for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
