@@ -1,0 +1,68 @@
+"""Timed CPU baseline: sum-allreduce and variable allgather of a CPU group over loopback sockets,
+the data path that plays the role of the reference's `RingAllreduce<CPU>` / `RingAllgather<CPU>`
+(tensorflow/contrib/mpi_collectives/ring.h:136-301, ring.cc:36-50).
+
+    python -m tensorflow_allreduce_b200.launch --nproc 2 --cpu bench/cpu_ring_bench.py [--max-mb 64]
+
+Wall-clock time per call (host timers, maximum over ranks) through the public, name-keyed API, so
+the coordinator round trip is included. Bus bandwidth as in the GPU sweep.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+
+import tensorflow_allreduce_b200 as bc
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--max-mb", type=int, default=64)
+    ap.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args()
+    bc.init(device="cpu")
+    rank, P = bc.rank(), bc.size()
+    s = 1 << 10
+    while s <= a.max_mb << 20:
+        n = s // 4
+        x = torch.full((n,), float(rank + 1))
+        want = float(P * (P + 1) // 2)
+        times = []
+        for it in range(a.iters + 2):
+            bc.barrier()
+            t0 = time.perf_counter()
+            y = bc.allreduce(x, average=False, name=f"ar.{s}.{it}")
+            t1 = time.perf_counter()
+            if it >= 2:
+                times.append(t1 - t0)
+        ok = bool(y[0] == want and y[-1] == want)
+        sec = max(bc.host_allgather(sorted(times)[len(times) // 2]))
+        rows = max(1, n // 256 // (P * (P + 1) // 2))
+        t = torch.full(((rank + 1) * rows, 256), float(rank))
+        gt = []
+        for it in range(a.iters + 2):
+            bc.barrier()
+            t0 = time.perf_counter()
+            g = bc.allgather(t, name=f"ag.{s}.{it}")
+            t1 = time.perf_counter()
+            if it >= 2:
+                gt.append(t1 - t0)
+        gsec = max(bc.host_allgather(sorted(gt)[len(gt) // 2]))
+        total = g.numel() * 4
+        if rank == 0:
+            print(json.dumps({"bytes": s, "world": P, "allreduce_ms": round(sec * 1e3, 4), "allreduce_busbw_gbs": round(s / sec * 2 * (P - 1) / P / 1e9, 3),
+                              "correct": ok, "allgather_total_bytes": total, "allgather_ms": round(gsec * 1e3, 4),
+                              "allgather_busbw_gbs": round(total / gsec * (P - 1) / P / 1e9, 3)}), flush=True)
+        s *= 4
+    bc.shutdown()
+
+
+if __name__ == "__main__":
+    main()
