@@ -54,7 +54,7 @@ static void rank_main(int rank, int size, int port) {
     o.size = size;
     o.port = port;
     o.device = -1;
-    o.timeout_s = 20;
+    o.timeout_s = 3;
     Runtime rt(o);
     EXPECT(rt.rank() == rank && rt.size() == size, "rank/size");
 
@@ -109,6 +109,26 @@ static void rank_main(int rank, int size, int port) {
       }
       rt.release(id);
       EXPECT(threw || size == 1, "mismatch not reported");
+    }
+    // failure path under the sanitizers: rank 1 never sends its request for "lost", so every rank
+    // gets a time-out that names the missing rank, and the runtime keeps working afterwards
+    if (size > 1) {
+      rt.set_fault("drop_request:rank=1:name=lost");
+      std::vector<float> a(8, 1.f), b(8, 0.f);
+      int64_t id = enqueue_allreduce(rt, "lost", a.data(), b.data(), {8}, false);
+      bool timed_out = false;
+      try {
+        rt.wait(id, 30);
+      } catch (const Error& e) {
+        timed_out = strstr(e.what(), "Timed out") != nullptr && strstr(e.what(), "1") != nullptr;
+      }
+      rt.release(id);
+      EXPECT(timed_out, "dropped request was not reported as a time-out");
+      rt.set_fault("");
+      int64_t id2 = enqueue_allreduce(rt, "after_timeout", a.data(), b.data(), {8}, false);
+      rt.wait(id2, 30);
+      rt.release(id2);
+      EXPECT(b[0] == (float)size, "runtime unusable after a time-out: got %f", b[0]);
     }
     auto blobs = rt.blob_gather("blob", std::string(1, (char)('a' + rank)));
     for (int r2 = 0; r2 < size; r2++) EXPECT(blobs[r2] == std::string(1, (char)('a' + r2)), "blob of rank %d", r2);
