@@ -44,6 +44,8 @@ def parse():
 
 
 def reference_unavailable():
+    if int(os.environ.get("RANK", "0")) != 0:      # under torchrun every rank runs this; one line is enough
+        return 0
     print(json.dumps({
         "impl": "reference",
         "unavailable": "the reference is a TensorFlow 1.3 fork: pip reports that its tree is not installable "
