@@ -203,7 +203,7 @@ def main():
     ms = max_over_ranks(e0.elapsed_time(e1))
     launches = getattr(opt, "launch_count", 0) + persistent_gru.launch_count - launches0
     persistent_gru.check_status()
-    final_loss = float(loss)
+    final_loss = float(loss.detach())
     clocks = clk.summary()
     bc.check_device_status()
 
