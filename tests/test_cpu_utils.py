@@ -88,3 +88,13 @@ def test_stats_jsonl_is_written_at_shutdown(tmp_path):
         names = {e["name"]: e for e in recs}
         assert names["x"]["op"] == "allreduce" and names["x"]["bytes"] == 400 and names["x"]["rank"] == r
         assert names["y"]["op"] == "allgather" and names["y"]["algo"] == "cpu_ring" and names["y"]["device"] == "cpu"
+
+
+def test_gru_workspace_size_and_dimension_checks(native_lib):
+    # Pure host arithmetic of the persistent GRU entry points (no GPU needed): the exchange
+    # workspace of the benchmark shape, and dimensions that the kernels do not take.
+    assert native_lib.bc_gru_workspace_bytes(350, 32, 1024, 2) == 2 * 64 * 16 * 32 * 16 * 4     # backward groups of 16
+    assert native_lib.bc_gru_workspace_bytes(10, 4, 128, 1) == 8 * 4 * 32 * 48 * 4             # forward groups of 4
+    for T, B, H, nd in ((10, 33, 128, 2), (10, 8, 100, 1), (10, 8, 2048, 2), (5000, 8, 128, 1), (10, 8, 128, 3)):
+        assert native_lib.bc_gru_workspace_bytes(T, B, H, nd) == 0
+        assert native_lib.bc_gru_supported(0, T, B, H, nd) == 0
