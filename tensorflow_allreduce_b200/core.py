@@ -83,16 +83,15 @@ def _resolve_port(rank_: int, size_: int, addr: str) -> int:
     port = int(os.environ.get("MASTER_PORT", "29500"))
     if size_ > 1 and os.environ.get("TORCHELASTIC_USE_AGENT_STORE", "") == "True":
         import datetime
-        import socket
 
         from torch.distributed import TCPStore
 
         store = TCPStore(addr, port, None, False, timeout=datetime.timedelta(seconds=120), wait_for_workers=False)
         key = "bcoll/ctrl_port/" + os.environ.get("TORCHELASTIC_RUN_ID", "0") + "/" + os.environ.get("TORCHELASTIC_RESTART_COUNT", "0")
         if rank_ == 0:
-            with socket.socket() as s:
-                s.bind(("", 0))
-                free = s.getsockname()[1]
+            from .utils.spawn import free_port
+
+            free = free_port()
             store.set(key, str(free))
             return free
         return int(store.get(key).decode())

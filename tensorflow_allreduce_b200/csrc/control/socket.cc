@@ -203,6 +203,19 @@ Socket Socket::connect_tcp(const std::string& addr, int port, double deadline) {
     int fd = ::socket(AF_INET, SOCK_STREAM, 0);
     if (fd >= 0) {
       if (::connect(fd, res->ai_addr, res->ai_addrlen) == 0) {
+        // While nobody listens on a local port of the ephemeral range yet, the kernel may give
+        // this socket that very port as its source and complete a TCP simultaneous open with
+        // itself. Such a socket also keeps the real listener from binding: drop it and retry.
+        struct sockaddr_in self, peer;
+        socklen_t sl = sizeof(self), pl = sizeof(peer);
+        if (getsockname(fd, (struct sockaddr*)&self, &sl) == 0 && getpeername(fd, (struct sockaddr*)&peer, &pl) == 0 &&
+            self.sin_port == peer.sin_port && self.sin_addr.s_addr == peer.sin_addr.s_addr) {
+          last = "connected to itself";
+          ::close(fd);
+          if (now_s() >= deadline) break;
+          std::this_thread::sleep_for(std::chrono::milliseconds(20));
+          continue;
+        }
         int one = 1;
         setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
         freeaddrinfo(res);

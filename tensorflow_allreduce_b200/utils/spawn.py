@@ -4,6 +4,7 @@ Used by the launcher module and by the test-suite."""
 from __future__ import annotations
 
 import os
+import signal
 import socket
 import subprocess
 import sys
@@ -13,6 +14,29 @@ from typing import Dict, List, Optional, Sequence
 
 
 def free_port() -> int:
+    """A port for rank 0's rendezvous listener that nothing is bound to right now.
+
+    Ports below the kernel's ephemeral range are tried first: a port of that range can be handed
+    to any other socket (a rank's own data listener, the source port of a connection attempt)
+    between this call and rank 0's bind, which then fails while the other ranks wait."""
+    import random
+
+    low = 32768
+    try:
+        with open("/proc/sys/net/ipv4/ip_local_port_range") as f:
+            low = int(f.read().split()[0])
+    except (OSError, ValueError, IndexError):
+        pass
+    if low > 21000:
+        rng = random.Random(os.getpid() * 1000003 + time.monotonic_ns())
+        for _ in range(64):
+            port = rng.randrange(20000, low)
+            with socket.socket() as s:
+                try:
+                    s.bind(("0.0.0.0", port))
+                except OSError:
+                    continue
+                return port
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         return s.getsockname()[1]
@@ -42,9 +66,11 @@ def rank_env(rank: int, size: int, port: int, extra: Optional[Dict[str, str]] = 
 
 
 def run_ranks(argv: Sequence[str], nranks: int, timeout: float = 120.0, env: Optional[Dict[str, str]] = None,
-              per_rank_env: Optional[Dict[int, Dict[str, str]]] = None, gpus: bool = False, cwd: Optional[str] = None) -> List[RankResult]:
+              per_rank_env: Optional[Dict[int, Dict[str, str]]] = None, gpus: bool = False, cwd: Optional[str] = None,
+              dump_stacks: bool = False) -> List[RankResult]:
     """Run `python <argv...>` as `nranks` processes and wait for all of them. A rank still running
-    at the deadline is killed (its own process only) and reported with returncode None."""
+    at the deadline is killed (its own process only) and reported with returncode None; with
+    `dump_stacks` it is sent SIGUSR1 first (for scripts that registered `faulthandler` on it)."""
     port = free_port()
     procs = []
     files = []
@@ -63,6 +89,13 @@ def run_ranks(argv: Sequence[str], nranks: int, timeout: float = 120.0, env: Opt
         try:
             rc = p.wait(timeout=max(0.1, deadline - time.time()))
         except subprocess.TimeoutExpired:
+            # A script that registered faulthandler on SIGUSR1 leaves its Python stacks in stderr.
+            if dump_stacks:
+                try:
+                    p.send_signal(signal.SIGUSR1)
+                    time.sleep(0.5)
+                except OSError:
+                    pass
             p.kill()
             p.wait()
             rc = None

@@ -9,7 +9,8 @@ from tensorflow_allreduce_b200.utils.spawn import run_script
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 PRELUDE = f"""
-import json, os, sys
+import faulthandler, json, os, signal, sys
+faulthandler.register(signal.SIGUSR1, all_threads=True)      # the runner asks for the stacks of a rank it is about to kill
 sys.path.insert(0, {ROOT!r})
 import torch
 import tensorflow_allreduce_b200 as bc
@@ -20,7 +21,10 @@ def emit(**kw):
 
 
 def run(body: str, nranks: int = 2, timeout: float = 120.0, env=None, per_rank_env=None, gpus=False, expect_ok=True):
-    res = run_script(PRELUDE + textwrap.dedent(body), nranks, timeout=timeout, env=env, per_rank_env=per_rank_env, gpus=gpus)
+    env = dict(env or {})
+    env.setdefault("BC_TIMEOUT_S", "60")       # a stuck host-side wait reports itself before the runner's deadline
+    res = run_script(PRELUDE + textwrap.dedent(body), nranks, timeout=timeout, env=env, per_rank_env=per_rank_env, gpus=gpus,
+                     dump_stacks=True)
     out = []
     for r in res:
         rec = None

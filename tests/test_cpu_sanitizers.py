@@ -2,18 +2,12 @@
 three ranks run as threads of one process (csrc/selftest/host_selftest.cc). The reference
 configures no sanitizer and its coordinator state has data races
 (tensorflow/contrib/mpi_collectives/mpi_ops.cc:593,621,816-821)."""
-import socket
 import subprocess
 
 import pytest
 
 from tensorflow_allreduce_b200 import build
-
-
-def _free_port():
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
+from tensorflow_allreduce_b200.utils.spawn import free_port as _free_port
 
 
 @pytest.mark.parametrize("sanitizer", ["thread", "address"])

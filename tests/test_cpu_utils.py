@@ -98,3 +98,34 @@ def test_gru_workspace_size_and_dimension_checks(native_lib):
     for T, B, H, nd in ((10, 33, 128, 2), (10, 8, 100, 1), (10, 8, 2048, 2), (5000, 8, 128, 1), (10, 8, 128, 3)):
         assert native_lib.bc_gru_workspace_bytes(T, B, H, nd) == 0
         assert native_lib.bc_gru_supported(0, T, B, H, nd) == 0
+
+
+def test_runner_kills_an_overstaying_rank_and_keeps_its_stacks():
+    # Rank 1 never finishes: the runner reports it with returncode None and its Python stacks
+    # (the scripts register faulthandler on SIGUSR1), rank 0 is unaffected.
+    from _util import run
+
+    t0 = time.time()
+    res = run("""
+    import time
+    def stuck_here():
+        time.sleep(600)
+    if RANK == 1:
+        stuck_here()
+    emit(done=True)
+    """, nranks=2, timeout=8, expect_ok=False)
+    assert time.time() - t0 < 60
+    (r0, rec0), (r1, rec1) = res
+    assert r0.returncode == 0 and rec0 == {"done": True}
+    assert r1.returncode is None and rec1 is None
+    assert "stuck_here" in r1.stderr
+
+
+def test_free_port_avoids_the_ephemeral_range():
+    from tensorflow_allreduce_b200.utils.spawn import free_port
+
+    low = int(open("/proc/sys/net/ipv4/ip_local_port_range").read().split()[0])
+    ports = {free_port() for _ in range(8)}
+    if low > 21000:
+        assert all(20000 <= p < low for p in ports)
+    assert len(ports) > 1
