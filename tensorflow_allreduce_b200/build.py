@@ -63,10 +63,34 @@ def _compile(src: Path, obj: Path, verbose: bool, extra: list[str]) -> None:
         print(r.stdout, r.stderr, flush=True)
 
 
+def _fingerprint(debug: bool) -> str:
+    """Hash of every source and header and of the compiler flags: what a built library is valid for."""
+    import hashlib
+
+    h = hashlib.sha256()
+    cc, cu = _sources()
+    hs = sorted(list(CSRC.rglob("*.h")) + list(CSRC.rglob("*.cuh")))
+    for p in cc + cu + hs:
+        h.update(str(p.relative_to(CSRC)).encode())
+        h.update(p.read_bytes())
+    h.update(" ".join(NVCC_FLAGS + CXX_FLAGS + (["-DBC_DEBUG"] if debug else [])).encode())
+    return h.hexdigest()
+
+
+def _stamp(debug: bool) -> Path:
+    return LIBDIR / (".fingerprint_debug" if debug else ".fingerprint")
+
+
 def needs_build(debug: bool = False) -> bool:
+    """True when the library is missing or was built from other sources. The record of what it
+    was built from is a hash beside it, so a copy or checkout that changes file times neither
+    forces a rebuild nor hides an edit; without that record the file times decide."""
     lib = LIB_DEBUG if debug else LIB
     if not lib.exists():
         return True
+    stamp = _stamp(debug)
+    if stamp.exists():
+        return stamp.read_text().strip() != _fingerprint(debug)
     cc, cu = _sources()
     newest = max([p.stat().st_mtime for p in cc + cu] + [_headers_mtime()])
     return newest > lib.stat().st_mtime
@@ -104,6 +128,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, 
         if r.returncode != 0:
             raise RuntimeError(f"linking failed:\n{r.stdout}\n{r.stderr}")
         os.replace(tmp, LIB)
+    _stamp(debug).write_text(_fingerprint(debug) + "\n")
     return LIB
 
 

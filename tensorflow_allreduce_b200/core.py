@@ -203,6 +203,18 @@ def on_gpu() -> bool:
     return bool(_call(_lib.lib().bc_on_gpu()))
 
 
+def n_nodes() -> int:
+    """Hosts of a group that runs in two levels, else 1. A GPU group whose ranks sit on several
+    hosts reduces inside each host with the NVLink kernels and between hosts over sockets (the
+    reference crosses hosts through MPI, `ring.h:183-225`); the gradient buckets in symmetric
+    memory and the fused update need all ranks on one host and are switched off then."""
+    return _call(_lib.lib().bc_n_nodes())
+
+
+def node_index() -> int:
+    return _call(_lib.lib().bc_node_index())
+
+
 def config() -> Config:
     if _state["config"] is None:
         raise CollectiveError("MPI has not been initialized; use Session or init() first.")

@@ -28,6 +28,17 @@ int bc_local_rank(void);
 int bc_local_size(void);
 int bc_on_gpu(void);
 int bc_broken(void);
+/* Hosts of a group that runs in two levels (a GPU group whose ranks span several hosts, or any
+ * group started with BC_NODE_GROUPS=1), else 1; and this rank's host among them. With more than
+ * one host the ordered launches, the fused update and user segments of symmetric memory are
+ * refused: use the negotiated collectives. */
+int bc_n_nodes(void);
+int bc_node_index(void);
+/* The two-level allreduce on a tensor in HOST memory, with the node group's control sockets
+ * standing in for the NVLink level (sum inside the host, slices over the rails, gather inside the
+ * host). Collective over all ranks; must not overlap any other collective of the job. Exists to
+ * check the slice arithmetic and the rails on machines without GPUs. */
+int bc_two_level_allreduce_host(void* data, long long count, int dtype, int average, int reduce_op);
 
 /* Negotiated, name-keyed collectives. The returned handle must be released. For CUDA tensors
  * `ready_event` (a cudaEvent_t or NULL) is what the private stream waits on before touching the

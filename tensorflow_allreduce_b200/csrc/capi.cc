@@ -15,6 +15,7 @@
 #include "cuda/comm.h"
 #include "cuda/gru_persistent.h"
 #include "runtime/runtime.h"
+#include "runtime/two_level.h"
 
 using namespace bc;
 
@@ -108,6 +109,30 @@ int bc_local_rank() { API_BEGIN return rt().local_rank(); API_END(-1) }
 int bc_local_size() { API_BEGIN return rt().local_size(); API_END(-1) }
 int bc_on_gpu() { API_BEGIN return rt().on_gpu() ? 1 : 0; API_END(-1) }
 int bc_broken() { API_BEGIN return rt().broken() ? 1 : 0; API_END(-1) }
+int bc_n_nodes() { API_BEGIN return rt().n_nodes(); API_END(-1) }
+int bc_node_index() { API_BEGIN return rt().node_group() ? rt().node_group()->node_index : 0; API_END(-1) }
+
+int bc_two_level_allreduce_host(void* data, long long count, int dtype, int average, int reduce_op) {
+  API_BEGIN
+  Runtime& r = rt();
+  NodeGroup* g = r.node_group();
+  if (!g) throw Error("no node groups: the ranks are on one host, or this CPU job was started without BC_NODE_GROUPS=1");
+  if (reduce_op < 0 || reduce_op > (int)ReduceOp::MAX) throw Error("unknown reduction");
+  if (average && reduce_op != (int)ReduceOp::SUM) throw Error("averaging goes with the sum only");
+  const double deadline = now_s() + r.options().timeout_s;
+  HostLocalLevel local(*g, data, deadline);
+  std::vector<char> staging(slice_len((size_t)count, g->local_size, 0) * dtype_size((DType)dtype) + 16);
+  two_level_allreduce(*g, local, staging.data(), (size_t)count, (DType)dtype, average ? 1.0 / r.size() : 1.0,
+                      average ? r.size() : 1, (ReduceOp)reduce_op, deadline);
+  return 0;
+  API_END(-1)
+}
+
+// Entry points that address the communicator directly assume that it spans the whole job.
+static void require_one_host(const char* what) {
+  if (rt().n_nodes() > 1)
+    throw Error(std::string(what) + " is not available while the GPU ranks span several hosts; use the negotiated collectives");
+}
 
 long long bc_allreduce_async(const char* name, const void* in, void* out, int dtype, int ndim, const long long* shape,
                              int device_kind, int average, int zero_copy, void* ready_event, int reduce_op) {
@@ -210,6 +235,7 @@ void* bc_symm_heap(long long* bytes) {
 
 void* bc_symm_new_segment(long long bytes, int* seg_id, int* has_multicast) {
   API_BEGIN
+  require_one_host("a user segment of symmetric memory");
   Runtime& r = rt();
   gpu::Comm& c = comm();
   const int64_t seq = g_segment_seq++;
@@ -263,6 +289,7 @@ static void stream_epilogue(cudaStream_t s, void* record_event) {
 int bc_allreduce_direct(int channel, const void* in, void* out, long long count, int dtype, int average,
                         void* wait_event, void* record_event) {
   API_BEGIN
+  require_one_host("an ordered allreduce");
   gpu::Comm& c = comm();
   if (c.device_status() != 0) throw Error("an earlier device-side wait timed out; the communicator cannot be used any more");
   cudaStream_t s = c.stream(channel);
@@ -278,6 +305,7 @@ int bc_fused_step(int channel, void* grad, long long count, int dtype, void* par
                   const bc_opt_hyper* h, float scale, void* wait_event, void* record_event) {
   API_BEGIN
   NvtxRange range("bcoll.fused_step");
+  require_one_host("the fused update");
   gpu::Comm& c = comm();
   if (c.device_status() != 0) throw Error("an earlier device-side wait timed out; the communicator cannot be used any more");
   cudaStream_t s = c.stream(channel);
@@ -294,6 +322,7 @@ int bc_fused_step(int channel, void* grad, long long count, int dtype, void* par
 int bc_allgatherv_direct(int channel, const void* in, long long bytes, void* out_symm, long long capacity_bytes,
                          unsigned long long* sizes_out, void* wait_event, void* record_event) {
   API_BEGIN
+  require_one_host("an ordered allgather");
   gpu::Comm& c = comm();
   if (c.device_status() != 0) throw Error("an earlier device-side wait timed out; the communicator cannot be used any more");
   cudaStream_t s = c.stream(channel);

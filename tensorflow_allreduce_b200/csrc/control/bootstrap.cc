@@ -78,6 +78,7 @@ Transport bootstrap(int rank, int size, const std::string& addr, int port, doubl
   const std::string me = local_hostname();
   if (size == 1) {
     t.hosts[0] = me;
+    t.ips.assign(1, addr);
     t.pids[0] = (int)getpid();
     std::random_device rd;
     t.job_id = ((uint64_t)rd() << 32) ^ rd();
@@ -159,6 +160,8 @@ Transport bootstrap(int rank, int size, const std::string& addr, int port, doubl
       t.local_size++;
     }
   }
+
+  t.ips = ips;
 
   // Data ring: connect to the next rank, accept from the previous one.
   const int next = (rank + 1) % size;

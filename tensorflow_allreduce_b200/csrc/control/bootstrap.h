@@ -22,6 +22,7 @@ struct Transport {
   int local_size = 1;
   uint64_t job_id = 0;
   std::vector<std::string> hosts;  // hostname of every rank
+  std::vector<std::string> ips;    // address at which every rank's listeners can be reached
   std::vector<int> pids;
   // Control star. On rank 0: ctrl[r] is the socket to rank r (ctrl[0] unused). On other ranks:
   // ctrl[0] is the socket to rank 0.

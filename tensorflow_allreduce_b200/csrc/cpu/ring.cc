@@ -150,7 +150,7 @@ void cpu_ring_allgatherv(Transport& t, const void* in, void* out, const std::vec
   std::vector<size_t> off(n + 1, 0);
   for (int i = 0; i < n; i++) off[i + 1] = off[i] + (size_t)rows[i] * row_bytes;
   char* o = (char*)out;
-  if (off[r + 1] > off[r]) memcpy(o + off[r], in, off[r + 1] - off[r]);
+  if (off[r + 1] > off[r] && in != o + off[r]) memcpy(o + off[r], in, off[r + 1] - off[r]);
   // At step k every rank forwards the slab that originated k ranks behind it.
   for (int k = 0; k < n - 1; k++) {
     const int out_i = ((r - k) % n + n) % n;

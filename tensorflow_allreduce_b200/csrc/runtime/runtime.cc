@@ -11,6 +11,7 @@
 
 #include "../cpu/ring.h"
 #include "../cuda/comm.h"
+#include "two_level.h"
 
 namespace bc {
 
@@ -75,8 +76,15 @@ Runtime::Runtime(const RuntimeOptions& o) : opt_(o) {
   t_ = bootstrap(o.rank, o.size, o.addr, o.port, o.timeout_s);
   local_rank_ = o.local_rank_override >= 0 ? o.local_rank_override : t_.local_rank;
   fault_ = FaultSpec::parse(o.fault);
+  // Ranks on several hosts: GPU collectives run in two levels (NVLink kernels inside a host, a
+  // ring of sockets between hosts). BC_NODE_GROUPS=1 builds the groups for a CPU job as well.
+  const char* want_groups = getenv("BC_NODE_GROUPS");
+  if (t_.local_size != t_.size && (o.device >= 0 || (want_groups && atoi(want_groups) > 0))) {
+    std::string why;
+    BC_CHECK(hosts_are_uniform(t_, &why), "GPU collectives over several hosts need the same number of ranks on each (" << why << ")");
+    node_.reset(new NodeGroup(build_node_group(t_, now_s() + o.timeout_s)));
+  }
   if (o.device >= 0) {
-    BC_CHECK(t_.local_size == t_.size, "GPU collectives need all ranks on one NVLink node (ranks span several hosts)");
     gpu::CommConfig cc;
     cc.staging_bytes = o.staging_bytes;
     cc.heap_bytes = o.heap_bytes;
@@ -89,9 +97,17 @@ Runtime::Runtime(const RuntimeOptions& o) : opt_(o) {
     cc.symm_mode = o.symm_mode == 1 ? gpu::SymmAllocator::Mode::VMM
                  : o.symm_mode == 2 ? gpu::SymmAllocator::Mode::IPC : gpu::SymmAllocator::Mode::AUTO;
     const double dl = o.timeout_s;
-    Transport* tp = &t_;
-    gpu::HostAllgather ag = [tp, dl](const std::string& mine) { return tp->allgather(mine, now_s() + dl); };
-    comm_.reset(new gpu::Comm(t_.rank, t_.size, o.device, t_.job_id, cc, ag, o.timeout_s));
+    if (node_) {
+      // The communicator covers the ranks of this host; its set-up talks over the node's star.
+      NodeGroup* ng = node_.get();
+      gpu::HostAllgather ag = [ng, dl](const std::string& mine) { return ng->allgather(mine, now_s() + dl); };
+      const uint64_t node_job = t_.job_id ^ (0x9E3779B97F4A7C15ull * (uint64_t)(node_->node_index + 1));
+      comm_.reset(new gpu::Comm(node_->local_rank, node_->local_size, o.device, node_job, cc, ag, o.timeout_s));
+    } else {
+      Transport* tp = &t_;
+      gpu::HostAllgather ag = [tp, dl](const std::string& mine) { return tp->allgather(mine, now_s() + dl); };
+      comm_.reset(new gpu::Comm(t_.rank, t_.size, o.device, t_.job_id, cc, ag, o.timeout_s));
+    }
   }
   wake_fd_ = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
   BC_CHECK(wake_fd_ >= 0, "eventfd failed");
@@ -139,6 +155,9 @@ void Runtime::shutdown() {
       } catch (...) {
       }
     }
+    if (pinned_) cudaFreeHost(pinned_);
+    if (scratch_) cudaFree(scratch_);
+    pinned_ = scratch_ = nullptr;
     comm_.reset();
   }
 }
@@ -313,7 +332,7 @@ void Runtime::send_request(const OpRecord& rec) {
   q.blob = rec.blob;
   q.symm_off = -1;
   q.red = rec.red;
-  if (rec.zero_copy && comm_) {
+  if (rec.zero_copy && comm_ && !node_) {
     int64_t n = 1;
     for (int64_t d : rec.shape) n *= d;
     gpu::Segment* seg = comm_->allocator().find(rec.in, (size_t)n * dtype_size(rec.dtype));
@@ -527,7 +546,10 @@ void Runtime::perform_allreduce(OpRecord& r) {
     cudaError_t e = cudaStreamWaitEvent(s, (cudaEvent_t)r.ready_event, 0);
     BC_CHECK(e == cudaSuccess, "cudaStreamWaitEvent: " << cudaGetErrorString(e));
   }
-  r.algo = (int)comm_->allreduce(0, r.in, r.out, count, r.dtype, (float)scale, (int)idiv, r.zero_copy, r.red);
+  if (node_)
+    two_level_allreduce(r, count, scale, idiv);
+  else
+    r.algo = (int)comm_->allreduce(0, r.in, r.out, count, r.dtype, (float)scale, (int)idiv, r.zero_copy, r.red);
   cudaError_t e = cudaEventRecord((cudaEvent_t)r.done_event, s);
   BC_CHECK(e == cudaSuccess, "cudaEventRecord: " << cudaGetErrorString(e));
 }
@@ -557,13 +579,124 @@ void Runtime::perform_allgather(OpRecord& r, const Response& resp) {
     cudaError_t e = cudaStreamWaitEvent(s, (cudaEvent_t)r.ready_event, 0);
     BC_CHECK(e == cudaSuccess, "cudaStreamWaitEvent: " << cudaGetErrorString(e));
   }
-  std::vector<unsigned long long> slab_bytes(r.dim0.size());
-  for (size_t i = 0; i < r.dim0.size(); i++) slab_bytes[i] = (unsigned long long)r.dim0[i] * row_bytes;
-  comm_->allgatherv(0, r.in, (size_t)r.shape[0] * row_bytes, is_symm ? r.out : nullptr, is_symm ? nullptr : r.out, total_bytes,
-                    nullptr, slab_bytes.data());
+  if (node_) {
+    two_level_allgather(r, row_bytes, total_bytes);
+  } else {
+    std::vector<unsigned long long> slab_bytes(r.dim0.size());
+    for (size_t i = 0; i < r.dim0.size(); i++) slab_bytes[i] = (unsigned long long)r.dim0[i] * row_bytes;
+    comm_->allgatherv(0, r.in, (size_t)r.shape[0] * row_bytes, is_symm ? r.out : nullptr, is_symm ? nullptr : r.out, total_bytes,
+                      nullptr, slab_bytes.data());
+  }
   r.algo = 0;
   cudaError_t e = cudaEventRecord((cudaEvent_t)r.done_event, s);
   BC_CHECK(e == cudaSuccess, "cudaEventRecord: " << cudaGetErrorString(e));
+}
+
+// ---- GPU groups over several hosts -----------------------------------------------------------
+
+void* Runtime::pinned(size_t bytes) {
+  if (bytes > pinned_bytes_) {
+    if (pinned_) cudaFreeHost(pinned_);
+    pinned_ = nullptr;
+    pinned_bytes_ = 0;
+    const size_t want = std::max<size_t>(bytes + bytes / 4, 1u << 20);
+    cudaError_t e = cudaMallocHost(&pinned_, want);
+    BC_CHECK(e == cudaSuccess, "cudaMallocHost(" << want << "): " << cudaGetErrorString(e));
+    pinned_bytes_ = want;
+  }
+  return pinned_;
+}
+
+void* Runtime::device_scratch(size_t bytes) {
+  if (bytes > scratch_bytes_) {
+    cudaStream_t s = comm_->stream(0);
+    cudaStreamSynchronize(s);          // an earlier gather may still read the old scratch
+    if (scratch_) cudaFree(scratch_);
+    scratch_ = nullptr;
+    scratch_bytes_ = 0;
+    const size_t want = std::max<size_t>(bytes + bytes / 4, 1u << 20);
+    cudaError_t e = cudaMalloc(&scratch_, want);
+    BC_CHECK(e == cudaSuccess, "cudaMalloc(" << want << "): " << cudaGetErrorString(e));
+    scratch_bytes_ = want;
+  }
+  return scratch_;
+}
+
+namespace {
+
+void check(cudaError_t e, const char* what) { BC_CHECK(e == cudaSuccess, what << ": " << cudaGetErrorString(e)); }
+
+// The levels inside a host on GPUs: the NVLink kernels of the host's communicator, and copies
+// between the device and pinned host memory on the communicator's stream.
+class GpuLocalLevel : public LocalLevel {
+ public:
+  GpuLocalLevel(gpu::Comm& c, const void* in, void* out, std::function<void*(size_t)> scratch)
+      : c_(c), in_(in), out_((char*)out), scratch_(std::move(scratch)), s_(c.stream(0)) {}
+
+  void reduce_in_node(size_t count, DType dtype, ReduceOp red) override {
+    if (c_.world() > 1)
+      c_.allreduce(0, in_, out_, count, dtype, 1.f, 1, false, red);
+    else if (in_ != out_ && count)
+      check(cudaMemcpyAsync(out_, in_, count * dtype_size(dtype), cudaMemcpyDeviceToDevice, s_), "cudaMemcpyAsync");
+  }
+
+  void fetch(void* dst, size_t begin, size_t len, DType dtype) override {
+    const size_t e = dtype_size(dtype);
+    if (len) check(cudaMemcpyAsync(dst, out_ + begin * e, len * e, cudaMemcpyDeviceToHost, s_), "cudaMemcpyAsync (to host)");
+    check(cudaStreamSynchronize(s_), "cudaStreamSynchronize");
+  }
+
+  void finish(const void* src, size_t begin, size_t len, const std::vector<size_t>& lens, DType dtype) override {
+    const size_t e = dtype_size(dtype);
+    if (c_.world() == 1) {
+      if (len) check(cudaMemcpyAsync(out_ + begin * e, src, len * e, cudaMemcpyHostToDevice, s_), "cudaMemcpyAsync (to device)");
+      return;
+    }
+    // The gather's input must not alias its output: the slice goes to scratch memory first.
+    void* mine = scratch_(len * e);
+    if (len) check(cudaMemcpyAsync(mine, src, len * e, cudaMemcpyHostToDevice, s_), "cudaMemcpyAsync (to device)");
+    std::vector<unsigned long long> slab(lens.size());
+    size_t total = 0;
+    for (size_t i = 0; i < lens.size(); i++) {
+      slab[i] = (unsigned long long)(lens[i] * e);
+      total += lens[i] * e;
+    }
+    c_.allgatherv(0, mine, len * e, nullptr, out_, total, nullptr, slab.data());
+  }
+
+ private:
+  gpu::Comm& c_;
+  const void* in_;
+  char* out_;
+  std::function<void*(size_t)> scratch_;
+  cudaStream_t s_;
+};
+
+}  // namespace
+
+void Runtime::two_level_allreduce(OpRecord& r, size_t count, double scale, int64_t idiv) {
+  const size_t e = dtype_size(r.dtype);
+  void* staging = pinned(slice_len(count, node_->local_size, 0) * e);
+  GpuLocalLevel local(*comm_, r.in, r.out, [this](size_t b) { return device_scratch(b); });
+  bc::two_level_allreduce(*node_, local, staging, count, r.dtype, scale, idiv, r.red, now_s() + opt_.timeout_s);
+  // The pinned slice is read by a copy that is still queued; the next operation reuses it.
+  check(cudaStreamSynchronize(comm_->stream(0)), "cudaStreamSynchronize");
+  r.algo = 0;
+}
+
+void Runtime::two_level_allgather(OpRecord& r, size_t row_bytes, size_t total_bytes) {
+  // Slabs travel through host memory over the ring of all ranks, as with the reference's MPI
+  // ring on a build without GPU-aware MPI; gathers carry little data (sparse gradients, shapes).
+  cudaStream_t s = comm_->stream(0);
+  char* host = (char*)pinned(total_bytes);
+  size_t my_off = 0;
+  for (int i = 0; i < t_.rank; i++) my_off += (size_t)r.dim0[i] * row_bytes;
+  const size_t my_bytes = (size_t)r.dim0[t_.rank] * row_bytes;
+  if (my_bytes) check(cudaMemcpyAsync(host + my_off, r.in, my_bytes, cudaMemcpyDeviceToHost, s), "cudaMemcpyAsync (to host)");
+  check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+  cpu_ring_allgatherv(t_, host + my_off, host, r.dim0, row_bytes, now_s() + opt_.timeout_s);   // own slab already in place
+  if (total_bytes) check(cudaMemcpyAsync(r.out, host, total_bytes, cudaMemcpyHostToDevice, s), "cudaMemcpyAsync (to device)");
+  check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
 }
 
 // ---- stats ---------------------------------------------------------------------------------

@@ -26,6 +26,7 @@
 
 #include "../common.h"
 #include "../control/bootstrap.h"
+#include "../control/node_group.h"
 #include "../control/wire.h"
 
 namespace bc {
@@ -110,6 +111,10 @@ class Runtime {
   int local_size() const { return t_.local_size; }
   bool on_gpu() const { return comm_ != nullptr; }
   gpu::Comm* comm() const { return comm_.get(); }
+  // Hosts of a GPU group that spans several of them (then `comm()` covers the ranks of this host
+  // only and collectives run in two levels); 1 otherwise.
+  int n_nodes() const { return node_ ? node_->n_nodes : 1; }
+  NodeGroup* node_group() const { return node_.get(); }
   const RuntimeOptions& options() const { return opt_; }
 
   // Queue a collective; returns its handle. Throws if the name is already in flight or the
@@ -142,6 +147,10 @@ class Runtime {
   void perform(const Response& resp);
   void perform_allreduce(OpRecord& r);
   void perform_allgather(OpRecord& r, const Response& resp);
+  void two_level_allreduce(OpRecord& r, size_t count, double scale, int64_t idiv);
+  void two_level_allgather(OpRecord& r, size_t row_bytes, size_t total_bytes);
+  void* pinned(size_t bytes);
+  void* device_scratch(size_t bytes);
   void finish(const std::shared_ptr<OpRecord>& r, bool ok, const std::string& err);
   void fail_everything(const std::string& why);
   void wake();
@@ -150,6 +159,11 @@ class Runtime {
   Transport t_;
   int local_rank_ = 0;
   std::unique_ptr<gpu::Comm> comm_;
+  std::unique_ptr<NodeGroup> node_;   // set when the ranks span several hosts (see build_node_group)
+  void* pinned_ = nullptr;            // host staging of the two-level path (background thread only)
+  size_t pinned_bytes_ = 0;
+  void* scratch_ = nullptr;           // device staging of the two-level path
+  size_t scratch_bytes_ = 0;
 
   std::thread thread_;
   int wake_fd_ = -1;

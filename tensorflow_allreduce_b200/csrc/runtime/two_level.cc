@@ -1,0 +1,73 @@
+#include "two_level.h"
+
+#include <string.h>
+
+#include "../cpu/ring.h"
+
+namespace bc {
+
+void two_level_allreduce(NodeGroup& g, LocalLevel& local, void* staging, size_t count, DType dtype, double scale,
+                         int64_t int_divisor, ReduceOp red, double deadline) {
+  local.reduce_in_node(count, dtype, red);
+  const int L = g.local_size;
+  std::vector<size_t> lens(L);
+  for (int i = 0; i < L; i++) lens[i] = slice_len(count, L, i);
+  const size_t begin = slice_begin(count, L, g.local_rank), len = lens[g.local_rank];
+  local.fetch(staging, begin, len, dtype);
+  // The ranks of one rail hold the same slice of their hosts' sums, so the lengths agree.
+  cpu_ring_allreduce(g.rail, staging, len, dtype, scale, int_divisor, deadline, red);
+  local.finish(staging, begin, len, lens, dtype);
+}
+
+namespace {
+
+template <typename T>
+void combine(T* dst, const T* src, size_t n, ReduceOp red) {
+  for (size_t i = 0; i < n; i++) {
+    switch (red) {
+      case ReduceOp::SUM: dst[i] += src[i]; break;
+      case ReduceOp::PROD: dst[i] *= src[i]; break;
+      case ReduceOp::MIN: dst[i] = src[i] < dst[i] ? src[i] : dst[i]; break;
+      case ReduceOp::MAX: dst[i] = src[i] > dst[i] ? src[i] : dst[i]; break;
+    }
+  }
+}
+
+}  // namespace
+
+void HostLocalLevel::reduce_in_node(size_t count, DType dtype, ReduceOp red) {
+  const size_t bytes = count * dtype_size(dtype);
+  std::vector<std::string> all = g_.allgather(std::string(t_, bytes), deadline_);
+  // every member folds the blobs in the same order, so the results agree bit for bit
+  memcpy(t_, all[0].data(), bytes);
+  for (int i = 1; i < g_.local_size; i++) {
+    BC_CHECK(all[i].size() == bytes, "node members passed tensors of different sizes");
+    switch (dtype) {
+      case DType::F32: combine((float*)t_, (const float*)all[i].data(), count, red); break;
+      case DType::F64: combine((double*)t_, (const double*)all[i].data(), count, red); break;
+      case DType::I32: combine((int32_t*)t_, (const int32_t*)all[i].data(), count, red); break;
+      case DType::I64: combine((int64_t*)t_, (const int64_t*)all[i].data(), count, red); break;
+      case DType::U8: combine((uint8_t*)t_, (const uint8_t*)all[i].data(), count, red); break;
+      default: throw Error("HostLocalLevel: unsupported element type");
+    }
+  }
+}
+
+void HostLocalLevel::fetch(void* dst, size_t begin, size_t len, DType dtype) {
+  const size_t e = dtype_size(dtype);
+  if (len) memcpy(dst, t_ + begin * e, len * e);
+}
+
+void HostLocalLevel::finish(const void* src, size_t begin, size_t len, const std::vector<size_t>& lens, DType dtype) {
+  const size_t e = dtype_size(dtype);
+  (void)begin;
+  std::vector<std::string> all = g_.allgather(std::string((const char*)src, len * e), deadline_);
+  size_t off = 0;
+  for (int i = 0; i < g_.local_size; i++) {
+    BC_CHECK(all[i].size() == lens[i] * e, "slice " << i << " arrived with " << all[i].size() << " bytes, expected " << lens[i] * e);
+    if (lens[i]) memcpy(t_ + off, all[i].data(), lens[i] * e);
+    off += lens[i] * e;
+  }
+}
+
+}  // namespace bc

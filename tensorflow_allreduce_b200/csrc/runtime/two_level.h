@@ -1,0 +1,61 @@
+// Allreduce of a job that spans several hosts, in two levels:
+//   1. the ranks of a host reduce the tensor among themselves (on GPUs: the NVLink kernels);
+//   2. the tensor is cut into local_size slices, and local rank j reduces slice j with the ranks
+//      of local rank j on the other hosts over its rail (a ring over the hosts), applying the
+//      averaging there;
+//   3. the ranks of a host gather the finished slices from one another.
+// Every rank moves 2 * (n_nodes - 1) / n_nodes / local_size of the tensor between hosts, against
+// 2 * (size - 1) / size of it in the reference's single ring over all ranks
+// (tensorflow/contrib/mpi_collectives/ring.h:130-133).
+//
+// The levels inside a host are behind an interface: the runtime implements it with the GPU
+// communicator, `HostLocalLevel` with host memory and the node group's control sockets (used to
+// test steps 2 and 3 and the slice arithmetic without a GPU).
+#pragma once
+
+#include <algorithm>
+#include <vector>
+
+#include "../common.h"
+#include "../control/node_group.h"
+
+namespace bc {
+
+class LocalLevel {
+ public:
+  virtual ~LocalLevel() {}
+  // The tensor (count elements) becomes its reduction over the ranks of this host, unscaled.
+  virtual void reduce_in_node(size_t count, DType dtype, ReduceOp red) = 0;
+  // Copy elements [begin, begin + len) of the tensor into host memory at `dst`; complete on return.
+  virtual void fetch(void* dst, size_t begin, size_t len, DType dtype) = 0;
+  // `src` (host memory, len elements) is this rank's finished slice; slice i of the tensor has
+  // slice_len[i] elements. On return of `finish` the tensor holds all slices (on a GPU: the work
+  // is queued on the communicator's stream).
+  virtual void finish(const void* src, size_t begin, size_t len, const std::vector<size_t>& slice_len, DType dtype) = 0;
+};
+
+// Element range of slice i when `count` elements are cut into n slices as evenly as possible
+// (the first count % n slices get one element more): the same rule as the ring's segments.
+inline size_t slice_begin(size_t count, int n, int i) { return (size_t)i * (count / n) + std::min<size_t>((size_t)i, count % n); }
+inline size_t slice_len(size_t count, int n, int i) { return count / n + ((size_t)i < count % n ? 1 : 0); }
+
+// `staging` must hold slice_len(count, local_size, 0) elements. Runs on the thread that owns the
+// rail's sockets.
+void two_level_allreduce(NodeGroup& g, LocalLevel& local, void* staging, size_t count, DType dtype, double scale,
+                         int64_t int_divisor, ReduceOp red, double deadline);
+
+// Host-memory stand-in for the levels inside a host: blobs through the node group's star.
+class HostLocalLevel : public LocalLevel {
+ public:
+  HostLocalLevel(NodeGroup& g, void* tensor, double deadline) : g_(g), t_((char*)tensor), deadline_(deadline) {}
+  void reduce_in_node(size_t count, DType dtype, ReduceOp red) override;
+  void fetch(void* dst, size_t begin, size_t len, DType dtype) override;
+  void finish(const void* src, size_t begin, size_t len, const std::vector<size_t>& slice_len, DType dtype) override;
+
+ private:
+  NodeGroup& g_;
+  char* t_;
+  double deadline_;
+};
+
+}  // namespace bc

@@ -64,6 +64,21 @@ class _Bucket:
         self.done_event = None
 
 
+def _chunks_by_bytes(tensors, limit: int):
+    """Consecutive runs of `tensors` whose sizes add up to at most `limit` bytes (a tensor larger
+    than that forms a run of its own)."""
+    run, size = [], 0
+    for t in tensors:
+        b = t.numel() * t.element_size()
+        if run and size + b > limit:
+            yield run
+            run, size = [], 0
+        run.append(t)
+        size += b
+    if run:
+        yield run
+
+
 def _fused_kind(opt) -> int:
     """1 = SGD, 2 = Adam/AdamW when the wrapped optimizer's options are covered by the fused
     kernels, else 0."""
@@ -122,7 +137,10 @@ class DistributedOptimizer(torch.optim.Optimizer):
         self._step_count = [0 for _ in self.param_groups]
         params = [p for g in self.param_groups for p in g["params"] if p.requires_grad]
         self._all_params = params
-        self._gpu = core.on_gpu() and len(params) > 0 and all(p.is_cuda for p in params)
+        # Gradient buckets in symmetric memory and ordered launches need all ranks on one host; a
+        # group over several hosts averages flat copies of the gradients through the negotiated
+        # (two-level) allreduce and runs the wrapped optimizer's own step.
+        self._gpu = core.on_gpu() and core.n_nodes() == 1 and len(params) > 0 and all(p.is_cuda for p in params)
         kind = _fused_kind(optimizer) if (fused is None or fused) else 0
         if fused and not kind:
             raise ValueError(f"{type(optimizer).__name__} with these options has no fused update")
@@ -414,16 +432,33 @@ class DistributedOptimizer(torch.optim.Optimizer):
         return loss
 
     def _reduce_cpu(self):
+        """Average every gradient with the negotiated allreduce: one collective per tensor on the
+        CPU (as the reference does, `mpi_collectives/__init__.py:199-220`), flat buffers of up to
+        `bucket_mb` per dtype for CUDA gradients of a group that spans hosts."""
         handles = []
         idx = 0
+        flat = {}            # (dtype, device) -> dense CUDA gradients, in parameter order
         for g in self.param_groups:
             for p in g["params"]:
                 if p.grad is not None:
                     if p.grad.is_sparse:
                         p.grad = core.allreduce(p.grad, average=True, name=f"{self.name}.grad.{idx}")
+                    elif p.grad.is_cuda:
+                        flat.setdefault((p.grad.dtype, p.grad.device), []).append(p.grad)
                     else:
                         handles.append(core.allreduce_async(p.grad, average=True, name=f"{self.name}.grad.{idx}", out=p.grad))
                 idx += 1
+        limit = int(core.config().bucket_mb * (1 << 20))
+        n = 0
+        for (dtype, _), grads in flat.items():
+            for chunk in _chunks_by_bytes(grads, limit):
+                buf = torch.cat([t.reshape(-1) for t in chunk])
+                core.allreduce_(buf, average=True, name=f"{self.name}.flat.{n}")
+                n += 1
+                off = 0
+                for t in chunk:
+                    t.copy_(buf[off:off + t.numel()].view_as(t))
+                    off += t.numel()
         for h in handles:
             h.wait()
 

@@ -1,0 +1,93 @@
+"""Groups whose ranks sit on several hosts: node groups, rails and the two-level allreduce, with
+one machine standing in for the hosts (every rank reports a host name of the test's choosing) and
+host memory standing in for the GPUs. The reference reaches other hosts through MPI
+(tensorflow/contrib/mpi_collectives/ring.h:183-225, mpi_ops.cc:609-613)."""
+import pytest
+
+from _util import run
+
+
+def _hosts(nranks, per_host, interleaved=False):
+    n_hosts = nranks // per_host
+    env = {}
+    for r in range(nranks):
+        h = r % n_hosts if interleaved else r // per_host
+        env[r] = {"BC_HOSTNAME": f"host{h}", "LOCAL_RANK": "-1", "BC_NODE_GROUPS": "1"}
+    return env
+
+
+BODY = """
+import ctypes as C
+from tensorflow_allreduce_b200 import _lib
+bc.init(device="cpu")
+lib = _lib.lib()
+bad = []
+from tensorflow_allreduce_b200.core import _DTYPES
+for dtype in (torch.float32, torch.float64, torch.int32, torch.int64):
+    for count in (0, 1, 3, 17, 1000, 4099):
+        for op, average in ((0, 0), (0, 1), (2, 0), (3, 0)):
+            g = torch.Generator().manual_seed(count * 7 + op)
+            per_rank = [(torch.randint(-50, 50, (count,), generator=g) + r).to(dtype) for r in range(SIZE)]
+            t = per_rank[RANK].clone()
+            rc = lib.bc_two_level_allreduce_host(C.c_void_p(t.data_ptr()), count, _DTYPES[dtype], average, op)
+            if rc != 0:
+                bad.append(["rc", str(dtype), count, op, _lib.last_error()]); continue
+            stack = torch.stack(per_rank) if count else torch.zeros(SIZE, 0, dtype=dtype)
+            if op == 0:
+                want = stack.sum(0)
+                if average:
+                    want = want / SIZE if dtype.is_floating_point else torch.div(want, SIZE, rounding_mode="trunc")
+            elif op == 2:
+                want = stack.min(0).values if count else stack[0]
+            else:
+                want = stack.max(0).values if count else stack[0]
+            ok = torch.allclose(t.double(), want.double(), rtol=1e-6, atol=1e-6)
+            if not ok:
+                bad.append([str(dtype), count, op, average])
+# the job-wide collectives still work next to the node groups
+s = bc.allreduce(torch.tensor([float(RANK)]), average=False)
+emit(bad=bad, nodes=bc.n_nodes(), node=bc.node_index(), local_rank=bc.local_rank(), local_size=bc.local_size(), s=s.item())
+bc.shutdown()
+"""
+
+
+@pytest.mark.parametrize("nranks,per_host,interleaved", [(4, 2, False), (6, 2, True), (6, 3, False), (3, 1, False)])
+def test_two_level_allreduce_over_fake_hosts(nranks, per_host, interleaved):
+    res = run(BODY, nranks=nranks, per_rank_env=_hosts(nranks, per_host, interleaved), timeout=180)
+    n_hosts = nranks // per_host
+    for r, (_, rec) in enumerate(res):
+        assert rec["bad"] == []
+        assert rec["nodes"] == n_hosts and rec["local_size"] == per_host
+        assert rec["node"] == (r % n_hosts if interleaved else r // per_host)
+        assert rec["local_rank"] == (r // n_hosts if interleaved else r % per_host)
+        assert rec["s"] == sum(range(nranks))
+
+
+def test_one_host_has_no_node_groups():
+    res = run("""
+    import ctypes as C
+    from tensorflow_allreduce_b200 import _lib
+    bc.init(device="cpu")
+    t = torch.ones(4)
+    rc = _lib.lib().bc_two_level_allreduce_host(C.c_void_p(t.data_ptr()), 4, 0, 0, 0)
+    emit(nodes=bc.n_nodes(), rc=rc, err=_lib.last_error())
+    bc.shutdown()
+    """, nranks=2, env={"BC_NODE_GROUPS": "1"})
+    for _, rec in res:
+        assert rec["nodes"] == 1 and rec["rc"] != 0 and "one host" in rec["err"]
+
+
+def test_hosts_with_different_rank_counts_are_refused():
+    env = {0: {"BC_HOSTNAME": "hostA"}, 1: {"BC_HOSTNAME": "hostA"}, 2: {"BC_HOSTNAME": "hostB"}}
+    for e in env.values():
+        e.update({"LOCAL_RANK": "-1", "BC_NODE_GROUPS": "1"})
+    res = run("""
+    try:
+        bc.init(device="cpu")
+        emit(ok=True)
+        bc.shutdown()
+    except Exception as e:
+        emit(ok=False, err=str(e))
+    """, nranks=3, per_rank_env=env)
+    for _, rec in res:
+        assert not rec["ok"] and "same number of ranks" in rec["err"] and "hostB" in rec["err"]
