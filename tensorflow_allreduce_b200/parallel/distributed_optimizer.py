@@ -434,16 +434,17 @@ class DistributedOptimizer(torch.optim.Optimizer):
     def _reduce_cpu(self):
         """Average every gradient with the negotiated allreduce: one collective per tensor on the
         CPU (as the reference does, `mpi_collectives/__init__.py:199-220`), flat buffers of up to
-        `bucket_mb` per dtype for CUDA gradients of a group that spans hosts."""
+        `bucket_mb` per dtype for CUDA gradients and for every group that runs in two levels."""
         handles = []
         idx = 0
-        flat = {}            # (dtype, device) -> dense CUDA gradients, in parameter order
+        flat = {}            # (dtype, device) -> dense gradients that travel in flat buffers, in parameter order
+        two_level = core.n_nodes() > 1
         for g in self.param_groups:
             for p in g["params"]:
                 if p.grad is not None:
                     if p.grad.is_sparse:
                         p.grad = core.allreduce(p.grad, average=True, name=f"{self.name}.grad.{idx}")
-                    elif p.grad.is_cuda:
+                    elif p.grad.is_cuda or two_level:
                         flat.setdefault((p.grad.dtype, p.grad.device), []).append(p.grad)
                     else:
                         handles.append(core.allreduce_async(p.grad, average=True, name=f"{self.name}.grad.{idx}", out=p.grad))

@@ -91,3 +91,32 @@ def test_hosts_with_different_rank_counts_are_refused():
     """, nranks=3, per_rank_env=env)
     for _, rec in res:
         assert not rec["ok"] and "same number of ranks" in rec["err"] and "hostB" in rec["err"]
+
+
+def test_distributed_optimizer_uses_flat_buffers_in_a_two_level_group():
+    # 2 hosts x 2 ranks: gradients are averaged in flat buffers (two with this small bucket
+    # size), and the
+    # result equals the single-process large-batch run.
+    res = run("""
+    bc.init(device="cpu")
+    def make():
+        torch.manual_seed(0)
+        return torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.Tanh(), torch.nn.Linear(32, 4))
+    mine, ref = make(), make()
+    o_mine = bc.DistributedOptimizer(torch.optim.SGD(mine.parameters(), lr=0.05, momentum=0.9))
+    o_ref = torch.optim.SGD(ref.parameters(), lr=0.05, momentum=0.9)
+    g = torch.Generator().manual_seed(5)
+    X = torch.randn(4, 8 * SIZE, 16, generator=g); Y = torch.randn(4, 8 * SIZE, 4, generator=g)
+    for it in range(4):
+        o_ref.zero_grad(); torch.nn.functional.mse_loss(ref(X[it]), Y[it]).backward(); o_ref.step()
+        sl = slice(RANK * 8, (RANK + 1) * 8)
+        o_mine.zero_grad(); torch.nn.functional.mse_loss(mine(X[it][sl]), Y[it][sl]).backward(); o_mine.step()
+    worst = max((a - b).abs().max().item() for a, b in zip(ref.parameters(), mine.parameters()))
+    names = sorted({s["name"] for s in bc.stats() if ".flat." in s["name"]})
+    emit(worst=worst, names=names, nodes=bc.n_nodes())
+    bc.shutdown()
+    """, nranks=4, per_rank_env=_hosts(4, 2), env={"BC_BUCKET_MB": "0.001"})
+    for _, rec in res:
+        assert rec["worst"] < 1e-6 and rec["nodes"] == 2
+        # 1048-byte buckets: the first weight (2048 bytes) alone, the other three tensors together
+        assert rec["names"] == ["DistributedSGD.flat.0", "DistributedSGD.flat.1"]
