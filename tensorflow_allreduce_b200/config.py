@@ -5,7 +5,11 @@ build-time MPI switch (`configure:823-897`). Everything here is new: algorithm c
 size, grid caps, deadlines, symmetric-memory sizes, NVLS on/off and the log level
 (`BC_LOG_LEVEL`, read by the native side). Read elsewhere: `BC_STATS_JSONL` (per-collective records
 appended at shutdown, `core.py`), `BC_NVTX` (`csrc/nvtx.cc`), `BC_DEBUG_KERNELS` (bounds-checked
-build, `_lib.py`), `BC_GRU_TIMEOUT_S` (`ops/persistent_gru.py`).
+build, `_lib.py`), `BC_GRU_TIMEOUT_S` (`ops/persistent_gru.py`), and by the native runtime at
+`init()`: `BC_SHM` (0 = CPU tensors of ranks on one host use the socket ring instead of shared
+memory), `BC_SHM_SLOT_KB` (chunk per rank in the shared segment, default 512), `BC_NODE_GROUPS`
+(1 = build the node groups and rails of a job over several hosts for a CPU group too),
+`BC_HOSTNAME` (the host name this rank reports).
 """
 from __future__ import annotations
 

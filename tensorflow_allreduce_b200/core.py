@@ -531,11 +531,11 @@ def stats() -> List[dict]:
     if not raw:
         raise CollectiveError(_lib.last_error())
     ops = {0: "allreduce", 1: "allgather", 2: "host_gather", 3: "shutdown"}
-    algos = {0: "cpu_ring", 1: "one_shot", 2: "two_shot", 3: "nvls"}
+    algos = {0: "cpu_ring", 1: "one_shot", 2: "two_shot", 3: "nvls", 4: "cpu_shm"}
     out = json.loads(raw.decode())
     for e in out:
         e["op"] = ops.get(e["op"], str(e["op"]))
-        e["algo"] = algos.get(e["algo"], str(e["algo"])) if e["device"] == 1 else "cpu_ring"
+        e["algo"] = algos.get(e["algo"], str(e["algo"])) if (e["device"] == 1 or e["algo"] == 4) else "cpu_ring"
         e["negotiation_us"] = (e["t_negotiated"] - e["t_enqueue"]) * 1e6
     return out
 

@@ -5,6 +5,7 @@
 #include <stdarg.h>
 #include <string.h>
 #include <sys/eventfd.h>
+#include <sys/socket.h>
 #include <unistd.h>
 
 #include <algorithm>
@@ -54,6 +55,7 @@ FaultSpec FaultSpec::parse(const std::string& s) {
       else if (kind == "delay_ms") { f.kind = DELAY_MS; if (eq != std::string::npos) f.ms = atoi(tok.c_str() + eq + 1); }
       else if (kind == "exit_before") f.kind = EXIT_BEFORE;
       else if (kind == "close_ctrl") f.kind = CLOSE_CTRL;
+      else if (kind == "exit_in_collective") f.kind = EXIT_IN_COLLECTIVE;
       else throw Error("unknown fault kind '" + kind + "'");
     } else {
       size_t eq = tok.find('=');
@@ -107,6 +109,38 @@ Runtime::Runtime(const RuntimeOptions& o) : opt_(o) {
       Transport* tp = &t_;
       gpu::HostAllgather ag = [tp, dl](const std::string& mine) { return tp->allgather(mine, now_s() + dl); };
       comm_.reset(new gpu::Comm(t_.rank, t_.size, o.device, t_.job_id, cc, ag, o.timeout_s));
+    }
+  }
+  // All ranks on this host: CPU tensors go through a shared-memory segment instead of the socket
+  // ring. BC_SHM=0 keeps the sockets, BC_SHM_SLOT_KB sets the chunk per rank.
+  const char* shm_env = getenv("BC_SHM");
+  if (t_.size > 1 && t_.local_size == t_.size && !(shm_env && atoi(shm_env) == 0)) {
+    const char* kb = getenv("BC_SHM_SLOT_KB");
+    const size_t slot = (size_t)std::max(4, kb ? atoi(kb) : 512) << 10;
+    char name[96];
+    snprintf(name, sizeof(name), "bcoll-%016llx-shm", (unsigned long long)t_.job_id);
+    Transport* tp = &t_;
+    const double dl = o.timeout_s;
+    try {
+      // The ring's sockets carry nothing while shared memory is in use, so end-of-file on one of
+      // them means that the neighbour's process has ended (the kernel closes its sockets even
+      // before the process is reaped).
+      auto peer_lost = [tp]() -> std::string {
+        const Socket* socks[2] = {&tp->ring_prev, &tp->ring_next};
+        for (const Socket* s : socks) {
+          char c;
+          if (s->valid() && ::recv(s->fd(), &c, 1, MSG_PEEK | MSG_DONTWAIT) == 0)
+            return std::string("the process of ring neighbour ") + (s == socks[0] ? "before" : "after") + " this rank has ended";
+        }
+        return std::string();
+      };
+      shm_.reset(new ShmGroup(t_.rank, t_.size, name, slot, [tp, dl](const std::string& mine) { return tp->allgather(mine, now_s() + dl); },
+                              peer_lost));
+    } catch (const CommLost&) {
+      throw;
+    } catch (const Error& e) {
+      // Every rank learns of a failed set-up in the same exchange, so all of them stay on sockets.
+      BC_LOG(1, "%s; CPU tensors use the socket ring", e.what());
     }
   }
   wake_fd_ = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
@@ -494,6 +528,19 @@ void Runtime::perform(const Response& resp) {
   }
   rec->t_negotiated = now_s();
   BC_LOG(2, "perform '%s' type=%d", rec->name.c_str(), (int)resp.type);
+  {
+    FaultSpec f;
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      f = fault_;
+    }
+    if (f.kind == FaultSpec::EXIT_IN_COLLECTIVE && f.matches(t_.rank, rec->name)) {
+      // The go-ahead has arrived and the peers are entering the data phase: leave now.
+      fprintf(stderr, "[bcoll] fault injection: exiting inside '%s'\n", rec->name.c_str());
+      fflush(stderr);
+      _exit(42);
+    }
+  }
   NvtxRange range(resp.type == ResponseType::ALLGATHER ? "bcoll.allgather" : resp.type == ResponseType::ALLREDUCE ? "bcoll.allreduce" : "bcoll.control");
   try {
     switch (resp.type) {
@@ -534,8 +581,11 @@ void Runtime::perform_allreduce(OpRecord& r) {
   const int64_t idiv = r.average ? t_.size : 1;
   if (r.device == DeviceKind::CPU) {
     if (r.in != r.out && count) memcpy(r.out, r.in, count * dtype_size(r.dtype));
-    cpu_ring_allreduce(t_, r.out, count, r.dtype, scale, idiv, now_s() + opt_.timeout_s, r.red);
-    r.algo = 0;
+    if (shm_)
+      shm_->allreduce(r.out, count, r.dtype, scale, idiv, r.red, now_s() + opt_.timeout_s);
+    else
+      cpu_ring_allreduce(t_, r.out, count, r.dtype, scale, idiv, now_s() + opt_.timeout_s, r.red);
+    r.algo = shm_ ? 4 : 0;
     return;
   }
   BC_CHECK(comm_, "GPU collective without a GPU communicator");
@@ -569,7 +619,11 @@ void Runtime::perform_allgather(OpRecord& r, const Response& resp) {
   const size_t total_bytes = (size_t)total_rows * row_bytes;
   BC_CHECK(r.out || total_bytes == 0, "the output allocator returned no buffer");
   if (r.device == DeviceKind::CPU) {
-    cpu_ring_allgatherv(t_, r.in, r.out, r.dim0, row_bytes, now_s() + opt_.timeout_s);
+    if (shm_)
+      shm_->allgatherv(r.in, r.out, r.dim0, row_bytes, now_s() + opt_.timeout_s);
+    else
+      cpu_ring_allgatherv(t_, r.in, r.out, r.dim0, row_bytes, now_s() + opt_.timeout_s);
+    r.algo = shm_ ? 4 : 0;
     return;
   }
   BC_CHECK(comm_, "GPU collective without a GPU communicator");

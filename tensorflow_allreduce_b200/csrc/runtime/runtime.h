@@ -28,6 +28,7 @@
 #include "../control/bootstrap.h"
 #include "../control/node_group.h"
 #include "../control/wire.h"
+#include "../cpu/shm_group.h"
 
 namespace bc {
 
@@ -83,7 +84,7 @@ struct RuntimeOptions {
 };
 
 struct FaultSpec {
-  enum Kind { NONE, DROP_REQUEST, DELAY_MS, EXIT_BEFORE, CLOSE_CTRL } kind = NONE;
+  enum Kind { NONE, DROP_REQUEST, DELAY_MS, EXIT_BEFORE, CLOSE_CTRL, EXIT_IN_COLLECTIVE } kind = NONE;
   int rank = -1;           // -1 = any rank
   std::string name;        // empty = any name
   int ms = 0;
@@ -160,6 +161,7 @@ class Runtime {
   int local_rank_ = 0;
   std::unique_ptr<gpu::Comm> comm_;
   std::unique_ptr<NodeGroup> node_;   // set when the ranks span several hosts (see build_node_group)
+  std::unique_ptr<ShmGroup> shm_;     // CPU tensors of a job whose ranks all run on this host (BC_SHM=0: sockets)
   void* pinned_ = nullptr;            // host staging of the two-level path (background thread only)
   size_t pinned_bytes_ = 0;
   void* scratch_ = nullptr;           // device staging of the two-level path

@@ -59,7 +59,7 @@ static void rank_main(int rank, int size, int port) {
     EXPECT(rt.rank() == rank && rt.size() == size, "rank/size");
 
     // many named allreduces in flight at once, enqueued in a rank-dependent order
-    const int K = 16, n = 1000;
+    const int K = 16, n = 5000;   // 20 kB: several chunks when the shared-memory slots are small
     std::vector<std::vector<float>> in(K, std::vector<float>(n)), out(K, std::vector<float>(n));
     std::vector<int64_t> h(K);
     for (int k = 0; k < K; k++)

@@ -22,7 +22,10 @@ def emit(**kw):
 
 def run(body: str, nranks: int = 2, timeout: float = 120.0, env=None, per_rank_env=None, gpus=False, expect_ok=True):
     env = dict(env or {})
-    env.setdefault("BC_TIMEOUT_S", "60")       # a stuck host-side wait reports itself before the runner's deadline
+    if not gpus:
+        # A stuck host-side wait reports itself before the runner's deadline. GPU ranks keep the
+        # library's default: context creation and the first launches can take a while on a cold box.
+        env.setdefault("BC_TIMEOUT_S", str(max(10, int(timeout * 0.8))))
     res = run_script(PRELUDE + textwrap.dedent(body), nranks, timeout=timeout, env=env, per_rank_env=per_rank_env, gpus=gpus,
                      dump_stacks=True)
     out = []

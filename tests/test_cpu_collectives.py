@@ -6,6 +6,14 @@ import pytest
 
 from _util import run
 
+# CPU tensors of ranks on one host travel through shared memory by default and over the socket
+# ring with BC_SHM=0 (the ring is also what ranks on different hosts use).
+TRANSPORTS = pytest.mark.parametrize("transport", ["shm", "ring"])
+
+
+def _tenv(transport):
+    return {"BC_SHM": "0"} if transport == "ring" else {"BC_SHM_SLOT_KB": "4"}      # 4 KiB slots: many chunks per tensor
+
 
 def test_rank_size_single_process():
     # Without a launcher the library falls back to rank 0 / size 1 (mpi_ops_test.py:61-62).
@@ -57,7 +65,8 @@ def test_ompi_env_names():
     assert all(r[1]["size"] == 2 for r in res)
 
 
-def test_plumbing_config_world2():
+@TRANSPORTS
+def test_plumbing_config_world2(transport):
     res = run("""
     bc.init(device="cpu")
     ok = True; worst = 0.0
@@ -77,14 +86,15 @@ def test_plumbing_config_world2():
     want = torch.cat([(r * 100 + torch.arange((r + 2) * 4, dtype=torch.float32)).reshape(r + 2, 4) for r in range(SIZE)])
     emit(ok=bool(ok), worst=worst, gshape=list(g.shape), gather_ok=bool(torch.equal(g, want)))
     bc.shutdown()
-    """, nranks=2)
+    """, nranks=2, env=_tenv(transport))
     for _, rec in res:
         assert rec["ok"] and rec["worst"] <= 1e-6
         assert rec["gshape"] == [5, 4] and rec["gather_ok"]
 
 
+@TRANSPORTS
 @pytest.mark.parametrize("n", [2, 3])
-def test_allreduce_cpu_like_reference(n):
+def test_allreduce_cpu_like_reference(n, transport):
     # int32 + float32, 1/2/3-D [17]*dim, same tensor on every rank => expected = tensor * size,
     # exact for size <= 3 (mpi_ops_test.py:84-112).
     res = run("""
@@ -112,12 +122,13 @@ def test_allreduce_cpu_like_reference(n):
                 bad.append([str(dtype), dim, "avg"])
     emit(bad=bad)
     bc.shutdown()
-    """, nranks=n)
+    """, nranks=n, env=_tenv(transport))
     for _, rec in res:
         assert rec["bad"] == []
 
 
-def test_prod_min_max_reductions():
+@TRANSPORTS
+def test_prod_min_max_reductions(transport):
     # The reductions of the reference's NCCL ops (contrib/nccl/python/ops/nccl_ops.py:34-137) on a
     # CPU group of three ranks; a mismatch in the reduction fails on every rank.
     res = run("""
@@ -146,7 +157,7 @@ def test_prod_min_max_reductions():
         refused = True
     emit(bad=bad, helpers=helpers, err=err, refused=refused)
     bc.shutdown()
-    """, nranks=3)
+    """, nranks=3, env=_tenv(transport))
     for _, rec in res:
         assert rec["bad"] == []
         assert rec["helpers"] == [6.0, 24.0, 3, 5]
@@ -154,20 +165,22 @@ def test_prod_min_max_reductions():
         assert rec["refused"]
 
 
-def test_integer_average_truncates():
+@TRANSPORTS
+def test_integer_average_truncates(transport):
     res = run("""
     bc.init(device="cpu")
     t = torch.tensor([RANK * 3 + 1, -(RANK * 3 + 1), 7], dtype=torch.int32)
     emit(avg=bc.allreduce(t, average=True).tolist())
     bc.shutdown()
-    """, nranks=2)
+    """, nranks=2, env=_tenv(transport))
     # sums: [5, -5, 14] -> truncating division by 2
     for _, rec in res:
         assert rec["avg"] == [2, -2, 7]
 
 
+@TRANSPORTS
 @pytest.mark.parametrize("n", [2, 3])
-def test_allgather_fixed_and_variable(n):
+def test_allgather_fixed_and_variable(n, transport):
     res = run("""
     bc.init(device="cpu")
     bad = []
@@ -196,7 +209,7 @@ def test_allgather_fixed_and_variable(n):
     if list(z.shape) != [0, 3]: bad.append(["empty-allreduce"])
     emit(bad=bad)
     bc.shutdown()
-    """, nranks=n)
+    """, nranks=n, env=_tenv(transport))
     for _, rec in res:
         assert rec["bad"] == []
 
@@ -238,7 +251,8 @@ def test_broadcast_and_named_out_of_order():
         assert rec["objs"] == [{"r": 0}, {"r": 1}]
 
 
-def test_dependent_allreduce_chain():
+@TRANSPORTS
+def test_dependent_allreduce_chain(transport):
     # Chained add -> allreduce stages with a closed-form result, as the reference's stress test
     # (mpi_allreduce_test.py:35-128), shortened for the CPU path.
     res = run("""
@@ -255,5 +269,5 @@ def test_dependent_allreduce_chain():
         ok = ok and bool(torch.allclose(x, torch.full_like(x, want)))
     emit(ok=ok)
     bc.shutdown()
-    """, nranks=2)
+    """, nranks=2, env=_tenv(transport))
     assert all(rec["ok"] for _, rec in res)

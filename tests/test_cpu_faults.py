@@ -1,8 +1,10 @@
 """Failure detection, exercised on the host only (CPU ranks, no GPU involved): a request that is
-never sent, a late rank, a rank that exits, a control connection that closes. The reference has
+never sent, a late rank, a rank that exits (before or inside a collective), a control connection that closes. The reference has
 none of this: a missing rank blocks everyone in MPI_Probe for ever
 (tensorflow/contrib/mpi_collectives/mpi_ops.cc:684,763)."""
 import time
+
+import pytest
 
 from _util import run
 
@@ -77,3 +79,31 @@ def test_closed_control_connection_is_detected():
     """, nranks=2, env={"BC_TIMEOUT_S": "10", "BC_FAULT": "close_ctrl:rank=1:name=x"}, timeout=60, expect_ok=False)
     for r, rec in res:
         assert rec is not None and rec["err"] is not None
+
+
+@pytest.mark.parametrize("transport", ["shm", "ring"])
+def test_rank_exit_inside_the_data_phase_is_detected(transport):
+    # Rank 2 leaves after the go-ahead, when the others are already exchanging data: over sockets
+    # they see the closed connection, in shared memory the waiting ranks notice that the process
+    # is gone. Either way well before the 60 s deadline.
+    env = {"BC_TIMEOUT_S": "60", "BC_FAULT": "exit_in_collective:rank=2:name=doomed"}
+    if transport == "ring":
+        env["BC_SHM"] = "0"
+    t0 = time.time()
+    res = run("""
+    import time
+    bc.init(device="cpu")
+    bc.allreduce(torch.ones(4), name="warm")
+    t0 = time.time()
+    try:
+        bc.allreduce(torch.ones(100000), name="doomed")
+        err = None
+    except bc.CollectiveError as e:
+        err = str(e)
+    emit(err=err, seconds=time.time() - t0)
+    """, nranks=3, env=env, timeout=100, expect_ok=False)
+    assert res[2][0].returncode == 42            # the injected exit
+    for r in (0, 1):
+        rec = res[r][1]
+        assert rec is not None, res[r][0].stderr[-2000:]
+        assert rec["err"] is not None and rec["seconds"] < 20, rec

@@ -87,7 +87,7 @@ def test_stats_jsonl_is_written_at_shutdown(tmp_path):
         recs = [json.loads(l) for l in open(path.replace("{rank}", str(r)))]
         names = {e["name"]: e for e in recs}
         assert names["x"]["op"] == "allreduce" and names["x"]["bytes"] == 400 and names["x"]["rank"] == r
-        assert names["y"]["op"] == "allgather" and names["y"]["algo"] == "cpu_ring" and names["y"]["device"] == "cpu"
+        assert names["y"]["op"] == "allgather" and names["y"]["algo"] == "cpu_shm" and names["y"]["device"] == "cpu"
 
 
 def test_gru_workspace_size_and_dimension_checks(native_lib):
