@@ -204,10 +204,11 @@ def on_gpu() -> bool:
 
 
 def n_nodes() -> int:
-    """Hosts of a group that runs in two levels, else 1. A GPU group whose ranks sit on several
-    hosts reduces inside each host with the NVLink kernels and between hosts over sockets (the
-    reference crosses hosts through MPI, `ring.h:183-225`); the gradient buckets in symmetric
-    memory and the fused update need all ranks on one host and are switched off then."""
+    """Hosts of a group that runs in two levels, else 1. A group whose ranks sit on several hosts
+    (the same number on each) reduces inside each host first, GPU tensors with the NVLink kernels
+    and CPU tensors in shared memory, and between hosts over sockets (the reference crosses hosts
+    through MPI, `ring.h:183-225`); the gradient buckets in symmetric memory and the fused update
+    need all ranks on one host and are switched off then."""
     return _call(_lib.lib().bc_n_nodes())
 
 

@@ -28,8 +28,9 @@ int bc_local_rank(void);
 int bc_local_size(void);
 int bc_on_gpu(void);
 int bc_broken(void);
-/* Hosts of a group that runs in two levels (a GPU group whose ranks span several hosts, or any
- * group started with BC_NODE_GROUPS=1), else 1; and this rank's host among them. With more than
+/* Hosts of a group that runs in two levels (ranks on several hosts: always for a GPU group, for a
+ * CPU group when every host runs several ranks or BC_NODE_GROUPS=1), else 1; and this rank's
+ * host among them. With more than
  * one host the ordered launches, the fused update and user segments of symmetric memory are
  * refused: use the negotiated collectives. */
 int bc_n_nodes(void);

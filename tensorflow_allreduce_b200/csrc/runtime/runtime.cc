@@ -80,11 +80,17 @@ Runtime::Runtime(const RuntimeOptions& o) : opt_(o) {
   fault_ = FaultSpec::parse(o.fault);
   // Ranks on several hosts: GPU collectives run in two levels (NVLink kernels inside a host, a
   // ring of sockets between hosts). BC_NODE_GROUPS=1 builds the groups for a CPU job as well.
-  const char* want_groups = getenv("BC_NODE_GROUPS");
-  if (t_.local_size != t_.size && (o.device >= 0 || (want_groups && atoi(want_groups) > 0))) {
+  // A CPU job gets them when its hosts run several ranks each (then CPU tensors are reduced in
+  // shared memory inside a host first); BC_NODE_GROUPS=1 / 0 forces / forbids them there.
+  const char* groups_env = getenv("BC_NODE_GROUPS");
+  const int want_groups = groups_env ? atoi(groups_env) : -1;
+  if (t_.local_size != t_.size) {
     std::string why;
-    BC_CHECK(hosts_are_uniform(t_, &why), "GPU collectives over several hosts need the same number of ranks on each (" << why << ")");
-    node_.reset(new NodeGroup(build_node_group(t_, now_s() + o.timeout_s)));
+    const bool uniform = hosts_are_uniform(t_, &why);
+    if (o.device >= 0 || want_groups > 0)
+      BC_CHECK(uniform, "collectives in two levels need the same number of ranks on every host (" << why << ")");
+    if (o.device >= 0 || want_groups > 0 || (want_groups != 0 && uniform && t_.local_size > 1))
+      node_.reset(new NodeGroup(build_node_group(t_, now_s() + o.timeout_s)));
   }
   if (o.device >= 0) {
     gpu::CommConfig cc;
@@ -114,13 +120,20 @@ Runtime::Runtime(const RuntimeOptions& o) : opt_(o) {
   // All ranks on this host: CPU tensors go through a shared-memory segment instead of the socket
   // ring. BC_SHM=0 keeps the sockets, BC_SHM_SLOT_KB sets the chunk per rank.
   const char* shm_env = getenv("BC_SHM");
-  if (t_.size > 1 && t_.local_size == t_.size && !(shm_env && atoi(shm_env) == 0)) {
+  const bool one_host = t_.size > 1 && t_.local_size == t_.size;
+  const bool host_level = node_ && node_->local_size > 1;
+  if ((one_host || host_level) && !(shm_env && atoi(shm_env) == 0)) {
     const char* kb = getenv("BC_SHM_SLOT_KB");
     const size_t slot = (size_t)std::max(4, kb ? atoi(kb) : 512) << 10;
     char name[96];
-    snprintf(name, sizeof(name), "bcoll-%016llx-shm", (unsigned long long)t_.job_id);
+    snprintf(name, sizeof(name), "bcoll-%016llx-shm-%d", (unsigned long long)t_.job_id, host_level ? node_->node_index : 0);
     Transport* tp = &t_;
+    NodeGroup* ng = node_.get();
     const double dl = o.timeout_s;
+    const int my = host_level ? ng->local_rank : t_.rank, n = host_level ? ng->local_size : t_.size;
+    ShmGroup::Allgather ag = [tp, ng, host_level, dl](const std::string& mine) {
+      return host_level ? ng->allgather(mine, now_s() + dl) : tp->allgather(mine, now_s() + dl);
+    };
     try {
       // The ring's sockets carry nothing while shared memory is in use, so end-of-file on one of
       // them means that the neighbour's process has ended (the kernel closes its sockets even
@@ -134,8 +147,7 @@ Runtime::Runtime(const RuntimeOptions& o) : opt_(o) {
         }
         return std::string();
       };
-      shm_.reset(new ShmGroup(t_.rank, t_.size, name, slot, [tp, dl](const std::string& mine) { return tp->allgather(mine, now_s() + dl); },
-                              peer_lost));
+      shm_.reset(new ShmGroup(my, n, name, slot, ag, peer_lost));
     } catch (const CommLost&) {
       throw;
     } catch (const Error& e) {
@@ -581,10 +593,17 @@ void Runtime::perform_allreduce(OpRecord& r) {
   const int64_t idiv = r.average ? t_.size : 1;
   if (r.device == DeviceKind::CPU) {
     if (r.in != r.out && count) memcpy(r.out, r.in, count * dtype_size(r.dtype));
-    if (shm_)
-      shm_->allreduce(r.out, count, r.dtype, scale, idiv, r.red, now_s() + opt_.timeout_s);
-    else
-      cpu_ring_allreduce(t_, r.out, count, r.dtype, scale, idiv, now_s() + opt_.timeout_s, r.red);
+    const double deadline = now_s() + opt_.timeout_s;
+    if (shm_ && node_) {
+      // several hosts with several ranks each: shared memory inside the host, rails between hosts
+      ShmLocalLevel local(*shm_, r.out, deadline);
+      cpu_staging_.resize(slice_len(count, node_->local_size, 0) * dtype_size(r.dtype) + 16);
+      bc::two_level_allreduce(*node_, local, cpu_staging_.data(), count, r.dtype, scale, idiv, r.red, deadline);
+    } else if (shm_) {
+      shm_->allreduce(r.out, count, r.dtype, scale, idiv, r.red, deadline);
+    } else {
+      cpu_ring_allreduce(t_, r.out, count, r.dtype, scale, idiv, deadline, r.red);
+    }
     r.algo = shm_ ? 4 : 0;
     return;
   }
@@ -619,11 +638,11 @@ void Runtime::perform_allgather(OpRecord& r, const Response& resp) {
   const size_t total_bytes = (size_t)total_rows * row_bytes;
   BC_CHECK(r.out || total_bytes == 0, "the output allocator returned no buffer");
   if (r.device == DeviceKind::CPU) {
-    if (shm_)
+    if (shm_ && !node_)
       shm_->allgatherv(r.in, r.out, r.dim0, row_bytes, now_s() + opt_.timeout_s);
     else
       cpu_ring_allgatherv(t_, r.in, r.out, r.dim0, row_bytes, now_s() + opt_.timeout_s);
-    r.algo = shm_ ? 4 : 0;
+    r.algo = (shm_ && !node_) ? 4 : 0;
     return;
   }
   BC_CHECK(comm_, "GPU collective without a GPU communicator");

@@ -161,7 +161,9 @@ class Runtime {
   int local_rank_ = 0;
   std::unique_ptr<gpu::Comm> comm_;
   std::unique_ptr<NodeGroup> node_;   // set when the ranks span several hosts (see build_node_group)
-  std::unique_ptr<ShmGroup> shm_;     // CPU tensors of a job whose ranks all run on this host (BC_SHM=0: sockets)
+  std::unique_ptr<ShmGroup> shm_;     // CPU tensors among the ranks of this host: the whole job, or with node_ this
+                                      // host's level of a two-level allreduce (BC_SHM=0: sockets only)
+  std::vector<char> cpu_staging_;     // this rank's slice on its way over the rail (background thread only)
   void* pinned_ = nullptr;            // host staging of the two-level path (background thread only)
   size_t pinned_bytes_ = 0;
   void* scratch_ = nullptr;           // device staging of the two-level path

@@ -3,6 +3,7 @@
 #include <string.h>
 
 #include "../cpu/ring.h"
+#include "../cpu/shm_group.h"
 
 namespace bc {
 
@@ -34,6 +35,22 @@ void combine(T* dst, const T* src, size_t n, ReduceOp red) {
 }
 
 }  // namespace
+
+void ShmLocalLevel::reduce_in_node(size_t count, DType dtype, ReduceOp red) {
+  shm_.allreduce(t_, count, dtype, 1.0, 1, red, deadline_);
+}
+
+void ShmLocalLevel::fetch(void* dst, size_t begin, size_t len, DType dtype) {
+  const size_t e = dtype_size(dtype);
+  if (len) memcpy(dst, t_ + begin * e, len * e);
+}
+
+void ShmLocalLevel::finish(const void* src, size_t begin, size_t len, const std::vector<size_t>& lens, DType dtype) {
+  (void)begin;
+  (void)len;
+  std::vector<int64_t> rows(lens.begin(), lens.end());     // one "row" per element
+  shm_.allgatherv(src, t_, rows, dtype_size(dtype), deadline_);
+}
 
 void HostLocalLevel::reduce_in_node(size_t count, DType dtype, ReduceOp red) {
   const size_t bytes = count * dtype_size(dtype);

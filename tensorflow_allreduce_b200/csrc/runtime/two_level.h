@@ -9,8 +9,8 @@
 // (tensorflow/contrib/mpi_collectives/ring.h:130-133).
 //
 // The levels inside a host are behind an interface: the runtime implements it with the GPU
-// communicator, `HostLocalLevel` with host memory and the node group's control sockets (used to
-// test steps 2 and 3 and the slice arithmetic without a GPU).
+// communicator, `ShmLocalLevel` with the host's shared-memory group (CPU tensors), and
+// `HostLocalLevel` with the node group's control sockets (a slow stand-in for tests).
 #pragma once
 
 #include <algorithm>
@@ -43,6 +43,21 @@ inline size_t slice_len(size_t count, int n, int i) { return count / n + ((size_
 // rail's sockets.
 void two_level_allreduce(NodeGroup& g, LocalLevel& local, void* staging, size_t count, DType dtype, double scale,
                          int64_t int_divisor, ReduceOp red, double deadline);
+
+// The levels inside a host for CPU tensors: the host's shared-memory group.
+class ShmGroup;
+class ShmLocalLevel : public LocalLevel {
+ public:
+  ShmLocalLevel(ShmGroup& shm, void* tensor, double deadline) : shm_(shm), t_((char*)tensor), deadline_(deadline) {}
+  void reduce_in_node(size_t count, DType dtype, ReduceOp red) override;
+  void fetch(void* dst, size_t begin, size_t len, DType dtype) override;
+  void finish(const void* src, size_t begin, size_t len, const std::vector<size_t>& slice_len, DType dtype) override;
+
+ private:
+  ShmGroup& shm_;
+  char* t_;
+  double deadline_;
+};
 
 // Host-memory stand-in for the levels inside a host: blobs through the node group's star.
 class HostLocalLevel : public LocalLevel {

@@ -120,3 +120,45 @@ def test_distributed_optimizer_uses_flat_buffers_in_a_two_level_group():
         assert rec["worst"] < 1e-6 and rec["nodes"] == 2
         # 1048-byte buckets: the first weight (2048 bytes) alone, the other three tensors together
         assert rec["names"] == ["DistributedSGD.flat.0", "DistributedSGD.flat.1"]
+
+
+PUBLIC = """
+bc.init(device="cpu")
+bad = []
+for dtype in (torch.float32, torch.float64, torch.int32, torch.int64, torch.bfloat16, torch.uint8):
+    for count in (0, 1, 5, 1000, 40001):
+        g = torch.Generator().manual_seed(count)
+        per_rank = [(torch.randint(0, 9, (count,), generator=g) + r).to(dtype) for r in range(SIZE)]
+        x = per_rank[RANK]
+        want = torch.stack([p.double() for p in per_rank]).sum(0) if count else torch.zeros(0, dtype=torch.float64)
+        got = bc.allreduce(x, average=False)
+        if got.dtype != dtype or not torch.equal(got.double(), want): bad.append(["sum", str(dtype), count])
+        if dtype.is_floating_point:
+            got = bc.allreduce(x, average=True)
+            if not torch.allclose(got.double(), want / SIZE, rtol=1e-2 if dtype == torch.bfloat16 else 1e-6): bad.append(["avg", str(dtype), count])
+        if count:
+            got = bc.all_min(x)
+            if not torch.equal(got.double(), torch.stack([p.double() for p in per_rank]).min(0).values): bad.append(["min", str(dtype), count])
+t = torch.full((RANK + 1, 3), float(RANK))
+g = bc.allgather(t)
+if g.shape[0] != SIZE * (SIZE + 1) // 2 or g[-1, 0] != SIZE - 1: bad.append(["allgather"])
+algos = sorted({s["algo"] for s in bc.stats() if s["op"] == "allreduce"})
+emit(bad=bad, nodes=bc.n_nodes(), algos=algos)
+bc.shutdown()
+"""
+
+
+@pytest.mark.parametrize("groups", ["default", "off"])
+def test_public_cpu_collectives_over_fake_hosts(groups):
+    # 2 hosts x 2 ranks. By default the allreduce runs in two levels (shared memory inside a host,
+    # rails between hosts; small slots so that tensors span many chunks); with BC_NODE_GROUPS=0 it
+    # is the single ring over all ranks.
+    env = {r: {"BC_HOSTNAME": f"host{r // 2}", "LOCAL_RANK": "-1", "BC_SHM_SLOT_KB": "4"} for r in range(4)}
+    if groups == "off":
+        for e in env.values():
+            e["BC_NODE_GROUPS"] = "0"
+    res = run(PUBLIC, nranks=4, per_rank_env=env, timeout=180)
+    for _, rec in res:
+        assert rec["bad"] == []
+        assert rec["nodes"] == (2 if groups == "default" else 1)
+        assert rec["algos"] == (["cpu_shm"] if groups == "default" else ["cpu_ring"])
