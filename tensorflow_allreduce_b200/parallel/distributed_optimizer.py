@@ -431,6 +431,36 @@ class DistributedOptimizer(torch.optim.Optimizer):
         self._next_bucket = 0
         return loss
 
+    # ---- the reference's spelling of a training step --------------------------------------------
+
+    def compute_gradients(self, loss: torch.Tensor):
+        """Back-propagate `loss` and average the gradients over all ranks; returns
+        `[(gradient, parameter), ...]` like the reference's `compute_gradients`
+        (`mpi_collectives/__init__.py:195-205`). The gradients can be changed in place before
+        `apply_gradients()`. Needs the unfused path (`fused=False`) on a CUDA group."""
+        self.zero_grad()
+        loss.backward()
+        self.synchronize()
+        return [(p.grad, p) for g in self.param_groups for p in g["params"] if p.grad is not None]
+
+    def apply_gradients(self, grads_and_vars=None):
+        """Apply the update with the gradients held by the parameters (`grads_and_vars`, if given,
+        must be the pairs returned by `compute_gradients`: they alias `p.grad`)."""
+        if grads_and_vars is not None:
+            for g, p in grads_and_vars:
+                if p.grad is not g:
+                    raise ValueError("apply_gradients() takes the pairs returned by compute_gradients()")
+        return self.step()
+
+    def minimize(self, loss: torch.Tensor):
+        """One training step from a loss: clear the gradients, back-propagate (the averaging
+        overlaps the backward pass on a CUDA group) and update. `tf.train.Optimizer.minimize` of the
+        wrapped optimizer in the reference (`mpi_collectives/__init__.py:167-236`)."""
+        self.zero_grad()
+        loss.backward()
+        self.step()
+        return loss.detach()
+
     def _reduce_cpu(self):
         """Average every gradient with the negotiated allreduce: one collective per tensor on the
         CPU (as the reference does, `mpi_collectives/__init__.py:199-220`), flat buffers of up to

@@ -110,3 +110,43 @@ def test_models_run_on_cpu():
     loss = g.loss(*gpt2.synthetic_batch(gcfg, 2, "cpu"))
     loss.backward()
     assert torch.isfinite(loss)
+
+
+def test_minimize_and_compute_apply_gradients():
+    # The reference's spelling of a step: opt.minimize(loss), or compute_gradients -> (edit) ->
+    # apply_gradients (mpi_collectives/__init__.py:195-236). Both equal the large-batch run.
+    res = run("""
+    bc.init(device="cpu")
+    def make():
+        torch.manual_seed(0)
+        return torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.Tanh(), torch.nn.Linear(16, 2))
+    mine, ref = make(), make()
+    o_mine = bc.DistributedOptimizer(torch.optim.SGD(mine.parameters(), lr=0.1, momentum=0.9))
+    o_ref = torch.optim.SGD(ref.parameters(), lr=0.1, momentum=0.9)
+    g = torch.Generator().manual_seed(3)
+    X = torch.randn(4, 6 * SIZE, 8, generator=g); Y = torch.randn(4, 6 * SIZE, 2, generator=g)
+    sl = slice(RANK * 6, (RANK + 1) * 6)
+    grads_match = True
+    for it in range(4):
+        o_ref.zero_grad(); torch.nn.functional.mse_loss(ref(X[it]), Y[it]).backward()
+        if it % 2 == 0:
+            o_ref.step()
+            o_mine.minimize(torch.nn.functional.mse_loss(mine(X[it][sl]), Y[it][sl]))
+        else:
+            pairs = o_mine.compute_gradients(torch.nn.functional.mse_loss(mine(X[it][sl]), Y[it][sl]))
+            for (gr, p), q in zip(pairs, ref.parameters()):
+                grads_match = grads_match and torch.allclose(gr, q.grad, atol=1e-6)
+                gr.mul_(0.5); q.grad.mul_(0.5)                 # edit the averaged gradients before the update
+            o_ref.step()
+            o_mine.apply_gradients(pairs)
+    worst = max((a - b).abs().max().item() for a, b in zip(ref.parameters(), mine.parameters()))
+    try:
+        o_mine.apply_gradients([(torch.zeros(1), next(mine.parameters()))])
+        refused = False
+    except ValueError:
+        refused = True
+    emit(worst=worst, grads_match=bool(grads_match), refused=refused)
+    bc.shutdown()
+    """, nranks=2)
+    for _, rec in res:
+        assert rec["worst"] < 1e-6 and rec["grads_match"] and rec["refused"]
