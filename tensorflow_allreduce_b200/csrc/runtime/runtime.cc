@@ -78,10 +78,10 @@ Runtime::Runtime(const RuntimeOptions& o) : opt_(o) {
   t_ = bootstrap(o.rank, o.size, o.addr, o.port, o.timeout_s);
   local_rank_ = o.local_rank_override >= 0 ? o.local_rank_override : t_.local_rank;
   fault_ = FaultSpec::parse(o.fault);
-  // Ranks on several hosts: GPU collectives run in two levels (NVLink kernels inside a host, a
-  // ring of sockets between hosts). BC_NODE_GROUPS=1 builds the groups for a CPU job as well.
-  // A CPU job gets them when its hosts run several ranks each (then CPU tensors are reduced in
-  // shared memory inside a host first); BC_NODE_GROUPS=1 / 0 forces / forbids them there.
+  // Ranks on several hosts: collectives run in two levels (inside a host the NVLink kernels for
+  // GPU tensors and shared memory for CPU tensors, rings of sockets between hosts). A GPU job
+  // always gets the node groups for that, a CPU job when its hosts run several ranks each;
+  // BC_NODE_GROUPS=1 / 0 forces / forbids them for a CPU job.
   const char* groups_env = getenv("BC_NODE_GROUPS");
   const int want_groups = groups_env ? atoi(groups_env) : -1;
   if (t_.local_size != t_.size) {
@@ -151,8 +151,14 @@ Runtime::Runtime(const RuntimeOptions& o) : opt_(o) {
     } catch (const CommLost&) {
       throw;
     } catch (const Error& e) {
-      // Every rank learns of a failed set-up in the same exchange, so all of them stay on sockets.
+      // Every rank of the host learns of a failed set-up in the same exchange.
       BC_LOG(1, "%s; CPU tensors use the socket ring", e.what());
+    }
+    if (host_level) {
+      // All hosts must take the same path: one host without shared memory puts every host on the ring.
+      bool all = true;
+      for (const std::string& ok : t_.allgather(shm_ ? "1" : "0", now_s() + dl)) all = all && ok == "1";
+      if (!all) shm_.reset();
     }
   }
   wake_fd_ = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
