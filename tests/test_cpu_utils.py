@@ -129,3 +129,37 @@ def test_free_port_avoids_the_ephemeral_range():
     if low > 21000:
         assert all(20000 <= p < low for p in ports)
     assert len(ports) > 1
+
+
+def test_one_launcher_per_host_forms_one_job(tmp_path):
+    # Two launchers (node-rank 0 and 1) on this machine, each reporting a host name of its own:
+    # 2 hosts x 2 ranks, global ranks 0..3, and the collectives run in two levels.
+    import os
+    import subprocess
+
+    from tensorflow_allreduce_b200.utils.spawn import free_port
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "job.py"
+    script.write_text(
+        "import os, sys\n"
+        f"sys.path.insert(0, {root!r})\n"
+        "import torch, tensorflow_allreduce_b200 as bc\n"
+        "with bc.Session(device='cpu'):\n"
+        "    s = bc.allreduce(torch.arange(5.0) + bc.rank(), average=False)\n"
+        "    sys.stdout.write(f'JOB {bc.rank()} {bc.size()} {bc.local_rank()} {bc.local_size()} {bc.n_nodes()} {bc.node_index()} {s.tolist()}\\n')\n"
+        "    sys.stdout.flush()\n")
+    port = str(free_port())
+    procs = []
+    for node in range(2):
+        env = dict(os.environ, BC_HOSTNAME=f"host{node}", BC_TIMEOUT_S="60")
+        cmd = [sys.executable, "-m", "tensorflow_allreduce_b200.launch", "--nnodes", "2", "--node-rank", str(node),
+               "--port", port, "--nproc", "2", "--cpu", str(script)]
+        procs.append(subprocess.Popen(cmd, cwd=root, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    lines = []
+    for p in procs:
+        out, err = p.communicate(timeout=120)
+        assert p.returncode == 0, err[-2000:]
+        lines += [l for l in out.splitlines() if l.startswith("JOB")]
+    want_sum = [float(4 * i + 6) for i in range(5)]
+    assert sorted(lines) == [f"JOB {r} 4 {r % 2} 2 2 {r // 2} {want_sum}" for r in range(4)]
