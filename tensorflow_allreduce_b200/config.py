@@ -9,7 +9,8 @@ build, `_lib.py`), `BC_GRU_TIMEOUT_S` (`ops/persistent_gru.py`), and by the nati
 `init()`: `BC_SHM` (0 = CPU tensors of ranks on one host use the socket ring instead of shared
 memory), `BC_SHM_SLOT_KB` (chunk per rank in the shared segment, default 512), `BC_NODE_GROUPS`
 (1 = build the node groups and rails of a job over several hosts for a CPU group too),
-`BC_HOSTNAME` (the host name this rank reports).
+`BC_HOSTNAME` (the host name this rank reports), `BC_SPIN_US` (how long the background thread and
+a waiting caller keep polling after an event before they sleep, default 100; 0 = sleep at once).
 """
 from __future__ import annotations
 

@@ -16,6 +16,14 @@
 
 namespace bc {
 
+namespace {
+inline void cpu_pause() {
+#if defined(__x86_64__) || defined(__i386__)
+  __builtin_ia32_pause();
+#endif
+}
+}  // namespace
+
 // ---- logging -------------------------------------------------------------------------------
 
 int log_level() {
@@ -161,6 +169,7 @@ Runtime::Runtime(const RuntimeOptions& o) : opt_(o) {
       if (!all) shm_.reset();
     }
   }
+  if (const char* us = getenv("BC_SPIN_US")) spin_s_ = std::max(0, atoi(us)) * 1e-6;
   wake_fd_ = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
   BC_CHECK(wake_fd_ >= 0, "eventfd failed");
   thread_ = std::thread([this] { loop(); });
@@ -272,6 +281,12 @@ void Runtime::wait(int64_t handle, double timeout_s) {
   BC_CHECK(it != handles_.end(), "unknown handle " << handle);
   std::shared_ptr<OpRecord> rec = it->second;
   const auto deadline = std::chrono::steady_clock::now() + std::chrono::duration<double>(timeout_s);
+  // Most collectives finish within tens of microseconds: look a few times before sleeping.
+  for (const double spin_until = now_s() + spin_s_; rec->state == OpRecord::PENDING && now_s() < spin_until;) {
+    lk.unlock();
+    for (int i = 0; i < 32; i++) cpu_pause();
+    lk.lock();
+  }
   while (rec->state == OpRecord::PENDING) {
     if (cv_.wait_until(lk, deadline) == std::cv_status::timeout && rec->state == OpRecord::PENDING)
       throw Error("timed out waiting for collective '" + rec->name + "'");
@@ -496,11 +511,22 @@ void Runtime::loop_body() {
     }
   }
   const int timeout_ms = (t_.rank == 0 && !pending_.empty()) ? 50 : 500;
-  int rc = ::poll(fds.data(), fds.size(), timeout_ms);
+  // Collectives come in bursts (one per gradient, one per step): for a short while after the last
+  // event the thread polls without sleeping, which saves a wake-up per message; then it blocks.
+  int rc = 0;
+  if (spin_s_ > 0 && now_s() - last_event_s_ < spin_s_) {
+    do {
+      rc = ::poll(fds.data(), fds.size(), 0);
+      if (rc != 0) break;
+      for (int i = 0; i < 32; i++) cpu_pause();
+    } while (now_s() - last_event_s_ < spin_s_);
+  }
+  if (rc == 0) rc = ::poll(fds.data(), fds.size(), timeout_ms);
   if (rc < 0) {
     if (errno == EINTR) return;
     throw CommLost(std::string("poll failed: ") + strerror(errno));
   }
+  if (rc > 0) last_event_s_ = now_s();
   if (fds[0].revents & POLLIN) {
     uint64_t v;
     while (::read(wake_fd_, &v, 8) == 8) {

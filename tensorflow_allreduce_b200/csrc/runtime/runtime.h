@@ -170,6 +170,8 @@ class Runtime {
   size_t scratch_bytes_ = 0;
 
   std::thread thread_;
+  double spin_s_ = 100e-6;            // how long the thread keeps polling after an event before it sleeps (BC_SPIN_US)
+  double last_event_s_ = 0;
   int wake_fd_ = -1;
   std::mutex mu_;
   std::condition_variable cv_;
