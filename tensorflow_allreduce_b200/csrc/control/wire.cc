@@ -65,6 +65,10 @@ Request decode_request(const std::string& s) {
   r.symm_off = rd.i64();
   r.red = (ReduceOp)rd.u8();
   BC_CHECK((uint8_t)r.red <= (uint8_t)ReduceOp::MAX, "bad reduction in request");
+  BC_CHECK((uint8_t)r.op <= (uint8_t)OpType::SHUTDOWN, "bad operation in request");
+  BC_CHECK((uint8_t)r.dtype <= (uint8_t)DType::U8 || r.dtype == DType::INVALID, "bad element type in request");
+  BC_CHECK((uint8_t)r.device <= (uint8_t)DeviceKind::GPU, "bad device kind in request");
+  BC_CHECK(rd.pos == s.size(), "trailing bytes after a request");
   return r;
 }
 
@@ -98,6 +102,8 @@ Response decode_response(const std::string& s) {
   r.blobs.resize(nb);
   for (uint32_t i = 0; i < nb; i++) r.blobs[i] = rd.str();
   r.flags = rd.u32();
+  BC_CHECK((uint8_t)r.type <= (uint8_t)ResponseType::ABORT, "bad response type");
+  BC_CHECK(rd.pos == s.size(), "trailing bytes after a response");
   return r;
 }
 
