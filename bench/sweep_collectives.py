@@ -13,6 +13,8 @@ Arms:
   ours_symm   the same through the name-keyed negotiated API (adds the coordinator round trip)
   ours_staged allreduce of an ordinary tensor (copied through the staging area)
   nccl        torch.distributed.all_reduce / all_gather on the same sizes
+  (--fake-hosts H: the ranks report H host names, so ours_staged runs in two levels: NVLink kernels
+   inside a "host", pinned memory and socket rings between them)
   ref_ring    the reference's algorithm (tensorflow/contrib/mpi_collectives/ring.h:136-228, ring.cu.cc:41-69):
               N-1 reduce-scatter steps of peer copy + a separate 32x256 accumulate launch + a
               stream synchronise after each, then N-1 allgather steps; a restatement over NCCL
@@ -84,11 +86,19 @@ def main():
     ap.add_argument("--dtypes", default="fp32,bf16")
     ap.add_argument("--no-allgather", action="store_true")
     ap.add_argument("--no-allreduce", action="store_true")
+    ap.add_argument("--fake-hosts", type=int, default=1,
+                    help="report this many host names (consecutive ranks share one): times the two-level path on one box")
     a = ap.parse_args()
     arms = a.arms.split(",")
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
+    if a.fake_hosts > 1:
+        if world % a.fake_hosts:
+            raise SystemExit("--fake-hosts must divide the number of ranks")
+        os.environ["BC_HOSTNAME"] = f"host{rank // (world // a.fake_hosts)}"
+        # tensors in symmetric memory and ordered launches need all ranks on one host
+        arms = [x for x in arms if x in ("ours_staged", "nccl", "ref_ring")]
     torch.cuda.set_device(local)
     cfg = bc.Config.from_env(heap_mb=max(6 * a.max_mb + 64, 256), staging_mb=64)
     bc.init(device=local, config=cfg)
