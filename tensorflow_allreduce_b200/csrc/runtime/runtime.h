@@ -181,11 +181,9 @@ class Runtime {
   int64_t next_id_ = 1;
   std::atomic<bool> broken_{false};
   std::atomic<bool> stop_{false};
-  bool shutdown_requested_ = false;
   bool shutdown_done_ = false;
   std::string broken_reason_;
   FaultSpec fault_;
-  int64_t blob_seq_ = 0;
 
   // coordinator (rank 0 only)
   struct Pending {
