@@ -6,8 +6,6 @@ Formulas: TensorFlow `ApplyMomentum` / `ApplyAdam`
 `torch.optim.SGD` / `Adam` / `AdamW`."""
 from __future__ import annotations
 
-import torch
-
 from .. import _lib
 
 
