@@ -163,3 +163,30 @@ def test_one_launcher_per_host_forms_one_job(tmp_path):
         lines += [l for l in out.splitlines() if l.startswith("JOB")]
     want_sum = [float(4 * i + 6) for i in range(5)]
     assert sorted(lines) == [f"JOB {r} 4 {r % 2} 2 2 {r // 2} {want_sum}" for r in range(4)]
+
+
+def test_ranks_started_by_torchrun_find_each_other(tmp_path):
+    # Under torchrun MASTER_PORT belongs to the launcher's store: rank 0 publishes a port of its
+    # own for the control plane through that store (core._resolve_port).
+    import os
+    import subprocess
+
+    from tensorflow_allreduce_b200.utils.spawn import free_port
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "job.py"
+    script.write_text(
+        "import sys\n"
+        f"sys.path.insert(0, {root!r})\n"
+        "import torch, tensorflow_allreduce_b200 as bc\n"
+        "bc.init(device='cpu')\n"
+        "s = bc.allreduce(torch.ones(3) * (bc.rank() + 1), average=False)\n"
+        "sys.stdout.write(f'TR {bc.rank()} {bc.size()} {bc.local_rank()} {s.tolist()}\\n'); sys.stdout.flush()\n"
+        "bc.shutdown()\n")
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", BC_TIMEOUT_S="60")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "3", "--master-addr", "127.0.0.1",
+           "--master-port", str(free_port()), str(script)]
+    r = subprocess.run(cmd, cwd=root, env=env, capture_output=True, text=True, timeout=240)
+    assert r.returncode == 0, r.stderr[-3000:]
+    lines = sorted(l for l in r.stdout.splitlines() if l.startswith("TR"))
+    assert lines == [f"TR {k} 3 {k} [6.0, 6.0, 6.0]" for k in range(3)]
