@@ -150,3 +150,16 @@ def test_minimize_and_compute_apply_gradients():
     """, nranks=2)
     for _, rec in res:
         assert rec["worst"] < 1e-6 and rec["grads_match"] and rec["refused"]
+
+
+def test_example_script_trains_on_two_cpu_ranks():
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "tensorflow_allreduce_b200.launch", "--nproc", "2", "--cpu",
+           os.path.join(root, "examples", "data_parallel_training.py"), "--steps", "12"]
+    r = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=240)
+    assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-2000:]
+    assert "identical weights True" in r.stdout
