@@ -271,3 +271,35 @@ def test_dependent_allreduce_chain(transport):
     bc.shutdown()
     """, nranks=2, env=_tenv(transport))
     assert all(rec["ok"] for _, rec in res)
+
+
+def test_concurrent_callers_from_several_threads():
+    # Four threads per rank issue named collectives at the same time (the reference's NcclManager test drives its manager from a thread pool,
+    # tensorflow/contrib/nccl/kernels/nccl_manager_test.cc:184-282). Names pair the requests up.
+    res = run("""
+    import threading
+    bc.init(device="cpu")
+    bad = []
+    def work(tid):
+        # a thread blocks in every call, so thread `tid` must walk its names in the same order on
+        # every rank; the threads of one rank run against each other freely
+        order = list(range(12))
+        if tid % 2: order.reverse()
+        try:
+            for k in order:
+                x = torch.full((257,), float(RANK + tid + k))
+                s = bc.allreduce(x, average=False, name=f"t{tid}.k{k}")
+                want = sum(r + tid + k for r in range(SIZE))
+                if not bool((s == want).all()): bad.append([tid, k])
+                g = bc.allgather(torch.full((RANK + 1, 2), float(tid)), name=f"g{tid}.k{k}")
+                if g.shape[0] != SIZE * (SIZE + 1) // 2 or not bool((g == tid).all()): bad.append(["g", tid, k])
+        except Exception as e:
+            bad.append([tid, "exception", str(e)])
+    ts = [threading.Thread(target=work, args=(t,)) for t in range(4)]
+    for t in ts: t.start()
+    for t in ts: t.join()
+    emit(bad=bad)
+    bc.shutdown()
+    """, nranks=3, timeout=120)
+    for _, rec in res:
+        assert rec["bad"] == []
