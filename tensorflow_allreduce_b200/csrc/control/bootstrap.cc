@@ -86,6 +86,13 @@ Transport bootstrap(int rank, int size, const std::string& addr, int port, doubl
   }
   const double deadline = now_s() + timeout_s;
 
+  // Rank 0 binds the rendezvous port before anything of this process asks the kernel for a port
+  // of its own choice: a port from the ephemeral range could otherwise go to the data listener.
+  Socket listener;
+  if (rank == 0) {
+    int bound = 0;
+    listener = Socket::listen_tcp("0.0.0.0", port, size + 8, &bound);
+  }
   int data_port = 0;
   Socket data_listener = Socket::listen_tcp("0.0.0.0", 0, 8, &data_port);
 
@@ -93,8 +100,6 @@ Transport bootstrap(int rank, int size, const std::string& addr, int port, doubl
   std::vector<int> data_ports(size, 0);
 
   if (rank == 0) {
-    int bound = 0;
-    Socket listener = Socket::listen_tcp("0.0.0.0", port, size + 8, &bound);
     t.hosts[0] = me;
     t.pids[0] = (int)getpid();
     ips[0] = addr;
