@@ -87,6 +87,8 @@ ShmGroup::ShmGroup(int local_rank, int local_size, const std::string& name, size
     fd = shm_open(path.c_str(), O_CREAT | O_EXCL | O_RDWR, 0600);
     if (fd < 0) err = std::string("shm_open(create): ") + strerror(errno);
     else if (ftruncate(fd, (off_t)map_bytes_) != 0) err = std::string("ftruncate: ") + strerror(errno);
+    else if (int rc = posix_fallocate(fd, 0, (off_t)map_bytes_))   // claim the pages now: a full /dev/shm must
+      err = std::string("posix_fallocate: ") + strerror(rc);       // show up here, not as SIGBUS on first touch
   }
   std::vector<std::string> st = ag(err);
   if (!st[0].empty()) {
