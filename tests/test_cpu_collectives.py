@@ -303,3 +303,17 @@ def test_concurrent_callers_from_several_threads():
     """, nranks=3, timeout=120)
     for _, rec in res:
         assert rec["bad"] == []
+
+
+def test_shared_memory_that_cannot_be_set_up_falls_back_to_sockets():
+    # Slots of 1 TiB cannot be reserved anywhere: every rank learns of it in the same exchange
+    # and the group runs over the socket ring.
+    res = run("""
+    bc.init(device="cpu")
+    s = bc.allreduce(torch.arange(1000.0) + RANK, average=False)
+    ok = bool(torch.equal(s, torch.arange(1000.0) * SIZE + sum(range(SIZE))))
+    emit(ok=ok, algo=[e["algo"] for e in bc.stats() if e["op"] == "allreduce"][-1])
+    bc.shutdown()
+    """, nranks=3, env={"BC_SHM_SLOT_KB": str(1 << 30)})
+    for _, rec in res:
+        assert rec["ok"] and rec["algo"] == "cpu_ring"
