@@ -317,3 +317,22 @@ def test_shared_memory_that_cannot_be_set_up_falls_back_to_sockets():
     """, nranks=3, env={"BC_SHM_SLOT_KB": str(1 << 30)})
     for _, rec in res:
         assert rec["ok"] and rec["algo"] == "cpu_ring"
+
+
+def test_collectives_carry_no_gradient():
+    # The reference registers its ops as NotDifferentiable (mpi_ops.py:135,163): results are
+    # plain tensors, and the input's autograd graph is left alone.
+    res = run("""
+    bc.init(device="cpu")
+    x = torch.ones(3, requires_grad=True)
+    y = bc.allreduce(x * 2, average=False)
+    g = bc.allgather((x * 3).reshape(1, 3))
+    b = bc.broadcast(x * 4, root=0)
+    (x * 5).sum().backward()
+    emit(flags=[y.requires_grad, g.requires_grad, b.requires_grad], fns=[y.grad_fn is None, g.grad_fn is None],
+         grad=x.grad.tolist(), y=y.tolist())
+    bc.shutdown()
+    """, nranks=2)
+    for _, rec in res:
+        assert rec["flags"] == [False, False, False] and rec["fns"] == [True, True]
+        assert rec["grad"] == [5.0, 5.0, 5.0] and rec["y"] == [4.0, 4.0, 4.0]
