@@ -27,6 +27,9 @@ struct Rd {
   std::string str() { int32_t n = i32(); BC_CHECK(n >= 0 && p + (size_t)n <= s.size(), "short bootstrap message"); std::string v = s.substr(p, n); p += n; return v; }
 };
 
+// Bumped whenever a control message or the bootstrap exchange changes its layout.
+constexpr int32_t kWireVersion = 3;
+
 std::string peer_ip(int fd) {
   struct sockaddr_in sa;
   socklen_t sl = sizeof(sa);
@@ -113,6 +116,9 @@ Transport bootstrap(int rank, int size, const std::string& addr, int port, doubl
       Rd rd(hello);
       int32_t magic = rd.i32();
       BC_CHECK(magic == 0x42434F4C, "unexpected client on the bootstrap port");
+      int32_t version = rd.i32();
+      BC_CHECK(version == kWireVersion, "a rank runs another version of this library (message format " << version
+               << ", rank 0 has " << kWireVersion << ")");
       int32_t r = rd.i32();
       int32_t sz = rd.i32();
       BC_CHECK(sz == size, "rank " << r << " was started with world size " << sz << ", rank 0 with " << size);
@@ -138,6 +144,7 @@ Transport bootstrap(int rank, int size, const std::string& addr, int port, doubl
     Socket s = Socket::connect_tcp(addr, port, deadline);
     Buf b;
     b.i32(0x42434F4C);
+    b.i32(kWireVersion);
     b.i32(rank);
     b.i32(size);
     b.str(me);
