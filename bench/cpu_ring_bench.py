@@ -1,8 +1,10 @@
-"""Timed CPU baseline: sum-allreduce and variable allgather of a CPU group over loopback sockets,
-the data path that plays the role of the reference's `RingAllreduce<CPU>` / `RingAllgather<CPU>`
-(tensorflow/contrib/mpi_collectives/ring.h:136-301, ring.cc:36-50).
+"""Timed CPU baseline: sum-allreduce and variable allgather of a CPU group, the data path that plays
+the role of the reference's `RingAllreduce<CPU>` / `RingAllgather<CPU>`
+(tensorflow/contrib/mpi_collectives/ring.h:136-301, ring.cc:36-50). Ranks of one host exchange the
+data through shared memory; `BC_SHM=0` times the socket ring (loopback TCP) instead.
 
     python -m tensorflow_allreduce_b200.launch --nproc 2 --cpu bench/cpu_ring_bench.py [--max-mb 64]
+    BC_SHM=0 python -m tensorflow_allreduce_b200.launch --nproc 2 --cpu bench/cpu_ring_bench.py
 
 Wall-clock time per call (host timers, maximum over ranks) through the public, name-keyed API, so
 the coordinator round trip is included. Bus bandwidth as in the GPU sweep.
@@ -57,7 +59,7 @@ def main():
         gsec = max(bc.host_allgather(sorted(gt)[len(gt) // 2]))
         total = g.numel() * 4
         if rank == 0:
-            print(json.dumps({"bytes": s, "world": P, "allreduce_ms": round(sec * 1e3, 4), "allreduce_busbw_gbs": round(s / sec * 2 * (P - 1) / P / 1e9, 3),
+            print(json.dumps({"bytes": s, "world": P, "transport": [e["algo"] for e in bc.stats() if e["op"] == "allreduce"][-1], "allreduce_ms": round(sec * 1e3, 4), "allreduce_busbw_gbs": round(s / sec * 2 * (P - 1) / P / 1e9, 3),
                               "correct": ok, "allgather_total_bytes": total, "allgather_ms": round(gsec * 1e3, 4),
                               "allgather_busbw_gbs": round(total / gsec * (P - 1) / P / 1e9, 3)}), flush=True)
         s *= 4
