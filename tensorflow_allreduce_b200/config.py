@@ -10,7 +10,8 @@ build, `_lib.py`), `BC_GRU_TIMEOUT_S` (`ops/persistent_gru.py`), and by the nati
 memory), `BC_SHM_SLOT_KB` (chunk per rank in the shared segment, default 512), `BC_NODE_GROUPS`
 (1 = build the node groups and rails of a job over several hosts for a CPU group too),
 `BC_HOSTNAME` (the host name this rank reports), `BC_SPIN_US` (how long the background thread and
-a waiting caller keep polling after an event before they sleep, default 100; 0 = sleep at once).
+a waiting caller keep polling after an event before they sleep; default 100, or 0 = sleep at once
+when the host has fewer than two cores per local rank).
 """
 from __future__ import annotations
 

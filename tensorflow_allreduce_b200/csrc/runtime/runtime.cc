@@ -169,7 +169,10 @@ Runtime::Runtime(const RuntimeOptions& o) : opt_(o) {
       if (!all) shm_.reset();
     }
   }
+  // Polling instead of sleeping pays while every thread has a core of its own (a caller and a
+  // background thread per rank); on a machine with fewer cores it only takes time from the peers.
   if (const char* us = getenv("BC_SPIN_US")) spin_s_ = std::max(0, atoi(us)) * 1e-6;
+  else if (std::thread::hardware_concurrency() < 2u * (unsigned)std::max(1, t_.local_size)) spin_s_ = 0;
   wake_fd_ = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
   BC_CHECK(wake_fd_ >= 0, "eventfd failed");
   thread_ = std::thread([this] { loop(); });
