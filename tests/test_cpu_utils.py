@@ -190,3 +190,17 @@ def test_ranks_started_by_torchrun_find_each_other(tmp_path):
     assert r.returncode == 0, r.stderr[-3000:]
     lines = sorted(l for l in r.stdout.splitlines() if l.startswith("TR"))
     assert lines == [f"TR {k} 3 {k} [6.0, 6.0, 6.0]" for k in range(3)]
+
+
+def test_info_command_reports_and_checks():
+    import json
+    import os
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", BC_BUCKET_MB="8")
+    r = subprocess.run([sys.executable, "-m", "tensorflow_allreduce_b200", "--check"], cwd=root, env=env, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr[-2000:]
+    info = json.loads(r.stdout)
+    assert info["library_built"] and info["library_matches_sources"] and info["check"] == {"cpu": True}
+    assert info["config"]["bucket_mb"] == 8.0 and info["environment"]["BC_BUCKET_MB"] == "8"
