@@ -86,20 +86,7 @@ Runtime::Runtime(const RuntimeOptions& o) : opt_(o) {
   t_ = bootstrap(o.rank, o.size, o.addr, o.port, o.timeout_s);
   local_rank_ = o.local_rank_override >= 0 ? o.local_rank_override : t_.local_rank;
   fault_ = FaultSpec::parse(o.fault);
-  // Ranks on several hosts: collectives run in two levels (inside a host the NVLink kernels for
-  // GPU tensors and shared memory for CPU tensors, rings of sockets between hosts). A GPU job
-  // always gets the node groups for that, a CPU job when its hosts run several ranks each;
-  // BC_NODE_GROUPS=1 / 0 forces / forbids them for a CPU job.
-  const char* groups_env = getenv("BC_NODE_GROUPS");
-  const int want_groups = groups_env ? atoi(groups_env) : -1;
-  if (t_.local_size != t_.size) {
-    std::string why;
-    const bool uniform = hosts_are_uniform(t_, &why);
-    if (o.device >= 0 || want_groups > 0)
-      BC_CHECK(uniform, "collectives in two levels need the same number of ranks on every host (" << why << ")");
-    if (o.device >= 0 || want_groups > 0 || (want_groups != 0 && uniform && t_.local_size > 1))
-      node_.reset(new NodeGroup(build_node_group(t_, now_s() + o.timeout_s)));
-  }
+  setup_node_group();
   if (o.device >= 0) {
     gpu::CommConfig cc;
     cc.staging_bytes = o.staging_bytes;
@@ -125,8 +112,37 @@ Runtime::Runtime(const RuntimeOptions& o) : opt_(o) {
       comm_.reset(new gpu::Comm(t_.rank, t_.size, o.device, t_.job_id, cc, ag, o.timeout_s));
     }
   }
-  // All ranks on this host: CPU tensors go through a shared-memory segment instead of the socket
-  // ring. BC_SHM=0 keeps the sockets, BC_SHM_SLOT_KB sets the chunk per rank.
+  setup_shared_memory();
+  // Polling instead of sleeping pays while every thread has a core of its own (a caller and a
+  // background thread per rank); on a machine with fewer cores it only takes time from the peers.
+  if (const char* us = getenv("BC_SPIN_US")) spin_s_ = std::max(0, atoi(us)) * 1e-6;
+  else if (std::thread::hardware_concurrency() < 2u * (unsigned)std::max(1, t_.local_size)) spin_s_ = 0;
+  wake_fd_ = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
+  BC_CHECK(wake_fd_ >= 0, "eventfd failed");
+  thread_ = std::thread([this] { loop(); });
+}
+
+void Runtime::setup_node_group() {
+  // Ranks on several hosts: collectives run in two levels (inside a host the NVLink kernels for
+  // GPU tensors and shared memory for CPU tensors, rings of sockets between hosts). A GPU job
+  // always gets the node groups for that, a CPU job when its hosts run several ranks each;
+  // BC_NODE_GROUPS=1 / 0 forces / forbids them for a CPU job.
+  const char* groups_env = getenv("BC_NODE_GROUPS");
+  const int want_groups = groups_env ? atoi(groups_env) : -1;
+  if (t_.local_size != t_.size) {
+    std::string why;
+    const bool uniform = hosts_are_uniform(t_, &why);
+    if (opt_.device >= 0 || want_groups > 0)
+      BC_CHECK(uniform, "collectives in two levels need the same number of ranks on every host (" << why << ")");
+    if (opt_.device >= 0 || want_groups > 0 || (want_groups != 0 && uniform && t_.local_size > 1))
+      node_.reset(new NodeGroup(build_node_group(t_, now_s() + opt_.timeout_s)));
+  }
+}
+
+void Runtime::setup_shared_memory() {
+  // CPU tensors among the ranks of one host go through a shared-memory segment: the whole job when
+  // it runs on one host, else the level inside a host of a job with node groups. BC_SHM=0 keeps
+  // the sockets, BC_SHM_SLOT_KB sets the chunk per rank.
   const char* shm_env = getenv("BC_SHM");
   const bool one_host = t_.size > 1 && t_.local_size == t_.size;
   const bool host_level = node_ && node_->local_size > 1;
@@ -137,15 +153,15 @@ Runtime::Runtime(const RuntimeOptions& o) : opt_(o) {
     snprintf(name, sizeof(name), "bcoll-%016llx-shm-%d", (unsigned long long)t_.job_id, host_level ? node_->node_index : 0);
     Transport* tp = &t_;
     NodeGroup* ng = node_.get();
-    const double dl = o.timeout_s;
+    const double dl = opt_.timeout_s;
     const int my = host_level ? ng->local_rank : t_.rank, n = host_level ? ng->local_size : t_.size;
     ShmGroup::Allgather ag = [tp, ng, host_level, dl](const std::string& mine) {
       return host_level ? ng->allgather(mine, now_s() + dl) : tp->allgather(mine, now_s() + dl);
     };
     try {
-      // The ring's sockets carry nothing while shared memory is in use, so end-of-file on one of
-      // them means that the neighbour's process has ended (the kernel closes its sockets even
-      // before the process is reaped).
+      // A rank waiting in shared memory looks at the ring's sockets now and then: end-of-file on
+      // one of them means that the neighbour's process has ended (the kernel closes its sockets
+      // even before the process is reaped). Data that is waiting there is left alone.
       auto peer_lost = [tp]() -> std::string {
         const Socket* socks[2] = {&tp->ring_prev, &tp->ring_next};
         for (const Socket* s : socks) {
@@ -169,13 +185,6 @@ Runtime::Runtime(const RuntimeOptions& o) : opt_(o) {
       if (!all) shm_.reset();
     }
   }
-  // Polling instead of sleeping pays while every thread has a core of its own (a caller and a
-  // background thread per rank); on a machine with fewer cores it only takes time from the peers.
-  if (const char* us = getenv("BC_SPIN_US")) spin_s_ = std::max(0, atoi(us)) * 1e-6;
-  else if (std::thread::hardware_concurrency() < 2u * (unsigned)std::max(1, t_.local_size)) spin_s_ = 0;
-  wake_fd_ = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
-  BC_CHECK(wake_fd_ >= 0, "eventfd failed");
-  thread_ = std::thread([this] { loop(); });
 }
 
 Runtime::~Runtime() {

@@ -139,6 +139,8 @@ class Runtime {
   void clear_stats();
 
  private:
+  void setup_node_group();      // constructor steps, collective over all ranks
+  void setup_shared_memory();
   void loop();
   void loop_body();
   void drain_local_queue();
