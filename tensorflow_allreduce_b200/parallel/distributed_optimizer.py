@@ -64,6 +64,22 @@ class _Bucket:
         self.done_event = None
 
 
+class _FlatBucket:
+    """Dense gradients of one dtype and device that travel as one flat buffer."""
+
+    def __init__(self, index, params):
+        self.index = index
+        self.params = params
+        self.offsets, n = [], 0
+        for p in params:
+            self.offsets.append(n)
+            n += p.numel()
+        self.buf = torch.zeros(n, dtype=params[0].dtype, device=params[0].device)
+        self.filled = set()
+        self.handle = None
+        self.dirty = False
+
+
 def _chunks_by_bytes(tensors, limit: int):
     """Consecutive runs of `tensors` whose sizes add up to at most `limit` bytes (a tensor larger
     than that forms a run of its own)."""
@@ -149,6 +165,7 @@ class DistributedOptimizer(torch.optim.Optimizer):
         self._next_bucket = 0
         self._launched_any = False
         self.launch_count = 0   # collective kernels launched by this optimizer so far
+        self._flat: List[_FlatBucket] = []     # groups in two levels: flat copies reduced while backward runs
         if self._gpu:
             cfg = core.config()
             self._bucket_bytes = int((bucket_mb if bucket_mb is not None else cfg.bucket_mb) * (1 << 20))
@@ -156,6 +173,11 @@ class DistributedOptimizer(torch.optim.Optimizer):
             self._verify_layout()
             for p in params:
                 self._hooks.append(p.register_post_accumulate_grad_hook(self._on_grad_ready))
+        elif core.n_nodes() > 1 and params:
+            limit = int((bucket_mb if bucket_mb is not None else core.config().bucket_mb) * (1 << 20))
+            self._build_flat_buckets(params, limit)
+            for p in params:
+                self._hooks.append(p.register_post_accumulate_grad_hook(self._on_flat_grad_ready))
 
     # ---- layout ------------------------------------------------------------------------------
 
@@ -431,6 +453,69 @@ class DistributedOptimizer(torch.optim.Optimizer):
         self._next_bucket = 0
         return loss
 
+    # ---- groups in two levels: flat buckets launched from hooks ------------------------------------
+
+    def _build_flat_buckets(self, params, limit: int):
+        """Parameters in reverse order (the order in which backward produces gradients), grouped by
+        dtype and device and cut into buckets of at most `limit` bytes."""
+        groups = {}
+        for p in reversed(params):
+            groups.setdefault((p.dtype, p.device), []).append(p)
+        self._flat_of = {}
+        for ps in groups.values():
+            for chunk in _chunks_by_bytes(ps, limit):
+                b = _FlatBucket(len(self._flat), chunk)
+                self._flat.append(b)
+                for q, off in zip(chunk, b.offsets):
+                    self._flat_of[q] = (b, off)
+
+    def _on_flat_grad_ready(self, p):
+        if not self._sync or p.grad is None or p.grad.is_sparse:
+            return
+        b, off = self._flat_of[p]
+        if b.handle is not None:
+            b.dirty = True                            # a second backward before step(): reduced again at step()
+            return
+        with torch.no_grad():
+            b.buf[off:off + p.numel()].copy_(p.grad.reshape(-1))
+        b.filled.add(p)
+        if len(b.filled) == len(b.params):
+            self._launch_flat(b)
+
+    def _launch_flat(self, b):
+        b.handle = core.allreduce_async(b.buf, average=True, name=f"{self.name}.flat.{b.index}", out=b.buf)
+
+    @torch.no_grad()
+    def _finish_flat(self):
+        """Launch what the hooks have not launched (missing gradients count as zeros, so that every
+        rank issues the same collectives), wait, and hand the averages back to the parameters."""
+        for b in self._flat:
+            if b.handle is not None and b.dirty:
+                b.handle.wait()                       # that average is out of date: the gradients have grown since
+                b.handle = None
+            if b.handle is None:
+                for q, off in zip(b.params, b.offsets):
+                    sl = b.buf[off:off + q.numel()]
+                    if q.grad is None or q.grad.is_sparse:
+                        sl.zero_()
+                    else:
+                        sl.copy_(q.grad.reshape(-1))          # also picks up gradients accumulated under no_sync()
+                self._launch_flat(b)
+        idx = 0
+        for g in self.param_groups:                            # sparse gradients: gathered one by one
+            for q in g["params"]:
+                if q.grad is not None and q.grad.is_sparse:
+                    q.grad = core.allreduce(q.grad, average=True, name=f"{self.name}.grad.{idx}")
+                idx += 1
+        for b in self._flat:
+            b.handle.wait()
+            for q, off in zip(b.params, b.offsets):
+                if q.grad is not None and not q.grad.is_sparse:
+                    q.grad.copy_(b.buf[off:off + q.numel()].view_as(q.grad))
+            b.handle = None
+            b.dirty = False
+            b.filled.clear()
+
     # ---- the reference's spelling of a training step --------------------------------------------
 
     def compute_gradients(self, loss: torch.Tensor):
@@ -462,34 +547,21 @@ class DistributedOptimizer(torch.optim.Optimizer):
         return loss.detach()
 
     def _reduce_cpu(self):
-        """Average every gradient with the negotiated allreduce: one collective per tensor on the
-        CPU (as the reference does, `mpi_collectives/__init__.py:199-220`), flat buffers of up to
-        `bucket_mb` per dtype for CUDA gradients and for every group that runs in two levels."""
+        """Average every gradient with the negotiated allreduce: one collective per tensor (as the
+        reference does, `mpi_collectives/__init__.py:199-220`), or the flat buckets of a group in
+        two levels."""
+        if self._flat:
+            return self._finish_flat()
         handles = []
         idx = 0
-        flat = {}            # (dtype, device) -> dense gradients that travel in flat buffers, in parameter order
-        two_level = core.n_nodes() > 1
         for g in self.param_groups:
             for p in g["params"]:
                 if p.grad is not None:
                     if p.grad.is_sparse:
                         p.grad = core.allreduce(p.grad, average=True, name=f"{self.name}.grad.{idx}")
-                    elif p.grad.is_cuda or two_level:
-                        flat.setdefault((p.grad.dtype, p.grad.device), []).append(p.grad)
                     else:
                         handles.append(core.allreduce_async(p.grad, average=True, name=f"{self.name}.grad.{idx}", out=p.grad))
                 idx += 1
-        limit = int(core.config().bucket_mb * (1 << 20))
-        n = 0
-        for (dtype, _), grads in flat.items():
-            for chunk in _chunks_by_bytes(grads, limit):
-                buf = torch.cat([t.reshape(-1) for t in chunk])
-                core.allreduce_(buf, average=True, name=f"{self.name}.flat.{n}")
-                n += 1
-                off = 0
-                for t in chunk:
-                    t.copy_(buf[off:off + t.numel()].view_as(t))
-                    off += t.numel()
         for h in handles:
             h.wait()
 

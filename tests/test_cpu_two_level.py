@@ -162,3 +162,48 @@ def test_public_cpu_collectives_over_fake_hosts(groups):
         assert rec["bad"] == []
         assert rec["nodes"] == (2 if groups == "default" else 1)
         assert rec["algos"] == (["cpu_shm"] if groups == "default" else ["cpu_ring"])
+
+
+def test_flat_buckets_with_accumulation_and_unused_parameters():
+    # Two backward passes before one step (with and without no_sync()), a parameter that never
+    # receives a gradient, and a check that the buckets really go out while backward still runs.
+    res = run("""
+    bc.init(device="cpu")
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            torch.manual_seed(0)
+            self.a = torch.nn.Linear(8, 16); self.b = torch.nn.Linear(16, 2); self.unused = torch.nn.Linear(3, 3)
+        def forward(self, x):
+            return self.b(torch.tanh(self.a(x)))
+    mine, ref = Net(), Net()
+    o_mine = bc.DistributedOptimizer(torch.optim.SGD(mine.parameters(), lr=0.1))
+    o_ref = torch.optim.SGD(ref.parameters(), lr=0.1)
+    g = torch.Generator().manual_seed(11)
+    X = torch.randn(6, 4 * SIZE, 8, generator=g); Y = torch.randn(6, 4 * SIZE, 2, generator=g)
+    sl = slice(RANK * 4, (RANK + 1) * 4)
+    loss = torch.nn.functional.mse_loss
+    launched_in_backward = []
+    for it in range(0, 6, 2):
+        o_ref.zero_grad()
+        loss(ref(X[it]), Y[it]).backward(); loss(ref(X[it + 1]), Y[it + 1]).backward()
+        o_ref.step()
+        o_mine.zero_grad()
+        if it == 2:
+            with o_mine.no_sync():
+                loss(mine(X[it][sl]), Y[it][sl]).backward()
+        else:
+            loss(mine(X[it][sl]), Y[it][sl]).backward()          # the buckets go out here already ...
+        launched_in_backward.append(sum(b.handle is not None for b in o_mine._flat))
+        loss(mine(X[it + 1][sl]), Y[it + 1][sl]).backward()      # ... and are reduced again after this one
+        o_mine.step()
+    worst = max((a - b).abs().max().item() for a, b in zip(ref.parameters(), mine.parameters()))
+    emit(worst=worst, launched=launched_in_backward, unused_grad=mine.unused.weight.grad is None, buckets=len(o_mine._flat))
+    bc.shutdown()
+    """, nranks=4, per_rank_env=_hosts(4, 2), env={"BC_BUCKET_MB": "0.0002"})     # 209-byte buckets: [unused.*, b.*], [a.bias], [a.weight]
+    for _, rec in res:
+        assert rec["worst"] < 1e-6, rec
+        assert rec["unused_grad"] and rec["buckets"] >= 3
+        # iterations 0 and 4: every bucket whose parameters all got gradients was launched during
+        # backward; iteration 2 ran under no_sync()
+        assert rec["launched"][1] == 0 and rec["launched"][0] >= 2 and rec["launched"][2] >= 2
