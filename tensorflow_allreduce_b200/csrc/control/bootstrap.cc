@@ -70,7 +70,7 @@ std::vector<std::string> Transport::allgather(const std::string& mine, double de
 
 void Transport::barrier(double deadline) { allgather(std::string(), deadline); }
 
-Transport bootstrap(int rank, int size, const std::string& addr, int port, double timeout_s) {
+Transport bootstrap(int rank, int size, const std::string& addr, int port, double timeout_s, const std::string& host) {
   BC_CHECK(size >= 1 && rank >= 0 && rank < size, "bad rank/size: " << rank << "/" << size);
   Transport t;
   t.rank = rank;
@@ -78,7 +78,7 @@ Transport bootstrap(int rank, int size, const std::string& addr, int port, doubl
   t.hosts.assign(size, "");
   t.pids.assign(size, 0);
   t.ctrl.resize(size);
-  const std::string me = local_hostname();
+  const std::string me = host.empty() ? local_hostname() : host;
   if (size == 1) {
     t.hosts[0] = me;
     t.ips.assign(1, addr);

@@ -38,6 +38,7 @@ struct Transport {
   std::string unix_name(int r, const char* purpose) const;
 };
 
-Transport bootstrap(int rank, int size, const std::string& addr, int port, double timeout_s);
+// `host` = the host name this rank reports (empty: local_hostname()).
+Transport bootstrap(int rank, int size, const std::string& addr, int port, double timeout_s, const std::string& host = std::string());
 
 }  // namespace bc

@@ -83,7 +83,7 @@ FaultSpec FaultSpec::parse(const std::string& s) {
 // ---- construction / teardown ---------------------------------------------------------------
 
 Runtime::Runtime(const RuntimeOptions& o) : opt_(o) {
-  t_ = bootstrap(o.rank, o.size, o.addr, o.port, o.timeout_s);
+  t_ = bootstrap(o.rank, o.size, o.addr, o.port, o.timeout_s, o.hostname);
   local_rank_ = o.local_rank_override >= 0 ? o.local_rank_override : t_.local_rank;
   fault_ = FaultSpec::parse(o.fault);
   setup_node_group();

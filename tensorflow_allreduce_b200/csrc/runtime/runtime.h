@@ -81,6 +81,7 @@ struct RuntimeOptions {
   int max_blocks = 0;
   int symm_mode = 0;              // 0 auto, 1 vmm, 2 ipc
   std::string fault;              // fault-injection spec (host side only)
+  std::string hostname;           // host name to report (empty: BC_HOSTNAME, else the machine's)
 };
 
 struct FaultSpec {

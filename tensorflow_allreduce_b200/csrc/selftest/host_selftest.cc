@@ -4,7 +4,8 @@
 // sanitizer configuration at all and its global state has real data races
 // (tensorflow/contrib/mpi_collectives/mpi_ops.cc:593,621,816-821).
 //
-//   host_selftest <nranks> <port>        exit code 0 = all checks passed
+//   host_selftest <nranks> <port> [<port2>]     exit code 0 = all checks passed
+//   (with <port2>: a second pass with 4 ranks that report two host names)
 #include <stdio.h>
 #include <string.h>
 
@@ -47,12 +48,13 @@ static int64_t enqueue_allreduce(Runtime& rt, const std::string& name, const flo
   return rt.enqueue(std::move(r));
 }
 
-static void rank_main(int rank, int size, int port) {
+static void rank_main(int rank, int size, int port, std::string hostname) {
   try {
     RuntimeOptions o;
     o.rank = rank;
     o.size = size;
     o.port = port;
+    o.hostname = hostname;
     o.device = -1;
     o.timeout_s = 3;
     Runtime rt(o);
@@ -200,9 +202,17 @@ int main(int argc, char** argv) {
   wire_checks();
   int n = argc > 1 ? atoi(argv[1]) : 3;
   int port = argc > 2 ? atoi(argv[2]) : 29650;
+  int port2 = argc > 3 ? atoi(argv[3]) : 0;
   std::vector<std::thread> ts;
-  for (int r = 0; r < n; r++) ts.emplace_back(rank_main, r, n, port);
+  for (int r = 0; r < n; r++) ts.emplace_back(rank_main, r, n, port, std::string());
   for (auto& t : ts) t.join();
+  if (port2 > 0) {
+    // The same program with the ranks spread over two host names (2 + 2): node groups, rails, and
+    // the allreduce in two levels (shared memory inside a "host" unless BC_SHM=0).
+    ts.clear();
+    for (int r = 0; r < 4; r++) ts.emplace_back(rank_main, r, 4, port2, std::string(r < 2 ? "hostA" : "hostB"));
+    for (auto& t : ts) t.join();
+  }
   if (g_failures.load() == 0) printf("host_selftest ok (%d ranks)\n", n);
   return g_failures.load() == 0 ? 0 : 1;
 }

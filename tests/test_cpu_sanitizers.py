@@ -22,7 +22,8 @@ def test_host_runtime_is_clean_under_sanitizer(sanitizer, transport):
         raise
     # CPU tensors through the shared-memory segment (small slots: several chunks) or the socket ring
     env = dict(os.environ, **({"BC_SHM": "0"} if transport == "ring" else {"BC_SHM_SLOT_KB": "4"}))
-    r = subprocess.run([str(exe), "3", str(_free_port())], capture_output=True, text=True, timeout=300, env=env)
+    # second port: a second pass with 4 ranks on two host names (node groups, rails, two levels)
+    r = subprocess.run([str(exe), "3", str(_free_port()), str(_free_port())], capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-6000:]
     assert "host_selftest ok" in r.stdout
     assert "WARNING: ThreadSanitizer" not in r.stderr and "ERROR: AddressSanitizer" not in r.stderr
