@@ -373,6 +373,30 @@ def allreduce(tensor: torch.Tensor, average: Optional[bool] = None, name: Option
     return allreduce_async(tensor, average=average, name=name, op=op).wait()
 
 
+def grouped_allreduce(tensors, average: Optional[bool] = None, name: Optional[str] = None, op: str = "sum") -> List[torch.Tensor]:
+    """`allreduce` of several dense tensors at the price of one collective per dtype and device:
+    the tensors are packed into one flat buffer, reduced, and cut apart again. Every rank must
+    pass tensors of the same shapes in the same order. (The reference reduces tensor by tensor,
+    `mpi_collectives/__init__.py:199-220`; each of those pays a negotiation round.)"""
+    tensors = list(tensors)
+    name = name or _auto_name("allreduce")
+    out: List[Optional[torch.Tensor]] = [None] * len(tensors)
+    groups = {}
+    for i, t in enumerate(tensors):
+        if t.is_sparse:
+            raise CollectiveError("grouped_allreduce takes dense tensors")
+        groups.setdefault((t.dtype, t.device), []).append(i)
+    for k, (key, idx) in enumerate(sorted(groups.items(), key=lambda kv: kv[1][0])):
+        flat = torch.cat([tensors[i].detach().reshape(-1) for i in idx])
+        allreduce_(flat, average=average, name=f"{name}.{k}", op=op)
+        off = 0
+        for i in idx:
+            n = tensors[i].numel()
+            out[i] = flat[off:off + n].view(tensors[i].shape)
+            off += n
+    return out
+
+
 def all_sum(tensor: torch.Tensor, name: Optional[str] = None) -> torch.Tensor:
     """Element-wise sum over all ranks (`nccl_ops.all_sum`, contrib/nccl/python/ops/nccl_ops.py:34-51)."""
     return allreduce(tensor, average=False, name=name, op="sum")

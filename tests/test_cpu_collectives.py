@@ -336,3 +336,22 @@ def test_collectives_carry_no_gradient():
     for _, rec in res:
         assert rec["flags"] == [False, False, False] and rec["fns"] == [True, True]
         assert rec["grad"] == [5.0, 5.0, 5.0] and rec["y"] == [4.0, 4.0, 4.0]
+
+
+def test_grouped_allreduce_packs_by_dtype():
+    res = run("""
+    bc.init(device="cpu")
+    ts = [torch.full((3, 2), 1.0 + RANK), torch.arange(5, dtype=torch.int64) * (RANK + 1), torch.full((), 2.0 * RANK), torch.zeros(0)]
+    bc.clear_stats()
+    avg = bc.grouped_allreduce(ts, name="grp")
+    tot = bc.grouped_allreduce(ts, average=False, name="grp2")
+    names = sorted(e["name"] for e in bc.stats() if e["op"] == "allreduce")
+    tri = SIZE * (SIZE + 1) // 2
+    ok = (torch.equal(tot[0], torch.full((3, 2), float(tri))) and torch.equal(tot[1], torch.arange(5) * tri)
+          and tot[2].item() == SIZE * (SIZE - 1) and tot[3].shape == (0,)
+          and torch.allclose(avg[0], torch.full((3, 2), tri / SIZE)) and avg[2].shape == () and [t.dtype for t in tot] == [t.dtype for t in ts])
+    emit(ok=bool(ok), names=names)
+    bc.shutdown()
+    """, nranks=3)
+    for _, rec in res:
+        assert rec["ok"] and rec["names"] == ["grp.0", "grp.1", "grp2.0", "grp2.1"]      # one collective per dtype
