@@ -185,5 +185,12 @@ def build_selftest(sanitizer: str = "thread", verbose: bool = False) -> Path:
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv, ptxas_info="--ptxas" in sys.argv, debug="--debug" in sys.argv)
-    print(path)
+    import argparse
+
+    ap = argparse.ArgumentParser(prog="python -m tensorflow_allreduce_b200.build", description="Build the native library in-tree.")
+    ap.add_argument("--force", action="store_true", help="recompile every source")
+    ap.add_argument("-v", "--verbose", action="store_true", help="print the compiler commands")
+    ap.add_argument("--ptxas", action="store_true", help="print registers, spills and shared memory of every kernel (-Xptxas -v)")
+    ap.add_argument("--debug", action="store_true", help="build the bounds-checked variant (-DBC_DEBUG, lib/libbcoll_debug.so)")
+    a = ap.parse_args()
+    print(build(force=a.force, verbose=a.verbose, ptxas_info=a.ptxas, debug=a.debug))
