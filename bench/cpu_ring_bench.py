@@ -7,7 +7,9 @@ data through shared memory; `BC_SHM=0` times the socket ring (loopback TCP) inst
     BC_SHM=0 python -m tensorflow_allreduce_b200.launch --nproc 2 --cpu bench/cpu_ring_bench.py
 
 Wall-clock time per call (host timers, maximum over ranks) through the public, name-keyed API, so
-the coordinator round trip is included. Bus bandwidth as in the GPU sweep.
+the coordinator round trip is included; `allreduce_inplace_ms` is the same without an output to
+allocate, `allreduce_data_phase_ms` the part after the negotiation (from `stats()`). Bus bandwidth
+as in the GPU sweep.
 """
 from __future__ import annotations
 
@@ -46,6 +48,21 @@ def main():
                 times.append(t1 - t0)
         ok = bool(y[0] == want and y[-1] == want)
         sec = max(bc.host_allgather(sorted(times)[len(times) // 2]))
+        # in place (no output to allocate and fault in), and the data phase alone from the library's records
+        z = torch.zeros(n)
+        bc.clear_stats()
+        tin = []
+        for it in range(a.iters + 2):
+            bc.barrier()
+            t0 = time.perf_counter()
+            bc.allreduce_(z, average=False, name=f"ip.{s}.{it}")
+            t1 = time.perf_counter()
+            if it >= 2:
+                tin.append(t1 - t0)
+        sec_in = max(bc.host_allgather(sorted(tin)[len(tin) // 2]))
+        recs = [e for e in bc.stats() if e["name"].startswith("ip.")][2:]
+        data = sorted(e["t_done"] - e["t_negotiated"] for e in recs)[len(recs) // 2]
+        sec_data = max(bc.host_allgather(data))
         rows = max(1, n // 256 // (P * (P + 1) // 2))
         t = torch.full(((rank + 1) * rows, 256), float(rank))
         gt = []
@@ -60,6 +77,7 @@ def main():
         total = g.numel() * 4
         if rank == 0:
             print(json.dumps({"bytes": s, "world": P, "transport": [e["algo"] for e in bc.stats() if e["op"] == "allreduce"][-1], "allreduce_ms": round(sec * 1e3, 4), "allreduce_busbw_gbs": round(s / sec * 2 * (P - 1) / P / 1e9, 3),
+                              "allreduce_inplace_ms": round(sec_in * 1e3, 4), "allreduce_data_phase_ms": round(sec_data * 1e3, 4),
                               "correct": ok, "allgather_total_bytes": total, "allgather_ms": round(gsec * 1e3, 4),
                               "allgather_busbw_gbs": round(total / gsec * (P - 1) / P / 1e9, 3)}), flush=True)
         s *= 4
