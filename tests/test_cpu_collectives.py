@@ -355,3 +355,23 @@ def test_grouped_allreduce_packs_by_dtype():
     """, nranks=3)
     for _, rec in res:
         assert rec["ok"] and rec["names"] == ["grp.0", "grp.1", "grp2.0", "grp2.1"]      # one collective per dtype
+
+
+def test_repeated_init_and_shutdown_leak_nothing():
+    # Twenty groups in a row in the same processes: descriptors are all closed again and no
+    # shared-memory object is left behind.
+    res = run("""
+    import glob
+    def nfds(): return len(os.listdir("/proc/self/fd"))
+    base = None
+    for it in range(20):
+        bc.init(device="cpu")                     # the same rendezvous port every time
+        s = bc.allreduce(torch.ones(1000) * (RANK + it), average=False)
+        assert s[0].item() == sum(r + it for r in range(SIZE))
+        bc.allgather(torch.ones(RANK + 1, 2))
+        bc.shutdown()
+        if it == 2: base = nfds()
+    emit(grew=nfds() - base, shm=sorted(glob.glob("/dev/shm/bcoll-*")))
+    """, nranks=3, timeout=180)
+    for _, rec in res:
+        assert rec["grew"] == 0 and rec["shm"] == []
