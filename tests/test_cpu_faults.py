@@ -107,3 +107,28 @@ def test_rank_exit_inside_the_data_phase_is_detected(transport):
         rec = res[r][1]
         assert rec is not None, res[r][0].stderr[-2000:]
         assert rec["err"] is not None and rec["seconds"] < 20, rec
+
+
+def test_survivors_form_a_new_group_after_a_rank_is_lost():
+    # Rank 2 ends inside a collective. The others get an error, shut the broken group down and
+    # start a group of two in the same processes (same rendezvous port), which works.
+    res = run("""
+    bc.init(device="cpu")
+    bc.allreduce(torch.ones(4), name="warm")
+    try:
+        bc.allreduce(torch.ones(1000), name="doomed")
+        err = None
+    except bc.CollectiveError as e:
+        err = str(e)
+    bc.shutdown()
+    bc.init(device="cpu", rank=RANK, size=2)
+    s = bc.allreduce(torch.arange(3.0) + RANK, average=False, name="again")
+    g = bc.allgather(torch.full((1, 1), float(RANK)))
+    emit(err=err, size=bc.size(), s=s.tolist(), g=g.flatten().tolist())
+    bc.shutdown()
+    """, nranks=3, env={"BC_TIMEOUT_S": "30", "BC_FAULT": "exit_in_collective:rank=2:name=doomed"}, timeout=100, expect_ok=False)
+    assert res[2][0].returncode == 42
+    for r in (0, 1):
+        rec = res[r][1]
+        assert rec is not None, res[r][0].stderr[-2000:]
+        assert rec["err"] is not None and rec["size"] == 2 and rec["s"] == [1.0, 3.0, 5.0] and rec["g"] == [0.0, 1.0]
