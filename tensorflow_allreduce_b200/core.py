@@ -203,6 +203,12 @@ def on_gpu() -> bool:
     return bool(_call(_lib.lib().bc_on_gpu()))
 
 
+def is_broken() -> bool:
+    """True once the group has lost a peer or a deadline ran out: every later collective fails at
+    once. The way on is `shutdown()` and a new `init()` among the ranks that are left."""
+    return bool(_call(_lib.lib().bc_broken()))
+
+
 def n_nodes() -> int:
     """Hosts of a group that runs in two levels, else 1. A group whose ranks sit on several hosts
     (the same number on each) reduces inside each host first, GPU tensors with the NVLink kernels

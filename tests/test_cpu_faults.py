@@ -120,15 +120,17 @@ def test_survivors_form_a_new_group_after_a_rank_is_lost():
         err = None
     except bc.CollectiveError as e:
         err = str(e)
+    broken = bc.is_broken()
     bc.shutdown()
     bc.init(device="cpu", rank=RANK, size=2)
+    broken = broken and not bc.is_broken()
     s = bc.allreduce(torch.arange(3.0) + RANK, average=False, name="again")
     g = bc.allgather(torch.full((1, 1), float(RANK)))
-    emit(err=err, size=bc.size(), s=s.tolist(), g=g.flatten().tolist())
+    emit(err=err, size=bc.size(), s=s.tolist(), g=g.flatten().tolist(), broken=broken)
     bc.shutdown()
     """, nranks=3, env={"BC_TIMEOUT_S": "30", "BC_FAULT": "exit_in_collective:rank=2:name=doomed"}, timeout=100, expect_ok=False)
     assert res[2][0].returncode == 42
     for r in (0, 1):
         rec = res[r][1]
         assert rec is not None, res[r][0].stderr[-2000:]
-        assert rec["err"] is not None and rec["size"] == 2 and rec["s"] == [1.0, 3.0, 5.0] and rec["g"] == [0.0, 1.0]
+        assert rec["err"] is not None and rec["broken"] and rec["size"] == 2 and rec["s"] == [1.0, 3.0, 5.0] and rec["g"] == [0.0, 1.0]
