@@ -5,6 +5,7 @@ data through shared memory; `BC_SHM=0` times the socket ring (loopback TCP) inst
 
     python -m tensorflow_allreduce_b200.launch --nproc 2 --cpu bench/cpu_ring_bench.py [--max-mb 64]
     BC_SHM=0 python -m tensorflow_allreduce_b200.launch --nproc 2 --cpu bench/cpu_ring_bench.py
+    ... bench/cpu_ring_bench.py --gloo        (adds torch.distributed's gloo all_reduce, in place, as a comparator)
 
 Wall-clock time per call (host timers, maximum over ranks) through the public, name-keyed API, so
 the coordinator round trip is included; `allreduce_inplace_ms` is the same without an output to
@@ -30,9 +31,15 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--max-mb", type=int, default=64)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--gloo", action="store_true", help="also time torch.distributed's gloo backend on the same tensors")
     a = ap.parse_args()
     bc.init(device="cpu")
     rank, P = bc.rank(), bc.size()
+    if a.gloo:
+        import torch.distributed as dist
+
+        port = bc.host_allgather(__import__("tensorflow_allreduce_b200.utils.spawn", fromlist=["free_port"]).free_port())[0]
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=P)
     s = 1 << 10
     while s <= a.max_mb << 20:
         n = s // 4
@@ -63,6 +70,18 @@ def main():
         recs = [e for e in bc.stats() if e["name"].startswith("ip.")][2:]
         data = sorted(e["t_done"] - e["t_negotiated"] for e in recs)[len(recs) // 2]
         sec_data = max(bc.host_allgather(data))
+        gloo_ms = None
+        if a.gloo:
+            w = torch.zeros(n)
+            tg = []
+            for it in range(a.iters + 2):
+                bc.barrier()
+                t0 = time.perf_counter()
+                dist.all_reduce(w)
+                t1 = time.perf_counter()
+                if it >= 2:
+                    tg.append(t1 - t0)
+            gloo_ms = round(max(bc.host_allgather(sorted(tg)[len(tg) // 2])) * 1e3, 4)
         rows = max(1, n // 256 // (P * (P + 1) // 2))
         t = torch.full(((rank + 1) * rows, 256), float(rank))
         gt = []
@@ -78,9 +97,12 @@ def main():
         if rank == 0:
             print(json.dumps({"bytes": s, "world": P, "transport": [e["algo"] for e in bc.stats() if e["op"] == "allreduce"][-1], "allreduce_ms": round(sec * 1e3, 4), "allreduce_busbw_gbs": round(s / sec * 2 * (P - 1) / P / 1e9, 3),
                               "allreduce_inplace_ms": round(sec_in * 1e3, 4), "allreduce_data_phase_ms": round(sec_data * 1e3, 4),
+                              "gloo_allreduce_inplace_ms": gloo_ms,
                               "correct": ok, "allgather_total_bytes": total, "allgather_ms": round(gsec * 1e3, 4),
                               "allgather_busbw_gbs": round(total / gsec * (P - 1) / P / 1e9, 3)}), flush=True)
         s *= 4
+    if a.gloo:
+        dist.destroy_process_group()
     bc.shutdown()
 
 
