@@ -352,6 +352,7 @@ void Runtime::finish(const std::shared_ptr<OpRecord>& r, bool ok, const std::str
     e.t_enqueue = r->t_enqueue;
     e.t_negotiated = r->t_negotiated;
     e.t_done = r->t_done;
+    for (int i = 0; i < 3; i++) e.two_level_s[i] = r->two_level_s[i];
     stats_.push_back(e);
     if (stats_.size() > 4096) stats_.pop_front();
   }
@@ -642,7 +643,7 @@ void Runtime::perform_allreduce(OpRecord& r) {
       // several hosts with several ranks each: shared memory inside the host, rails between hosts
       ShmLocalLevel local(*shm_, r.out, deadline);
       cpu_staging_.resize(slice_len(count, node_->local_size, 0) * dtype_size(r.dtype) + 16);
-      bc::two_level_allreduce(*node_, local, cpu_staging_.data(), count, r.dtype, scale, idiv, r.red, deadline);
+      bc::two_level_allreduce(*node_, local, cpu_staging_.data(), count, r.dtype, scale, idiv, r.red, deadline, r.two_level_s);
     } else if (shm_) {
       shm_->allreduce(r.out, count, r.dtype, scale, idiv, r.red, deadline);
     } else {
@@ -795,7 +796,7 @@ void Runtime::two_level_allreduce(OpRecord& r, size_t count, double scale, int64
   const size_t e = dtype_size(r.dtype);
   void* staging = pinned(slice_len(count, node_->local_size, 0) * e);
   GpuLocalLevel local(*comm_, r.in, r.out, [this](size_t b) { return device_scratch(b); });
-  bc::two_level_allreduce(*node_, local, staging, count, r.dtype, scale, idiv, r.red, now_s() + opt_.timeout_s);
+  bc::two_level_allreduce(*node_, local, staging, count, r.dtype, scale, idiv, r.red, now_s() + opt_.timeout_s, r.two_level_s);
   // The pinned slice is read by a copy that is still queued; the next operation reuses it.
   check(cudaStreamSynchronize(comm_->stream(0)), "cudaStreamSynchronize");
   r.algo = 0;
@@ -834,7 +835,10 @@ std::string Runtime::stats_json() {
     os.precision(9);
     os << "\",\"op\":" << e.op << ",\"algo\":" << e.algo << ",\"device\":" << e.device << ",\"blocks\":" << e.blocks
        << ",\"bytes\":" << e.bytes << std::fixed << ",\"t_enqueue\":" << e.t_enqueue << ",\"t_negotiated\":" << e.t_negotiated
-       << ",\"t_done\":" << e.t_done << "}";
+       << ",\"t_done\":" << e.t_done;
+    if (e.two_level_s[0] > 0 || e.two_level_s[1] > 0 || e.two_level_s[2] > 0)
+      os << ",\"two_level_s\":[" << e.two_level_s[0] << "," << e.two_level_s[1] << "," << e.two_level_s[2] << "]";
+    os << "}";
   }
   os << "]";
   return os.str();

@@ -62,6 +62,7 @@ struct OpRecord {
   enum State { PENDING, DONE, FAILED } state = PENDING;
   std::string error;
   double t_enqueue = 0, t_negotiated = 0, t_done = 0;
+  double two_level_s[3] = {0, 0, 0};   // allreduce in two levels: inside the host, over the rail, back inside the host
 };
 
 struct RuntimeOptions {
@@ -100,6 +101,7 @@ struct StatEntry {
   int op = 0, algo = 0, device = 0, blocks = 0;
   int64_t bytes = 0;
   double t_enqueue = 0, t_negotiated = 0, t_done = 0;
+  double two_level_s[3] = {0, 0, 0};
 };
 
 class Runtime {

@@ -8,16 +8,24 @@
 namespace bc {
 
 void two_level_allreduce(NodeGroup& g, LocalLevel& local, void* staging, size_t count, DType dtype, double scale,
-                         int64_t int_divisor, ReduceOp red, double deadline) {
+                         int64_t int_divisor, ReduceOp red, double deadline, double* seconds) {
+  const double t0 = now_s();
   local.reduce_in_node(count, dtype, red);
   const int L = g.local_size;
   std::vector<size_t> lens(L);
   for (int i = 0; i < L; i++) lens[i] = slice_len(count, L, i);
   const size_t begin = slice_begin(count, L, g.local_rank), len = lens[g.local_rank];
   local.fetch(staging, begin, len, dtype);
+  const double t1 = now_s();
   // The ranks of one rail hold the same slice of their hosts' sums, so the lengths agree.
   cpu_ring_allreduce(g.rail, staging, len, dtype, scale, int_divisor, deadline, red);
+  const double t2 = now_s();
   local.finish(staging, begin, len, lens, dtype);
+  if (seconds) {
+    seconds[0] = t1 - t0;
+    seconds[1] = t2 - t1;
+    seconds[2] = now_s() - t2;
+  }
 }
 
 namespace {

@@ -41,8 +41,10 @@ inline size_t slice_len(size_t count, int n, int i) { return count / n + ((size_
 
 // `staging` must hold slice_len(count, local_size, 0) elements. Runs on the thread that owns the
 // rail's sockets.
+// `seconds`, if given, receives the host time spent in the three steps (inside the host, over the
+// rail, back inside the host; on GPUs the last two include only what the host waits for).
 void two_level_allreduce(NodeGroup& g, LocalLevel& local, void* staging, size_t count, DType dtype, double scale,
-                         int64_t int_divisor, ReduceOp red, double deadline);
+                         int64_t int_divisor, ReduceOp red, double deadline, double* seconds = nullptr);
 
 // The levels inside a host for CPU tensors: the host's shared-memory group.
 class ShmGroup;

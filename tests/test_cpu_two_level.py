@@ -143,7 +143,8 @@ t = torch.full((RANK + 1, 3), float(RANK))
 g = bc.allgather(t)
 if g.shape[0] != SIZE * (SIZE + 1) // 2 or g[-1, 0] != SIZE - 1: bad.append(["allgather"])
 algos = sorted({s["algo"] for s in bc.stats() if s["op"] == "allreduce"})
-emit(bad=bad, nodes=bc.n_nodes(), algos=algos)
+phases = [s.get("two_level_s") for s in bc.stats() if s["op"] == "allreduce" and s["bytes"] > 100000][-1]
+emit(bad=bad, nodes=bc.n_nodes(), algos=algos, phases=phases)
 bc.shutdown()
 """
 
@@ -162,6 +163,11 @@ def test_public_cpu_collectives_over_fake_hosts(groups):
         assert rec["bad"] == []
         assert rec["nodes"] == (2 if groups == "default" else 1)
         assert rec["algos"] == (["cpu_shm"] if groups == "default" else ["cpu_ring"])
+        # the records of a two-level allreduce carry the time of its three steps
+        if groups == "default":
+            assert len(rec["phases"]) == 3 and all(p > 0 for p in rec["phases"])
+        else:
+            assert rec["phases"] is None
 
 
 def test_flat_buckets_with_accumulation_and_unused_parameters():
