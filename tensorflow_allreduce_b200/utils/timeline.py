@@ -4,7 +4,8 @@ The reference has no tracing of its own; under TensorFlow's `RunOptions.trace_le
 allreduce shows up as one async op whose span runs from enqueue to completion, negotiation wait
 included (`tensorflow/python/client/timeline.py`). Here every collective contributes two spans:
 "negotiate" (enqueue -> go-ahead from the coordinator) and "launch"/"run" (go-ahead -> kernel
-enqueued on the private stream for CUDA tensors, or ring finished for CPU tensors).
+enqueued on the private stream for CUDA tensors, or ring finished for CPU tensors); an allreduce
+in two levels adds its three steps.
 """
 from __future__ import annotations
 
@@ -28,6 +29,13 @@ def chrome_trace(records: Optional[Iterable[dict]] = None, pid: Optional[int] = 
                    "ts": (r["t_enqueue"] - t0) * 1e6, "dur": max(0.0, (r["t_negotiated"] - r["t_enqueue"]) * 1e6), "args": args})
         ev.append({"name": r["name"], "cat": r["op"] + (".launch" if r["device"] else ".run"), "ph": "X", "pid": pid, "tid": 1,
                    "ts": (r["t_negotiated"] - t0) * 1e6, "dur": max(0.0, (r["t_done"] - r["t_negotiated"]) * 1e6), "args": args})
+        if r.get("two_level_s"):
+            # an allreduce over several hosts: its three steps, one after the other, on a row of their own
+            ts = (r["t_negotiated"] - t0) * 1e6
+            for step, sec in zip(("inside the host", "rail between hosts", "gather inside the host"), r["two_level_s"]):
+                ev.append({"name": step, "cat": r["op"] + ".two_level", "ph": "X", "pid": pid, "tid": 2, "ts": ts, "dur": sec * 1e6,
+                           "args": {"collective": r["name"]}})
+                ts += sec * 1e6
     return ev
 
 

@@ -44,6 +44,11 @@ def test_timeline_export():
     assert abs(ev[0]["dur"] - 200.0) < 1e-3
     s = timeline.summary(recs)
     assert s["allreduce/nvls"]["calls"] == 1 and s["allgather/cpu_ring"]["bytes"] == 100
+    # an allreduce in two levels shows its three steps back to back
+    two = dict(recs[0], name="c", two_level_s=[1e-4, 3e-4, 2e-4])
+    steps = [e for e in timeline.chrome_trace([two], pid=0) if e["cat"] == "allreduce.two_level"]
+    assert [e["name"] for e in steps] == ["inside the host", "rail between hosts", "gather inside the host"]
+    assert abs(steps[1]["ts"] - steps[0]["ts"] - 100.0) < 1e-3 and abs(steps[2]["dur"] - 200.0) < 1e-3
 
 
 def test_launcher_starts_ranks_and_propagates_failure(tmp_path):
