@@ -152,14 +152,18 @@ def test_minimize_and_compute_apply_gradients():
         assert rec["worst"] < 1e-6 and rec["grads_match"] and rec["refused"]
 
 
-def test_example_script_trains_on_two_cpu_ranks():
+def test_example_scripts_train_on_two_cpu_ranks():
     import os
     import subprocess
     import sys
 
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    cmd = [sys.executable, "-m", "tensorflow_allreduce_b200.launch", "--nproc", "2", "--cpu",
-           os.path.join(root, "examples", "data_parallel_training.py"), "--steps", "12"]
-    r = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=240)
+    launch = [sys.executable, "-m", "tensorflow_allreduce_b200.launch", "--nproc", "2", "--cpu"]
+    r = subprocess.run(launch + [os.path.join(root, "examples", "data_parallel_training.py"), "--steps", "12"],
+                       cwd=root, capture_output=True, text=True, timeout=240)
     assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-2000:]
     assert "identical weights True" in r.stdout
+    # the example of the reference's module docstring (mpi_collectives/__init__.py:81-111)
+    r = subprocess.run(launch + [os.path.join(root, "examples", "linear_regression.py")], cwd=root, capture_output=True, text=True, timeout=240)
+    assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-2000:]
+    assert "MPI Size: 2" in r.stdout and "Average Loss:" in r.stdout
