@@ -209,3 +209,24 @@ def test_info_command_reports_and_checks():
     info = json.loads(r.stdout)
     assert info["library_built"] and info["library_matches_sources"] and info["check"] == {"cpu": True}
     assert info["config"]["bucket_mb"] == 8.0 and info["environment"]["BC_BUCKET_MB"] == "8"
+
+
+def test_bench_reference_arm_reports_unavailable():
+    # The reference (a TensorFlow 1.3 fork) cannot be installed offline: its arm prints one JSON
+    # line saying so and exits 0, also when every rank of a torchrun launch runs it.
+    import json
+    import os
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for rank in ("0", "1"):
+        env = dict(os.environ, RANK=rank, WORLD_SIZE="2")
+        r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "2", "--warmup", "3"],
+                           cwd=root, env=env, capture_output=True, text=True, timeout=120)
+        assert r.returncode == 0, r.stderr[-2000:]
+        lines = [l for l in r.stdout.splitlines() if l.strip()]
+        if rank == "0":
+            rec = json.loads(lines[-1])
+            assert rec["impl"] == "reference" and "unavailable" in rec and len(lines) == 1
+        else:
+            assert lines == []
