@@ -230,3 +230,17 @@ def test_bench_reference_arm_reports_unavailable():
             assert rec["impl"] == "reference" and "unavailable" in rec and len(lines) == 1
         else:
             assert lines == []
+
+
+def test_entry_point_build_leaves_both_libraries_current():
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    import __graft_entry__ as entry
+    from tensorflow_allreduce_b200 import build
+
+    entry.build()
+    assert build.LIB.exists() and build.LIB_DEBUG.exists()
+    assert not build.needs_build() and not build.needs_build(debug=True)
+    assert callable(entry.smoke)
