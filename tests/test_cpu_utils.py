@@ -244,3 +244,25 @@ def test_entry_point_build_leaves_both_libraries_current():
     assert build.LIB.exists() and build.LIB_DEBUG.exists()
     assert not build.needs_build() and not build.needs_build(debug=True)
     assert callable(entry.smoke)
+
+
+def test_chunks_by_bytes_partitions_in_order():
+    import torch
+    from hypothesis import given, settings, strategies as st
+
+    from tensorflow_allreduce_b200.parallel.distributed_optimizer import _chunks_by_bytes
+
+    @settings(max_examples=200, deadline=None)
+    @given(st.lists(st.integers(min_value=0, max_value=50), max_size=30), st.integers(min_value=1, max_value=120))
+    def check(sizes, limit):
+        tensors = [torch.empty(n, dtype=torch.float32) for n in sizes]
+        runs = list(_chunks_by_bytes(tensors, limit))
+        flat = [t for run in runs for t in run]
+        assert len(flat) == len(tensors) and all(a is b for a, b in zip(flat, tensors))      # same tensors, same order
+        for i, run in enumerate(runs):
+            size = sum(t.numel() * 4 for t in run)
+            assert run and (size <= limit or len(run) == 1)                                    # only a lone tensor may exceed the limit
+            if i + 1 < len(runs):                                                              # greedy: the next tensor did not fit
+                assert size + runs[i + 1][0].numel() * 4 > limit
+
+    check()
