@@ -229,8 +229,9 @@ def config() -> Config:
 
 
 def set_fault(spec: str) -> None:
-    """Arm a host-side fault (tests): `drop_request`, `delay_ms=N`, `exit_before`, `close_ctrl`,
-    each optionally followed by `:rank=R` and `:name=NAME`."""
+    """Arm a host-side fault (tests): `drop_request`, `delay_ms=N`, `exit_before`,
+    `exit_in_collective`, `close_ctrl`, each optionally followed by `:rank=R` and `:name=NAME`;
+    an empty string disarms."""
     _call(_lib.lib().bc_set_fault(spec.encode()))
 
 

@@ -134,3 +134,32 @@ def test_survivors_form_a_new_group_after_a_rank_is_lost():
         rec = res[r][1]
         assert rec is not None, res[r][0].stderr[-2000:]
         assert rec["err"] is not None and rec["broken"] and rec["size"] == 2 and rec["s"] == [1.0, 3.0, 5.0] and rec["g"] == [0.0, 1.0]
+
+
+def test_fault_specs_are_parsed_or_refused():
+    # Any text is either a fault specification or an error; a specification that names another
+    # rank or another collective leaves this one alone.
+    res = run("""
+    from hypothesis import given, settings, strategies as st
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"): os.environ.pop(k, None)
+    bc.init(device="cpu")
+    outcomes = {"ok": 0, "refused": 0}
+    @settings(max_examples=300, deadline=None)
+    @given(st.text(alphabet="abcdefghijklmnopqrstuvwxyz_=:0123456789-", max_size=40))
+    def check(text):
+        try:
+            bc.set_fault(text)
+            outcomes["ok"] += 1
+        except bc.CollectiveError as e:
+            assert "unknown fault kind" in str(e)
+            outcomes["refused"] += 1
+    check()
+    bc.set_fault("exit_before:rank=5:name=elsewhere")
+    bc.set_fault("drop_request:name=other")
+    s = bc.allreduce(torch.ones(3), name="mine")
+    bc.set_fault("")
+    emit(outcomes=outcomes, s=s.tolist())
+    bc.shutdown()
+    """, nranks=1)
+    rec = res[0][1]
+    assert rec["s"] == [1.0, 1.0, 1.0] and rec["outcomes"]["ok"] >= 1 and rec["outcomes"]["refused"] >= 1
