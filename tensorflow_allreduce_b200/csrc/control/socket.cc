@@ -144,7 +144,7 @@ int Socket::recv_fd(int32_t* tag, double deadline) const {
     char ctrl[CMSG_SPACE(sizeof(int))];
     msg.msg_control = ctrl;
     msg.msg_controllen = sizeof(ctrl);
-    ssize_t k = ::recvmsg(fd_, &msg, 0);
+    ssize_t k = ::recvmsg(fd_, &msg, MSG_CMSG_CLOEXEC);
     if (k < 0 && (errno == EINTR || errno == EAGAIN)) continue;
     if (k <= 0) throw CommLost("recvmsg(SCM_RIGHTS) failed or peer closed");
     struct cmsghdr* c = CMSG_FIRSTHDR(&msg);
@@ -158,7 +158,7 @@ int Socket::recv_fd(int32_t* tag, double deadline) const {
 }
 
 Socket Socket::listen_tcp(const std::string& addr, int port, int backlog, int* bound_port) {
-  int fd = ::socket(AF_INET, SOCK_STREAM, 0);
+  int fd = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
   BC_CHECK(fd >= 0, "socket(): " << strerror(errno));
   int one = 1;
   setsockopt(fd, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
@@ -200,7 +200,7 @@ Socket Socket::connect_tcp(const std::string& addr, int port, double deadline) {
   BC_CHECK(grc == 0 && res, "cannot resolve " << addr << ": " << gai_strerror(grc));
   std::string last = "no attempt";
   for (;;) {
-    int fd = ::socket(AF_INET, SOCK_STREAM, 0);
+    int fd = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
     if (fd >= 0) {
       if (::connect(fd, res->ai_addr, res->ai_addrlen) == 0) {
         // While nobody listens on a local port of the ephemeral range yet, the kernel may give
@@ -241,7 +241,7 @@ static socklen_t fill_abstract(struct sockaddr_un* sa, const std::string& name) 
 }
 
 Socket Socket::listen_unix(const std::string& name, int backlog) {
-  int fd = ::socket(AF_UNIX, SOCK_STREAM, 0);
+  int fd = ::socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
   BC_CHECK(fd >= 0, "socket(AF_UNIX): " << strerror(errno));
   struct sockaddr_un sa;
   socklen_t len = fill_abstract(&sa, name);
@@ -258,7 +258,7 @@ Socket Socket::connect_unix(const std::string& name, double deadline) {
   socklen_t len = fill_abstract(&sa, name);
   std::string last;
   for (;;) {
-    int fd = ::socket(AF_UNIX, SOCK_STREAM, 0);
+    int fd = ::socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
     if (fd >= 0) {
       if (::connect(fd, (struct sockaddr*)&sa, len) == 0) return Socket(fd);
       last = strerror(errno);
@@ -273,7 +273,7 @@ Socket Socket::connect_unix(const std::string& name, double deadline) {
 Socket Socket::accept(double deadline) const {
   for (;;) {
     wait_fd(fd_, POLLIN, deadline, "accept");
-    int fd = ::accept(fd_, nullptr, nullptr);
+    int fd = ::accept4(fd_, nullptr, nullptr, SOCK_CLOEXEC);   // not inherited by programs a rank starts
     if (fd >= 0) {
       int one = 1;
       setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));  // harmless on unix sockets
