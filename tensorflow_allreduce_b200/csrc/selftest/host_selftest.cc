@@ -6,8 +6,10 @@
 //
 //   host_selftest <nranks> <port> [<port2>]     exit code 0 = all checks passed
 //   (with <port2>: a second pass with 4 ranks that report two host names)
+#include <fcntl.h>
 #include <stdio.h>
 #include <string.h>
+#include <unistd.h>
 
 #include <atomic>
 #include <thread>
@@ -198,8 +200,36 @@ static void wire_checks() {
   }
 }
 
+// A descriptor handed over a unix socket (how the ranks of a host share their GPU allocations)
+// arrives usable, tagged, and close-on-exec.
+static void descriptor_passing_check() {
+  char name[64];
+  snprintf(name, sizeof(name), "bcoll-selftest-%d", (int)getpid());
+  Socket listener = Socket::listen_unix(name, 2);
+  std::thread sender([&] {
+    Socket c = Socket::connect_unix(name, now_s() + 5);
+    int fds[2];
+    if (pipe(fds) != 0) { g_failures++; return; }
+    c.send_fd(fds[0], 77, now_s() + 5);       // the read end travels
+    ::close(fds[0]);
+    const char msg[] = "through the pipe";
+    if (write(fds[1], msg, sizeof(msg)) != (ssize_t)sizeof(msg)) g_failures++;
+    ::close(fds[1]);
+  });
+  Socket a = listener.accept(now_s() + 5);
+  int32_t tag = 0;
+  int fd = a.recv_fd(&tag, now_s() + 5);
+  sender.join();
+  char buf[32] = {0};
+  ssize_t k = read(fd, buf, sizeof(buf));
+  EXPECT(tag == 77 && k == 17 && strcmp(buf, "through the pipe") == 0, "descriptor passing: tag %d, %zd bytes", (int)tag, k);
+  EXPECT((fcntl(fd, F_GETFD) & FD_CLOEXEC) != 0, "received descriptor is not close-on-exec");
+  ::close(fd);
+}
+
 int main(int argc, char** argv) {
   wire_checks();
+  descriptor_passing_check();
   int n = argc > 1 ? atoi(argv[1]) : 3;
   int port = argc > 2 ? atoi(argv[2]) : 29650;
   int port2 = argc > 3 ? atoi(argv[3]) : 0;
