@@ -266,3 +266,61 @@ def test_chunks_by_bytes_partitions_in_order():
                 assert size + runs[i + 1][0].numel() * 4 > limit
 
     check()
+
+
+def test_symmetric_heap_allocator_never_overlaps_and_coalesces():
+    # The first-fit allocator that sub-divides the symmetric heap, driven without a GPU: random
+    # allocations and frees, blocks whose reuse waits for an event, and full recovery at the end.
+    import random
+
+    import torch
+
+    from tensorflow_allreduce_b200.ops.symmetric import _ALIGN, _Heap
+
+    class FakeEvent:
+        def __init__(self):
+            self.done = False
+            self.waited = False
+
+        def query(self):
+            return self.done
+
+        def synchronize(self):
+            self.waited = self.done = True
+
+    rng = random.Random(7)
+    size = 64 * _ALIGN
+    heap = _Heap(0, size, torch.device("cpu"))
+    live = {}                                   # offset -> length (rounded)
+    events = []
+    for step in range(3000):
+        if live and rng.random() < 0.45:
+            off = rng.choice(sorted(live))
+            length = live.pop(off)
+            if rng.random() < 0.5:
+                ev = FakeEvent()
+                events.append(ev)
+                heap.limbo.append((ev, off, length))          # reuse must wait for this event
+            else:
+                heap.release_later(off, length)               # no CUDA here: free at once
+        else:
+            nbytes = rng.choice([1, 100, _ALIGN, _ALIGN + 1, 5 * _ALIGN, 17 * _ALIGN])
+            need = (nbytes + _ALIGN - 1) // _ALIGN * _ALIGN
+            off = heap.alloc(nbytes)
+            if off is None:
+                # refused only when no hole fits, even after waiting for every pending free
+                assert all(e.done for e in events)
+                assert all(l < need for _, l in heap.free)
+                continue
+            assert off % _ALIGN == 0 and 0 <= off and off + need <= size
+            for o, l in live.items():
+                assert off + need <= o or o + l <= off, "overlapping blocks"
+            live[off] = need
+        if rng.random() < 0.1:
+            for e in events:
+                e.done = True
+    for off, length in list(live.items()):
+        heap.release_later(off, length)
+    for e in events:
+        e.done = True
+    assert heap.alloc(size) == 0                # everything came back and merged into one hole
