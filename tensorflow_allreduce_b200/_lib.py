@@ -60,6 +60,8 @@ def _declare(lib):
         "bc_n_nodes": (i, []),
         "bc_node_index": (i, []),
         "bc_two_level_allreduce_host": (i, [vp, ll, i, i, i]),
+        "bc_select_algo": (i, [i, ll, i, i, i, i, ll, ll, i]),
+        "bc_choose_blocks": (i, [ll, i, i, i, i, i]),
         "bc_allreduce_async": (ll, [cp, vp, vp, i, i, P(ll), i, i, i, vp, i]),
         "bc_allgather_async": (ll, [cp, vp, i, i, P(ll), i, ALLOC_FN, vp, vp]),
         "bc_wait": (i, [ll, d]),

@@ -39,6 +39,12 @@ int bc_node_index(void);
  * standing in for the NVLink level (sum inside the host, slices over the rails, gather inside the
  * host). Collective over all ranks; must not overlap any other collective of the job. Exists to
  * check the slice arithmetic and the rails on machines without GPUs. */
+/* The algorithm selector and the grid size as pure functions (no GPU, no group needed): what a
+ * group of `world` ranks would use for a reduction of `bytes` bytes. Algorithms: 1 one-shot,
+ * 2 two-shot, 3 NVLS; force_algo 0 = choose. Negative thresholds mean the defaults. */
+int bc_select_algo(int world, long long bytes, int dtype, int in_place_or_fused, int has_multicast, int force_algo,
+                   long long one_shot_max_bytes, long long nvls_min_bytes, int use_nvls);
+int bc_choose_blocks(long long bytes, int world, int algo, int fused_update, int sm_count, int cap_override);
 int bc_two_level_allreduce_host(void* data, long long count, int dtype, int average, int reduce_op);
 
 /* Negotiated, name-keyed collectives. The returned handle must be released. For CUDA tensors

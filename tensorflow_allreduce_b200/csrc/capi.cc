@@ -128,6 +128,24 @@ int bc_two_level_allreduce_host(void* data, long long count, int dtype, int aver
   API_END(-1)
 }
 
+int bc_select_algo(int world, long long bytes, int dtype, int in_place_or_fused, int has_multicast, int force_algo,
+                   long long one_shot_max_bytes, long long nvls_min_bytes, int use_nvls) {
+  API_BEGIN
+  gpu::CommConfig cfg;
+  cfg.force_algo = force_algo;
+  if (one_shot_max_bytes >= 0) cfg.one_shot_max_bytes = (size_t)one_shot_max_bytes;
+  if (nvls_min_bytes >= 0) cfg.nvls_min_bytes = (size_t)nvls_min_bytes;
+  cfg.use_nvls = use_nvls != 0;
+  return (int)gpu::select_algo(cfg, world, (size_t)bytes, (DType)dtype, in_place_or_fused != 0, has_multicast != 0);
+  API_END(-1)
+}
+
+int bc_choose_blocks(long long bytes, int world, int algo, int fused_update, int sm_count, int cap_override) {
+  API_BEGIN
+  return gpu::choose_blocks((size_t)bytes, world, algo, fused_update != 0, sm_count, cap_override);
+  API_END(-1)
+}
+
 // Entry points that address the communicator directly assume that it spans the whole job.
 static void require_one_host(const char* what) {
   if (rt().n_nodes() > 1)

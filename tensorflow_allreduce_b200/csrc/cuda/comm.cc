@@ -72,18 +72,22 @@ RankCtx Comm::make_ctx(int channel) const {
   return c;
 }
 
-Algo Comm::choose_algo(size_t bytes, DType dtype, bool in_place_or_fused, bool has_mc) const {
+Algo select_algo(const CommConfig& cfg, int world, size_t bytes, DType dtype, bool in_place_or_fused, bool has_mc) {
   const bool is_float = dtype == DType::F32 || dtype == DType::BF16 || dtype == DType::F16;
-  Algo forced = (Algo)cfg_.force_algo;
+  Algo forced = (Algo)cfg.force_algo;
   if (forced == Algo::ONE_SHOT && !in_place_or_fused) return forced;
   if (forced == Algo::TWO_SHOT) return forced;
   if (forced == Algo::NVLS && has_mc && is_float) return forced;
   if (forced != Algo::AUTO) return Algo::TWO_SHOT;
-  if (!in_place_or_fused && bytes <= cfg_.one_shot_max_bytes) return Algo::ONE_SHOT;
+  if (!in_place_or_fused && bytes <= cfg.one_shot_max_bytes) return Algo::ONE_SHOT;
   // With two ranks the switch-side reduction saves no traffic (each GPU moves N/2 either way)
   // and measured slower than plain peer loads and stores; it pays from four ranks on.
-  if (has_mc && cfg_.use_nvls && is_float && world_ >= 4 && bytes >= cfg_.nvls_min_bytes) return Algo::NVLS;
+  if (has_mc && cfg.use_nvls && is_float && world >= 4 && bytes >= cfg.nvls_min_bytes) return Algo::NVLS;
   return Algo::TWO_SHOT;
+}
+
+Algo Comm::choose_algo(size_t bytes, DType dtype, bool in_place_or_fused, bool has_mc) const {
+  return select_algo(cfg_, world_, bytes, dtype, in_place_or_fused, has_mc);
 }
 
 void Comm::fill_ar_rank(ArRank* r, int channel, Segment* seg, size_t off) const {

@@ -31,6 +31,10 @@ struct CommConfig {
   SymmAllocator::Mode symm_mode = SymmAllocator::Mode::AUTO;
 };
 
+// The algorithm for a reduction of `bytes` bytes in a group of `world` ranks: a pure function of
+// its arguments, so every rank computes the same answer (and it can be checked without a GPU).
+Algo select_algo(const CommConfig& cfg, int world, size_t bytes, DType dtype, bool in_place_or_fused, bool has_mc);
+
 struct OpTiming {
   cudaEvent_t start = nullptr, stop = nullptr;
 };

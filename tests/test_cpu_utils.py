@@ -324,3 +324,32 @@ def test_symmetric_heap_allocator_never_overlaps_and_coalesces():
     for e in events:
         e.done = True
     assert heap.alloc(size) == 0                # everything came back and merged into one hole
+
+
+def test_algorithm_selector_table(native_lib):
+    # The selector is a pure function, so the table it implements is checked without a GPU:
+    # small separate outputs one-shot; floats from 512 KiB on NVLS when a multicast mapping exists
+    # and the group has at least 4 ranks; everything else two-shot; forced choices fall back to
+    # two-shot where they cannot apply.
+    F32, I32, BF16 = 0, 1, 3
+    ONE, TWO, NVLS = 1, 2, 3
+
+    def sel(world, nbytes, dtype=F32, in_place=True, mc=True, force=0, one_max=-1, nvls_min=-1, use_nvls=1):
+        return native_lib.bc_select_algo(world, nbytes, dtype, int(in_place), int(mc), force, one_max, nvls_min, use_nvls)
+
+    assert sel(8, 4 << 10, in_place=False) == ONE and sel(8, 256 << 10, in_place=False) == ONE
+    assert sel(8, (256 << 10) + 4, in_place=False, mc=False) == TWO
+    assert sel(8, 4 << 10, in_place=True) == TWO                      # in place / fused: never one-shot
+    assert sel(8, 512 << 10) == NVLS and sel(8, (512 << 10) - 4) == TWO and sel(4, 64 << 20, BF16) == NVLS
+    assert sel(2, 256 << 20) == TWO                                   # two ranks: the switch saves nothing
+    assert sel(8, 64 << 20, mc=False) == TWO and sel(8, 64 << 20, use_nvls=0) == TWO
+    assert sel(8, 64 << 20, I32) == TWO                               # the switch adds floats only
+    assert sel(8, 1 << 20, nvls_min=2 << 20) == TWO and sel(8, 1 << 20, in_place=False, one_max=1 << 20) == ONE
+    assert sel(2, 1 << 20, force=NVLS) == NVLS and sel(8, 1 << 20, force=NVLS, mc=False) == TWO
+    assert sel(8, 1 << 30, force=ONE, in_place=False) == ONE and sel(8, 1 << 20, force=ONE, in_place=True) == TWO
+    assert sel(8, 4 << 10, in_place=False, force=TWO) == TWO
+    # grid: one block per 32 KiB, at most 128; a fused update may take two blocks per SM
+    blocks = native_lib.bc_choose_blocks
+    assert blocks(1, 8, TWO, 0, 148, 0) == 1 and blocks(32 << 10, 8, TWO, 0, 148, 0) == 1 and blocks((32 << 10) + 1, 8, TWO, 0, 148, 0) == 2
+    assert blocks(1 << 30, 8, NVLS, 0, 148, 0) == 128 and blocks(1 << 30, 8, NVLS, 1, 148, 0) == 296
+    assert blocks(1 << 30, 8, TWO, 0, 148, 16) == 16
