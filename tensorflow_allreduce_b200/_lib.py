@@ -62,6 +62,7 @@ def _declare(lib):
         "bc_two_level_allreduce_host": (i, [vp, ll, i, i, i]),
         "bc_select_algo": (i, [i, ll, i, i, i, i, ll, ll, i]),
         "bc_choose_blocks": (i, [ll, i, i, i, i, i]),
+        "bc_plan_gather_rounds": (ll, [i, P(C.c_ulonglong), ll, P(C.c_ulonglong)]),
         "bc_allreduce_async": (ll, [cp, vp, vp, i, i, P(ll), i, i, i, vp, i]),
         "bc_allgather_async": (ll, [cp, vp, i, i, P(ll), i, ALLOC_FN, vp, vp]),
         "bc_wait": (i, [ll, d]),

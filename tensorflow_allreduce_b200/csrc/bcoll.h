@@ -45,6 +45,9 @@ int bc_node_index(void);
 int bc_select_algo(int world, long long bytes, int dtype, int in_place_or_fused, int has_multicast, int force_algo,
                    long long one_shot_max_bytes, long long nvls_min_bytes, int use_nvls);
 int bc_choose_blocks(long long bytes, int world, int algo, int fused_update, int sm_count, int cap_override);
+/* How a gathered result larger than the staging area is cut into rounds (pure function): returns
+ * the number of rounds and writes every rank's piece size per round. */
+long long bc_plan_gather_rounds(int world, const unsigned long long* all_bytes, long long staging_bytes, unsigned long long* pieces_out);
 int bc_two_level_allreduce_host(void* data, long long count, int dtype, int average, int reduce_op);
 
 /* Negotiated, name-keyed collectives. The returned handle must be released. For CUDA tensors

@@ -140,6 +140,15 @@ int bc_select_algo(int world, long long bytes, int dtype, int in_place_or_fused,
   API_END(-1)
 }
 
+long long bc_plan_gather_rounds(int world, const unsigned long long* all_bytes, long long staging_bytes, unsigned long long* pieces_out) {
+  API_BEGIN
+  std::vector<size_t> piece;
+  const size_t rounds = gpu::plan_gather_rounds(all_bytes, world, (size_t)staging_bytes, &piece);
+  for (int p = 0; p < world; p++) pieces_out[p] = piece[p];
+  return (long long)rounds;
+  API_END(-1)
+}
+
 int bc_choose_blocks(long long bytes, int world, int algo, int fused_update, int sm_count, int cap_override) {
   API_BEGIN
   return gpu::choose_blocks((size_t)bytes, world, algo, fused_update != 0, sm_count, cap_override);

@@ -72,6 +72,18 @@ RankCtx Comm::make_ctx(int channel) const {
   return c;
 }
 
+size_t plan_gather_rounds(const unsigned long long* all_bytes, int world, size_t staging_bytes, std::vector<size_t>* piece) {
+  size_t total = 0;
+  for (int p = 0; p < world; p++) total += (size_t)all_bytes[p];
+  BC_CHECK(staging_bytes > 32 * (size_t)world, "the staging area is too small for a gather in rounds");
+  // Pieces are rounded up to 16 bytes, which can add up to 16 bytes per rank to a round.
+  const size_t room = staging_bytes - 16 * (size_t)world;
+  const size_t rounds = std::max<size_t>(1, (total + room - 1) / room);
+  piece->assign(world, 0);
+  for (int p = 0; p < world; p++) (*piece)[p] = align_up(((size_t)all_bytes[p] + rounds - 1) / rounds, 16);
+  return rounds;
+}
+
 Algo select_algo(const CommConfig& cfg, int world, size_t bytes, DType dtype, bool in_place_or_fused, bool has_mc) {
   const bool is_float = dtype == DType::F32 || dtype == DType::BF16 || dtype == DType::F16;
   Algo forced = (Algo)cfg.force_algo;
@@ -228,12 +240,11 @@ void Comm::allgatherv(int channel, const void* in, size_t bytes, void* out_symm,
   // same piece sizes from the slab sizes agreed during negotiation.
   BC_CHECK(all_bytes && out_private, "allgatherv: a result of " << total_bytes << " bytes fits neither the symmetric heap nor the "
            "staging area and the slab sizes are not known on the host; raise BC_HEAP_MB or BC_STAGING_MB");
-  const size_t room = cfg_.staging_bytes - 16 * (size_t)world_;
-  const size_t rounds = (total_bytes + room - 1) / room;
-  std::vector<size_t> piece(world_), disp(world_);
+  std::vector<size_t> piece;
+  const size_t rounds = plan_gather_rounds(all_bytes, world_, cfg_.staging_bytes, &piece);
+  std::vector<size_t> disp(world_);
   size_t acc = 0;
   for (int p = 0; p < world_; p++) {
-    piece[p] = align_up(((size_t)all_bytes[p] + rounds - 1) / rounds, 16);
     disp[p] = acc;
     acc += (size_t)all_bytes[p];
   }

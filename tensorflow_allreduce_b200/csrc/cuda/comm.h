@@ -35,6 +35,11 @@ struct CommConfig {
 // its arguments, so every rank computes the same answer (and it can be checked without a GPU).
 Algo select_algo(const CommConfig& cfg, int world, size_t bytes, DType dtype, bool in_place_or_fused, bool has_mc);
 
+// A gathered result that is larger than the staging area goes through it in rounds: in round j
+// rank p contributes bytes [j * piece[p], (j + 1) * piece[p]) of its slab. Returns the number of
+// rounds; every round's pieces fit the staging area together, and the pieces are multiples of 16.
+size_t plan_gather_rounds(const unsigned long long* all_bytes, int world, size_t staging_bytes, std::vector<size_t>* piece);
+
 struct OpTiming {
   cudaEvent_t start = nullptr, stop = nullptr;
 };

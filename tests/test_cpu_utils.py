@@ -353,3 +353,27 @@ def test_algorithm_selector_table(native_lib):
     assert blocks(1, 8, TWO, 0, 148, 0) == 1 and blocks(32 << 10, 8, TWO, 0, 148, 0) == 1 and blocks((32 << 10) + 1, 8, TWO, 0, 148, 0) == 2
     assert blocks(1 << 30, 8, NVLS, 0, 148, 0) == 128 and blocks(1 << 30, 8, NVLS, 1, 148, 0) == 296
     assert blocks(1 << 30, 8, TWO, 0, 148, 16) == 16
+
+
+def test_gather_rounds_cover_every_slab_and_fit_the_staging_area(native_lib):
+    import ctypes as C
+
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=300, deadline=None)
+    @given(st.lists(st.integers(min_value=0, max_value=5_000_000), min_size=1, max_size=8), st.integers(min_value=4096, max_value=1 << 20))
+    def check(slabs, staging):
+        world = len(slabs)
+        arr = (C.c_ulonglong * world)(*slabs)
+        pieces = (C.c_ulonglong * world)()
+        rounds = native_lib.bc_plan_gather_rounds(world, arr, staging, pieces)
+        assert rounds >= 1
+        for p in range(world):
+            assert pieces[p] % 16 == 0 and rounds * pieces[p] >= slabs[p]          # every byte of every slab gets its round
+        for j in range(rounds):                                                     # what round j puts into the staging area
+            total = sum(min(pieces[p], max(0, slabs[p] - j * pieces[p])) for p in range(world))
+            assert total <= staging
+        if rounds > 1:                                                              # no more rounds than the sizes call for
+            assert sum(slabs) > (rounds - 1) * (staging - 16 * world)
+
+    check()
