@@ -166,10 +166,12 @@ void ShmGroup::barrier(double deadline) {
   }
 }
 
-void ShmGroup::allreduce(void* data, size_t count, DType dtype, double scale, int64_t int_divisor, ReduceOp red, double deadline) {
+void ShmGroup::allreduce(const void* in, void* data, size_t count, DType dtype, double scale, int64_t int_divisor, ReduceOp red,
+                         double deadline) {
   const size_t e = dtype_size(dtype);
   if (count == 0) return;
   if (n_ == 1) {
+    if (in != data) memcpy(data, in, count * e);
     switch (dtype) {
       case DType::F32: scale_float((float*)data, count, scale); break;
       case DType::F64: scale_float((double*)data, count, scale); break;
@@ -185,7 +187,7 @@ void ShmGroup::allreduce(void* data, size_t count, DType dtype, double scale, in
   for (size_t off = 0; off < count; off += chunk) {
     const size_t n = std::min(chunk, count - off);
     char* mine = (char*)data + off * e;
-    memcpy(slot(r_), mine, n * e);
+    memcpy(slot(r_), (const char*)in + off * e, n * e);
     barrier(deadline);
     // slice r of this chunk, cut like the ring's segments
     const size_t q = n / n_, rem = n % n_;

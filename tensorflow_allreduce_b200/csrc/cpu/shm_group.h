@@ -36,7 +36,11 @@ class ShmGroup {
   ShmGroup(const ShmGroup&) = delete;
   ShmGroup& operator=(const ShmGroup&) = delete;
 
-  void allreduce(void* data, size_t count, DType dtype, double scale, int64_t int_divisor, ReduceOp red, double deadline);
+  // `in` and `out` may be the same buffer; they must not overlap otherwise.
+  void allreduce(const void* in, void* out, size_t count, DType dtype, double scale, int64_t int_divisor, ReduceOp red, double deadline);
+  void allreduce(void* data, size_t count, DType dtype, double scale, int64_t int_divisor, ReduceOp red, double deadline) {
+    allreduce(data, data, count, dtype, scale, int_divisor, red, deadline);
+  }
   void allgatherv(const void* in, void* out, const std::vector<int64_t>& rows, size_t row_bytes, double deadline);
   size_t slot_bytes() const { return slot_bytes_; }
 

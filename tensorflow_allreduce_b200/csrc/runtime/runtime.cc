@@ -637,15 +637,19 @@ void Runtime::perform_allreduce(OpRecord& r) {
   const double scale = r.average ? 1.0 / t_.size : 1.0;
   const int64_t idiv = r.average ? t_.size : 1;
   if (r.device == DeviceKind::CPU) {
-    if (r.in != r.out && count) memcpy(r.out, r.in, count * dtype_size(r.dtype));
     const double deadline = now_s() + opt_.timeout_s;
+    if (shm_ && !node_) {
+      // reads the input where it is and writes the result where it belongs: no copy in between
+      shm_->allreduce(r.in, r.out, count, r.dtype, scale, idiv, r.red, deadline);
+      r.algo = 4;
+      return;
+    }
+    if (r.in != r.out && count) memcpy(r.out, r.in, count * dtype_size(r.dtype));
     if (shm_ && node_) {
       // several hosts with several ranks each: shared memory inside the host, rails between hosts
       ShmLocalLevel local(*shm_, r.out, deadline);
       cpu_staging_.resize(slice_len(count, node_->local_size, 0) * dtype_size(r.dtype) + 16);
       bc::two_level_allreduce(*node_, local, cpu_staging_.data(), count, r.dtype, scale, idiv, r.red, deadline, r.two_level_s);
-    } else if (shm_) {
-      shm_->allreduce(r.out, count, r.dtype, scale, idiv, r.red, deadline);
     } else {
       cpu_ring_allreduce(t_, r.out, count, r.dtype, scale, idiv, deadline, r.red);
     }
