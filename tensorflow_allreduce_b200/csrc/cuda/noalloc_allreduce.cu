@@ -19,8 +19,9 @@ constexpr size_t kStage = BC_STATIC_MAX_BYTES_PER_RANK;                   // sta
 constexpr size_t kFlags = (size_t)kMaxBlocks * kMaxRanks * sizeof(uint32_t);  // barrier flags of one rank
 constexpr size_t kEpochs = (size_t)kMaxBlocks * sizeof(uint32_t);          // barrier counters of one rank
 constexpr size_t kCtlOff = BC_STATIC_MAX_RANKS * kStage;                   // flags and counters follow the staging areas
-constexpr size_t kCtlBytes = BC_STATIC_MAX_RANKS * (kFlags + kEpochs) + 256;  // + a private status word
+constexpr size_t kCtlBytes = BC_STATIC_MAX_RANKS * (kFlags + kEpochs) + 256;  // + a spare, unused word
 constexpr size_t kScratchBytes = kCtlOff + kCtlBytes;
+static_assert(kScratchBytes == BC_STATIC_SCRATCH_BYTES, "the header states another size of the static scratch");
 
 // The scratch. In host code this name is only a handle for cudaGetSymbolAddress, never a pointer
 // that a kernel could use.
@@ -69,17 +70,27 @@ extern "C" int bc_group_allreduce_static(int nranks, const void* const* ins, voi
   const size_t es = dtype_size((DType)dtype);
   if (es == 0) return fail(err, err_cap, "unknown dtype code " + std::to_string(dtype));
   if (count < 0) return fail(err, err_cap, "count must not be negative");
+  // Compared before the multiplication: count * es wraps around for counts near 2^62.
+  if ((unsigned long long)count > kStage / es)
+    return fail(err, err_cap, "request of " + std::to_string(count) + " elements of " + std::to_string(es) +
+                " bytes per rank exceeds the static scratch limit of " + std::to_string(kStage) + " bytes per rank");
   const size_t bytes = (size_t)count * es;
-  if (bytes > kStage)
-    return fail(err, err_cap, "request of " + std::to_string(bytes) + " bytes per rank exceeds the static scratch limit of " +
-                std::to_string(kStage) + " bytes per rank");
+  if (!status_out) return fail(err, err_cap, "status_out must not be null: it is the only place where a timed-out wait is reported");
+  auto overlap = [bytes](const void* a, const void* b) {
+    const uintptr_t x = (uintptr_t)a, y = (uintptr_t)b;
+    return x < y + bytes && y < x + bytes;
+  };
   for (int r = 0; r < nranks; r++) {
     if (!ins[r] || !outs[r]) return fail(err, err_cap, "null buffer for rank " + std::to_string(r));
     if ((((uintptr_t)ins[r] | (uintptr_t)outs[r]) & 15) != 0) return fail(err, err_cap, "buffers must be 16-byte aligned");
-    for (int q = 0; q < nranks; q++)
-      if (outs[r] == ins[q]) return fail(err, err_cap, "an output aliases an input");
   }
   if (count == 0) return 0;
+  for (int r = 0; r < nranks; r++) {
+    for (int q = 0; q < nranks; q++) {
+      if (overlap(outs[r], ins[q])) return fail(err, err_cap, "an output aliases an input (their byte ranges overlap)");
+      if (q != r && overlap(outs[r], outs[q])) return fail(err, err_cap, "two outputs alias (their byte ranges overlap)");
+    }
+  }
 
   std::string why;
   unsigned char* base = scratch_for_current_device(&why);
@@ -96,14 +107,11 @@ extern "C" int bc_group_allreduce_static(int nranks, const void* const* ins, voi
 
   cudaStream_t s = (cudaStream_t)stream;
   unsigned char* ctl = base + kCtlOff;
-  uint32_t* own_status = (uint32_t*)(ctl + BC_STATIC_MAX_RANKS * (kFlags + kEpochs));
   // The array still holds the previous call's flags and counters: start from zero.
   cudaError_t e = cudaMemsetAsync(ctl, 0, kCtlBytes, s);
   if (e != cudaSuccess) return fail(err, err_cap, std::string("clearing the scratch: ") + cudaGetErrorString(e));
-  if (status_out) {
-    e = cudaMemsetAsync(status_out, 0, sizeof(unsigned), s);
-    if (e != cudaSuccess) return fail(err, err_cap, std::string("clearing status_out: ") + cudaGetErrorString(e));
-  }
+  e = cudaMemsetAsync(status_out, 0, sizeof(unsigned), s);
+  if (e != cudaSuccess) return fail(err, err_cap, std::string("clearing status_out: ") + cudaGetErrorString(e));
   for (int r = 0; r < nranks; r++) {
     e = cudaMemcpyAsync(base + (size_t)r * kStage, ins[r], bytes, cudaMemcpyDeviceToDevice, s);
     if (e != cudaSuccess) return fail(err, err_cap, std::string("staging the input of rank ") + std::to_string(r) + ": " + cudaGetErrorString(e));
@@ -126,7 +134,7 @@ extern "C" int bc_group_allreduce_static(int nranks, const void* const* ins, voi
       a.r[r].in[p] = (char*)(base + (size_t)p * kStage);
     }
     c.epochs = (uint32_t*)(ctl + BC_STATIC_MAX_RANKS * kFlags + (size_t)r * kEpochs);
-    c.status = status_out ? (uint32_t*)status_out : own_status;
+    c.status = (uint32_t*)status_out;
     c.timeout_ns = 20ull * 1000 * 1000 * 1000;
     a.r[r].out = outs[r];
   }

@@ -377,3 +377,38 @@ def test_gather_rounds_cover_every_slab_and_fit_the_staging_area(native_lib):
             assert sum(slabs) > (rounds - 1) * (staging - 16 * world)
 
     check()
+
+
+def test_static_allreduce_refuses_bad_requests_before_touching_a_device(native_lib):
+    # Every refusal of bc_group_allreduce_static is decided on the host before the first CUDA
+    # call, so the checks run here with made-up addresses: a count whose byte size would wrap
+    # around to zero, too many ranks, overlapping byte ranges, a missing status word.
+    import ctypes as C
+
+    fn = native_lib.bc_group_allreduce_static
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_longlong, C.c_int, C.c_float, C.c_int,
+                   C.c_void_p, C.c_void_p, C.c_char_p, C.c_int]
+
+    def call(ins, outs, count, dtype=0, status=0x1000):
+        n = len(ins)
+        err = C.create_string_buffer(512)
+        rc = fn(n, (C.c_void_p * n)(*ins), (C.c_void_p * n)(*outs), count, dtype, 1.0, 1,
+                C.c_void_p(status) if status else None, None, err, len(err))
+        return rc, err.value.decode()
+
+    ins, outs = [0x10000, 0x20000], [0x30000, 0x40000]
+    for dtype, count in ((0, 1 << 61), (0, 1 << 62), (2, 1 << 61), (6, (1 << 63) - 1), (0, (1 << 18) + 1)):
+        rc, err = call(ins, outs, count, dtype)
+        assert rc == -1 and "exceeds the static scratch limit" in err, (dtype, count, err)
+    assert call(ins * 5, outs * 5, 16) == (-1, "nranks must be between 1 and 8")
+    rc, err = call(ins, [0x10020, 0x40000], 16)
+    assert rc == -1 and "aliases an input" in err
+    rc, err = call(ins, [0x30000, 0x30010], 16)
+    assert rc == -1 and "two outputs alias" in err
+    rc, err = call(ins, outs, 16, status=0)
+    assert rc == -1 and "status_out" in err
+    rc, err = call(ins, outs, 16, dtype=99)
+    assert rc == -1 and "dtype" in err
+    rc, err = call(ins, [0x30004, 0x40000], 16)
+    assert rc == -1 and "aligned" in err

@@ -1,8 +1,8 @@
 """`bc_group_allreduce_static`: the group allreduce for callers that cannot allocate device memory
 (a process whose GPU memory is owned by one pool, or a loop that cannot afford the device-wide
-synchronisation inside cudaMalloc). It is called here through its exported C symbol, twice in a
-row, and each result is compared with the allocating entry point (`bc_emu_allreduce`) on the
-same data. The scratch of the new entry point is one static array shared by all calls, so the
+synchronisation inside cudaMalloc). It is called here through its exported C symbol, several times
+in a row, and each result is compared with the allocating entry point (`bc_emu_allreduce`) on the
+same data and with a plain PyTorch sum in fp32 (rank order, rounded once). The scratch of the new entry point is one static array shared by all calls, so the
 second call also proves that leftovers of the first one do no harm.
 
 This file sorts last on purpose: a run that stops at the first failure has then already run
@@ -30,12 +30,26 @@ def _static_fn():
 
 def _call_static(fn, ins, outs, count, dtype, scale, blocks, status):
     n = len(ins)
-    ip = (C.c_void_p * n)(*[t.data_ptr() for t in ins])
-    op = (C.c_void_p * n)(*[t.data_ptr() for t in outs])
+    ip = (C.c_void_p * n)(*[t if isinstance(t, int) else t.data_ptr() for t in ins])
+    op = (C.c_void_p * n)(*[t if isinstance(t, int) else t.data_ptr() for t in outs])
     err = C.create_string_buffer(512)
-    rc = fn(n, ip, op, count, DT[dtype], scale, blocks, C.c_void_p(status.data_ptr()),
+    rc = fn(n, ip, op, count, DT[dtype], scale, blocks, C.c_void_p(status.data_ptr()) if status is not None else None,
             C.c_void_p(torch.cuda.current_stream().cuda_stream), err, len(err))
     return rc, err.value.decode()
+
+
+def _torch_sum(xs, scale):
+    """The same sum in plain PyTorch: rank order, fp32 accumulation for the 16-bit types, one rounding."""
+    dtype = xs[0].dtype
+    if not dtype.is_floating_point:
+        acc = xs[0].clone()
+        for x in xs[1:]:
+            acc += x
+        return acc
+    acc = xs[0].float()
+    for x in xs[1:]:
+        acc = acc + x.float()
+    return (acc * scale).to(dtype)
 
 
 def _fill(dtype, n, seed):
@@ -68,8 +82,10 @@ def test_static_entry_point_matches_allocating_one_twice():
         assert rc == 0, err
         torch.cuda.synchronize()
         assert g.status == 0 and int(status.item()) == 0
+        ref = _torch_sum(keep, scale)
         for r in range(nranks):
             assert torch.equal(got[r], want[r]), f"call {call} rank {r}"
+            assert torch.equal(got[r], ref), f"call {call} rank {r}: differs from the PyTorch sum"
             assert torch.equal(xs[r], keep[r]), "inputs must stay untouched"
         g.close()
 
@@ -86,6 +102,18 @@ def test_static_entry_point_refuses_oversize_requests():
     assert rc == -1 and "nranks" in err
     rc, err = _call_static(fn, xs, xs, 16, torch.float32, 1.0, 1, status)
     assert rc == -1 and "aliases" in err
+    # byte ranges that overlap without starting at the same address
+    rc, err = _call_static(fn, xs, [xs[0].data_ptr() + 32, outs[1]], 16, torch.float32, 1.0, 1, status)
+    assert rc == -1 and "aliases an input" in err
+    rc, err = _call_static(fn, xs, [outs[0], outs[0].data_ptr() + 16], 16, torch.float32, 1.0, 1, status)
+    assert rc == -1 and "two outputs alias" in err
+    # a count whose size in bytes wraps around to zero must be refused as well
+    for huge in (1 << 61, 1 << 62, (1 << 63) - 1):
+        rc, err = _call_static(fn, xs, outs, huge, torch.float32, 1.0, 1, status)
+        assert rc == -1 and "exceeds the static scratch limit" in err, (huge, err)
+    # without a status word a timed-out wait could not be reported
+    rc, err = _call_static(fn, xs, outs, 16, torch.float32, 1.0, 1, None)
+    assert rc == -1 and "status_out" in err
     torch.cuda.synchronize()
     assert float(outs[0][0]) == 7.0              # nothing was launched
     # the limit itself is accepted
