@@ -12,9 +12,15 @@ with CUDA events between barriers, maximum over ranks. `e2e` repeats the measure
 public API with the per-step host->device copy of the inputs from pinned memory and the
 device->host read of the loss inside the timed region.
 
+After its own numbers an `--impl ours` run measures, in the same process and with the same steps
+and warm-up, torch DistributedDataParallel + NCCL + the plain torch optimizer on the same model:
+once with the same GRU kernels (`ddp_nccl_same_kernels`, which isolates what the collectives
+library is worth) and once with cuDNN's GRU (`ddp_nccl_cudnn`). They go under `comparators` and are
+labelled as what they are: not the reference. `--no-comparators` skips them.
+
 Other arms: `--impl reference` reports the reference's own build (unavailable on this image);
-`--impl ddp` runs torch DistributedDataParallel + NCCL + torch.optim.SGD on the same model as a
-same-box comparator. `--model gpt2|resnet50` run the other two data-parallel configurations.
+`--impl ddp` runs only the torch DDP comparator. `--model gpt2|resnet50` run the other two
+data-parallel configurations.
 """
 from __future__ import annotations
 
@@ -40,6 +46,8 @@ def parse():
     ap.add_argument("--rnn", default="auto", choices=["auto", "persistent", "cudnn"],
                     help="ds2: GRU stack on the library's persistent tcgen05 kernels (auto: ours yes, ddp no) or on cuDNN")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-comparators", action="store_true",
+                    help="skip the torch DDP + NCCL arms that an `--impl ours` run measures after its own numbers")
     return ap.parse_args()
 
 
@@ -123,53 +131,39 @@ def build_model(name: str, device, batch: int, persistent_rnn: bool = True):
     return model, opt, make, loss_fn, b, meta
 
 
-def main():
-    a = parse()
-    if a.impl == "reference":
-        return reference_unavailable()
+# Same-box comparators recorded in BASELINE.md section 4 (torch DDP + NCCL + torch.optim.SGD + cuDNN GRU on the
+# DeepSpeech2-style configuration, samples/s by number of GPUs). They are NOT the reference's own build, which cannot
+# be installed on this image; they are the only published figures that `vs_baseline` can be taken against.
+BASELINE_MD_DS2_DDP_CUDNN = {1: 376.1, 2: 698.6, 4: 1285.4}
 
+
+def run_arm(a, impl: str, rnn: str, device, rank: int, world: int, local: int, with_e2e: bool):
+    """Build the model and its optimizer for one arm, run warm-up and the timed steps, and return the
+    measurements. `impl`: "ours" (DistributedOptimizer of this library) or "ddp" (torch DistributedDataParallel over
+    NCCL with the plain torch optimizer; a single process without DDP when world == 1)."""
     import torch
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != a.gpus:
-        if world == 1 and a.gpus > 1:
-            # convenience: start the ranks ourselves when not launched by torchrun
-            from tensorflow_allreduce_b200 import launch
-            return launch.main(["--nproc", str(a.gpus), os.path.abspath(__file__)] + sys.argv[1:])
-        raise SystemExit(f"--gpus {a.gpus} but WORLD_SIZE={world}")
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    torch.backends.cudnn.allow_tf32 = True
-    torch.backends.cuda.matmul.allow_tf32 = True
-    torch.backends.cudnn.benchmark = True
-    torch.manual_seed(1234)          # same initial weights on every rank, as the reference requires
-
     import tensorflow_allreduce_b200 as bc
+    from tensorflow_allreduce_b200.ops import persistent_gru
     from tensorflow_allreduce_b200.utils.clocks import ClockSampler
 
-    bc.init(device=local)
-    persistent = a.rnn == "persistent" or (a.rnn == "auto" and a.impl == "ours")
+    torch.manual_seed(1234)          # same initial weights on every rank, as the reference requires
+    persistent = rnn == "persistent"
     model, base_opt, make, loss_fn, per_gpu_batch, meta = build_model(a.model, device, a.batch, persistent)
-    from tensorflow_allreduce_b200.ops import persistent_gru
-
     ddp = None
     fwd = model
-    if a.impl == "ddp":
+    if impl == "ddp":
         import torch.distributed as dist
         from torch.nn.parallel import DistributedDataParallel
 
         if world > 1:
-            dist.init_process_group("nccl", device_id=device)
+            if not dist.is_initialized():
+                dist.init_process_group("nccl", device_id=device)
             ddp = DistributedDataParallel(model, device_ids=[local], gradient_as_bucket_view=True)
             fwd = ddp
         opt = base_opt
     else:
         opt = bc.DistributedOptimizer(base_opt)
-
-    def loss_call(batch_):
-        return loss_fn(fwd, batch_)
 
     torch.manual_seed(100 + rank)
     dev_batch = make(False)
@@ -178,7 +172,7 @@ def main():
     def step(batch_):
         flush.zero_()
         opt.zero_grad()
-        loss = loss_call(batch_)
+        loss = loss_fn(fwd, batch_)
         loss.backward()
         opt.step()
         return loss
@@ -203,12 +197,14 @@ def main():
     ms = max_over_ranks(e0.elapsed_time(e1))
     launches = getattr(opt, "launch_count", 0) + persistent_gru.launch_count - launches0
     persistent_gru.check_status()
-    final_loss = float(loss.detach())
-    clocks = clk.summary()
     bc.check_device_status()
-
-    e2e = None
-    if not a.no_e2e:
+    res = {
+        "impl": impl, "rnn": rnn, "ms": ms, "per_gpu_batch": per_gpu_batch, "meta": meta, "launches": launches,
+        "value": world * per_gpu_batch * a.steps / (ms / 1e3), "final_loss": float(loss.detach()), "clocks": clk.summary(),
+        "n_params": sum(p.numel() for p in model.parameters()), "grad_buckets": len(getattr(opt, "buckets", [])),
+        "fused": bool(getattr(opt, "fused", False)), "e2e": None,
+    }
+    if with_e2e:
         pinned = make(True)
         h2d = sum(t.numel() * t.element_size() for t in pinned)
         loss_host = 0.0
@@ -224,36 +220,99 @@ def main():
         t1 = time.perf_counter()
         bc.barrier()
         e2e_s = max_over_ranks(t1 - t0)
-        e2e = {"value": round(world * per_gpu_batch * a.steps / e2e_s, 3), "unit": "samples/s", "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": 4, "ms_per_step": round(e2e_s * 1e3 / a.steps, 3), "last_loss": loss_host}
+        res["e2e"] = {"value": round(world * per_gpu_batch * a.steps / e2e_s, 3), "unit": "samples/s", "h2d_bytes_per_step": h2d,
+                      "d2h_bytes_per_step": 4, "ms_per_step": round(e2e_s * 1e3 / a.steps, 3), "last_loss": loss_host}
+    # free this arm's memory before the next one
+    del opt, fwd, ddp, model, base_opt, dev_batch, flush
+    import gc
+
+    gc.collect()
+    torch.cuda.empty_cache()
+    return res
+
+
+def main():
+    a = parse()
+    if a.impl == "reference":
+        return reference_unavailable()
+
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != a.gpus:
+        if world == 1 and a.gpus > 1:
+            # convenience: start the ranks ourselves when not launched by torchrun
+            from tensorflow_allreduce_b200 import launch
+            return launch.main(["--nproc", str(a.gpus), os.path.abspath(__file__)] + sys.argv[1:])
+        raise SystemExit(f"--gpus {a.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    torch.backends.cudnn.allow_tf32 = True
+    torch.backends.cuda.matmul.allow_tf32 = True
+    torch.backends.cudnn.benchmark = True
+
+    import tensorflow_allreduce_b200 as bc
+
+    bc.init(device=local)
+    persistent = a.rnn == "persistent" or (a.rnn == "auto" and a.impl == "ours")
+    main_rnn = ("persistent" if persistent else "cudnn") if a.model == "ds2" else "none"
+    r = run_arm(a, a.impl, main_rnn, device, rank, world, local, with_e2e=not a.no_e2e)
+
+    # Comparators in the same process, on the same model, with the same steps and warm-up. They are torch's own
+    # data-parallel stack (DDP over NCCL, torch.optim), not the reference: its build is unavailable here.
+    comps = None
+    if a.impl == "ours" and not a.no_comparators:
+        comps = {"note": "same-box comparators measured in this invocation; torch DDP + NCCL + torch.optim, NOT the reference"}
+        arms = [("ddp_nccl_same_kernels", "persistent"), ("ddp_nccl_cudnn", "cudnn")] if a.model == "ds2" else [("ddp_nccl", "none")]
+        if a.model == "ds2" and main_rnn != "persistent":
+            arms = [("ddp_nccl_cudnn", "cudnn")]
+        for key, rnn in arms:
+            c = run_arm(a, "ddp", rnn, device, rank, world, local, with_e2e=not a.no_e2e)
+            comps[key] = {"value": round(c["value"], 3), "ms_per_step": round(c["ms"] / a.steps, 3),
+                          "e2e": c["e2e"]["value"] if c["e2e"] else None}
+        same = comps.get("ddp_nccl_same_kernels") or comps.get("ddp_nccl")
+        if same:
+            comps["ratio_same_kernels"] = round(r["value"] / same["value"], 4)
+            if r["e2e"] and same["e2e"]:
+                comps["e2e_ratio_same_kernels"] = round(r["e2e"]["value"] / same["e2e"], 4)
+        if "ddp_nccl_cudnn" in comps:
+            comps["ratio_cudnn"] = round(r["value"] / comps["ddp_nccl_cudnn"]["value"], 4)
 
     if rank == 0:
-        n_params = sum(p.numel() for p in model.parameters())
+        meta, clocks, ms = r["meta"], r["clocks"], r["ms"]
+        base = BASELINE_MD_DS2_DDP_CUDNN.get(world) if (a.model == "ds2" and not a.batch) else None
         out = {
             "metric": f"{a.model}_train_samples_per_sec",
-            "value": round(world * per_gpu_batch * a.steps / (ms / 1e3), 3),
+            "value": round(r["value"], 3),
             "unit": "samples/s",
             "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": round(ms / a.steps, 3),
             "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None,
+            "vs_baseline": round(r["value"] / base, 4) if base else None,
+            "vs_baseline_of": ("torch DDP + NCCL + torch.optim.SGD + cuDNN GRU on the same B200 boxes (BASELINE.md section 4); "
+                               "the reference publishes no number and its own build is unavailable") if base else None,
             "dtype": meta["dtype"], "data": "synthetic (random inputs and labels, random-init weights)",
             "impl": a.impl,
-            "config": {"model": meta["model"], "global_batch": world * per_gpu_batch, "seq_len": meta["seq_len"],
-                       "parallelism": f"dp{world}", "optimizer": meta["optimizer"], "params_m": round(n_params / 1e6, 2),
+            "config": {"model": meta["model"], "global_batch": world * r["per_gpu_batch"], "seq_len": meta["seq_len"],
+                       "parallelism": f"dp{world}", "optimizer": meta["optimizer"], "params_m": round(r["n_params"] / 1e6, 2),
                        "l2": "256 MB buffer written between steps (L2 flush); working set exceeds L2 anyway",
-                       "grad_buckets": len(getattr(opt, "buckets", [])), "fused_update": bool(getattr(opt, "fused", False)),
+                       "grad_buckets": r["grad_buckets"], "fused_update": r["fused"],
                        "rnn": ("persistent tcgen05 kernels" if persistent else "cudnn") if a.model == "ds2" else None},
             "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"), "reasons": clocks.get("reasons", []),
                        "power_w_max": clocks.get("power_w_max"), "samples": clocks.get("samples"), "source": clocks.get("source")},
-            "gpu_launches": launches,
-            "final_loss": final_loss,
+            "gpu_launches": r["launches"],
+            "final_loss": r["final_loss"],
         }
-        if e2e is not None:
-            out["e2e"] = e2e
+        if r["e2e"] is not None:
+            out["e2e"] = r["e2e"]
+        if comps is not None:
+            out["comparators"] = comps
         print(json.dumps(out), flush=True)
-    if ddp is not None:
-        import torch.distributed as dist
+    import torch.distributed as dist
+
+    if dist.is_initialized():
         dist.destroy_process_group()
     bc.shutdown()
     return 0

@@ -37,12 +37,28 @@ import tensorflow_allreduce_b200 as bc
 from tensorflow_allreduce_b200.ops import symmetric
 
 
-def timed(fn, iters, warmup=3):
+def timed(fn, iters=0, warmup=3):
+    """Device time of one call of `fn` in ms (CUDA events around a loop, maximum over ranks).
+
+    `iters` = 0 sizes the loop for about 30 ms of device time (10 to 200 calls, the same number on
+    every rank). One more call runs between the host barrier and the first event: the collective
+    itself lines the GPUs up, so the clock does not start while a rank is still on its way out of
+    the barrier (with 5 calls of 0.2 ms such a skew was a tenth of the measurement)."""
     for _ in range(warmup):
         fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if iters <= 0:
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(3):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        est = max(bc.host_allgather(e0.elapsed_time(e1) / 3))
+        iters = int(min(200, max(10, 30.0 / max(est, 1e-3))))
     torch.cuda.synchronize()
     bc.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    fn()
     e0.record()
     for _ in range(iters):
         fn()
@@ -50,6 +66,29 @@ def timed(fn, iters, warmup=3):
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / iters
     return max(bc.host_allgather(ms))
+
+
+def phases_of(fn):
+    """Time stamps of block 0 inside the reduction kernel of one call of `fn` (%globaltimer at kernel entry, after
+    the first barrier, after phase 1, after the second barrier, at the end), as durations in microseconds:
+    [barrier 1, phase 1, barrier 2, phase 2]; maximum over ranks of each."""
+    import ctypes as C
+
+    from tensorflow_allreduce_b200 import _lib
+
+    stamps = torch.zeros(8, dtype=torch.int64, device="cuda")
+    lib = _lib.lib()
+    fn()
+    torch.cuda.synchronize()
+    bc.barrier()
+    lib.bc_set_allreduce_profile(C.c_void_p(stamps.data_ptr()))
+    fn()
+    torch.cuda.synchronize()
+    lib.bc_set_allreduce_profile(None)
+    t = stamps.tolist()
+    d = [(t[i + 1] - t[i]) / 1e3 for i in range(4)]
+    allv = bc.host_allgather(d)
+    return [round(max(v[i] for v in allv), 2) for i in range(4)]
 
 
 def ref_ring_allreduce(buf, tmp, rank, world):
@@ -74,6 +113,46 @@ def ref_ring_allreduce(buf, tmp, rank, world):
         torch.cuda.current_stream().synchronize()
 
 
+def _size(n):
+    for unit, sh in (("GiB", 30), ("MiB", 20), ("KiB", 10)):
+        if n >= (1 << sh):
+            v = n / (1 << sh)
+            return f"{v:.0f} {unit}" if v == int(v) else f"{v:.1f} {unit}"
+    return f"{n} B"
+
+
+def markdown(rows, world, link_measured=764.0, link_nominal=900.0):
+    """The rows of one run as markdown tables (one per operation and dtype): time, bus GB/s per arm, the best of
+    this library's arms as a fraction of the measured and of the nominal link rate, correctness flags."""
+    out = []
+    for op in ("allreduce", "allgather"):
+        for dname in ("fp32", "bf16"):
+            sel = [r for r in rows if r["op"] == op and r["dtype"] == dname]
+            if not sel:
+                continue
+            arms = [k[:-6] for k in ("ours_direct_busbw", "ours_symm_busbw", "ours_staged_busbw", "ours_busbw", "nccl_busbw",
+                                      "nccl_padded_busbw", "ref_ring_busbw") if any(k in r for r in sel)]
+            out.append(f"\n### {op}, {world} GPUs, {dname}\n")
+            head = ["bytes"] + [f"{a_} ms" for a_ in arms if a_.startswith("ours")] + [f"{a_} GB/s" for a_ in arms]
+            head += [f"ours / {link_measured:.0f}", f"ours / {link_nominal:.0f}", "correct"]
+            if any("direct_phases_us" in r for r in sel):
+                head.append("direct: barrier 1 / phase 1 / barrier 2 / phase 2 (us)")
+            out.append("| " + " | ".join(head) + " |")
+            out.append("|" + "---|" * len(head))
+            for r in sel:
+                cells = [_size(r["bytes"])]
+                cells += [f'{r[a_ + "_ms"]:.4f}' if a_ + "_ms" in r else "-" for a_ in arms if a_.startswith("ours")]
+                cells += [f'{r[a_ + "_busbw"]:.1f}' if a_ + "_busbw" in r else "-" for a_ in arms]
+                best = max([r[a_ + "_busbw"] for a_ in arms if a_.startswith("ours") and a_ + "_busbw" in r] or [0.0])
+                cells += [f"{best / link_measured:.2f}", f"{best / link_nominal:.2f}"]
+                flags = [k.split("_")[0] + ("=ok" if r[k] else "=WRONG") for k in ("direct_correct", "symm_correct", "staged_correct", "correct") if k in r]
+                cells.append(" ".join(flags) or "-")
+                if any("direct_phases_us" in x for x in sel):
+                    cells.append(" / ".join(f"{v:.1f}" for v in r["direct_phases_us"]) if "direct_phases_us" in r else "-")
+                out.append("| " + " | ".join(cells) + " |")
+    return "\n".join(out) + "\n"
+
+
 def main():
     if os.environ.get("BC_SWEEP_WATCHDOG_S"):
         import faulthandler
@@ -86,6 +165,9 @@ def main():
     ap.add_argument("--dtypes", default="fp32,bf16")
     ap.add_argument("--no-allgather", action="store_true")
     ap.add_argument("--no-allreduce", action="store_true")
+    ap.add_argument("--phases", action="store_true", help="ours_direct: also record the kernel's phase times (block 0 time stamps)")
+    ap.add_argument("--phases-min-kb", type=int, default=1024)
+    ap.add_argument("--staging-mb", type=int, default=0, help="size of the staging area (0 = the library's default)")
     ap.add_argument("--fake-hosts", type=int, default=1,
                     help="report this many host names (consecutive ranks share one): times the two-level path on one box")
     a = ap.parse_args()
@@ -100,7 +182,7 @@ def main():
         # tensors in symmetric memory and ordered launches need all ranks on one host
         arms = [x for x in arms if x in ("ours_staged", "nccl", "ref_ring")]
     torch.cuda.set_device(local)
-    cfg = bc.Config.from_env(heap_mb=max(6 * a.max_mb + 64, 256), staging_mb=64)
+    cfg = bc.Config.from_env(heap_mb=max(6 * a.max_mb + 64, 256), staging_mb=a.staging_mb or None)
     bc.init(device=local, config=cfg)
     use_nccl = ("nccl" in arms or "ref_ring" in arms) and world > 1
     if use_nccl:
@@ -117,7 +199,7 @@ def main():
         es = 4 if dtype == torch.float32 else 2
         for nbytes in ([] if a.no_allreduce else sizes):
             n = nbytes // es
-            iters = 50 if nbytes <= (1 << 20) else (20 if nbytes <= (64 << 20) else 5)
+            iters = 0
             g = torch.Generator(device="cuda").manual_seed(rank)
             x = (torch.rand(n, generator=g, device="cuda") * 2 - 1).to(dtype)
             row = {"op": "allreduce", "dtype": dname, "bytes": nbytes, "world": P}
@@ -133,6 +215,8 @@ def main():
                 ms = timed(lambda: allreduce_direct_(sx), iters)
                 row["ours_direct_ms"] = ms
                 row["ours_direct_busbw"] = nbytes / (ms * 1e-3) * factor / 1e9
+                if a.phases and nbytes >= (a.phases_min_kb << 10) and nbytes <= (512 << 20):
+                    row["direct_phases_us"] = phases_of(lambda: allreduce_direct_(sx))
                 del sx
             if "ours_symm" in arms and nbytes <= (16 << 20):
                 sx = symmetric.empty((n,), dtype)
@@ -158,6 +242,14 @@ def main():
                 def f2():
                     i[0] += 1
                     bc.allreduce(x, average=False, name=f"t.{dname}.{nbytes}.{i[0]}")
+                got = bc.allreduce(x, average=False, name=f"tchk.{dname}.{nbytes}")
+                ref = x.clone()
+                if use_nccl:
+                    dist.all_reduce(ref)
+                    # NCCL's summation order differs: equal within the rounding of a P-term sum
+                    tol = 1e-5 * P if dtype == torch.float32 else 1e-2 * P
+                    row["staged_correct"] = bool(torch.allclose(got.float(), ref.float(), rtol=tol, atol=tol))
+                del got, ref
                 ms = timed(f2, iters)
                 row["ours_staged_ms"] = ms
                 row["ours_staged_busbw"] = nbytes / (ms * 1e-3) * factor / 1e9
@@ -169,7 +261,7 @@ def main():
             if "ref_ring" in arms and use_nccl and nbytes >= (1 << 12) and nbytes <= (256 << 20):
                 y = x.clone()
                 tmp = torch.empty(n // P + 1, dtype=dtype, device="cuda")
-                ms = timed(lambda: ref_ring_allreduce(y, tmp, rank, P), max(2, iters // 5), warmup=1)
+                ms = timed(lambda: ref_ring_allreduce(y, tmp, rank, P), 3 if nbytes <= (64 << 20) else 2, warmup=1)
                 row["ref_ring_ms"] = ms
                 row["ref_ring_busbw"] = nbytes / (ms * 1e-3) * factor / 1e9
             rows.append(row)
@@ -186,7 +278,7 @@ def main():
             total = es * cols * k * (P * (P + 1) // 2)
             if total > (a.max_mb << 20):
                 continue
-            iters = 50 if total <= (1 << 20) else (20 if total <= (64 << 20) else 5)
+            iters = 0
             row = {"op": "allgather", "dtype": dname, "bytes": total, "world": P}
             out = bc.allgather(t, name=f"agchk.{dname}.{nbytes}")
             lo, ok = 0, True
@@ -241,6 +333,8 @@ def main():
     if rank == 0 and a.out:
         with open(a.out, "w") as f:
             json.dump({"world": P, "symm": symmetric.describe(), "rows": rows}, f, indent=1)
+        with open(os.path.splitext(a.out)[0] + ".md", "w") as f:
+            f.write(markdown(rows, P))
     if use_nccl:
         dist.destroy_process_group()
     bc.shutdown()

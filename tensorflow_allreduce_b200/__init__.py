@@ -17,7 +17,7 @@ tensorflow_allreduce_b200.launch`).
 from .config import Config
 from .core import (CollectiveError, all_max, all_min, all_prod, all_sum, allgather, allgather_async, allreduce, allreduce_, allreduce_async, barrier,
                    broadcast, check_device_status, clear_stats, config, grouped_allreduce, host_allgather, init, is_broken, is_initialized,
-                   local_rank, local_size, n_nodes, node_index, on_gpu, rank, set_fault, shutdown, size, stats)
+                   local_rank, local_size, n_nodes, node_index, on_gpu, rank, set_device_timing, set_fault, shutdown, size, stats)
 from .session import Session
 from .parallel.distributed_optimizer import DistributedOptimizer
 from .parallel.broadcast import broadcast_optimizer_state, broadcast_parameters
@@ -27,6 +27,6 @@ __all__ = [
     "rank", "local_rank", "local_size", "allreduce", "allreduce_", "allreduce_async", "all_sum", "all_prod", "all_min",
     "all_max", "grouped_allreduce", "allgather", "allgather_async",
     "broadcast", "broadcast_parameters", "broadcast_optimizer_state", "barrier", "host_allgather", "stats",
-    "clear_stats", "on_gpu", "n_nodes", "node_index", "config", "set_fault", "check_device_status",
+    "clear_stats", "on_gpu", "n_nodes", "node_index", "config", "set_fault", "set_device_timing", "check_device_status",
 ]
 __version__ = "0.1.0"

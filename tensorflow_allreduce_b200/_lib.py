@@ -61,7 +61,7 @@ def _declare(lib):
         "bc_node_index": (i, []),
         "bc_two_level_allreduce_host": (i, [vp, ll, i, i, i]),
         "bc_select_algo": (i, [i, ll, i, i, i, i, ll, ll, i]),
-        "bc_choose_blocks": (i, [ll, i, i, i, i, i]),
+        "bc_choose_blocks": (i, [ll, i, i, i, i, i, i]),
         "bc_plan_gather_rounds": (ll, [i, P(C.c_ulonglong), ll, P(C.c_ulonglong)]),
         "bc_allreduce_async": (ll, [cp, vp, vp, i, i, P(ll), i, i, i, vp, i]),
         "bc_allgather_async": (ll, [cp, vp, i, i, P(ll), i, ALLOC_FN, vp, vp]),
@@ -84,21 +84,23 @@ def _declare(lib):
         "bc_comm_stream": (vp, [i]),
         "bc_stream_wait_event": (i, [vp, vp]),
         "bc_allreduce_direct": (i, [i, vp, vp, ll, i, i, vp, vp]),
-        "bc_fused_step": (i, [i, vp, ll, i, vp, vp, vp, vp, P(OptHyper), f, vp, vp]),
+        "bc_fused_step": (i, [i, vp, ll, i, vp, vp, vp, vp, P(OptHyper), f, vp, vp, i]),
+        "bc_set_option": (i, [cp, ll]),
+        "bc_set_allreduce_profile": (i, [vp]),
         "bc_allgatherv_direct": (i, [i, vp, ll, vp, ll, vp, vp, vp]),
         "bc_emu_create": (vp, [i, i, ll]),
         "bc_emu_destroy": (i, [vp]),
         "bc_emu_buffer": (vp, [vp, i]),
         "bc_emu_status": (C.c_uint, [vp]),
+        "bc_emu_clear_status": (i, [vp]),
         "bc_emu_damaged_guard_bytes": (ll, [vp]),
-        "bc_emu_allreduce": (i, [vp, ll, P(vp), ll, i, i, f, i, i, vp, i]),
+        "bc_emu_allreduce": (i, [vp, ll, P(vp), ll, i, i, f, i, i, vp, i, P(vp), P(C.c_ulonglong), vp]),
         "bc_emu_fused_step": (i, [vp, ll, ll, i, P(vp), P(vp), P(vp), P(vp), P(OptHyper), f, i, vp]),
         "bc_emu_allgatherv": (i, [vp, P(vp), P(C.c_ulonglong), P(C.c_ulonglong), i, vp]),
         "bc_emu_barrier_probe": (i, [vp, i, d, vp]),
         "bc_max_emulated_blocks": (i, [i, i]),
         "bc_gru_supported": (i, [i, i, i, i, i]),
         "bc_gru_set_profile": (i, [vp]),
-        "bc_gru_set_debug": (i, [i]),
         "bc_gru_workspace_bytes": (ll, [i, i, i, i]),
         "bc_gru_forward": (i, [i, i, i, i, vp, vp, vp, vp, vp, vp, vp, vp, d, vp]),
         "bc_gru_backward": (i, [i, i, i, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, d, vp]),

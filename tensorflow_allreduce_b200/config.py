@@ -39,7 +39,7 @@ class Config:
 
     timeout_s: float = 300.0           # host-side deadline: bootstrap, negotiation, ring steps
     device_timeout_s: float = 30.0     # bound of every device-side wait on a peer
-    staging_mb: int = 64               # symmetric staging area for tensors outside symmetric memory
+    staging_mb: int = 256              # symmetric staging area for tensors outside symmetric memory (a quarter per channel)
     heap_mb: int = 256                 # symmetric heap for allgather outputs and `symm_empty`
     algo: str = "auto"                 # force one of: one_shot, two_shot, nvls
     one_shot_max_kb: int = 256         # messages up to this size use the one-shot kernel
@@ -48,6 +48,12 @@ class Config:
     max_blocks: int = 0                # cap on CTAs per collective kernel (0 = heuristic)
     symm: str = "auto"                 # symmetric memory back end: vmm (fd passing) or ipc
     bucket_mb: float = 32.0            # DistributedOptimizer gradient bucket size
+    overlap_blocks: int = 0            # CTAs of a bucket launch that runs beside backward (0 = two per SM left free
+                                       # by a 128-SM persistent kernel, at least 16)
+    device_timing_every: int = 0       # DistributedOptimizer: time every bucket launch of every Nth step on the device
+                                       # (CUDA events; records in stats() carry device_us and bus GB/s); 0 = never
+    link_gbs: float = 764.0            # NVLink rate per direction per GPU that stats() reports fractions of
+                                       # (measured peer copy on B200 / NVSwitch; nominal 900)
     fault: str = ""                    # host-side fault injection, e.g. "drop_request:rank=1:name=x"
 
     @classmethod
@@ -64,6 +70,9 @@ class Config:
             max_blocks=_env("BC_MAX_BLOCKS", int, cls.max_blocks),
             symm=_env("BC_SYMM", str, cls.symm),
             bucket_mb=_env("BC_BUCKET_MB", float, cls.bucket_mb),
+            overlap_blocks=_env("BC_OVERLAP_BLOCKS", int, cls.overlap_blocks),
+            device_timing_every=_env("BC_DEVICE_TIMING_EVERY", int, cls.device_timing_every),
+            link_gbs=_env("BC_LINK_GBS", float, cls.link_gbs),
             fault=_env("BC_FAULT", str, cls.fault),
         )
         for k, v in overrides.items():

@@ -25,7 +25,7 @@ __all__ = [
     "CollectiveError", "init", "shutdown", "is_initialized", "size", "rank", "local_rank", "local_size",
     "allreduce", "allreduce_", "allreduce_async", "all_sum", "all_prod", "all_min", "all_max", "allgather",
     "allgather_async", "broadcast", "barrier",
-    "host_allgather", "stats", "clear_stats", "on_gpu", "config", "set_fault", "check_device_status",
+    "host_allgather", "stats", "clear_stats", "on_gpu", "config", "set_fault", "check_device_status", "set_device_timing", "bus_gbs",
 ]
 
 
@@ -139,6 +139,8 @@ def init(device=None, config: Optional[Config] = None, rank: Optional[int] = Non
                       cfg.nvls_min_kb << 10, int(cfg.nvls), cfg.max_blocks, cfg.symm_code, cfg.fault.encode()), "bc_init")
     _state["config"] = cfg
     _state["device"] = dev_index
+    if dev_index >= 0 and cfg.overlap_blocks > 0:
+        _call(lib.bc_set_option(b"overlap_blocks", cfg.overlap_blocks), "bc_set_option")
     for k in _counters:
         _counters[k] = itertools.count()
 
@@ -168,10 +170,14 @@ def _dump_stats_jsonl() -> None:
         recs = stats()
         with open(path.replace("{rank}", str(r)), "a") as f:
             for e in recs:
-                f.write(json.dumps({"rank": r, "name": e["name"], "op": e["op"], "algo": e["algo"], "bytes": e["bytes"],
-                                    "blocks": e["blocks"], "device": "cuda" if e["device"] else "cpu",
-                                    "negotiation_us": round(e["negotiation_us"], 1),
-                                    "run_us": round((e["t_done"] - e["t_negotiated"]) * 1e6, 1)}) + "\n")
+                rec = {"rank": r, "name": e["name"], "op": e["op"], "algo": e["algo"], "bytes": e["bytes"],
+                       "blocks": e["blocks"], "device": "cuda" if e["device"] else "cpu",
+                       "negotiation_us": round(e["negotiation_us"], 1),
+                       "run_us": round((e["t_done"] - e["t_negotiated"]) * 1e6, 1)}
+                if "device_us" in e:
+                    rec.update(device_us=round(e["device_us"], 2), bus_gbs=round(e.get("bus_gbs", 0.0), 2),
+                               link_frac=round(e.get("link_frac", 0.0), 4))
+                f.write(json.dumps(rec) + "\n")
     except Exception:      # observability must never break a shutdown
         pass
 
@@ -238,6 +244,9 @@ def set_fault(spec: str) -> None:
 def check_device_status() -> None:
     """Raise if a device-side wait on a peer has timed out since `init()`."""
     st = _lib.lib().bc_device_status()
+    if st & 0x20000000:
+        raise CollectiveError(f"an in-place reduction found its tensor at different offsets of symmetric memory on different "
+                              f"ranks (status 0x{st:08x}); its result is wrong and the group is unusable")
     if st:
         raise CollectiveError(f"a device-side wait on a peer timed out (status 0x{st:08x}); the group is unusable")
 
@@ -556,19 +565,47 @@ def barrier(name: Optional[str] = None) -> None:
     host_allgather(None, name=name or _auto_name("barrier"))
 
 
+def bus_gbs(op: str, nbytes: int, world: int, seconds: float) -> float:
+    """Bus bandwidth in GB/s of one collective, the figure that is comparable between group sizes
+    and with the link rate: allreduce `bytes / time * 2 (P - 1) / P`, allgather (`nbytes` = the
+    gathered total) `bytes / time * (P - 1) / P`. One rank moves nothing: 0."""
+    if seconds <= 0 or world <= 1:
+        return 0.0
+    factor = 2.0 * (world - 1) / world if op == "allreduce" else (world - 1) / world
+    return nbytes / seconds * factor / 1e9
+
+
+def set_device_timing(on: bool) -> None:
+    """Switch the device timing of GPU collectives on or off: while on, every ordered launch
+    (gradient buckets, `allreduce_direct_`) and every negotiated GPU allreduce is bracketed by two
+    timing CUDA events on its private stream, and its record in `stats()` carries `device_us`,
+    `bus_gbs` and `link_frac`. Costs two event records per launch and nothing else; the host never
+    waits (a record shows up in `stats()` once its kernels have finished)."""
+    _call(_lib.lib().bc_set_option(b"device_timing", int(bool(on))), "bc_set_option")
+
+
 def stats() -> List[dict]:
     """One record per completed collective since the last `clear_stats()`: name, operation,
-    algorithm, bytes, CTA count and host timestamps (enqueue, negotiated, done/launched)."""
+    algorithm, bytes, CTA count and host timestamps (enqueue, negotiated, done/launched). Records
+    taken while device timing was on (`set_device_timing`, `Config.device_timing_every`) also
+    have `device_us` (time of the kernels between two CUDA events), `bus_gbs` and `link_frac`
+    (bus bandwidth as a fraction of `Config.link_gbs`), and `channel` for ordered launches."""
     raw = _lib.lib().bc_stats_json()
     if not raw:
         raise CollectiveError(_lib.last_error())
     ops = {0: "allreduce", 1: "allgather", 2: "host_gather", 3: "shutdown"}
     algos = {0: "cpu_ring", 1: "one_shot", 2: "two_shot", 3: "nvls", 4: "cpu_shm"}
     out = json.loads(raw.decode())
+    world = size()
+    cfg = _state.get("config")
+    link = cfg.link_gbs if cfg is not None else 764.0
     for e in out:
         e["op"] = ops.get(e["op"], str(e["op"]))
         e["algo"] = algos.get(e["algo"], str(e["algo"])) if (e["device"] == 1 or e["algo"] == 4) else "cpu_ring"
         e["negotiation_us"] = (e["t_negotiated"] - e["t_enqueue"]) * 1e6
+        if e.get("device_us", -1) > 0:
+            e["bus_gbs"] = bus_gbs(e["op"], e["bytes"], world, e["device_us"] * 1e-6)
+            e["link_frac"] = e["bus_gbs"] / link if link > 0 else 0.0
     return out
 
 

@@ -44,7 +44,7 @@ int bc_node_index(void);
  * 2 two-shot, 3 NVLS; force_algo 0 = choose. Negative thresholds mean the defaults. */
 int bc_select_algo(int world, long long bytes, int dtype, int in_place_or_fused, int has_multicast, int force_algo,
                    long long one_shot_max_bytes, long long nvls_min_bytes, int use_nvls);
-int bc_choose_blocks(long long bytes, int world, int algo, int fused_update, int sm_count, int cap_override);
+int bc_choose_blocks(long long bytes, int world, int algo, int fused_update, int sm_count, int cap_override, int beside_compute);
 /* How a gathered result larger than the staging area is cut into rounds (pure function): returns
  * the number of rounds and writes every rank's piece size per round. */
 long long bc_plan_gather_rounds(int world, const unsigned long long* all_bytes, long long staging_bytes, unsigned long long* pieces_out);
@@ -96,8 +96,17 @@ typedef struct bc_opt_hyper {
  * same sequence of calls per channel. `wait_event` / `record_event` are cudaEvent_t or NULL. */
 int bc_allreduce_direct(int channel, const void* in, void* out, long long count, int dtype, int average,
                         void* wait_event, void* record_event);
+/* `beside_compute` != 0: the launch overlaps the backward pass; its grid is capped to the SMs that a
+ * persistent compute kernel leaves free (option "overlap_blocks"), so all its blocks can be resident. */
 int bc_fused_step(int channel, void* grad, long long count, int dtype, void* param, float* master, float* s1, float* s2,
-                  const bc_opt_hyper* h, float scale, void* wait_event, void* record_event);
+                  const bc_opt_hyper* h, float scale, void* wait_event, void* record_event, int beside_compute);
+/* Run-time switches: "device_timing" (1: ordered launches and negotiated GPU allreduces are bracketed
+ * by timing events and their records in bc_stats_json() carry "device_us"), "overlap_blocks". */
+int bc_set_option(const char* key, long long value);
+/* Tuning aid: device array of 5 uint64 that block 0 of later reduction launches fills with %globaltimer
+ * at kernel entry, after the first barrier, after phase 1, after the second barrier and at the end
+ * (one-shot: entry, barrier, reduction, end barrier, end). NULL switches it off. */
+int bc_set_allreduce_profile(void* stamps);
 
 /* Variable allgather into `out_symm`, a buffer of `capacity_bytes` (equal on all ranks) inside the
  * symmetric heap. Row counts are exchanged on the device; `sizes_out` (device memory, one entry per
@@ -110,10 +119,14 @@ void* bc_emu_create(int device, int nranks, long long bytes_per_rank);
 int bc_emu_destroy(void* g);
 void* bc_emu_buffer(void* g, int r);
 unsigned bc_emu_status(void* g);
+int bc_emu_clear_status(void* g);
 /* Guard regions surround every buffer and pad of the group; number of guard bytes overwritten. */
 long long bc_emu_damaged_guard_bytes(void* g);
+/* `srcs` (or NULL): per rank a private input that the kernel copies into the rank's buffer first (the staged
+ * path). `places` (or NULL): per rank the offset it claims to reduce in place; ranks that disagree set status
+ * bit 0x20000000. `prof` (or NULL): device array of 5 uint64 time stamps, see bc_set_allreduce_profile(). */
 int bc_emu_allreduce(void* g, long long off, void* const* outs, long long count, int dtype, int algo, float scale, int idiv,
-                     int blocks, void* stream, int reduce_op);
+                     int blocks, void* stream, int reduce_op, const void* const* srcs, const unsigned long long* places, void* prof);
 int bc_emu_fused_step(void* g, long long off, long long count, int dtype, void* const* params, float* const* masters,
                       float* const* s1, float* const* s2, const bc_opt_hyper* h, float scale, int blocks, void* stream);
 int bc_emu_allgatherv(void* g, const void* const* ins, const unsigned long long* bytes, const unsigned long long* out_offs,
@@ -129,8 +142,6 @@ long long bc_gru_workspace_bytes(int T, int B, int H, int ndir);
 int bc_gru_supported(int device, int T, int B, int H, int ndir);
 /* Tuning aid: device buffer of 8 x T uint64 that block (0,0) of later launches fills with time stamps; NULL = off. */
 int bc_gru_set_profile(void* stamps);
-/* Tuning only: 1 = no MMAs, 2 = no operand copies (results wrong). */
-int bc_gru_set_debug(int flags);
 int bc_gru_forward(int T, int B, int H, int ndir, const float* w_hh, const float* b_hh, const float* gx, float* y, float* rsv,
                    float* workspace, unsigned* sync, unsigned* status, double timeout_s, void* stream);
 int bc_gru_backward(int T, int B, int H, int ndir, const float* w_hh_t, const float* y, const float* rsv, const float* dy,

@@ -149,10 +149,23 @@ long long bc_plan_gather_rounds(int world, const unsigned long long* all_bytes, 
   API_END(-1)
 }
 
-int bc_choose_blocks(long long bytes, int world, int algo, int fused_update, int sm_count, int cap_override) {
+int bc_choose_blocks(long long bytes, int world, int algo, int fused_update, int sm_count, int cap_override, int beside_compute) {
   API_BEGIN
-  return gpu::choose_blocks((size_t)bytes, world, algo, fused_update != 0, sm_count, cap_override);
+  return gpu::choose_blocks((size_t)bytes, world, algo, fused_update != 0, sm_count, cap_override, beside_compute != 0);
   API_END(-1)
+}
+
+static void require_healthy(gpu::Comm& c) {
+  const unsigned st = c.device_status();
+  if (st == 0) return;
+  if (st & dev::kStatusLayout)
+    throw Error("an in-place reduction found its tensor at different offsets of symmetric memory on different ranks; its result "
+                "is wrong and the communicator cannot be used any more");
+  throw Error("an earlier device-side wait timed out; the communicator cannot be used any more");
+}
+
+static void check_channel(int channel) {
+  if (channel < 0 || channel >= dev::kUserChannels) throw Error("bad channel (0.." + std::to_string(dev::kUserChannels - 1) + ")");
 }
 
 // Entry points that address the communicator directly assume that it spans the whole job.
@@ -292,7 +305,7 @@ const char* bc_symm_describe() {
 
 void* bc_comm_stream(int channel) {
   API_BEGIN
-  if (channel < 0 || channel >= dev::kChannels) throw Error("bad channel");
+  check_channel(channel);
   return comm().stream(channel);
   API_END(nullptr)
 }
@@ -317,32 +330,64 @@ int bc_allreduce_direct(int channel, const void* in, void* out, long long count,
                         void* wait_event, void* record_event) {
   API_BEGIN
   require_one_host("an ordered allreduce");
+  check_channel(channel);
   gpu::Comm& c = comm();
-  if (c.device_status() != 0) throw Error("an earlier device-side wait timed out; the communicator cannot be used any more");
+  require_healthy(c);
   cudaStream_t s = c.stream(channel);
   stream_prologue(s, wait_event);
   const int n = c.world();
-  gpu::Algo a = c.allreduce(channel, in, out, (size_t)count, (DType)dtype, average ? 1.f / n : 1.f, average ? n : 1, in == out);
+  TimedLaunch timed;
+  if (rt().device_timing()) timed = rt().timed_begin(s);
+  // Nothing was negotiated: whether the tensor is symmetric is this rank's own finding, so the
+  // kernel compares the offsets that the ranks pass (check_place).
+  gpu::Algo a = c.allreduce(channel, in, out, (size_t)count, (DType)dtype, average ? 1.f / n : 1.f, average ? n : 1, in == out,
+                            ReduceOp::SUM, true);
+  if (timed.stop) rt().timed_end(timed, s, "allreduce_direct", (int)a, c.last_blocks, count * (long long)dtype_size((DType)dtype), channel);
   stream_epilogue(s, record_event);
   return (int)a;
   API_END(-1)
 }
 
 int bc_fused_step(int channel, void* grad, long long count, int dtype, void* param, float* master, float* s1, float* s2,
-                  const bc_opt_hyper* h, float scale, void* wait_event, void* record_event) {
+                  const bc_opt_hyper* h, float scale, void* wait_event, void* record_event, int beside_compute) {
   API_BEGIN
   NvtxRange range("bcoll.fused_step");
   require_one_host("the fused update");
+  check_channel(channel);
   gpu::Comm& c = comm();
-  if (c.device_status() != 0) throw Error("an earlier device-side wait timed out; the communicator cannot be used any more");
+  require_healthy(c);
   cudaStream_t s = c.stream(channel);
   stream_prologue(s, wait_event);
   static_assert(sizeof(bc_opt_hyper) == sizeof(gpu::OptHyper), "bc_opt_hyper must mirror OptHyper");
   gpu::OptHyper hh;
   memcpy(&hh, h, sizeof(hh));
-  gpu::Algo a = c.fused_step(channel, grad, (size_t)count, (DType)dtype, param, master, s1, s2, hh, scale, nullptr);
+  TimedLaunch timed;
+  if (rt().device_timing()) timed = rt().timed_begin(s);
+  gpu::Algo a = c.fused_step(channel, grad, (size_t)count, (DType)dtype, param, master, s1, s2, hh, scale, nullptr, beside_compute != 0);
+  if (timed.stop) rt().timed_end(timed, s, "fused_step", (int)a, c.last_blocks, count * (long long)dtype_size((DType)dtype), channel);
   stream_epilogue(s, record_event);
   return (int)a;
+  API_END(-1)
+}
+
+int bc_set_option(const char* key, long long value) {
+  API_BEGIN
+  const std::string k = key ? key : "";
+  if (k == "device_timing") {
+    rt().set_device_timing(value != 0);
+  } else if (k == "overlap_blocks") {
+    comm().set_overlap_blocks((int)value);
+  } else {
+    throw Error("unknown option '" + k + "'");
+  }
+  return 0;
+  API_END(-1)
+}
+
+int bc_set_allreduce_profile(void* stamps) {
+  API_BEGIN
+  comm().set_profile((unsigned long long*)stamps);
+  return 0;
   API_END(-1)
 }
 
@@ -350,8 +395,9 @@ int bc_allgatherv_direct(int channel, const void* in, long long bytes, void* out
                          unsigned long long* sizes_out, void* wait_event, void* record_event) {
   API_BEGIN
   require_one_host("an ordered allgather");
+  check_channel(channel);
   gpu::Comm& c = comm();
-  if (c.device_status() != 0) throw Error("an earlier device-side wait timed out; the communicator cannot be used any more");
+  require_healthy(c);
   cudaStream_t s = c.stream(channel);
   stream_prologue(s, wait_event);
   c.allgatherv(channel, in, (size_t)bytes, out_symm, nullptr, (size_t)capacity_bytes, sizes_out);
@@ -380,12 +426,15 @@ long long bc_emu_damaged_guard_bytes(void* g) {
 
 unsigned bc_emu_status(void* g) { API_BEGIN return ((gpu::EmuGroup*)g)->status(); API_END(0u) }
 
+int bc_emu_clear_status(void* g) { API_BEGIN ((gpu::EmuGroup*)g)->clear_status(); return 0; API_END(-1) }
+
 int bc_emu_allreduce(void* g, long long off, void* const* outs, long long count, int dtype, int algo, float scale, int idiv,
-                     int blocks, void* stream, int reduce_op) {
+                     int blocks, void* stream, int reduce_op, const void* const* srcs, const unsigned long long* places, void* prof) {
   API_BEGIN
   if (reduce_op < 0 || reduce_op > (int)ReduceOp::MAX) throw Error("unknown reduction");
   check_cuda(((gpu::EmuGroup*)g)->allreduce((size_t)off, outs, (size_t)count, (DType)dtype, (gpu::Algo)algo, scale, idiv, blocks,
-                                            (cudaStream_t)stream, (ReduceOp)reduce_op), "emulated allreduce launch");
+                                            (cudaStream_t)stream, (ReduceOp)reduce_op, srcs, places, (unsigned long long*)prof),
+             "emulated allreduce launch");
   return 0;
   API_END(-1)
 }
@@ -429,11 +478,6 @@ int bc_gru_supported(int device, int T, int B, int H, int ndir) {
 
 int bc_gru_set_profile(void* stamps) {
   gpu::gru_persistent_set_profile((unsigned long long*)stamps);
-  return 0;
-}
-
-int bc_gru_set_debug(int flags) {
-  gpu::gru_persistent_set_debug(flags);
   return 0;
 }
 

@@ -16,6 +16,10 @@
 //
 // Block b of a rank only ever waits for block b of its peers, and touches only elements that
 // block b of the producing rank wrote, so per-block flag barriers are sufficient.
+//
+// Staged inputs: a tensor outside symmetric memory is copied into this rank's staging buffer by
+// the kernel itself before the first barrier (ArRank::src), with the index mapping of the phase
+// that reads it, so the rule above still holds and no separate copy launch is needed.
 #include "collectives.h"
 #include "device_prims.cuh"
 
@@ -222,6 +226,26 @@ __device__ __forceinline__ void epilogue_scalar(const ArRank& R, const ArArgs& a
   }
 }
 
+// Copy of the packs begin + first, begin + first + stride, ... below `end` from `src` to `dst`
+// (both local, 16-byte aligned), four independent loads in flight per thread.
+__device__ __forceinline__ void copy_packs(char* dst, const char* src, size_t begin, size_t end, size_t first, size_t stride) {
+  size_t i = begin + first;
+  for (; i + 3 * stride < end; i += 4 * stride) {
+    const uint4 v0 = ld_local16(src + i * 16), v1 = ld_local16(src + (i + stride) * 16);
+    const uint4 v2 = ld_local16(src + (i + 2 * stride) * 16), v3 = ld_local16(src + (i + 3 * stride) * 16);
+    st_local16(dst + i * 16, v0);
+    st_local16(dst + (i + stride) * 16, v1);
+    st_local16(dst + (i + 2 * stride) * 16, v2);
+    st_local16(dst + (i + 3 * stride) * 16, v3);
+  }
+  for (; i < end; i += stride) st_local16(dst + i * 16, ld_local16(src + i * 16));
+}
+
+// Time stamp k of a profiled launch (block 0 of the first rank slot only).
+__device__ __forceinline__ void stamp(const ArArgs& a, int k) {
+  if (a.prof && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) a.prof[k] = global_timer();
+}
+
 template <typename T>
 __device__ __forceinline__ uint4 nvls_reduce(const char* mc) {
   if constexpr (sizeof(T) == 4) return multimem_ld_reduce_f32(mc);
@@ -242,23 +266,48 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t first = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
 
+  stamp(a, 0);
   if (P == 1) {
     // Single rank: the reduction is the identity; only the epilogue runs.
+    const char* in0 = R.src ? R.src : R.in[0];
     for (size_t i = first; i < npacks; i += stride) {
       Acc acc[E];
-      PK::unpack(ld_local16(R.in[0] + i * 16), acc);
+      PK::unpack(ld_local16(in0 + i * 16), acc);
 #pragma unroll
       for (int e = 0; e < E; e++) acc[e] = finish<Acc>(acc[e], a.scale, a.idiv);
       epilogue_pack<T, OPT>(R, a, i, acc, 0);
     }
     if (blockIdx.x == 0)
       for (size_t e = tail0 + threadIdx.x; e < a.count; e += blockDim.x)
-        epilogue_scalar<T, OPT>(R, a, e, finish<typename Scalar<T>::Acc>(Scalar<T>::ld(reinterpret_cast<const T*>(R.in[0]) + e), a.scale, a.idiv), 0);
+        epilogue_scalar<T, OPT>(R, a, e, finish<typename Scalar<T>::Acc>(Scalar<T>::ld(reinterpret_cast<const T*>(in0) + e), a.scale, a.idiv), 0);
     return;
   }
 
+  if (R.src) {
+    // Staged input: bring it into this rank's symmetric buffer. Every pack is written by the
+    // thread index that reads it from all ranks in the next phase (one-shot: pack i by thread
+    // i mod stride; two-phase: the same inside every rank's slice), so the per-block barrier
+    // below is all the ordering that the readers need.
+    if constexpr (ALGO == ALGO_ONE) {
+      copy_packs(R.in[me], R.src, 0, npacks, first, stride);
+    } else {
+      for (int q = 0; q < P; q++) copy_packs(R.in[me], R.src, npacks * (size_t)q / P, npacks * (size_t)(q + 1) / P, first, stride);
+    }
+    if (blockIdx.x == 0)
+      for (size_t e = tail0 + threadIdx.x; e < a.count; e += blockDim.x)
+        reinterpret_cast<T*>(R.in[me])[e] = reinterpret_cast<const T*>(R.src)[e];
+  }
+  if (R.place && blockIdx.x == 0 && (int)threadIdx.x < P) c.meta[threadIdx.x][(size_t)me * 2] = R.place;
+
   uint32_t epoch = load_epoch(c);
   if (!peer_barrier(c, epoch)) { store_epoch(c, epoch); return; }
+  stamp(a, 1);
+  if (R.place && blockIdx.x == 0 && (int)threadIdx.x < P) {
+    // In place on symmetric memory: every rank must have passed the same offset, or the peers'
+    // buffers are not where this rank looks for them. The result is then wrong; say so.
+    const unsigned long long theirs = *(const volatile unsigned long long*)&c.meta[me][(size_t)threadIdx.x * 2];
+    if (theirs != R.place) atomicOr(c.status, kStatusLayout | (1u << threadIdx.x) | ((uint32_t)me << 8));
+  }
 
   if constexpr (ALGO == ALGO_ONE) {
     reduce_range_any<T, OPT == OPT_RED>(R, P, 0, npacks, first, stride, npacks, a.red, [&](size_t i, Acc* acc) {
@@ -269,9 +318,12 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
     if (blockIdx.x == 0)
       for (size_t e = tail0 + threadIdx.x; e < a.count; e += blockDim.x)
         epilogue_scalar<T, OPT>(R, a, e, finish<typename Scalar<T>::Acc>(reduce_scalar<T>(R, P, e, a.red), a.scale, a.idiv), me);
+    stamp(a, 2);
     // Peers may still be reading this rank's input: nobody leaves before everybody is done.
     peer_barrier(c, epoch);
     store_epoch(c, epoch);
+    stamp(a, 3);
+    stamp(a, 4);
     return;
   } else {
     // Phase 1: reduce this rank's slice and store the result into every rank's buffer.
@@ -337,8 +389,10 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
         for (int p = 0; p < P; p++) Scalar<T>::st(reinterpret_cast<T*>(R.in[p]) + e, g);
       }
     }
+    stamp(a, 2);
     if (!peer_barrier(c, epoch)) { store_epoch(c, epoch); return; }
     store_epoch(c, epoch);
+    stamp(a, 3);
 
     // Phase 2: local epilogue. Block b reads, inside each slice, exactly the packs that block b
     // of the owning rank produced.
@@ -346,17 +400,23 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
     if (copy_needed) {
       for (int q = 0; q < P; q++) {
         const size_t qb = npacks * (size_t)q / P, qe = npacks * (size_t)(q + 1) / P;
-        for (size_t i = qb + first; i < qe; i += stride) {
-          if (!in_bounds(c, i < npacks)) continue;
-          Acc acc[E];
-          PK::unpack(ld_local16(R.in[me] + i * 16), acc);
-          epilogue_pack<T, OPT>(R, a, i, acc, me);
+        if constexpr (OPT == OPT_NONE || OPT == OPT_RED) {
+          // plain copy of the reduced buffer to a separate output
+          if (in_bounds(c, qe <= npacks)) copy_packs(reinterpret_cast<char*>(R.out), R.in[me], qb, qe, first, stride);
+        } else {
+          for (size_t i = qb + first; i < qe; i += stride) {
+            if (!in_bounds(c, i < npacks)) continue;
+            Acc acc[E];
+            PK::unpack(ld_local16(R.in[me] + i * 16), acc);
+            epilogue_pack<T, OPT>(R, a, i, acc, me);
+          }
         }
       }
       if (blockIdx.x == 0)
         for (size_t e = tail0 + threadIdx.x; e < a.count; e += blockDim.x)
           epilogue_scalar<T, OPT>(R, a, e, Scalar<T>::ld(reinterpret_cast<const T*>(R.in[me]) + e), me);
     }
+    stamp(a, 4);
   }
 }
 
@@ -456,15 +516,43 @@ int max_emulated_blocks(int device, int nranks, int threads) {
   return g < 1 ? 1 : g;
 }
 
-int choose_blocks(size_t bytes, int world, int algo, bool fused_opt, int sm_count, int cap_override) {
-  // One block per 32 KiB of payload, at least 1. The default cap keeps SMs free for the backward
-  // pass that runs beside a gradient reduction; a fused update is HBM-bound in its second phase
-  // and gets one block per SM.
-  (void)world;
-  (void)algo;
-  size_t want = (bytes + (32u << 10) - 1) / (32u << 10);
-  int cap = cap_override > 0 ? cap_override : (fused_opt ? 2 * sm_count : 128);
+int choose_blocks(size_t bytes, int world, int algo, bool fused_opt, int sm_count, int cap_override, bool beside_compute) {
+  // How much payload one block of 512 threads should have, and how many blocks pay at most.
+  //   one-shot : every block loads all P copies of its packs, so the work per byte grows with P;
+  //              the messages are small (latency-bound), one block per 32 KiB.
+  //   two-shot : a rank reduces 1/P of the message but reads it from P places and stores it to
+  //              P places over NVLink: one block per 32 KiB, up to 128 (64 SMs at two resident
+  //              blocks each); with two ranks each rank owns half of the message, up to one
+  //              block per SM.
+  //   NVLS     : the switch does the reduction and the fan-out, a thread only issues one
+  //              multimem load and one store per 16 bytes: one block per 64 KiB, up to 64 for
+  //              messages of 16 MiB and less and up to 128 above.
+  //   fused update: the second phase streams the parameters and the optimizer state through
+  //              HBM (6 to 9 times the gradient bytes) and wants every SM: two blocks per SM.
+  //   beside compute: gradient buckets that go out while backward runs share the GPU with a
+  //              compute kernel that may hold most SMs for milliseconds (the persistent GRU
+  //              layer keeps 128 of 148). A grid that fits the SMs left free lets all blocks of
+  //              a launch be resident together on every rank, so the per-block barriers never
+  //              wait for a block that cannot start; two blocks per free SM, at least 16.
+  size_t per_block = 32u << 10;
+  int cap = 128;
+  if (algo == (int)Algo::NVLS) {
+    per_block = 64u << 10;
+    cap = bytes <= (16u << 20) ? 64 : 128;
+  } else if (algo == (int)Algo::TWO_SHOT && world == 2) {
+    cap = sm_count;
+  }
+  if (fused_opt) {
+    per_block = 32u << 10;
+    cap = 2 * sm_count;
+  }
+  if (beside_compute) {
+    const int free_sms = sm_count - 128;
+    cap = free_sms * 2 > 16 ? free_sms * 2 : 16;
+  }
+  if (cap_override > 0) cap = cap_override;
   if (cap > kMaxBlocks) cap = kMaxBlocks;
+  size_t want = (bytes + per_block - 1) / per_block;
   if (want < 1) want = 1;
   return (int)(want > (size_t)cap ? (size_t)cap : want);
 }

@@ -58,6 +58,9 @@ struct ArRank {
   dev::RankCtx ctx;
   char* in[dev::kMaxRanks];   // every rank's input buffer as mapped here (16-byte aligned)
   char* mc_in;                // multicast mapping of the same buffer (NVLS) or null
+  const char* src;            // private input that the kernel first copies into in[rank] (staged path), or null
+  unsigned long long place;   // in place on symmetric memory: 1 + the offset this rank passed, compared across
+                              // the ranks on the device (a mismatch sets kStatusLayout); 0 = not checked
   void* out;                  // local result; may alias in[rank]
   // fused optimizer operands (local, flat, same element order as the gradient)
   void* param;                // fp32 or same 16-bit type as the gradient
@@ -73,6 +76,8 @@ struct ArArgs {
   float scale;                // applied to floating sums (1/size when averaging)
   int idiv;                   // integer divisor when averaging integer tensors
   int red;                    // ReduceOp; anything but SUM goes with no scale, no update and no NVLS
+  unsigned long long* prof;   // optional device array of kProfStamps: %globaltimer of block 0 of rank slot 0 at
+                              // kernel entry, after barrier 1, after phase 1, after barrier 2, at the end
   OptHyper opt;
   ArRank r[dev::kMaxRanks];
 };
@@ -94,6 +99,8 @@ struct AgArgs {
   AgRank r[dev::kMaxRanks];
 };
 
+constexpr int kProfStamps = 5;
+
 struct LaunchCfg {
   int blocks = 0;     // 0 = choose from size
   int threads = 512;
@@ -108,7 +115,10 @@ cudaError_t launch_copy(void* dst, const void* src, size_t bytes, cudaStream_t s
 
 // Largest grid.x for which an emulated launch of `nranks` ranks is co-resident on `device`.
 int max_emulated_blocks(int device, int nranks, int threads);
-int choose_blocks(size_t bytes, int world, int algo, bool fused_opt, int sm_count, int cap_override);
+// Grid of a reduction launch: a pure function of its arguments, the same on every rank.
+// `beside_compute`: the launch overlaps the backward pass (gradient buckets launched from
+// hooks), so it is sized for the SMs that a persistent compute kernel leaves free.
+int choose_blocks(size_t bytes, int world, int algo, bool fused_opt, int sm_count, int cap_override, bool beside_compute = false);
 
 }  // namespace gpu
 }  // namespace bc

@@ -30,10 +30,15 @@ Comm::Comm(int rank, int world, int device, uint64_t job_id, const CommConfig& c
   int lo = 0, hi = 0;
   CUDA_RT(cudaDeviceGetStreamPriorityRange(&lo, &hi));
   for (int c = 0; c < kChannels; c++) CUDA_RT(cudaStreamCreateWithPriority(&streams_[c], cudaStreamNonBlocking, hi));
+  for (int c = 0; c < kUserChannels; c++) {
+    CUDA_RT(cudaEventCreateWithFlags(&fork_[c], cudaEventDisableTiming));
+    CUDA_RT(cudaEventCreateWithFlags(&join_[c], cudaEventDisableTiming));
+  }
   alloc_.reset(new SymmAllocator(rank, world, device, job_id, cfg.symm_mode, cfg.use_nvls, host_timeout_s));
   pad_off_ = 0;
   staging_off_ = align_up(kPadBytes, 1u << 20);
-  cfg_.staging_bytes = align_up(std::max<size_t>(cfg_.staging_bytes, 1u << 20), 1u << 20);
+  // one slice per user channel, each cut into two halves for the two lanes: keep all of them on 1 MiB boundaries
+  cfg_.staging_bytes = align_up(std::max<size_t>(cfg_.staging_bytes, 8u << 20), (size_t)kUserChannels * (2u << 20));
   heap_off_ = staging_off_ + cfg_.staging_bytes;
   cfg_.heap_bytes = align_up(cfg_.heap_bytes, 1u << 20);
   seg0_ = alloc_->alloc(heap_off_ + cfg_.heap_bytes, ag);
@@ -54,6 +59,10 @@ Comm::~Comm() {
   if (status_host_) cudaFreeHost(status_host_);
   for (int c = 0; c < kChannels; c++)
     if (streams_[c]) cudaStreamDestroy(streams_[c]);
+  for (int c = 0; c < kUserChannels; c++) {
+    if (fork_[c]) cudaEventDestroy(fork_[c]);
+    if (join_[c]) cudaEventDestroy(join_[c]);
+  }
 }
 
 RankCtx Comm::make_ctx(int channel) const {
@@ -110,11 +119,13 @@ void Comm::fill_ar_rank(ArRank* r, int channel, Segment* seg, size_t off) const 
 }
 
 Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType dtype, float scale, int idiv,
-                     bool zero_copy_agreed, ReduceOp red) {
+                     bool zero_copy_agreed, ReduceOp red, bool check_place) {
   CUDA_RT(cudaSetDevice(device_));
+  BC_CHECK(channel >= 0 && channel < kUserChannels, "bad channel");
   cudaStream_t s = streams_[channel];
   const size_t es = dtype_size(dtype);
   const size_t bytes = count * es;
+  last_launches = 0;
   if (count == 0) return Algo::ONE_SHOT;
   BC_CHECK((((uintptr_t)in | (uintptr_t)out) & 15) == 0, "allreduce: device pointers must be 16-byte aligned");
   ArArgs a;
@@ -123,6 +134,7 @@ Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType
   a.scale = scale;
   a.idiv = idiv;
   a.red = (int)red;
+  a.prof = prof_;
   LaunchCfg cfg;
   // The switch only adds; other reductions use the peer-load kernels.
   auto pick = [&](size_t nbytes, bool in_place, bool has_mc) {
@@ -140,6 +152,7 @@ Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType
     cfg.blocks = choose_blocks(bytes, 1, a.algo, true, sm_count_, cfg_.max_blocks);
     CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, s));
     last_blocks = cfg.blocks;
+    last_launches = 1;
     return Algo::ONE_SHOT;
   }
 
@@ -155,9 +168,11 @@ Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType
       const size_t nb = std::min(kMaxLaunchBytes, bytes - done);
       fill_ar_rank(&a.r[0], channel, seg, off + done);
       a.r[0].out = (char*)out + done;
+      if (check_place) a.r[0].place = 1 + (((unsigned long long)seg->id << 48) | (unsigned long long)(off + done));
       a.count = nb / es;
       cfg.blocks = choose_blocks(nb, world_, a.algo, false, sm_count_, cfg_.max_blocks);
       CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, s));
+      last_launches++;
     }
     last_blocks = cfg.blocks;
     return algo;
@@ -172,25 +187,50 @@ Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType
     cfg.blocks = choose_blocks(bytes, world_, a.algo, false, sm_count_, cfg_.max_blocks);
     CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, s));
     last_blocks = cfg.blocks;
+    last_launches = 1;
     return Algo::ONE_SHOT;
   }
 
-  // Staged: copy a chunk into the symmetric staging area, reduce from there into `out`.
-  const size_t chunk_elems = (cfg_.staging_bytes / 16) * (16 / es);
+  // Staged: the kernel copies a chunk of the input into this channel's slice of the staging area
+  // (ArRank::src), reduces there and writes the result to `out`. A tensor of more than half a
+  // slice goes in chunks of half a slice that alternate between the channel's two lanes (two
+  // streams, two signal pads, two halves of the slice): the kernel of chunk k + 1 copies in and
+  // out through HBM while the kernel of chunk k is in its NVLink phase. A half is reused by the
+  // chunk after next on the same stream, i.e. after the kernel that used it has ended, and a
+  // kernel ends only after all peers have finished reading its half (second barrier).
+  const size_t half = staging_slice_bytes() / 2;
+  const size_t chunk_elems = (half / 16) * (16 / es);
+  const bool two_lanes = count > chunk_elems;
+  cudaStream_t lane_stream[2] = {s, streams_[channel + kUserChannels]};
+  if (two_lanes) {
+    CUDA_RT(cudaEventRecord(fork_[channel], s));
+    CUDA_RT(cudaStreamWaitEvent(lane_stream[1], fork_[channel], 0));
+  }
   Algo used = Algo::TWO_SHOT;
-  for (size_t done = 0; done < count; done += chunk_elems) {
+  int k = 0;
+  for (size_t done = 0; done < count; done += chunk_elems, k++) {
+    const int lane = two_lanes ? (k & 1) : 0;
+    const int lane_channel = channel + lane * kUserChannels;
     const size_t n = std::min(chunk_elems, count - done);
     const size_t nb = n * es;
-    CUDA_RT(launch_copy(staging(), (const char*)in + done * es, nb, s));
+    const size_t off = staging_offset(channel) + (size_t)lane * half;
     Algo algo = pick(nb, false, seg0_->mc != nullptr);
-    fill_ar_rank(&a.r[0], channel, seg0_, staging_off_);
+    fill_ar_rank(&a.r[0], lane_channel, seg0_, off);
+    a.r[0].src = (const char*)in + done * es;
     a.r[0].out = (char*)out + done * es;
     a.algo = (int)algo;
     a.count = n;
+    // two kernels run side by side: each gets half of the usual grid
     cfg.blocks = choose_blocks(nb, world_, a.algo, false, sm_count_, cfg_.max_blocks);
-    CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, s));
+    if (two_lanes && cfg.blocks > 64) cfg.blocks = 64;
+    CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, lane_stream[lane]));
     last_blocks = cfg.blocks;
+    last_launches++;
     used = algo;
+  }
+  if (two_lanes) {
+    CUDA_RT(cudaEventRecord(join_[channel], lane_stream[1]));
+    CUDA_RT(cudaStreamWaitEvent(s, join_[channel], 0));
   }
   return used;
 }
@@ -198,8 +238,10 @@ Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType
 void Comm::allgatherv(int channel, const void* in, size_t bytes, void* out_symm, void* out_private, size_t total_bytes,
                       unsigned long long* sizes_out, const unsigned long long* all_bytes) {
   CUDA_RT(cudaSetDevice(device_));
+  BC_CHECK(channel >= 0 && channel < kUserChannels, "bad channel");
   cudaStream_t s = streams_[channel];
   if (total_bytes == 0) return;
+  const size_t slice = staging_slice_bytes(), slice_off = staging_offset(channel);
   AgArgs a;
   memset(&a, 0, sizeof(a));
   a.nranks_here = 1;
@@ -229,19 +271,19 @@ void Comm::allgatherv(int channel, const void* in, size_t bytes, void* out_symm,
     launch(in, bytes, (char*)out_symm - seg0_->local, total_bytes);
     return;
   }
-  if (total_bytes <= cfg_.staging_bytes) {
-    launch(in, bytes, staging_off_, total_bytes);
-    if (out_private) CUDA_RT(launch_copy(out_private, staging(), total_bytes, s));
+  if (total_bytes <= slice) {
+    launch(in, bytes, slice_off, total_bytes);
+    if (out_private) CUDA_RT(launch_copy(out_private, staging(channel), total_bytes, s));
     return;
   }
   // The result is larger than the staging area and lies in private memory: gather it in rounds.
   // In round j every rank contributes piece j of its slab; the pieces land back to back in the
-  // staging area and are copied from there to their places in the result. Every rank derives the
+  // channel's slice of the staging area and are copied from there to their places in the result. Every rank derives the
   // same piece sizes from the slab sizes agreed during negotiation.
   BC_CHECK(all_bytes && out_private, "allgatherv: a result of " << total_bytes << " bytes fits neither the symmetric heap nor the "
            "staging area and the slab sizes are not known on the host; raise BC_HEAP_MB or BC_STAGING_MB");
   std::vector<size_t> piece;
-  const size_t rounds = plan_gather_rounds(all_bytes, world_, cfg_.staging_bytes, &piece);
+  const size_t rounds = plan_gather_rounds(all_bytes, world_, slice, &piece);
   std::vector<size_t> disp(world_);
   size_t acc = 0;
   for (int p = 0; p < world_; p++) {
@@ -257,17 +299,17 @@ void Comm::allgatherv(int channel, const void* in, size_t bytes, void* out_symm,
       round_total += len[p];
     }
     if (round_total == 0) break;
-    launch((const char*)in + std::min<size_t>(j * piece[rank_], bytes), len[rank_], staging_off_, round_total);
+    launch((const char*)in + std::min<size_t>(j * piece[rank_], bytes), len[rank_], slice_off, round_total);
     size_t src_off = 0;
     for (int p = 0; p < world_; p++) {
-      if (len[p]) CUDA_RT(launch_copy((char*)out_private + disp[p] + j * piece[p], staging() + src_off, len[p], s));
+      if (len[p]) CUDA_RT(launch_copy((char*)out_private + disp[p] + j * piece[p], staging(channel) + src_off, len[p], s));
       src_off += len[p];
     }
   }
 }
 
 Algo Comm::fused_step(int channel, void* grad, size_t count, DType dtype, void* param, float* master, float* s1, float* s2,
-                      const OptHyper& h, float scale, cudaStream_t stream_override) {
+                      const OptHyper& h, float scale, cudaStream_t stream_override, bool beside_compute) {
   CUDA_RT(cudaSetDevice(device_));
   cudaStream_t s = stream_override ? stream_override : streams_[channel];
   const size_t bytes = count * dtype_size(dtype);
@@ -279,6 +321,7 @@ Algo Comm::fused_step(int channel, void* grad, size_t count, DType dtype, void* 
   a.idiv = 1;
   a.count = count;
   a.opt = h;
+  a.prof = prof_;
   Algo algo = Algo::TWO_SHOT;
   if (world_ == 1) {
     a.r[0].ctx = make_ctx(channel);
@@ -296,7 +339,8 @@ Algo Comm::fused_step(int channel, void* grad, size_t count, DType dtype, void* 
   a.r[0].state1 = s1;
   a.r[0].state2 = s2;
   LaunchCfg cfg;
-  cfg.blocks = choose_blocks(bytes, world_, a.algo, true, sm_count_, cfg_.max_blocks);
+  cfg.blocks = choose_blocks(bytes, world_, a.algo, true, sm_count_, beside_compute && cfg_.overlap_blocks > 0 ? cfg_.overlap_blocks : cfg_.max_blocks,
+                             beside_compute);
   CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, s));
   last_blocks = cfg.blocks;
   return algo;
@@ -371,7 +415,8 @@ RankCtx EmuGroup::ctx(int r, int channel) const {
 }
 
 cudaError_t EmuGroup::allreduce(size_t off, void* const* outs, size_t count, DType dtype, Algo algo, float scale, int idiv,
-                                int blocks, cudaStream_t s, ReduceOp red) {
+                                int blocks, cudaStream_t s, ReduceOp red, const void* const* srcs, const unsigned long long* places,
+                                unsigned long long* prof) {
   ArArgs a;
   memset(&a, 0, sizeof(a));
   a.nranks_here = n_;
@@ -380,10 +425,13 @@ cudaError_t EmuGroup::allreduce(size_t off, void* const* outs, size_t count, DTy
   a.scale = scale;
   a.idiv = idiv;
   a.red = (int)red;
+  a.prof = prof;
   for (int r = 0; r < n_; r++) {
     a.r[r].ctx = ctx(r, 0);
     for (int p = 0; p < n_; p++) a.r[r].in[p] = bufs_[p] + off;
     a.r[r].out = outs[r];
+    a.r[r].src = srcs ? (const char*)srcs[r] : nullptr;
+    a.r[r].place = places ? places[r] : 0;
   }
   LaunchCfg cfg;
   cfg.cooperative = true;

@@ -20,7 +20,7 @@ namespace bc {
 namespace gpu {
 
 struct CommConfig {
-  size_t staging_bytes = 64u << 20;     // staging area for tensors outside symmetric memory
+  size_t staging_bytes = 256u << 20;    // staging area for tensors outside symmetric memory, cut into one slice per user channel
   size_t heap_bytes = 256u << 20;       // general symmetric heap inside segment 0 (allgather outputs, user tensors)
   double device_timeout_s = 30.0;       // bound of every device-side wait
   int force_algo = 0;                   // Algo, 0 = pick from the table
@@ -28,6 +28,8 @@ struct CommConfig {
   size_t nvls_min_bytes = 512u << 10;
   bool use_nvls = true;
   int max_blocks = 0;                   // 0 = heuristic
+  int overlap_blocks = 0;               // grid cap of launches that run beside the backward pass (0 = two per SM that a
+                                        // 128-SM persistent kernel leaves free, at least 16)
   SymmAllocator::Mode symm_mode = SymmAllocator::Mode::AUTO;
 };
 
@@ -59,15 +61,18 @@ class Comm {
   // Status word written by kernels whose wait ran out; 0 while healthy.
   uint32_t device_status() const { return status_host_ ? *(volatile uint32_t*)status_host_ : 0; }
   void set_device_timeout(double s) { cfg_.device_timeout_s = s; }
+  void set_overlap_blocks(int n) { cfg_.overlap_blocks = n; }
 
   // Algorithm for a reduction of `bytes` bytes (all ranks compute the same answer).
   Algo choose_algo(size_t bytes, DType dtype, bool in_place_or_fused, bool has_mc) const;
 
   // Sum-allreduce of `count` elements, launched on stream(channel). `in` may be anywhere on the
   // device; data outside symmetric memory is staged. `scale`/`idiv` implement averaging.
-  // Returns the algorithm used.
+  // `zero_copy_agreed`: every rank passes the same tensor of symmetric memory (in == out) and
+  // has said so; `check_place` then lets the kernel compare the offsets of all ranks (for callers
+  // that could not agree beforehand). Returns the algorithm used.
   Algo allreduce(int channel, const void* in, void* out, size_t count, DType dtype, float scale, int idiv,
-                 bool zero_copy_agreed, ReduceOp red = ReduceOp::SUM);
+                 bool zero_copy_agreed, ReduceOp red = ReduceOp::SUM, bool check_place = false);
   // Variable allgather: `in` = this rank's slab, `out_symm` must lie in segment 0's heap or be null
   // (then the staging area is the landing zone and `out_private` receives a copy; a result larger
   // than the staging area is gathered in rounds, for which `all_bytes` = every rank's slab size
@@ -76,11 +81,19 @@ class Comm {
                   unsigned long long* sizes_out = nullptr, const unsigned long long* all_bytes = nullptr);
 
   // Fused reduce + optimizer update on a gradient bucket that lives in symmetric memory.
+  // `beside_compute`: the launch shares the GPU with the backward pass; its grid is capped so
+  // that all of its blocks can be resident together (see choose_blocks).
   Algo fused_step(int channel, void* grad, size_t count, DType dtype, void* param, float* master, float* s1, float* s2,
-                  const OptHyper& h, float scale, cudaStream_t stream_override);
+                  const OptHyper& h, float scale, cudaStream_t stream_override, bool beside_compute = false);
 
-  // Segment-0 heap offsets
-  char* staging() const { return seg0_->local + staging_off_; }
+  // Device array of kProfStamps time stamps that the next reduction launches fill in (null: off).
+  void set_profile(unsigned long long* stamps) { prof_ = stamps; }
+
+  // Segment-0 layout: every user channel owns one slice of the staging area, so staged
+  // collectives on different channels (different streams) never share bytes.
+  size_t staging_slice_bytes() const { return cfg_.staging_bytes / dev::kUserChannels; }
+  size_t staging_offset(int channel) const { return staging_off_ + (size_t)(channel % dev::kUserChannels) * staging_slice_bytes(); }
+  char* staging(int channel) const { return seg0_->local + staging_offset(channel); }
   size_t staging_bytes() const { return cfg_.staging_bytes; }
   char* heap_base() const { return seg0_->local + heap_off_; }
   size_t heap_bytes() const { return cfg_.heap_bytes; }
@@ -92,6 +105,7 @@ class Comm {
 
   // last launch info (for stats)
   int last_blocks = 0;
+  int last_launches = 0;   // kernel launches of the last allreduce() call
 
  private:
   void fill_ar_rank(ArRank* r, int channel, Segment* seg, size_t off) const;
@@ -105,6 +119,9 @@ class Comm {
   uint32_t* status_host_ = nullptr;   // pinned, mapped
   uint32_t* status_dev_ = nullptr;
   cudaStream_t streams_[dev::kChannels] = {nullptr};
+  cudaEvent_t fork_[dev::kUserChannels] = {nullptr};   // lane 1 of a channel starts behind its lane 0 ...
+  cudaEvent_t join_[dev::kUserChannels] = {nullptr};   // ... and lane 0 continues behind lane 1
+  unsigned long long* prof_ = nullptr;
   int sm_count_ = 148;
 };
 
@@ -127,8 +144,12 @@ class EmuGroup {
   size_t damaged_guard_bytes();
 
   // In-place-capable allreduce over ranks' buffers at `off`; outs[r] may equal the input.
+  // `srcs` (optional): private inputs that the kernel copies into the ranks' buffers first, as the
+  // staged path does. `places` (optional): the offsets the ranks claim to have passed (the kernel
+  // compares them and sets kStatusLayout on a mismatch).
   cudaError_t allreduce(size_t off, void* const* outs, size_t count, DType dtype, Algo algo, float scale, int idiv,
-                        int blocks, cudaStream_t s, ReduceOp red = ReduceOp::SUM);
+                        int blocks, cudaStream_t s, ReduceOp red = ReduceOp::SUM, const void* const* srcs = nullptr,
+                        const unsigned long long* places = nullptr, unsigned long long* prof = nullptr);
   cudaError_t fused_step(size_t off, size_t count, DType dtype, void* const* params, float* const* masters,
                          float* const* s1, float* const* s2, const OptHyper& h, float scale, int blocks, cudaStream_t s);
   cudaError_t allgatherv(const void* const* ins, const unsigned long long* bytes, const unsigned long long* out_offs,

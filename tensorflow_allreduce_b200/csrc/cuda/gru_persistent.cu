@@ -69,7 +69,6 @@ struct Params {
   uint32_t* status;
   unsigned long long timeout_ns;
   unsigned long long* prof;   // optional: 8 time stamps per step of block (0, 0), for tuning
-  int debug;                  // tuning only: 1 = issue no MMA, 2 = issue no operand copies (results are then wrong)
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
@@ -195,14 +194,13 @@ struct Driver {
 __device__ __forceinline__ uint32_t drive_product(Driver& dr, const CUtensorMap* tm_x, int row0, int col0, int ntiles, uint32_t w_addr,
                                                   int w_tile_bytes, uint32_t x_addr, uint32_t bars, uint32_t tmem, uint32_t idesc,
                                                   const uint32_t* ctr, uint32_t target, unsigned long long timeout_ns,
-                                                  unsigned long long* stamp, int debug) {
+                                                  unsigned long long* stamp) {
   const uint32_t full0 = bars, empty0 = bars + 16, done = bars + 32;
   if (!wait_counter(ctr, target, timeout_ns)) return kGruTimeoutGrid;
   if (stamp) stamp[1] = gtimer();
   fence_proxy_async();   // peers wrote the operand with ordinary stores; TMA reads it through the async proxy
   const int nstages = (ntiles + kTilesPerStage - 1) / kTilesPerStage;
   auto load_stage = [&](int sg) {
-    if (debug & 2) return;
     const int st = sg & 1, t0 = sg * kTilesPerStage, nt = min(kTilesPerStage, ntiles - t0);
     mbar_expect_tx(full0 + 8 * st, (uint32_t)(nt * kXTileBytes));
     dr.pending[st] = true;
@@ -216,25 +214,21 @@ __device__ __forceinline__ uint32_t drive_product(Driver& dr, const CUtensorMap*
   const uint64_t a_desc0 = operand_desc(x_addr), b_desc0 = operand_desc(w_addr);
   for (int sg = 0; sg < nstages; sg++) {
     const int st = sg & 1, t0 = sg * kTilesPerStage, nt = min(kTilesPerStage, ntiles - t0);
-    if (!(debug & 2)) {
-      if (!mbar_wait(full0 + 8 * st, dr.full_phase[st], timeout_ns, nullptr)) return kGruTimeoutCopy;
-      dr.full_phase[st] ^= 1;
-      dr.pending[st] = false;
-    }
+    if (!mbar_wait(full0 + 8 * st, dr.full_phase[st], timeout_ns, nullptr)) return kGruTimeoutCopy;
+    dr.full_phase[st] ^= 1;
+    dr.pending[st] = false;
     if (stamp && sg == 0) stamp[2] = gtimer();
     tc_fence_after();
-    if (!(debug & 1)) {
-      for (int i = 0; i < nt; i++) {
-        const uint64_t a_i = a_desc0 + (uint64_t)((st * kStageBytes + i * kXTileBytes) >> 4);
-        const uint64_t b_i = b_desc0 + (uint64_t)(((uint32_t)(t0 + i) * (uint32_t)w_tile_bytes) >> 4);
-        if (t0 + i == 0) {
-          tc_mma_tf32(tmem, a_i, b_i, idesc, 0u);
+    for (int i = 0; i < nt; i++) {
+      const uint64_t a_i = a_desc0 + (uint64_t)((st * kStageBytes + i * kXTileBytes) >> 4);
+      const uint64_t b_i = b_desc0 + (uint64_t)(((uint32_t)(t0 + i) * (uint32_t)w_tile_bytes) >> 4);
+      if (t0 + i == 0) {
+        tc_mma_tf32(tmem, a_i, b_i, idesc, 0u);
 #pragma unroll
-          for (int ks = 1; ks < 4; ks++) tc_mma_tf32_acc(tmem, a_i + 2 * ks, b_i + 2 * ks, idesc);
-        } else {
+        for (int ks = 1; ks < 4; ks++) tc_mma_tf32_acc(tmem, a_i + 2 * ks, b_i + 2 * ks, idesc);
+      } else {
 #pragma unroll
-          for (int ks = 0; ks < 4; ks++) tc_mma_tf32_acc(tmem, a_i + 2 * ks, b_i + 2 * ks, idesc);
-        }
+        for (int ks = 0; ks < 4; ks++) tc_mma_tf32_acc(tmem, a_i + 2 * ks, b_i + 2 * ks, idesc);
       }
     }
     if (sg + 2 < nstages) {
@@ -473,7 +467,7 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
       if (s > 0) {
         if (driver) {
           fail = drive_product(dr, &tm_x, tprev * B, dir * H + q * kq, ntiles, smem_u32(w_s), w_tile, smem_u32(x_s), bars, tmem, idesc,
-                               dir_ctr, (uint32_t)nblocks * (uint32_t)s, p.timeout_ns, stamp, p.debug);
+                               dir_ctr, (uint32_t)nblocks * (uint32_t)s, p.timeout_ns, stamp);
           if (fail) { atomicOr(p.status, fail); *abort_s = 1; }
         }
         __syncwarp();
@@ -566,7 +560,7 @@ __global__ void __launch_bounds__(kThreads, 1) gru_persistent_kernel(const __gri
         load_bwd_inputs(p, pre, dir ? s + 1 : T - 2 - s, dir, u0 + u, bq);
         if (driver) {
           fail = drive_product(dr, &tm_x, t * B, dir * 3 * H + q * kq, ntiles, smem_u32(w_s), w_tile, smem_u32(x_s), bars, tmem, idesc,
-                               dir_ctr, (uint32_t)nblocks * (uint32_t)(s + 1), p.timeout_ns, stamp, p.debug);
+                               dir_ctr, (uint32_t)nblocks * (uint32_t)(s + 1), p.timeout_ns, stamp);
           if (fail) { atomicOr(p.status, fail); *abort_s = 1; }
         }
         __syncwarp();
@@ -638,7 +632,6 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, ui
 }
 
 unsigned long long* g_prof = nullptr;   // set by gru_persistent_set_profile()
-int g_debug = 0;
 
 size_t smem_bytes(const GruDims& d, bool bwd) {
   const size_t kdim = bwd ? 3 * (size_t)d.H : (size_t)d.H;
@@ -689,7 +682,6 @@ cudaError_t launch(const GruDims& d, const CUtensorMap& tm_w, const CUtensorMap&
 }  // namespace
 
 void gru_persistent_set_profile(unsigned long long* stamps) { g_prof = stamps; }
-void gru_persistent_set_debug(int flags) { g_debug = flags; }
 
 bool gru_persistent_supported(const GruDims& d, int device) {
   if (!dims_ok(d) || !encode_fn()) return false;
@@ -724,7 +716,6 @@ cudaError_t gru_persistent_forward(const GruDims& d, const float* w_hh, const fl
   p.status = status;
   p.timeout_ns = (unsigned long long)(timeout_s * 1e9);
   p.prof = g_prof;
-  p.debug = g_debug;
   return launch<false>(d, tm_w, tm_x, p, stream);
 }
 
@@ -748,7 +739,6 @@ cudaError_t gru_persistent_backward(const GruDims& d, const float* w_hh_t, const
   p.status = status;
   p.timeout_ns = (unsigned long long)(timeout_s * 1e9);
   p.prof = g_prof;
-  p.debug = g_debug;
   return launch<true>(d, tm_w, tm_x, p, stream);
 }
 

@@ -68,8 +68,6 @@ size_t gru_persistent_workspace_bytes(const GruDims& d);
 // published, [2] first operand stage landed, [3] last MMA issued, [4] accumulator complete,
 // [5] gate math and stores done, [6] step published. Null switches it off.
 void gru_persistent_set_profile(unsigned long long* stamps);
-// Tuning only: 1 = issue no MMA, 2 = issue no operand copies. Results are wrong with either bit.
-void gru_persistent_set_debug(int flags);
 
 // True if this device and these dimensions can run the persistent kernels.
 bool gru_persistent_supported(const GruDims& d, int device);

@@ -11,19 +11,26 @@ namespace dev {
 constexpr int kMaxRanks = 8;
 constexpr int kMaxBlocks = 512;     // barrier slots per channel
 constexpr int kMetaBlocks = 64;     // blocks that may exchange per-call metadata (allgatherv)
-constexpr int kChannels = 4;
+constexpr int kUserChannels = 4;   // channels a caller can name: each has a stream, a signal pad and a staging slice
+// Every user channel c has a second lane, channel c + kUserChannels, with a stream and a pad of
+// its own: a large staged allreduce alternates its chunks between the two lanes, so that the
+// local copies of one chunk run beside the NVLink phase of the next.
+constexpr int kChannels = 2 * kUserChannels;
 
 // Layout of one channel inside a rank's signal pad (all offsets in bytes).
 constexpr size_t kFlagBytes = (size_t)kMaxBlocks * kMaxRanks * sizeof(uint32_t);          // 16 KiB
 constexpr size_t kMetaBytes = (size_t)kMetaBlocks * kMaxRanks * 2 * sizeof(uint64_t);     // 16 KiB
 constexpr size_t kChannelBytes = kFlagBytes + kMetaBytes;
-constexpr size_t kPadBytes = kChannels * kChannelBytes;                                  // 64 KiB
+constexpr size_t kPadBytes = kChannels * kChannelBytes;                                  // 256 KiB
 
 // Status word written by a block whose wait ran out (host-mapped memory).
 constexpr uint32_t kStatusTimeout = 0x80000000u;
 // Status bit written by a bounds-checked build (-DBC_DEBUG) when an index left its tensor; the
 // access is skipped, nothing traps.
 constexpr uint32_t kStatusBounds = 0x40000000u;
+// Status bit written when the ranks of an in-place reduction on symmetric memory did not all
+// pass the same offset (the tensor is not at the same place on every rank).
+constexpr uint32_t kStatusLayout = 0x20000000u;
 
 // What one (real or emulated) rank needs to synchronise with its peers on one channel.
 struct RankCtx {

@@ -228,6 +228,17 @@ void Runtime::shutdown() {
       } catch (...) {
       }
     }
+    {
+      std::lock_guard<std::mutex> g(stats_mu_);
+      collect_timed_locked();
+      for (auto& t : timed_) {
+        cudaEventDestroy((cudaEvent_t)t.start);
+        cudaEventDestroy((cudaEvent_t)t.stop);
+      }
+      timed_.clear();
+      for (void* e : event_pool_) cudaEventDestroy((cudaEvent_t)e);
+      event_pool_.clear();
+    }
     if (pinned_) cudaFreeHost(pinned_);
     if (scratch_) cudaFree(scratch_);
     pinned_ = scratch_ = nullptr;
@@ -353,8 +364,19 @@ void Runtime::finish(const std::shared_ptr<OpRecord>& r, bool ok, const std::str
     e.t_negotiated = r->t_negotiated;
     e.t_done = r->t_done;
     for (int i = 0; i < 3; i++) e.two_level_s[i] = r->two_level_s[i];
-    stats_.push_back(e);
-    if (stats_.size() > 4096) stats_.pop_front();
+    if (r->timed_stop) {
+      // the device time is known once the stop event has completed: the record waits for it
+      TimedLaunch t;
+      t.entry = e;
+      t.entry.channel = 0;
+      t.start = r->timed_start;
+      t.stop = r->timed_stop;
+      r->timed_start = r->timed_stop = nullptr;
+      timed_.push_back(t);
+    } else {
+      stats_.push_back(e);
+      if (stats_.size() > 4096) stats_.pop_front();
+    }
   }
   {
     std::lock_guard<std::mutex> g(mu_);
@@ -664,10 +686,18 @@ void Runtime::perform_allreduce(OpRecord& r) {
     cudaError_t e = cudaStreamWaitEvent(s, (cudaEvent_t)r.ready_event, 0);
     BC_CHECK(e == cudaSuccess, "cudaStreamWaitEvent: " << cudaGetErrorString(e));
   }
+  TimedLaunch timed;
+  if (device_timing()) timed = timed_begin(s);
   if (node_)
     two_level_allreduce(r, count, scale, idiv);
   else
     r.algo = (int)comm_->allreduce(0, r.in, r.out, count, r.dtype, (float)scale, (int)idiv, r.zero_copy, r.red);
+  if (timed.stop) {
+    cudaError_t te = cudaEventRecord((cudaEvent_t)timed.stop, s);
+    BC_CHECK(te == cudaSuccess, "cudaEventRecord: " << cudaGetErrorString(te));
+    r.timed_start = timed.start;
+    r.timed_stop = timed.stop;
+  }
   cudaError_t e = cudaEventRecord((cudaEvent_t)r.done_event, s);
   BC_CHECK(e == cudaSuccess, "cudaEventRecord: " << cudaGetErrorString(e));
 }
@@ -823,8 +853,68 @@ void Runtime::two_level_allgather(OpRecord& r, size_t row_bytes, size_t total_by
 
 // ---- stats ---------------------------------------------------------------------------------
 
+TimedLaunch Runtime::timed_begin(void* stream) {
+  TimedLaunch t;
+  {
+    std::lock_guard<std::mutex> g(stats_mu_);
+    for (void** e : {&t.start, &t.stop}) {
+      if (!event_pool_.empty()) {
+        *e = event_pool_.back();
+        event_pool_.pop_back();
+      }
+    }
+  }
+  for (void** e : {&t.start, &t.stop}) {
+    if (!*e) {
+      cudaEvent_t ev = nullptr;
+      cudaError_t rc = cudaEventCreate(&ev);
+      BC_CHECK(rc == cudaSuccess, "cudaEventCreate: " << cudaGetErrorString(rc));
+      *e = ev;
+    }
+  }
+  t.entry.t_enqueue = now_s();
+  cudaError_t rc = cudaEventRecord((cudaEvent_t)t.start, (cudaStream_t)stream);
+  BC_CHECK(rc == cudaSuccess, "cudaEventRecord: " << cudaGetErrorString(rc));
+  return t;
+}
+
+void Runtime::timed_end(TimedLaunch t, void* stream, const char* name, int algo, int blocks, int64_t bytes, int channel) {
+  cudaError_t rc = cudaEventRecord((cudaEvent_t)t.stop, (cudaStream_t)stream);
+  BC_CHECK(rc == cudaSuccess, "cudaEventRecord: " << cudaGetErrorString(rc));
+  t.entry.name = name;
+  t.entry.op = (int)OpType::ALLREDUCE;
+  t.entry.algo = algo;
+  t.entry.device = (int)DeviceKind::GPU;
+  t.entry.blocks = blocks;
+  t.entry.bytes = bytes;
+  t.entry.channel = channel;
+  t.entry.t_negotiated = t.entry.t_enqueue;     // an ordered launch is not negotiated
+  t.entry.t_done = now_s();
+  std::lock_guard<std::mutex> g(stats_mu_);
+  timed_.push_back(t);
+  if (timed_.size() > 1024) collect_timed_locked();
+}
+
+void Runtime::collect_timed_locked() {
+  while (!timed_.empty()) {
+    TimedLaunch& t = timed_.front();
+    if (cudaEventQuery((cudaEvent_t)t.stop) != cudaSuccess) {
+      cudaGetLastError();      // "not ready" is not an error to keep
+      break;
+    }
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, (cudaEvent_t)t.start, (cudaEvent_t)t.stop) == cudaSuccess) t.entry.device_us = (double)ms * 1e3;
+    stats_.push_back(t.entry);
+    if (stats_.size() > 4096) stats_.pop_front();
+    event_pool_.push_back(t.start);
+    event_pool_.push_back(t.stop);
+    timed_.pop_front();
+  }
+}
+
 std::string Runtime::stats_json() {
   std::lock_guard<std::mutex> g(stats_mu_);
+  collect_timed_locked();
   std::ostringstream os;
   os << "[";
   bool first = true;
@@ -842,6 +932,8 @@ std::string Runtime::stats_json() {
        << ",\"t_done\":" << e.t_done;
     if (e.two_level_s[0] > 0 || e.two_level_s[1] > 0 || e.two_level_s[2] > 0)
       os << ",\"two_level_s\":[" << e.two_level_s[0] << "," << e.two_level_s[1] << "," << e.two_level_s[2] << "]";
+    if (e.device_us >= 0) os << ",\"device_us\":" << e.device_us;
+    if (e.channel >= 0) os << ",\"channel\":" << e.channel;
     os << "}";
   }
   os << "]";

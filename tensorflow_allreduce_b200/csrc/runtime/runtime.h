@@ -63,6 +63,8 @@ struct OpRecord {
   std::string error;
   double t_enqueue = 0, t_negotiated = 0, t_done = 0;
   double two_level_s[3] = {0, 0, 0};   // allreduce in two levels: inside the host, over the rail, back inside the host
+  void* timed_start = nullptr;         // timing events around the kernels of a GPU collective while device timing is on
+  void* timed_stop = nullptr;
 };
 
 struct RuntimeOptions {
@@ -73,7 +75,7 @@ struct RuntimeOptions {
   int device = -1;                // CUDA device ordinal, -1 = CPU only
   double timeout_s = 300.0;       // host-side deadline for negotiation and ring steps
   double device_timeout_s = 30.0;
-  size_t staging_bytes = 64u << 20;
+  size_t staging_bytes = 256u << 20;
   size_t heap_bytes = 256u << 20;
   int force_algo = 0;
   size_t one_shot_max_bytes = 256u << 10;
@@ -102,6 +104,16 @@ struct StatEntry {
   int64_t bytes = 0;
   double t_enqueue = 0, t_negotiated = 0, t_done = 0;
   double two_level_s[3] = {0, 0, 0};
+  double device_us = -1;    // time of the kernels on the device (CUDA events), where it was sampled
+  int channel = -1;         // private stream of an ordered launch
+};
+
+// An ordered launch whose device time is being measured: two timing events around it on its
+// stream. The record joins the statistics once the stop event has completed.
+struct TimedLaunch {
+  StatEntry entry;
+  void* start = nullptr;    // cudaEvent_t
+  void* stop = nullptr;
 };
 
 class Runtime {
@@ -140,6 +152,13 @@ class Runtime {
 
   std::string stats_json();
   void clear_stats();
+
+  // Device timing of ordered launches (gradient buckets): while switched on, the entry points
+  // bracket every launch with two timing events (`timed_begin` before, `timed_end` after).
+  void set_device_timing(bool on) { device_timing_.store(on); }
+  bool device_timing() const { return device_timing_.load(); }
+  TimedLaunch timed_begin(void* stream);
+  void timed_end(TimedLaunch t, void* stream, const char* name, int algo, int blocks, int64_t bytes, int channel);
 
  private:
   void setup_node_group();      // constructor steps, collective over all ranks
@@ -201,6 +220,10 @@ class Runtime {
 
   std::mutex stats_mu_;
   std::deque<StatEntry> stats_;
+  std::atomic<bool> device_timing_{false};
+  std::deque<TimedLaunch> timed_;          // launched, stop event not yet seen complete
+  std::vector<void*> event_pool_;          // timing events ready for reuse
+  void collect_timed_locked();             // moves completed launches into stats_ (stats_mu_ held)
 };
 
 }  // namespace bc

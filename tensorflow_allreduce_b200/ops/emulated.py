@@ -67,9 +67,15 @@ class EmulatedGroup:
         return int(self.lib.bc_max_emulated_blocks(self.device, self.nranks))
 
     def allreduce(self, count: int, dtype: torch.dtype, algo: str = "two_shot", outs: Optional[Sequence[torch.Tensor]] = None,
-                  scale: float = 1.0, idiv: int = 1, blocks: int = 4, offset_bytes: int = 0, op: str = "sum"):
+                  scale: float = 1.0, idiv: int = 1, blocks: int = 4, offset_bytes: int = 0, op: str = "sum",
+                  srcs: Optional[Sequence[torch.Tensor]] = None, places: Optional[Sequence[int]] = None,
+                  profile: Optional[torch.Tensor] = None):
         """Reduce the first `count` elements (at `offset_bytes`) of all ranks' buffers. `outs`
-        defaults to in place (two-shot only). `op`: sum, prod, min or max."""
+        defaults to in place (two-shot only). `op`: sum, prod, min or max. `srcs`: private inputs
+        that the kernel itself copies into the ranks' buffers first (the staged path of a real
+        group). `places`: the offsets that the ranks claim for an in-place reduction; ranks that
+        disagree set the layout bit of the status word. `profile`: int64 CUDA tensor of 5 time
+        stamps written by block 0 of rank 0."""
         n = self.nranks
         arr = (C.c_void_p * n)()
         for r in range(n):
@@ -77,9 +83,19 @@ class EmulatedGroup:
                 arr[r] = int(self.lib.bc_emu_buffer(self._g, r)) + offset_bytes
             else:
                 arr[r] = outs[r].data_ptr()
+        sp = None
+        if srcs is not None:
+            sp = (C.c_void_p * n)(*[t.data_ptr() for t in srcs])
+        pl = None
+        if places is not None:
+            pl = (C.c_ulonglong * n)(*[int(v) for v in places])
         s = torch.cuda.current_stream(self.device).cuda_stream
         _check(self.lib.bc_emu_allreduce(self._g, offset_bytes, arr, count, _DTYPES[dtype], ALGOS[algo], float(scale), int(idiv),
-                                         blocks, C.c_void_p(s), {"sum": 0, "prod": 1, "min": 2, "max": 3}[op]), "emulated allreduce")
+                                         blocks, C.c_void_p(s), {"sum": 0, "prod": 1, "min": 2, "max": 3}[op], sp, pl,
+                                         C.c_void_p(profile.data_ptr()) if profile is not None else None), "emulated allreduce")
+
+    def clear_status(self):
+        self.lib.bc_emu_clear_status(self._g)
 
     def fused_step(self, count: int, dtype: torch.dtype, params: Sequence[torch.Tensor], hyper: "_lib.OptHyper",
                    masters: Optional[Sequence[torch.Tensor]] = None, state1: Optional[Sequence[torch.Tensor]] = None,

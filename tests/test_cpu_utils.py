@@ -32,6 +32,16 @@ def test_clock_sampler_reads_nvml(monkeypatch):
     assert c.samples[0][0] == "5"                                       # CUDA ordinal 1 -> NVML index 5
 
 
+def test_bus_bandwidth_arithmetic():
+    # allreduce: bytes / time * 2 (P - 1) / P; allgather: total bytes / time * (P - 1) / P
+    from tensorflow_allreduce_b200.core import bus_gbs
+
+    assert abs(bus_gbs("allreduce", 1 << 30, 8, 2.4e-3) - (1 << 30) / 2.4e-3 * 1.75 / 1e9) < 1e-9
+    assert abs(bus_gbs("allreduce", 64 << 20, 2, 1e-3) - (64 << 20) / 1e-3 / 1e9) < 1e-9
+    assert abs(bus_gbs("allgather", 1 << 20, 4, 1e-4) - (1 << 20) / 1e-4 * 0.75 / 1e9) < 1e-9
+    assert bus_gbs("allreduce", 1 << 20, 1, 1e-3) == 0.0 and bus_gbs("allreduce", 1 << 20, 8, 0.0) == 0.0
+
+
 def test_timeline_export():
     from tensorflow_allreduce_b200.utils import timeline
 
@@ -49,6 +59,12 @@ def test_timeline_export():
     steps = [e for e in timeline.chrome_trace([two], pid=0) if e["cat"] == "allreduce.two_level"]
     assert [e["name"] for e in steps] == ["inside the host", "rail between hosts", "gather inside the host"]
     assert abs(steps[1]["ts"] - steps[0]["ts"] - 100.0) < 1e-3 and abs(steps[2]["dur"] - 200.0) < 1e-3
+    # a record that was timed on the device adds a span of that length on the lane of its channel
+    timed = dict(recs[0], name="fused_step", device_us=250.0, channel=1, bus_gbs=512.0, link_frac=0.67)
+    dev = [e for e in timeline.chrome_trace([timed], pid=0) if e["cat"] == "allreduce.device"]
+    assert len(dev) == 1 and dev[0]["tid"] == 11 and dev[0]["dur"] == 250.0 and dev[0]["args"]["bus_gbs"] == 512.0
+    s = timeline.summary(recs + [timed])
+    assert s["allreduce/nvls"]["calls"] == 2 and s["allreduce/nvls"]["device_timed"] == 1 and s["allreduce/nvls"]["device_us"] == 250.0
 
 
 def test_launcher_starts_ranks_and_propagates_failure(tmp_path):
@@ -348,11 +364,18 @@ def test_algorithm_selector_table(native_lib):
     assert sel(2, 1 << 20, force=NVLS) == NVLS and sel(8, 1 << 20, force=NVLS, mc=False) == TWO
     assert sel(8, 1 << 30, force=ONE, in_place=False) == ONE and sel(8, 1 << 20, force=ONE, in_place=True) == TWO
     assert sel(8, 4 << 10, in_place=False, force=TWO) == TWO
-    # grid: one block per 32 KiB, at most 128; a fused update may take two blocks per SM
+    # grid, per algorithm and group size (bytes, world, algo, fused, SMs, cap override, beside compute):
     blocks = native_lib.bc_choose_blocks
-    assert blocks(1, 8, TWO, 0, 148, 0) == 1 and blocks(32 << 10, 8, TWO, 0, 148, 0) == 1 and blocks((32 << 10) + 1, 8, TWO, 0, 148, 0) == 2
-    assert blocks(1 << 30, 8, NVLS, 0, 148, 0) == 128 and blocks(1 << 30, 8, NVLS, 1, 148, 0) == 296
-    assert blocks(1 << 30, 8, TWO, 0, 148, 16) == 16
+    # peer loads: one block per 32 KiB, at most 128 (two ranks: one per SM)
+    assert blocks(1, 8, TWO, 0, 148, 0, 0) == 1 and blocks(32 << 10, 8, TWO, 0, 148, 0, 0) == 1 and blocks((32 << 10) + 1, 8, TWO, 0, 148, 0, 0) == 2
+    assert blocks(1 << 30, 8, TWO, 0, 148, 0, 0) == 128 and blocks(1 << 30, 4, TWO, 0, 148, 0, 0) == 128 and blocks(1 << 30, 2, TWO, 0, 148, 0, 0) == 148
+    assert blocks(256 << 10, 8, ONE, 0, 148, 0, 0) == 8
+    # NVLS: one block per 64 KiB, at most 64 up to 16 MiB and 128 above
+    assert blocks(1 << 20, 8, NVLS, 0, 148, 0, 0) == 16 and blocks(16 << 20, 8, NVLS, 0, 148, 0, 0) == 64 and blocks(1 << 30, 8, NVLS, 0, 148, 0, 0) == 128
+    # a fused update wants every SM twice; beside the backward pass only what a 128-SM kernel leaves free
+    assert blocks(1 << 30, 8, NVLS, 1, 148, 0, 0) == 296 and blocks(1 << 30, 8, NVLS, 1, 148, 0, 1) == 40
+    assert blocks(1 << 30, 8, NVLS, 1, 132, 0, 1) == 16 and blocks(64 << 10, 8, TWO, 1, 148, 0, 1) == 2
+    assert blocks(1 << 30, 8, TWO, 0, 148, 16, 0) == 16 and blocks(1 << 30, 8, NVLS, 1, 148, 24, 1) == 24
 
 
 def test_gather_rounds_cover_every_slab_and_fit_the_staging_area(native_lib):
@@ -412,3 +435,80 @@ def test_static_allreduce_refuses_bad_requests_before_touching_a_device(native_l
     assert rc == -1 and "dtype" in err
     rc, err = call(ins, [0x30004, 0x40000], 16)
     assert rc == -1 and "aligned" in err
+
+
+def test_bucket_plan_covers_every_parameter_once_and_cuts_on_pack_boundaries():
+    # plan_buckets is pure arithmetic: random units (single parameters and shared storages with
+    # gaps), checked for disjoint ranges, full coverage, 16-byte aligned starts and sizes.
+    from hypothesis import given, settings, strategies as st
+
+    from tensorflow_allreduce_b200.parallel.distributed_optimizer import plan_buckets
+
+    member = st.tuples(st.integers(min_value=1, max_value=5000), st.integers(min_value=0, max_value=40))   # (numel, gap after it)
+    unit = st.lists(member, min_size=1, max_size=12)
+
+    @settings(max_examples=300, deadline=None)
+    @given(st.lists(unit, min_size=1, max_size=8), st.sampled_from([2, 4]), st.integers(min_value=64, max_value=20000), st.randoms())
+    def check(raw, esize, bucket_bytes, rnd):
+        units, reg, sizes = [], 0, {}
+        for ui, ms in enumerate(raw):
+            members, off = [], 0
+            regs = list(range(reg, reg + len(ms)))
+            reg += len(ms)
+            if len(ms) > 2:
+                rnd.shuffle(regs)                       # storage order need not be registration order
+            for (n, gap), r in zip(ms, regs):
+                key = (ui, len(members))
+                members.append((key, off, n, r))
+                sizes[key] = n
+                off += n + gap
+            units.append((off, members))
+        total, placements, ranges = plan_buckets(units, esize, bucket_bytes)
+        assert len(placements) == len(units) and all(p * esize % 256 == 0 for p in placements)
+        where = {}
+        for lo, hi, slots in ranges:
+            assert 0 <= lo < hi <= total and lo * esize % 16 == 0 and slots
+            for key, o in slots:
+                assert key not in where
+                assert 0 <= o and o + sizes[key] <= hi - lo
+                where[key] = (lo + o, lo + o + sizes[key])
+        assert set(where) == set(sizes)                                  # every parameter in exactly one range
+        spans = sorted((lo, hi) for lo, hi, _ in ranges)
+        assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:]))      # ranges do not overlap
+        for (numel, members), p in zip(units, placements):               # parameters keep their place inside a unit
+            for key, o, n, _ in members:
+                assert where[key] == (p + o, p + o + n)
+
+    check()
+
+
+def test_bucket_plan_of_a_recurrent_stack_follows_the_layers():
+    # Five bidirectional GRU layers of 1024 in one flat storage (as after flatten_parameters()),
+    # in two storage orders: parameters of a layer together, or all matrices first and all bias
+    # vectors last. Either way every layer-direction becomes one range of its own, launched in
+    # the order in which backward finishes the layers, and no matrix range waits for a vector of
+    # an earlier layer.
+    from tensorflow_allreduce_b200.parallel.distributed_optimizer import plan_buckets
+
+    names, reg = [], 0
+    for layer in range(5):
+        inp = 1312 if layer == 0 else 2048
+        for d in range(2):
+            for kind, n in (("w_ih", 3072 * inp), ("w_hh", 3072 * 1024), ("b_ih", 3072), ("b_hh", 3072)):
+                names.append(((layer, d, kind), n, reg))
+                reg += 1
+    for biases_last in (False, True):
+        order = names if not biases_last else [m for m in names if m[0][2][0] == "w"] + [m for m in names if m[0][2][0] == "b"]
+        members, off = [], 0
+        for key, n, r in order:
+            members.append((key, off, n, r))
+            off += n
+        total, placements, ranges = plan_buckets([(off, members)], 4, 32 << 20)
+        assert total == off and placements == [0]
+        matrix_ranges = [r for r in ranges if any(k[2][0] == "w" for k, _ in r[2])]
+        assert len(matrix_ranges) == 10
+        for i, (lo, hi, slots) in enumerate(matrix_ranges):
+            layers = {(k[0], k[1]) for k, _ in slots}
+            assert layers == {(4 - i // 2, 1 - i % 2)}                   # layer 4 reverse first, layer 0 forward last
+            assert (hi - lo) * 4 <= 40 << 20
+        assert len(ranges) == (11 if biases_last else 10)

@@ -261,3 +261,61 @@ def test_bounded_wait_reports_status_and_returns():
     x = torch.ones(10, device="cuda") * 2  # the device still works
     assert float(x.sum()) == 20.0
     g.close()
+
+
+@pytest.mark.parametrize("nranks", [2, 3, 8])
+@pytest.mark.parametrize("algo", ["one_shot", "two_shot"])
+def test_staged_inputs_are_copied_in_by_the_kernel(emu, nranks, algo):
+    # The staged path of a real group: the inputs are private tensors, the kernel copies them into
+    # the ranks' symmetric buffers before the first barrier and writes the result to separate
+    # outputs. The buffers hold garbage beforehand; the private inputs must stay untouched.
+    g = emu(nranks)
+    for dtype in (torch.float32, torch.bfloat16, torch.int64, torch.uint8):
+        e = PACK[dtype]
+        for n, blocks in ((1, 1), (e - 1, 2), (e, 1), (5 * e * nranks + 3, 3), ((1 << 18) + 7, 4), ((1 << 18) + 7, 1)):
+            xs = [_fill(dtype, n, 31 * r + n % 13) for r in range(nranks)]
+            keep = [x.clone() for x in xs]
+            for r in range(nranks):
+                g.buffer(r, torch.uint8, max(n, 1) * torch.empty((), dtype=dtype).element_size()).fill_(0x5A)
+            outs = [torch.empty(n, dtype=dtype, device="cuda") for _ in range(nranks)]
+            g.allreduce(n, dtype, algo, outs=outs, blocks=blocks, srcs=xs)
+            torch.cuda.synchronize()
+            assert g.status == 0
+            want = _reference_sum(keep, dtype)
+            for r in range(nranks):
+                assert torch.equal(outs[r], want), f"rank {r} n={n} {dtype} {algo}"
+                assert torch.equal(xs[r], keep[r])
+
+
+def test_ranks_that_disagree_about_the_place_are_reported(emu):
+    # An in-place reduction on symmetric memory assumes the tensor at the same offset on every
+    # rank. Ordered launches cannot agree on that beforehand, so the kernel compares the offsets
+    # the ranks pass: equal -> nothing happens; one differs -> the layout bit of the status word.
+    g = emu(4)
+    n = 5000
+    for r in range(4):
+        g.buffer(r, torch.float32, n).fill_(float(r + 1))
+    g.allreduce(n, torch.float32, "two_shot", blocks=2, places=[4097] * 4)
+    torch.cuda.synchronize()
+    assert g.status == 0 and float(g.buffer(3, torch.float32, n)[n - 1]) == 10.0
+    g.allreduce(n, torch.float32, "two_shot", blocks=2, places=[4097, 4097, 8193, 4097])
+    torch.cuda.synchronize()
+    assert g.status & 0x20000000, hex(g.status)
+    assert not g.status & 0x80000000          # nobody waited in vain: the barriers still work
+    g.clear_status()
+    g.allreduce(n, torch.float32, "two_shot", blocks=2, places=[1] * 4)    # the group stays usable
+    torch.cuda.synchronize()
+    assert g.status == 0
+
+
+def test_profile_stamps_are_ordered(emu):
+    g = emu(8)
+    n = 1 << 20
+    stamps = torch.zeros(8, dtype=torch.int64, device="cuda")
+    for algo, outs in (("two_shot", None), ("one_shot", [torch.empty(n, device="cuda") for _ in range(8)])):
+        stamps.zero_()
+        g.allreduce(n, torch.float32, algo, outs=outs, blocks=4, profile=stamps)
+        torch.cuda.synchronize()
+        t = stamps[:5].tolist()
+        assert t[0] > 0 and all(b >= a for a, b in zip(t, t[1:])), t
+        assert t[4] - t[0] < 1e9

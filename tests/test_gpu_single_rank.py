@@ -170,3 +170,104 @@ def test_cudnn_rnn_weights_stay_flat(group):
             out.sum().backward()
             opt.step()
     assert torch.isfinite(out).all()
+
+
+def test_flattened_rnn_weights_split_into_buckets_match_torch(group):
+    # The flat cuDNN weight buffer is cut into several launch ranges; a reference GRU with
+    # separate weights and plain torch SGD must see the same parameters after a few steps, and
+    # the module must still own one flat buffer (no re-packing warning).
+    import warnings
+
+    bc = group
+    torch.manual_seed(0)
+    ref = torch.nn.GRU(24, 32, num_layers=3, bidirectional=True).cuda()
+    mine = copy.deepcopy(ref)
+    mine.flatten_parameters()
+    o_ref = torch.optim.SGD(ref.parameters(), lr=0.05, momentum=0.9, weight_decay=1e-3)
+    o_mine = bc.DistributedOptimizer(torch.optim.SGD(mine.parameters(), lr=0.05, momentum=0.9, weight_decay=1e-3), bucket_mb=0.02)
+    assert o_mine.fused and len(o_mine.buckets) >= 4, o_mine.buckets
+    covered = [p for ps in o_mine.bucket_parameters for p in ps]
+    assert len(covered) == len(list(mine.parameters())) == len({id(p) for p in covered})
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        for it in range(4):
+            x = torch.randn(6, 5, 24, device="cuda")
+            for m, o in ((ref, o_ref), (mine, o_mine)):
+                o.zero_grad()
+                m(x)[0].square().mean().backward()
+                o.step()
+    for a, b in zip(ref.parameters(), mine.parameters()):
+        torch.testing.assert_close(a, b, rtol=1e-4, atol=5e-6)
+    storages = {p.untyped_storage().data_ptr() for p in mine.parameters()}
+    assert len(storages) == 1
+
+
+def test_restored_momentum_is_continued_with_dampening(group):
+    # With dampening torch seeds a NEW momentum buffer with the gradient itself; a buffer that
+    # comes from a state dict must be continued with the recurrence instead.
+    bc = group
+    mk = lambda ps: torch.optim.SGD(ps, lr=0.05, momentum=0.9, dampening=0.5)
+    ref = _mlp()
+    mine = copy.deepcopy(ref)
+    o_ref = mk(ref.parameters())
+    o_mine = bc.DistributedOptimizer(mk(mine.parameters()))
+    torch.manual_seed(3)
+    data = [(torch.randn(16, 37, device="cuda"), torch.randn(16, 5, device="cuda")) for _ in range(4)]
+    for x, y in data[:2]:
+        for m, o in ((ref, o_ref), (mine, o_mine)):
+            o.zero_grad()
+            torch.nn.functional.mse_loss(m(x), y).backward()
+            o.step()
+    # a fresh wrapper around a fresh optimizer, restored from the state dict
+    sd = copy.deepcopy(o_mine.state_dict())
+    again = copy.deepcopy(mine)
+    o_again = bc.DistributedOptimizer(mk(again.parameters()))
+    o_again.load_state_dict(sd)
+    for x, y in data[2:]:
+        for m, o in ((ref, o_ref), (again, o_again)):
+            o.zero_grad()
+            torch.nn.functional.mse_loss(m(x), y).backward()
+            o.step()
+    for a, b in zip(ref.parameters(), again.parameters()):
+        torch.testing.assert_close(a, b, rtol=1e-4, atol=5e-6)
+
+
+def test_device_time_of_every_bucket_in_sampled_steps(group):
+    # timing_every=2: in steps 0 and 2 every bucket launch is bracketed by CUDA events; stats()
+    # then holds one record per bucket and sampled step with the time on the device.
+    bc = group
+    model = _mlp()
+    opt = bc.DistributedOptimizer(torch.optim.SGD(model.parameters(), lr=0.05, momentum=0.9), bucket_mb=0.01, timing_every=2)
+    nb = len(opt.buckets)
+    assert nb > 1
+    torch.cuda.synchronize()
+    bc.clear_stats()
+    for it in range(3):
+        x = torch.randn(16, 37, device="cuda")
+        y = torch.randn(16, 5, device="cuda")
+        opt.zero_grad()
+        torch.nn.functional.mse_loss(model(x), y).backward()
+        opt.step()
+    torch.cuda.synchronize()
+    recs = [e for e in bc.stats() if e["name"] == "fused_step"]
+    assert len(recs) == 2 * nb, (len(recs), nb)
+    assert all(e["device_us"] > 0 and e["channel"] == 1 and e["bytes"] > 0 and e["blocks"] >= 1 for e in recs)
+    assert sorted(e["bytes"] for e in recs[:nb]) == sorted(n * 4 for _, n in opt.buckets)
+    # the switch also covers the other ordered launches and the negotiated GPU allreduce
+    from tensorflow_allreduce_b200.ops import symmetric
+    from tensorflow_allreduce_b200.ops.direct import allreduce_direct_
+
+    bc.clear_stats()
+    bc.set_device_timing(True)
+    s = symmetric.empty((1 << 16,), torch.float32)
+    s.fill_(1.0)
+    allreduce_direct_(s, average=True)
+    bc.allreduce(torch.ones(1 << 16, device="cuda"), name="timed.negotiated")
+    bc.set_device_timing(False)
+    bc.allreduce(torch.ones(1 << 16, device="cuda"), name="untimed")
+    torch.cuda.synchronize()
+    by_name = {e["name"]: e for e in bc.stats()}
+    assert by_name["allreduce_direct"]["device_us"] >= 0 and by_name["timed.negotiated"]["device_us"] > 0
+    assert "device_us" not in by_name["untimed"]
+    from tensorflow_allreduce_b200.utils import timeline
+    assert any(e["cat"] == "allreduce.device" for e in timeline.chrome_trace())

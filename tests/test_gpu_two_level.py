@@ -1,19 +1,14 @@
 """A GPU group whose ranks report several hosts (one box stands in for them): the NVLink kernels
 reduce inside each host, the rails carry the slices between hosts, and the optimizer wrapper
 falls back to flat negotiated allreduces. 2 GPUs = 2 hosts x 1 rank, 4 GPUs = 2 hosts x 2 ranks.
-The reference crosses hosts through a GPU-aware MPI (tensorflow/contrib/mpi_collectives/ring.h:183-225).
-
-Opt-in (BC_TEST_TWO_LEVEL_GPU=1) until this path has had its first run on GPUs."""
-import os
-
+8 GPUs = 2 hosts x 4 ranks.
+The reference crosses hosts through a GPU-aware MPI (tensorflow/contrib/mpi_collectives/ring.h:183-225)."""
 import pytest
 import torch
 
 from _util import run
 
-pytestmark = [pytest.mark.gpu, pytest.mark.multigpu,
-              pytest.mark.skipif(os.environ.get("BC_TEST_TWO_LEVEL_GPU", "0") != "1",
-                                 reason="two-level GPU path: opt in with BC_TEST_TWO_LEVEL_GPU=1")]
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
 
 def _ngpu():
@@ -24,6 +19,8 @@ def _layouts():
     out = [(2, 1)]
     if _ngpu() >= 4:
         out.append((4, 2))
+    if _ngpu() >= 8:
+        out.append((8, 4))
     return out
 
 
