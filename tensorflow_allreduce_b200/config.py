@@ -48,8 +48,8 @@ class Config:
     max_blocks: int = 0                # cap on CTAs per collective kernel (0 = heuristic)
     symm: str = "auto"                 # symmetric memory back end: vmm (fd passing) or ipc
     bucket_mb: float = 32.0            # DistributedOptimizer gradient bucket size
-    overlap_blocks: int = 0            # CTAs of a bucket launch that runs beside backward (0 = two per SM left free
-                                       # by a 128-SM persistent kernel, at least 16)
+    overlap_blocks: int = 0            # CTAs of a bucket launch that runs beside backward (0 = one per SM left free
+                                       # by a 128-SM persistent kernel, at least 8)
     device_timing_every: int = 0       # DistributedOptimizer: time every bucket launch of every Nth step on the device
                                        # (CUDA events; records in stats() carry device_us and bus GB/s); 0 = never
     link_gbs: float = 764.0            # NVLink rate per direction per GPU that stats() reports fractions of

@@ -529,11 +529,16 @@ int choose_blocks(size_t bytes, int world, int algo, bool fused_opt, int sm_coun
   //              messages of 16 MiB and less and up to 128 above.
   //   fused update: the second phase streams the parameters and the optimizer state through
   //              HBM (6 to 9 times the gradient bytes) and wants every SM: two blocks per SM.
-  //   beside compute: gradient buckets that go out while backward runs share the GPU with a
-  //              compute kernel that may hold most SMs for milliseconds (the persistent GRU
-  //              layer keeps 128 of 148). A grid that fits the SMs left free lets all blocks of
-  //              a launch be resident together on every rank, so the per-block barriers never
-  //              wait for a block that cannot start; two blocks per free SM, at least 16.
+  //   beside compute: gradient buckets that go out while backward runs share the GPU with
+  //              compute kernels that may want most SMs for milliseconds: the persistent GRU
+  //              layer is a cooperative launch of 128 blocks that each need an SM of their own,
+  //              so it cannot start while more than sm_count - 128 SMs hold a block of another
+  //              kernel. Blocks are spread one per SM while SMs are free; a grid of at most
+  //              sm_count - 128 blocks (20 on B200) therefore never keeps such a layer waiting,
+  //              whichever of the two kernels starts first, and all of its own blocks are
+  //              resident together on every rank, so no barrier waits for a block that cannot
+  //              start. Measured with 40 blocks on one GPU: every bucket launch delayed the next
+  //              layer's kernel, 0.8 ms per step in total. At least 8.
   size_t per_block = 32u << 10;
   int cap = 128;
   if (algo == (int)Algo::NVLS) {
@@ -548,7 +553,7 @@ int choose_blocks(size_t bytes, int world, int algo, bool fused_opt, int sm_coun
   }
   if (beside_compute) {
     const int free_sms = sm_count - 128;
-    cap = free_sms * 2 > 16 ? free_sms * 2 : 16;
+    cap = free_sms > 8 ? free_sms : 8;
   }
   if (cap_override > 0) cap = cap_override;
   if (cap > kMaxBlocks) cap = kMaxBlocks;

@@ -28,8 +28,8 @@ struct CommConfig {
   size_t nvls_min_bytes = 512u << 10;
   bool use_nvls = true;
   int max_blocks = 0;                   // 0 = heuristic
-  int overlap_blocks = 0;               // grid cap of launches that run beside the backward pass (0 = two per SM that a
-                                        // 128-SM persistent kernel leaves free, at least 16)
+  int overlap_blocks = 0;               // grid cap of launches that run beside the backward pass (0 = one per SM that a
+                                        // 128-SM persistent kernel leaves free, at least 8)
   SymmAllocator::Mode symm_mode = SymmAllocator::Mode::AUTO;
 };
 

@@ -373,8 +373,8 @@ def test_algorithm_selector_table(native_lib):
     # NVLS: one block per 64 KiB, at most 64 up to 16 MiB and 128 above
     assert blocks(1 << 20, 8, NVLS, 0, 148, 0, 0) == 16 and blocks(16 << 20, 8, NVLS, 0, 148, 0, 0) == 64 and blocks(1 << 30, 8, NVLS, 0, 148, 0, 0) == 128
     # a fused update wants every SM twice; beside the backward pass only what a 128-SM kernel leaves free
-    assert blocks(1 << 30, 8, NVLS, 1, 148, 0, 0) == 296 and blocks(1 << 30, 8, NVLS, 1, 148, 0, 1) == 40
-    assert blocks(1 << 30, 8, NVLS, 1, 132, 0, 1) == 16 and blocks(64 << 10, 8, TWO, 1, 148, 0, 1) == 2
+    assert blocks(1 << 30, 8, NVLS, 1, 148, 0, 0) == 296 and blocks(1 << 30, 8, NVLS, 1, 148, 0, 1) == 20
+    assert blocks(1 << 30, 8, NVLS, 1, 132, 0, 1) == 8 and blocks(64 << 10, 8, TWO, 1, 148, 0, 1) == 2
     assert blocks(1 << 30, 8, TWO, 0, 148, 16, 0) == 16 and blocks(1 << 30, 8, NVLS, 1, 148, 24, 1) == 24
 
 
