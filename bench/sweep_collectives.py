@@ -81,10 +81,14 @@ def phases_of(fn):
     fn()
     torch.cuda.synchronize()
     bc.barrier()
+    # Two calls queued back to back: the first lines the GPUs up (the ranks leave a host barrier
+    # tens of microseconds apart, and the first barrier of a kernel would show that skew), the
+    # second is the one that writes the stamps.
+    fn()
     lib.bc_set_allreduce_profile(C.c_void_p(stamps.data_ptr()))
     fn()
-    torch.cuda.synchronize()
     lib.bc_set_allreduce_profile(None)
+    torch.cuda.synchronize()
     t = stamps.tolist()
     d = [(t[i + 1] - t[i]) / 1e3 for i in range(4)]
     allv = bc.host_allgather(d)

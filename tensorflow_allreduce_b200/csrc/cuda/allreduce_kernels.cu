@@ -227,18 +227,19 @@ __device__ __forceinline__ void epilogue_scalar(const ArRank& R, const ArArgs& a
 }
 
 // Copy of the packs begin + first, begin + first + stride, ... below `end` from `src` to `dst`
-// (both local, 16-byte aligned), four independent loads in flight per thread.
+// (both local, 16-byte aligned), four independent loads in flight per thread (eight cost spills
+// under the 64-register bound of two resident blocks per SM).
 __device__ __forceinline__ void copy_packs(char* dst, const char* src, size_t begin, size_t end, size_t first, size_t stride) {
+  constexpr int U = 4;
   size_t i = begin + first;
-  for (; i + 3 * stride < end; i += 4 * stride) {
-    const uint4 v0 = ld_local16(src + i * 16), v1 = ld_local16(src + (i + stride) * 16);
-    const uint4 v2 = ld_local16(src + (i + 2 * stride) * 16), v3 = ld_local16(src + (i + 3 * stride) * 16);
-    st_local16(dst + i * 16, v0);
-    st_local16(dst + (i + stride) * 16, v1);
-    st_local16(dst + (i + 2 * stride) * 16, v2);
-    st_local16(dst + (i + 3 * stride) * 16, v3);
+  for (; i + (U - 1) * stride < end; i += U * stride) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) v[u] = ld_stream16(src + (i + u * stride) * 16);
+#pragma unroll
+    for (int u = 0; u < U; u++) st_local16(dst + (i + u * stride) * 16, v[u]);
   }
-  for (; i < end; i += stride) st_local16(dst + i * 16, ld_local16(src + i * 16));
+  for (; i < end; i += stride) st_local16(dst + i * 16, ld_stream16(src + i * 16));
 }
 
 // Time stamp k of a profiled launch (block 0 of the first rank slot only).
@@ -519,7 +520,8 @@ int max_emulated_blocks(int device, int nranks, int threads) {
 int choose_blocks(size_t bytes, int world, int algo, bool fused_opt, int sm_count, int cap_override, bool beside_compute) {
   // How much payload one block of 512 threads should have, and how many blocks pay at most.
   //   one-shot : every block loads all P copies of its packs, so the work per byte grows with P;
-  //              the messages are small (latency-bound), one block per 32 KiB.
+  //              the messages are small (latency-bound), one block per 32 KiB. (Two ranks use it
+  //              for staged tensors of any size: up to one block per SM, as two-shot below.)
   //   two-shot : a rank reduces 1/P of the message but reads it from P places and stores it to
   //              P places over NVLink: one block per 32 KiB, up to 128 (64 SMs at two resident
   //              blocks each); with two ranks each rank owns half of the message, up to one
@@ -544,7 +546,7 @@ int choose_blocks(size_t bytes, int world, int algo, bool fused_opt, int sm_coun
   if (algo == (int)Algo::NVLS) {
     per_block = 64u << 10;
     cap = bytes <= (16u << 20) ? 64 : 128;
-  } else if (algo == (int)Algo::TWO_SHOT && world == 2) {
+  } else if (world == 2) {
     cap = sm_count;
   }
   if (fused_opt) {

@@ -101,6 +101,10 @@ Algo select_algo(const CommConfig& cfg, int world, size_t bytes, DType dtype, bo
   if (forced == Algo::NVLS && has_mc && is_float) return forced;
   if (forced != Algo::AUTO) return Algo::TWO_SHOT;
   if (!in_place_or_fused && bytes <= cfg.one_shot_max_bytes) return Algo::ONE_SHOT;
+  // Two ranks, separate output: one-shot moves as many bytes over NVLink as two-shot does (each
+  // rank reads the other's copy once), needs one pass instead of three over the local buffers
+  // and no second exchange: measured 30 % faster for staged tensors of 64 MiB and more.
+  if (!in_place_or_fused && world == 2) return Algo::ONE_SHOT;
   // With two ranks the switch-side reduction saves no traffic (each GPU moves N/2 either way)
   // and measured slower than plain peer loads and stores; it pays from four ranks on.
   if (has_mc && cfg.use_nvls && is_float && world >= 4 && bytes >= cfg.nvls_min_bytes) return Algo::NVLS;
@@ -220,9 +224,11 @@ Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType
     a.r[0].out = (char*)out + done * es;
     a.algo = (int)algo;
     a.count = n;
-    // two kernels run side by side: each gets half of the usual grid
+    // Two kernels run side by side. Their copy phases want as many SMs as a full-grid copy, so
+    // each keeps the usual grid up to 128 blocks: 256 together, below the 2 x SMs that can be
+    // resident at once.
     cfg.blocks = choose_blocks(nb, world_, a.algo, false, sm_count_, cfg_.max_blocks);
-    if (two_lanes && cfg.blocks > 64) cfg.blocks = 64;
+    if (two_lanes && cfg.blocks > 128) cfg.blocks = 128;
     CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, lane_stream[lane]));
     last_blocks = cfg.blocks;
     last_launches++;

@@ -20,7 +20,7 @@ namespace bc {
 namespace gpu {
 
 struct CommConfig {
-  size_t staging_bytes = 256u << 20;    // staging area for tensors outside symmetric memory, cut into one slice per user channel
+  size_t staging_bytes = 512u << 20;    // staging area for tensors outside symmetric memory, cut into one slice per user channel
   size_t heap_bytes = 256u << 20;       // general symmetric heap inside segment 0 (allgather outputs, user tensors)
   double device_timeout_s = 30.0;       // bound of every device-side wait
   int force_algo = 0;                   // Algo, 0 = pick from the table

@@ -358,6 +358,7 @@ def test_algorithm_selector_table(native_lib):
     assert sel(8, 4 << 10, in_place=True) == TWO                      # in place / fused: never one-shot
     assert sel(8, 512 << 10) == NVLS and sel(8, (512 << 10) - 4) == TWO and sel(4, 64 << 20, BF16) == NVLS
     assert sel(2, 256 << 20) == TWO                                   # two ranks: the switch saves nothing
+    assert sel(2, 256 << 20, in_place=False) == ONE and sel(4, 256 << 20, in_place=False, mc=False) == TWO   # two ranks, separate output
     assert sel(8, 64 << 20, mc=False) == TWO and sel(8, 64 << 20, use_nvls=0) == TWO
     assert sel(8, 64 << 20, I32) == TWO                               # the switch adds floats only
     assert sel(8, 1 << 20, nvls_min=2 << 20) == TWO and sel(8, 1 << 20, in_place=False, one_max=1 << 20) == ONE
@@ -369,7 +370,7 @@ def test_algorithm_selector_table(native_lib):
     # peer loads: one block per 32 KiB, at most 128 (two ranks: one per SM)
     assert blocks(1, 8, TWO, 0, 148, 0, 0) == 1 and blocks(32 << 10, 8, TWO, 0, 148, 0, 0) == 1 and blocks((32 << 10) + 1, 8, TWO, 0, 148, 0, 0) == 2
     assert blocks(1 << 30, 8, TWO, 0, 148, 0, 0) == 128 and blocks(1 << 30, 4, TWO, 0, 148, 0, 0) == 128 and blocks(1 << 30, 2, TWO, 0, 148, 0, 0) == 148
-    assert blocks(256 << 10, 8, ONE, 0, 148, 0, 0) == 8
+    assert blocks(256 << 10, 8, ONE, 0, 148, 0, 0) == 8 and blocks(64 << 20, 2, ONE, 0, 148, 0, 0) == 148
     # NVLS: one block per 64 KiB, at most 64 up to 16 MiB and 128 above
     assert blocks(1 << 20, 8, NVLS, 0, 148, 0, 0) == 16 and blocks(16 << 20, 8, NVLS, 0, 148, 0, 0) == 64 and blocks(1 << 30, 8, NVLS, 0, 148, 0, 0) == 128
     # a fused update wants every SM twice; beside the backward pass only what a 128-SM kernel leaves free
