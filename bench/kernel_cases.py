@@ -114,7 +114,7 @@ def main():
             rc = lib.bc_fused_step(1, C.c_void_p(grad.data_ptr()), n, 3 if bf16 else 0, C.c_void_p(param.data_ptr()),
                                    C.c_void_p(master.data_ptr()) if bf16 else None, C.c_void_p(s1.data_ptr()),
                                    C.c_void_p(s2.data_ptr()) if bf16 else None, C.byref(h), 1.0, C.c_void_p(ev0.cuda_event),
-                                   C.c_void_p(ev1.cuda_event))
+                                   C.c_void_p(ev1.cuda_event), 0)
             assert rc >= 0, _lib.last_error()
             stream.wait_event(ev1)
 

@@ -70,27 +70,52 @@ __device__ __forceinline__ float sgd_step(float p, float g, float* buf, const Op
   return fmaf(-h.lr, g, p);
 }
 
-__device__ __forceinline__ float adam_step(float p, float g, float* m, float* v, const OptHyper& h) {
-  if (h.weight_decay != 0.f) {
-    if (h.decoupled_wd) p *= (1.f - h.lr * h.weight_decay);
-    else g = fmaf(h.weight_decay, p, g);
+// sqrt.approx / div.approx: about one and two units in the last place. The update is a product
+// of several rounded factors anyway, and the IEEE sequences that the compiler emits for `sqrtf`
+// and `/` cost tens of instructions per element: with them the Adam epilogue was bound by
+// instruction issue (0.81 of the HBM copy rate), not by memory.
+__device__ __forceinline__ float sqrt_fast(float x) {
+  float y;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float div_fast(float a, float b) {
+  float y;
+  asm("div.approx.ftz.f32 %0, %1, %2;" : "=f"(y) : "f"(a), "f"(b));
+  return y;
+}
+
+// What an Adam step needs from the hyper-parameters, computed once per thread.
+struct AdamConst {
+  float step;         // torch form: lr / bc1;  TF form: lr * sqrt(bc2) / bc1
+  float inv_sqrt_bc2; // torch form: 1 / sqrt(bc2);  TF form: 1
+  float decay;        // decoupled weight decay: 1 - lr * wd, else 1
+  float l2;           // coupled weight decay: wd, else 0
+  __device__ explicit AdamConst(const OptHyper& h) {
+    const float s2 = sqrtf(h.bias_c2);
+    step = h.tf_epsilon_hat ? h.lr * s2 / h.bias_c1 : h.lr / h.bias_c1;
+    inv_sqrt_bc2 = h.tf_epsilon_hat ? 1.f : 1.f / s2;
+    decay = (h.weight_decay != 0.f && h.decoupled_wd) ? 1.f - h.lr * h.weight_decay : 1.f;
+    l2 = (h.weight_decay != 0.f && !h.decoupled_wd) ? h.weight_decay : 0.f;
   }
+};
+
+__device__ __forceinline__ float adam_step(float p, float g, float* m, float* v, const OptHyper& h, const AdamConst& k) {
+  p *= k.decay;
+  g = fmaf(k.l2, p, g);
   const float mm = fmaf(h.beta1, *m, (1.f - h.beta1) * g);
   const float vv = fmaf(h.beta2, *v, (1.f - h.beta2) * g * g);
   *m = mm;
   *v = vv;
-  if (h.tf_epsilon_hat) {
-    const float step = h.lr * sqrtf(h.bias_c2) / h.bias_c1;
-    return p - step * mm / (sqrtf(vv) + h.eps);
-  }
-  const float denom = sqrtf(vv) / sqrtf(h.bias_c2) + h.eps;
-  return p - (h.lr / h.bias_c1) * mm / denom;
+  // torch: p -= (lr / bc1) * m / (sqrt(v) / sqrt(bc2) + eps);  TF: p -= lr sqrt(bc2) / bc1 * m / (sqrt(v) + eps)
+  const float denom = fmaf(sqrt_fast(vv), k.inv_sqrt_bc2, h.eps);
+  return fmaf(-k.step, div_fast(mm, denom), p);
 }
 
 template <int OPT>
-__device__ __forceinline__ float opt_step(float p, float g, float* s1, float* s2, const OptHyper& h) {
+__device__ __forceinline__ float opt_step(float p, float g, float* s1, float* s2, const OptHyper& h, const AdamConst& k) {
   if (OPT == OPT_SGD) return sgd_step(p, g, s1, h);
-  return adam_step(p, g, s1, s2, h);
+  return adam_step(p, g, s1, s2, h, k);
 }
 
 // Sum of packs over all ranks' buffers, in rank order (identical on every rank), for the packs
@@ -159,42 +184,33 @@ __device__ __forceinline__ void epilogue_pack(const ArRank& R, const ArArgs& a, 
     st_local16(reinterpret_cast<char*>(R.out) + i * 16, PK::pack(acc));
   } else if constexpr (IsFloatGrad<T>::value) {
     const OptHyper& h = a.opt;
+    const AdamConst k(h);      // loop-invariant: the compiler computes it once per thread
     const size_t e0 = i * E;
     float p[E], s1[E], s2[E];
-    // parameters in fp32: the tensor itself (fp32 model) or the master copy (16-bit model)
+    // parameters in fp32: the tensor itself (fp32 model) or the master copy (16-bit model).
+    // E floats of an fp32 array are one 16-byte access (E = 4) or one 32-byte access (E = 8).
+    auto ld_f32 = [](const float* q, float* o) {
+      if constexpr (E == 8) ld_local32(q, o);
+      else Pack<float>::unpack(ld_local16(q), o);
+    };
+    auto st_f32 = [](float* q, const float* o) {
+      if constexpr (E == 8) st_local32(q, o);
+      else st_local16(q, Pack<float>::pack(o));
+    };
     const float* p32 = sizeof(T) == 4 ? reinterpret_cast<const float*>(R.param) : R.master;
-    if (p32) {
-#pragma unroll
-      for (int k = 0; k < E / 4; k++) Pack<float>::unpack(ld_local16(p32 + e0 + 4 * k), p + 4 * k);
-    } else {
-      PK::unpack(ld_local16(reinterpret_cast<const char*>(R.param) + i * 16), p);
-    }
+    if (p32) ld_f32(p32 + e0, p);
+    else PK::unpack(ld_local16(reinterpret_cast<const char*>(R.param) + i * 16), p);
     const bool has_s1 = (OPT == OPT_ADAM) || (h.momentum != 0.f);
-    if (has_s1 && !(OPT == OPT_SGD && h.first_step)) {
+    if (has_s1 && !(OPT == OPT_SGD && h.first_step)) ld_f32(R.state1 + e0, s1);
+    if (OPT == OPT_ADAM) ld_f32(R.state2 + e0, s2);
 #pragma unroll
-      for (int k = 0; k < E / 4; k++) Pack<float>::unpack(ld_local16(R.state1 + e0 + 4 * k), s1 + 4 * k);
-    }
-    if (OPT == OPT_ADAM) {
-#pragma unroll
-      for (int k = 0; k < E / 4; k++) Pack<float>::unpack(ld_local16(R.state2 + e0 + 4 * k), s2 + 4 * k);
-    }
-#pragma unroll
-    for (int e = 0; e < E; e++) p[e] = opt_step<OPT>(p[e], acc[e], &s1[e], &s2[e], h);
-    if (has_s1) {
-#pragma unroll
-      for (int k = 0; k < E / 4; k++) st_local16(R.state1 + e0 + 4 * k, Pack<float>::pack(s1 + 4 * k));
-    }
-    if (OPT == OPT_ADAM) {
-#pragma unroll
-      for (int k = 0; k < E / 4; k++) st_local16(R.state2 + e0 + 4 * k, Pack<float>::pack(s2 + 4 * k));
-    }
+    for (int e = 0; e < E; e++) p[e] = opt_step<OPT>(p[e], acc[e], &s1[e], &s2[e], h, k);
+    if (has_s1) st_f32(R.state1 + e0, s1);
+    if (OPT == OPT_ADAM) st_f32(R.state2 + e0, s2);
     if (sizeof(T) == 4) {
-      st_local16(reinterpret_cast<float*>(R.param) + e0, Pack<float>::pack(p));
+      st_f32(reinterpret_cast<float*>(R.param) + e0, p);
     } else {
-      if (R.master) {
-#pragma unroll
-        for (int k = 0; k < E / 4; k++) st_local16(R.master + e0 + 4 * k, Pack<float>::pack(p + 4 * k));
-      }
+      if (R.master) st_f32(R.master + e0, p);
       st_local16(reinterpret_cast<char*>(R.param) + i * 16, PK::pack(p));
     }
     if (h.zero_grad) st_local16(R.in[me] + i * 16, make_uint4(0, 0, 0, 0));
@@ -214,7 +230,7 @@ __device__ __forceinline__ void epilogue_scalar(const ArRank& R, const ArArgs& a
     const bool has_s1 = (OPT == OPT_ADAM) || (h.momentum != 0.f);
     if (has_s1 && !(OPT == OPT_SGD && h.first_step)) s1 = R.state1[e];
     if (OPT == OPT_ADAM) s2 = R.state2[e];
-    p = opt_step<OPT>(p, (float)g, &s1, &s2, h);
+    p = opt_step<OPT>(p, (float)g, &s1, &s2, h, AdamConst(h));
     if (has_s1) R.state1[e] = s1;
     if (OPT == OPT_ADAM) R.state2[e] = s2;
     if (sizeof(T) == 4) reinterpret_cast<float*>(R.param)[e] = p;
@@ -475,6 +491,11 @@ cudaError_t launch_allreduce(const ArArgs& a, DType dtype, DType param_dtype, co
   if (cfg.blocks <= 0 || cfg.blocks > kMaxBlocks || cfg.threads < 32 || cfg.threads > 512) return cudaErrorInvalidConfiguration;
   if (a.opt.kind != OPT_NONE) {
     if (!(param_dtype == dtype)) return cudaErrorInvalidValue;
+    if (dtype == DType::BF16 || dtype == DType::F16) {
+      // the fp32 arrays that go with 16-bit gradients are accessed 32 bytes at a time
+      for (int r = 0; r < a.nranks_here; r++)
+        if ((((uintptr_t)a.r[r].master | (uintptr_t)a.r[r].state1 | (uintptr_t)a.r[r].state2) & 31) != 0) return cudaErrorMisalignedAddress;
+    }
     switch (dtype) {
       case DType::F32: return dispatch_fused<float>(a, cfg, s);
       case DType::BF16: return dispatch_fused<__nv_bfloat16>(a, cfg, s);

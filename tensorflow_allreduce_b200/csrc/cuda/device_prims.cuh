@@ -55,6 +55,19 @@ __device__ __forceinline__ void st16(void* p, uint4 v) {
 }
 __device__ __forceinline__ uint4 ld_local16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 __device__ __forceinline__ void st_local16(void* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
+// 32-byte accesses (sm_100: 256-bit global loads and stores) for the fp32 arrays that go with a
+// 16-byte pack of 16-bit gradients: eight floats per thread in ONE instruction. Two 16-byte
+// accesses per thread instead make every warp-wide instruction touch only half of each 32-byte
+// sector (the second instruction then hits L1: measured 54 % L1 hit rate and the load/store
+// queue as a stall reason in the Adam epilogue). `p` must be 32-byte aligned.
+__device__ __forceinline__ void ld_local32(const float* p, float* o) {
+  asm volatile("ld.global.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=f"(o[0]), "=f"(o[1]), "=f"(o[2]), "=f"(o[3]), "=f"(o[4]), "=f"(o[5]), "=f"(o[6]), "=f"(o[7]) : "l"(p));
+}
+__device__ __forceinline__ void st_local32(float* p, const float* o) {
+  asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "f"(o[0]), "f"(o[1]), "f"(o[2]), "f"(o[3]),
+               "f"(o[4]), "f"(o[5]), "f"(o[6]), "f"(o[7]) : "memory");
+}
 
 // NVLS: the switch sums the 16 bytes at this multicast address over all bound GPUs.
 __device__ __forceinline__ uint4 multimem_ld_reduce_f32(const void* mc) {
