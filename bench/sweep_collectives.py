@@ -11,7 +11,9 @@ Arms:
   ours_direct in-place allreduce on a tensor in symmetric memory, ordered launch without negotiation
               (zero-copy; the path gradient buckets take)
   ours_symm   the same through the name-keyed negotiated API (adds the coordinator round trip)
-  ours_staged allreduce of an ordinary tensor (copied through the staging area)
+  ours_staged allreduce of an ordinary tensor through the name-keyed API (negotiation + staging area)
+  ours_private the same ordinary tensor with an ordered launch (`allreduce_direct_`): staging without negotiation,
+              which is what NCCL's ordered `all_reduce` is comparable with
   nccl        torch.distributed.all_reduce / all_gather on the same sizes
   (--fake-hosts H: the ranks report H host names, so ours_staged runs in two levels: NVLink kernels
    inside a "host", pinned memory and socket rings between them)
@@ -134,7 +136,7 @@ def markdown(rows, world, link_measured=764.0, link_nominal=900.0):
             sel = [r for r in rows if r["op"] == op and r["dtype"] == dname]
             if not sel:
                 continue
-            arms = [k[:-6] for k in ("ours_direct_busbw", "ours_symm_busbw", "ours_staged_busbw", "ours_busbw", "nccl_busbw",
+            arms = [k[:-6] for k in ("ours_direct_busbw", "ours_symm_busbw", "ours_staged_busbw", "ours_private_busbw", "ours_busbw", "nccl_busbw",
                                       "nccl_padded_busbw", "ref_ring_busbw") if any(k in r for r in sel)]
             out.append(f"\n### {op}, {world} GPUs, {dname}\n")
             head = ["bytes"] + [f"{a_} ms" for a_ in arms if a_.startswith("ours")] + [f"{a_} GB/s" for a_ in arms]
@@ -149,7 +151,7 @@ def markdown(rows, world, link_measured=764.0, link_nominal=900.0):
                 cells += [f'{r[a_ + "_busbw"]:.1f}' if a_ + "_busbw" in r else "-" for a_ in arms]
                 best = max([r[a_ + "_busbw"] for a_ in arms if a_.startswith("ours") and a_ + "_busbw" in r] or [0.0])
                 cells += [f"{best / link_measured:.2f}", f"{best / link_nominal:.2f}"]
-                flags = [k.split("_")[0] + ("=ok" if r[k] else "=WRONG") for k in ("direct_correct", "symm_correct", "staged_correct", "correct") if k in r]
+                flags = [k.split("_")[0] + ("=ok" if r[k] else "=WRONG") for k in ("direct_correct", "symm_correct", "staged_correct", "private_correct", "correct") if k in r]
                 cells.append(" ".join(flags) or "-")
                 if any("direct_phases_us" in x for x in sel):
                     cells.append(" / ".join(f"{v:.1f}" for v in r["direct_phases_us"]) if "direct_phases_us" in r else "-")
@@ -165,7 +167,7 @@ def main():
     ap.add_argument("--max-mb", type=int, default=1024)
     ap.add_argument("--min-kb", type=int, default=1)
     ap.add_argument("--out", default="")
-    ap.add_argument("--arms", default="ours_direct,ours_symm,ours_staged,nccl,ref_ring")
+    ap.add_argument("--arms", default="ours_direct,ours_symm,ours_staged,ours_private,nccl,ref_ring")
     ap.add_argument("--dtypes", default="fp32,bf16")
     ap.add_argument("--no-allgather", action="store_true")
     ap.add_argument("--no-allreduce", action="store_true")
@@ -184,7 +186,7 @@ def main():
             raise SystemExit("--fake-hosts must divide the number of ranks")
         os.environ["BC_HOSTNAME"] = f"host{rank // (world // a.fake_hosts)}"
         # tensors in symmetric memory and ordered launches need all ranks on one host
-        arms = [x for x in arms if x in ("ours_staged", "nccl", "ref_ring")]
+        arms = [x for x in arms if x in ("ours_staged", "nccl", "ref_ring")]   # ours_private is an ordered launch as well
     torch.cuda.set_device(local)
     cfg = bc.Config.from_env(heap_mb=max(6 * a.max_mb + 64, 256), staging_mb=a.staging_mb or None)
     bc.init(device=local, config=cfg)
@@ -257,6 +259,21 @@ def main():
                 ms = timed(f2, iters)
                 row["ours_staged_ms"] = ms
                 row["ours_staged_busbw"] = nbytes / (ms * 1e-3) * factor / 1e9
+            if "ours_private" in arms:
+                from tensorflow_allreduce_b200.ops.direct import allreduce_direct_
+                y = x.clone()
+                allreduce_direct_(y)
+                ref = x.clone()
+                if use_nccl:
+                    dist.all_reduce(ref)
+                    tol = 1e-5 * P if dtype == torch.float32 else 1e-2 * P
+                    row["private_correct"] = bool(torch.allclose(y.float(), ref.float(), rtol=tol, atol=tol))
+                y.zero_()
+                del ref
+                ms = timed(lambda: allreduce_direct_(y), iters)
+                row["ours_private_ms"] = ms
+                row["ours_private_busbw"] = nbytes / (ms * 1e-3) * factor / 1e9
+                del y
             if "nccl" in arms and use_nccl:
                 y = x.clone()
                 ms = timed(lambda: dist.all_reduce(y), iters)

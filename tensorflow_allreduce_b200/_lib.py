@@ -104,6 +104,8 @@ def _declare(lib):
         "bc_gru_workspace_bytes": (ll, [i, i, i, i]),
         "bc_gru_forward": (i, [i, i, i, i, vp, vp, vp, vp, vp, vp, vp, vp, d, vp]),
         "bc_gru_backward": (i, [i, i, i, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, d, vp]),
+        "bc_bn_clip_forward": (i, [vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, f, f, f, vp]),
+        "bc_bn_clip_backward": (i, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, f, vp]),
         "bc_test_validate": (i, [i, P(i), P(i), P(i), P(i), P(ll), cp, i, P(ll)]),
     }
     for name, (res, args) in sig.items():

@@ -39,7 +39,7 @@ class Config:
 
     timeout_s: float = 300.0           # host-side deadline: bootstrap, negotiation, ring steps
     device_timeout_s: float = 30.0     # bound of every device-side wait on a peer
-    staging_mb: int = 512              # symmetric staging area for tensors outside symmetric memory (a quarter per channel)
+    staging_mb: int = 1024             # symmetric staging area for tensors outside symmetric memory (a quarter per channel)
     heap_mb: int = 256                 # symmetric heap for allgather outputs and `symm_empty`
     algo: str = "auto"                 # force one of: one_shot, two_shot, nvls
     one_shot_max_kb: int = 256         # messages up to this size use the one-shot kernel

@@ -147,6 +147,16 @@ int bc_gru_forward(int T, int B, int H, int ndir, const float* w_hh, const float
 int bc_gru_backward(int T, int B, int H, int ndir, const float* w_hh_t, const float* y, const float* rsv, const float* dy,
                     float* dgx, float* dgh, float* workspace, unsigned* sync, unsigned* status, double timeout_s, void* stream);
 
+/* Training-mode batch normalisation of [N, C, HW] fp32 activations fused with the clipped ReLU behind it
+ * (y = clamp(bn(x), 0, clip_hi)); csrc/cuda/bn_clip.h. `acc` = scratch of 2 * C doubles; running_* may be NULL.
+ * These need no initialised group. */
+int bc_bn_clip_forward(const float* x, float* y, const float* gamma, const float* beta, float* running_mean, float* running_var,
+                       float* save_mean, float* save_rstd, double* acc, int N, int C, int HW, float eps, float momentum, float clip_hi,
+                       void* stream);
+int bc_bn_clip_backward(const float* x, const float* dy, const float* gamma, const float* beta, const float* save_mean,
+                        const float* save_rstd, float* dx, float* dgamma, float* dbeta, double* acc, int N, int C, int HW,
+                        float clip_hi, void* stream);
+
 /* Coordinator validation run on synthetic requests (unit tests). Returns the response type. */
 int bc_test_validate(int nranks, const int* ops, const int* dtypes, const int* devices, const int* ndims,
                      const long long* shapes, char* err_out, int err_cap, long long* dim0_out);

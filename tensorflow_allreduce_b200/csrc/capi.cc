@@ -13,6 +13,7 @@
 #include <mutex>
 
 #include "cuda/comm.h"
+#include "cuda/bn_clip.h"
 #include "cuda/gru_persistent.h"
 #include "runtime/runtime.h"
 #include "runtime/two_level.h"
@@ -504,6 +505,28 @@ int bc_gru_backward(int T, int B, int H, int ndir, const float* w_hh_t, const fl
   gpu::GruDims d{T, B, H, ndir};
   check_cuda(gpu::gru_persistent_backward(d, w_hh_t, y, rsv, dy, dgx, dgh, workspace, sync, status, timeout_s, (cudaStream_t)stream),
              "persistent GRU backward launch");
+  return 0;
+  API_END(-1)
+}
+
+// ---- batch normalisation fused with the clipped ReLU ---------------------------------------------
+
+int bc_bn_clip_forward(const float* x, float* y, const float* gamma, const float* beta, float* running_mean, float* running_var,
+                       float* save_mean, float* save_rstd, double* acc, int N, int C, int HW, float eps, float momentum, float clip_hi,
+                       void* stream) {
+  API_BEGIN
+  check_cuda(gpu::bn_clip_forward(x, y, gamma, beta, running_mean, running_var, save_mean, save_rstd, acc, N, C, HW, eps, momentum,
+                                  clip_hi, (cudaStream_t)stream), "batch-norm + clip forward launch");
+  return 0;
+  API_END(-1)
+}
+
+int bc_bn_clip_backward(const float* x, const float* dy, const float* gamma, const float* beta, const float* save_mean,
+                        const float* save_rstd, float* dx, float* dgamma, float* dbeta, double* acc, int N, int C, int HW,
+                        float clip_hi, void* stream) {
+  API_BEGIN
+  check_cuda(gpu::bn_clip_backward(x, dy, gamma, beta, save_mean, save_rstd, dx, dgamma, dbeta, acc, N, C, HW, clip_hi,
+                                   (cudaStream_t)stream), "batch-norm + clip backward launch");
   return 0;
   API_END(-1)
 }

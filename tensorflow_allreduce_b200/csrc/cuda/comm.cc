@@ -29,16 +29,25 @@ Comm::Comm(int rank, int world, int device, uint64_t job_id, const CommConfig& c
   CUDA_RT(cudaDeviceGetAttribute(&sm_count_, cudaDevAttrMultiProcessorCount, device));
   int lo = 0, hi = 0;
   CUDA_RT(cudaDeviceGetStreamPriorityRange(&lo, &hi));
-  for (int c = 0; c < kChannels; c++) CUDA_RT(cudaStreamCreateWithPriority(&streams_[c], cudaStreamNonBlocking, hi));
+  // Streams that carry collective kernels (the channels and their second lanes) get the highest
+  // priority, the streams of the local staging copies the lowest: where a reduction and a copy
+  // become runnable together, the reduction's blocks are placed first and the copy fills what
+  // is left.
+  for (int c = 0; c < kChannels; c++)
+    CUDA_RT(cudaStreamCreateWithPriority(&streams_[c], cudaStreamNonBlocking, c < 2 * kUserChannels ? hi : lo));
   for (int c = 0; c < kUserChannels; c++) {
     CUDA_RT(cudaEventCreateWithFlags(&fork_[c], cudaEventDisableTiming));
-    CUDA_RT(cudaEventCreateWithFlags(&join_[c], cudaEventDisableTiming));
+    for (int h = 0; h < 2; h++) CUDA_RT(cudaEventCreateWithFlags(&join_[c][h], cudaEventDisableTiming));
+    for (int h = 0; h < kStageBuffers; h++) {
+      CUDA_RT(cudaEventCreateWithFlags(&in_done_[c][h], cudaEventDisableTiming));
+      CUDA_RT(cudaEventCreateWithFlags(&red_done_[c][h], cudaEventDisableTiming));
+    }
   }
   alloc_.reset(new SymmAllocator(rank, world, device, job_id, cfg.symm_mode, cfg.use_nvls, host_timeout_s));
   pad_off_ = 0;
   staging_off_ = align_up(kPadBytes, 1u << 20);
-  // one slice per user channel, each cut into two halves for the two lanes: keep all of them on 1 MiB boundaries
-  cfg_.staging_bytes = align_up(std::max<size_t>(cfg_.staging_bytes, 8u << 20), (size_t)kUserChannels * (2u << 20));
+  // one slice per user channel, each cut into kStageBuffers parts: keep all of them on 512 KiB boundaries
+  cfg_.staging_bytes = align_up(std::max<size_t>(cfg_.staging_bytes, 8u << 20), (size_t)kUserChannels * kStageBuffers * (512u << 10));
   heap_off_ = staging_off_ + cfg_.staging_bytes;
   cfg_.heap_bytes = align_up(cfg_.heap_bytes, 1u << 20);
   seg0_ = alloc_->alloc(heap_off_ + cfg_.heap_bytes, ag);
@@ -61,7 +70,12 @@ Comm::~Comm() {
     if (streams_[c]) cudaStreamDestroy(streams_[c]);
   for (int c = 0; c < kUserChannels; c++) {
     if (fork_[c]) cudaEventDestroy(fork_[c]);
-    if (join_[c]) cudaEventDestroy(join_[c]);
+    for (int h = 0; h < 2; h++)
+      if (join_[c][h]) cudaEventDestroy(join_[c][h]);
+    for (int h = 0; h < kStageBuffers; h++) {
+      if (in_done_[c][h]) cudaEventDestroy(in_done_[c][h]);
+      if (red_done_[c][h]) cudaEventDestroy(red_done_[c][h]);
+    }
   }
 }
 
@@ -195,49 +209,98 @@ Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType
     return Algo::ONE_SHOT;
   }
 
-  // Staged: the kernel copies a chunk of the input into this channel's slice of the staging area
-  // (ArRank::src), reduces there and writes the result to `out`. A tensor of more than half a
-  // slice goes in chunks of half a slice that alternate between the channel's two lanes (two
-  // streams, two signal pads, two halves of the slice): the kernel of chunk k + 1 copies in and
-  // out through HBM while the kernel of chunk k is in its NVLink phase. A half is reused by the
-  // chunk after next on the same stream, i.e. after the kernel that used it has ended, and a
-  // kernel ends only after all peers have finished reading its half (second barrier).
-  const size_t half = staging_slice_bytes() / 2;
-  const size_t chunk_elems = (half / 16) * (16 / es);
-  const bool two_lanes = count > chunk_elems;
-  cudaStream_t lane_stream[2] = {s, streams_[channel + kUserChannels]};
-  if (two_lanes) {
-    CUDA_RT(cudaEventRecord(fork_[channel], s));
-    CUDA_RT(cudaStreamWaitEvent(lane_stream[1], fork_[channel], 0));
-  }
-  Algo used = Algo::TWO_SHOT;
-  int k = 0;
-  for (size_t done = 0; done < count; done += chunk_elems, k++) {
-    const int lane = two_lanes ? (k & 1) : 0;
-    const int lane_channel = channel + lane * kUserChannels;
-    const size_t n = std::min(chunk_elems, count - done);
-    const size_t nb = n * es;
-    const size_t off = staging_offset(channel) + (size_t)lane * half;
-    Algo algo = pick(nb, false, seg0_->mc != nullptr);
-    fill_ar_rank(&a.r[0], lane_channel, seg0_, off);
-    a.r[0].src = (const char*)in + done * es;
-    a.r[0].out = (char*)out + done * es;
+  // Staged. A tensor of at most one part (a quarter) of the channel's slice: ONE kernel copies
+  // the input into the staging area (ArRank::src), reduces there and writes the result to `out`.
+  const size_t part = staging_slice_bytes() / kStageBuffers;
+  const size_t part_elems = (part / 16) * (16 / es);
+  if (count <= part_elems) {
+    Algo algo = pick(bytes, false, seg0_->mc != nullptr);
+    fill_ar_rank(&a.r[0], channel, seg0_, staging_offset(channel));
+    a.r[0].src = (const char*)in;
+    a.r[0].out = out;
     a.algo = (int)algo;
-    a.count = n;
-    // Two kernels run side by side. Their copy phases want as many SMs as a full-grid copy, so
-    // each keeps the usual grid up to 128 blocks: 256 together, below the 2 x SMs that can be
-    // resident at once.
+    a.count = count;
+    cfg.blocks = choose_blocks(bytes, world_, a.algo, false, sm_count_, cfg_.max_blocks);
+    // The copy phases of this kernel want many blocks, its NVLS phase few: 64 is the compromise
+    // (64 MiB on 4 GPUs: 445 GB/s with 64 blocks, 290 with 16, 456 with 128).
+    if (algo == Algo::NVLS && cfg_.max_blocks <= 0) cfg.blocks = choose_blocks(bytes, world_, (int)Algo::TWO_SHOT, false, sm_count_, 64);
+    CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, s));
+    last_blocks = cfg.blocks;
+    last_launches = 1;
+    return algo;
+  }
+  // Chunks of the pipeline below: equal shares of at most one part, in multiples of 256 bytes.
+  const size_t nchunks = (count + part_elems - 1) / part_elems;
+  const size_t chunk_elems = align_up((count + nchunks - 1) / nchunks, 256 / es);
+  // A larger tensor goes in chunks of one part through a pipeline on three streams: the
+  // reductions (NVLink-bound) alternate between the channel's stream and its second lane, so
+  // that two are in flight and the fixed costs of one (barriers, ramp-up, drain: about 35 us)
+  // hide behind the data phase of the other; the copies in and out (local, HBM-bound) run on a
+  // third stream of low priority beside them. (Each chunk costs the host about ten CUDA calls,
+  // so chunks far below the size of a part would make the pipeline launch-bound: 8 MiB chunks
+  // measured slower than the single fused kernel.) Chunk k lives in part k % 4 of the slice. The NVLS
+  // reductions run on 16 blocks each (choose_blocks), which also leaves the SMs to the copies:
+  // with 64 blocks per lane 1 GiB took 2.80 ms on 4 GPUs, with 16 it takes 2.41 (in place: 2.37).
+  //   copies : in(0) in(1) in(2) out(0) in(3) out(1) in(4) out(2) ...    (out(k) waits for red(k))
+  //   lane 0 :   red(0)      red(2)      red(4) ...                      (red(k) waits for in(k))
+  //   lane 1 :      red(1)      red(3)      red(5) ...
+  // in(k + 4) follows out(k) in stream order, and a reduction ends only after all peers have
+  // finished reading this rank's part (last barrier), so a part is never overwritten early.
+  // Measured on 4 GPUs, 1 GiB: one fused kernel per chunk on two lanes 3.16 ms (the lanes fall
+  // into step: both copy, then both reduce), copies on a stream of their own beside ONE lane of
+  // reductions 3.31 ms (the copies hide, but 64 MiB launches run at 544 GB/s where 512 MiB ones
+  // reach 673), in place on symmetric memory 2.39 ms.
+  // Two ranks reduce one-shot straight into `out`, which needs no copy-out; all others reduce in
+  // place on their part of the staging area.
+  cudaStream_t lane[2] = {s, streams_[channel + kUserChannels]};
+  cudaStream_t cpy = streams_[channel + 2 * kUserChannels];
+  const Algo first_algo = pick(std::min(chunk_elems, count) * es, false, seg0_->mc != nullptr);
+  const bool to_out = first_algo == Algo::ONE_SHOT;
+  CUDA_RT(cudaEventRecord(fork_[channel], s));
+  CUDA_RT(cudaStreamWaitEvent(lane[1], fork_[channel], 0));
+  CUDA_RT(cudaStreamWaitEvent(cpy, fork_[channel], 0));
+  Algo used = Algo::TWO_SHOT;
+  struct Chunk { size_t done, n; };
+  std::vector<Chunk> chunks;
+  for (size_t done = 0; done < count; done += chunk_elems) chunks.push_back({done, std::min(chunk_elems, count - done)});
+  auto part_of = [&](size_t k) { return seg0_->local + staging_offset(channel) + (k % kStageBuffers) * part; };
+  auto copy_out = [&](size_t k) {
+    const Chunk& c = chunks[k];
+    CUDA_RT(cudaStreamWaitEvent(cpy, red_done_[channel][k % kStageBuffers], 0));
+    if (!to_out) CUDA_RT(launch_copy((char*)out + c.done * es, part_of(k), c.n * es, cpy));
+  };
+  for (size_t k = 0; k < chunks.size(); k++) {
+    const Chunk& c = chunks[k];
+    const int b = (int)(k % kStageBuffers), l = (int)(k & 1);
+    const size_t nb = c.n * es;
+    // one-shot has no copy-out to order in(k) behind: the part is free once red(k - 4) has ended
+    if (to_out && k >= (size_t)kStageBuffers) CUDA_RT(cudaStreamWaitEvent(cpy, red_done_[channel][b], 0));
+    CUDA_RT(launch_copy(part_of(k), (const char*)in + c.done * es, nb, cpy));
+    CUDA_RT(cudaEventRecord(in_done_[channel][b], cpy));
+    if (k >= 2 && !to_out) copy_out(k - 2);
+    CUDA_RT(cudaStreamWaitEvent(lane[l], in_done_[channel][b], 0));
+    Algo algo = to_out ? Algo::ONE_SHOT : pick(nb, true, seg0_->mc != nullptr);
+    fill_ar_rank(&a.r[0], channel + l * kUserChannels, seg0_, (size_t)(part_of(k) - seg0_->local));
+    a.r[0].out = to_out ? (void*)((char*)out + c.done * es) : (void*)part_of(k);
+    a.algo = (int)algo;
+    a.count = c.n;
     cfg.blocks = choose_blocks(nb, world_, a.algo, false, sm_count_, cfg_.max_blocks);
-    if (two_lanes && cfg.blocks > 128) cfg.blocks = 128;
-    CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, lane_stream[lane]));
+    // two reductions side by side: kernels whose blocks do the loads and stores themselves share the SMs
+    if (a.algo != (int)Algo::NVLS && cfg.blocks > 74 && cfg_.max_blocks <= 0) cfg.blocks = 74;
+    CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, lane[l]));
+    CUDA_RT(cudaEventRecord(red_done_[channel][b], lane[l]));
     last_blocks = cfg.blocks;
     last_launches++;
-    used = algo;
+    if (k == 0) used = algo;
   }
-  if (two_lanes) {
-    CUDA_RT(cudaEventRecord(join_[channel], lane_stream[1]));
-    CUDA_RT(cudaStreamWaitEvent(s, join_[channel], 0));
+  if (!to_out) {
+    if (chunks.size() >= 2) copy_out(chunks.size() - 2);
+    copy_out(chunks.size() - 1);
   }
+  CUDA_RT(cudaEventRecord(join_[channel][0], cpy));
+  CUDA_RT(cudaEventRecord(join_[channel][1], lane[1]));
+  CUDA_RT(cudaStreamWaitEvent(s, join_[channel][0], 0));
+  CUDA_RT(cudaStreamWaitEvent(s, join_[channel][1], 0));
   return used;
 }
 

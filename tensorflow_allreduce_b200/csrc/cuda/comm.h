@@ -20,7 +20,7 @@ namespace bc {
 namespace gpu {
 
 struct CommConfig {
-  size_t staging_bytes = 512u << 20;    // staging area for tensors outside symmetric memory, cut into one slice per user channel
+  size_t staging_bytes = 1024u << 20;   // staging area for tensors outside symmetric memory, cut into one slice per user channel
   size_t heap_bytes = 256u << 20;       // general symmetric heap inside segment 0 (allgather outputs, user tensors)
   double device_timeout_s = 30.0;       // bound of every device-side wait
   int force_algo = 0;                   // Algo, 0 = pick from the table
@@ -119,8 +119,12 @@ class Comm {
   uint32_t* status_host_ = nullptr;   // pinned, mapped
   uint32_t* status_dev_ = nullptr;
   cudaStream_t streams_[dev::kChannels] = {nullptr};
-  cudaEvent_t fork_[dev::kUserChannels] = {nullptr};   // lane 1 of a channel starts behind its lane 0 ...
-  cudaEvent_t join_[dev::kUserChannels] = {nullptr};   // ... and lane 0 continues behind lane 1
+  // Events of the pipeline that carries a large staged tensor (Comm::allreduce).
+  static constexpr int kStageBuffers = 4;                      // parts of a channel's staging slice in rotation
+  cudaEvent_t fork_[dev::kUserChannels] = {nullptr};           // the helper streams start behind the channel's stream ...
+  cudaEvent_t join_[dev::kUserChannels][2] = {{nullptr}};      // ... and the channel's stream continues behind them
+  cudaEvent_t in_done_[dev::kUserChannels][kStageBuffers] = {{nullptr}};    // chunk copied into part b of the slice
+  cudaEvent_t red_done_[dev::kUserChannels][kStageBuffers] = {{nullptr}};   // chunk in part b reduced
   unsigned long long* prof_ = nullptr;
   int sm_count_ = 148;
 };

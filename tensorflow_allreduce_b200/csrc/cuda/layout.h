@@ -12,16 +12,17 @@ constexpr int kMaxRanks = 8;
 constexpr int kMaxBlocks = 512;     // barrier slots per channel
 constexpr int kMetaBlocks = 64;     // blocks that may exchange per-call metadata (allgatherv)
 constexpr int kUserChannels = 4;   // channels a caller can name: each has a stream, a signal pad and a staging slice
-// Every user channel c has a second lane, channel c + kUserChannels, with a stream and a pad of
-// its own: a large staged allreduce alternates its chunks between the two lanes, so that the
-// local copies of one chunk run beside the NVLink phase of the next.
-constexpr int kChannels = 2 * kUserChannels;
+// A large staged allreduce of user channel c uses two more streams: c + kUserChannels, a second
+// lane (stream and pad) on which every other chunk is reduced, so that the fixed costs of one
+// reduction kernel (barriers, ramp-up, drain) hide behind the data phase of the other; and
+// c + 2 * kUserChannels, on which the local copies into and out of the staging area run.
+constexpr int kChannels = 3 * kUserChannels;
 
 // Layout of one channel inside a rank's signal pad (all offsets in bytes).
 constexpr size_t kFlagBytes = (size_t)kMaxBlocks * kMaxRanks * sizeof(uint32_t);          // 16 KiB
 constexpr size_t kMetaBytes = (size_t)kMetaBlocks * kMaxRanks * 2 * sizeof(uint64_t);     // 16 KiB
 constexpr size_t kChannelBytes = kFlagBytes + kMetaBytes;
-constexpr size_t kPadBytes = kChannels * kChannelBytes;                                  // 256 KiB
+constexpr size_t kPadBytes = kChannels * kChannelBytes;                                  // 384 KiB
 
 // Status word written by a block whose wait ran out (host-mapped memory).
 constexpr uint32_t kStatusTimeout = 0x80000000u;

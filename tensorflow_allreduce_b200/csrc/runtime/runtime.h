@@ -75,7 +75,7 @@ struct RuntimeOptions {
   int device = -1;                // CUDA device ordinal, -1 = CPU only
   double timeout_s = 300.0;       // host-side deadline for negotiation and ring steps
   double device_timeout_s = 30.0;
-  size_t staging_bytes = 512u << 20;
+  size_t staging_bytes = 1024u << 20;
   size_t heap_bytes = 256u << 20;
   int force_algo = 0;
   size_t one_shot_max_bytes = 256u << 10;

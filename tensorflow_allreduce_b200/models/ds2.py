@@ -4,8 +4,9 @@ Two 2-D convolutions over (frequency, time) with batch norm and clipped ReLU, a 
 bidirectional GRU layers, a linear layer to the character classes and CTC loss. The reference
 ships no such model; its pieces there are Conv2D/cuDNN, FusedBatchNorm, Relu6-style clipping,
 GRU cells (tensorflow/contrib/rnn/kernels/gru_ops.h:69-119) or CudnnRNN, and a CPU-only CTC loss
-(tensorflow/core/kernels/ctc_loss_op.cc:167). Here the convolutions, batch norms, the output layer
-and the loss are plain torch.nn modules on cuDNN/cuBLAS; the GRU stack keeps its `nn.GRU` module
+(tensorflow/core/kernels/ctc_loss_op.cc:167). Here the convolutions, the output layer and the loss
+are plain torch.nn modules on cuDNN/cuBLAS; batch norm and the clipped ReLU behind it are one
+module on the library's two-pass kernels (`ops/bn_clip.py`); the GRU stack keeps its `nn.GRU` module
 and parameters but, on a GPU that supports them, is evaluated by the library's persistent
 tcgen05 kernels (`ops/persistent_gru.py`); the gradient reduction and update around the model are
 the library's fused collectives.
@@ -29,6 +30,7 @@ class DS2Config:
     n_classes: int = 29          # blank + 28 characters
     label_len: int = 100
     persistent_rnn: bool = True  # run the GRU stack on the library's persistent tcgen05 kernels when they support the shape
+    fused_norm: bool = True      # batch norm + clipped ReLU as one module on the library's two-pass kernels (ops/bn_clip.py)
 
 
 class DeepSpeech2(nn.Module):
@@ -36,13 +38,20 @@ class DeepSpeech2(nn.Module):
         super().__init__()
         self.cfg = cfg
         c = cfg.conv_channels
+
+        def norm_act():
+            # Two modules either way, so that the parameter names (conv.1.*, conv.4.*) do not depend on the choice.
+            if cfg.fused_norm:
+                from ..ops.bn_clip import BatchNormClip2d
+
+                return [BatchNormClip2d(c, clip=20.0), nn.Identity()]
+            return [nn.BatchNorm2d(c), nn.Hardtanh(0.0, 20.0, inplace=True)]
+
         self.conv = nn.Sequential(
             nn.Conv2d(1, c, kernel_size=(41, 11), stride=(2, 2), padding=(20, 5), bias=False),
-            nn.BatchNorm2d(c),
-            nn.Hardtanh(0.0, 20.0, inplace=True),
+            *norm_act(),
             nn.Conv2d(c, c, kernel_size=(21, 11), stride=(2, 1), padding=(10, 5), bias=False),
-            nn.BatchNorm2d(c),
-            nn.Hardtanh(0.0, 20.0, inplace=True),
+            *norm_act(),
         )
         f = (cfg.n_freq + 2 * 20 - 41) // 2 + 1
         f = (f + 2 * 10 - 21) // 2 + 1

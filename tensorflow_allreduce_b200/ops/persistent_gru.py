@@ -39,9 +39,10 @@ _work: Dict[int, torch.Tensor] = {}
 
 
 def _workspace(device: torch.device, T: int, B: int, H: int, nd: int) -> torch.Tensor:
-    """Scratch for the flagged partial sums that the blocks of a group exchange. It starts zeroed
-    (no launch uses flag 0) and is reused by every launch; kernels on one stream use it one after
-    the other, so one buffer per device is enough."""
+    """Scratch through which the blocks of a group exchange their partial sums (coalesced 16-byte
+    tiles; a release and a per-step counter in `sync` tell the readers when a tile is complete, so
+    the contents need no initial value). It is reused by every launch; kernels on one stream use
+    it one after the other, so one buffer per device is enough."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
     need = int(_lib.lib().bc_gru_workspace_bytes(T, B, H, nd))
     t = _work.get(idx)
