@@ -6,6 +6,7 @@
     python bench/kernel_cases.py --case emu_one_shot --kb 256   (8 emulated ranks, one-shot, small message)
     python bench/kernel_cases.py --case emu_allgatherv
     python bench/kernel_cases.py --case gru [--T 350]    (one bidirectional GRU layer 2048 -> 1024, batch 32: persistent kernels vs cuDNN)
+    python bench/kernel_cases.py --case bn_clip          (batch norm + clipped ReLU on [32, 32, 81, 350], the speech model's first block: fused kernels vs torch)
 
 Each case prints one JSON line with the CUDA-event time per launch, the algorithmic bytes moved and
 the resulting GB/s next to the measured copy bandwidth (`MEASURED_PEAKS.json` when present).
@@ -47,7 +48,7 @@ def timed(fn, iters):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", required=True, choices=["fused_sgd", "fused_adamw_bf16", "emu_allreduce", "emu_one_shot", "emu_allgatherv", "gru"])
+    ap.add_argument("--case", required=True, choices=["fused_sgd", "fused_adamw_bf16", "emu_allreduce", "emu_one_shot", "emu_allgatherv", "gru", "bn_clip"])
     ap.add_argument("--mb", type=int, default=256, help="gradient / message size in MiB")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--blocks", type=int, default=0)
@@ -58,6 +59,41 @@ def main():
     hbm, src = peak_hbm()
     out = {"case": a.case, "mb": a.mb}
 
+    if a.case == "bn_clip":
+        import torch.nn.functional as F
+
+        from tensorflow_allreduce_b200.ops.bn_clip import bn_clip
+
+        n, c, h, w = 32, 32, 81, 350
+        torch.manual_seed(0)
+        x = torch.randn(n, c, h, w, device="cuda").requires_grad_(True)
+        wt = (torch.rand(c, device="cuda") + 0.5).requires_grad_(True)
+        b = torch.randn(c, device="cuda").requires_grad_(True)
+        rm, rv = torch.zeros(c, device="cuda"), torch.ones(c, device="cuda")
+        dy = torch.randn(n, c, h, w, device="cuda")
+        res = {}
+        for name, fn in (("fused", lambda: bn_clip(x, wt, b, rm, rv, 1e-5, 0.1, 20.0)),
+                         ("torch", lambda: F.hardtanh(F.batch_norm(x, rm, rv, wt, b, True, 0.1, 1e-5), 0.0, 20.0))):
+            f, bw = [], []
+            for it in range(a.iters + 3):
+                x.grad = wt.grad = b.grad = None
+                e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+                torch.cuda.synchronize()
+                e0.record(); y = fn(); e1.record(); y.backward(dy); e2.record()
+                torch.cuda.synchronize()
+                if it >= 3:
+                    f.append(e0.elapsed_time(e1)); bw.append(e1.elapsed_time(e2))
+            res[name] = {"fwd_ms": sum(f) / len(f), "bwd_ms": sum(bw) / len(bw)}
+        nbytes = x.numel() * 4
+        # forward: x read twice, y written; backward: x and dy read twice, dx written
+        out.update(shape=[n, c, h, w], tensor_mb=round(nbytes / 2 ** 20, 1),
+                   **{k + "_" + kk: round(vv, 4) for k, v in res.items() for kk, vv in v.items()},
+                   fused_fwd_gbs=3 * nbytes / res["fused"]["fwd_ms"] / 1e6, fused_bwd_gbs=5 * nbytes / res["fused"]["bwd_ms"] / 1e6)
+        out["hbm_peak_gbs"] = hbm
+        out["fwd_frac_of_hbm_copy_" + src] = out["fused_fwd_gbs"] / hbm
+        out["bwd_frac_of_hbm_copy_" + src] = out["fused_bwd_gbs"] / hbm
+        print(json.dumps(out))
+        return
     if a.case == "gru":
         from tensorflow_allreduce_b200.ops import persistent_gru as pg
 

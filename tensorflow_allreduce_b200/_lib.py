@@ -94,8 +94,8 @@ def _declare(lib):
         "bc_emu_status": (C.c_uint, [vp]),
         "bc_emu_clear_status": (i, [vp]),
         "bc_emu_damaged_guard_bytes": (ll, [vp]),
-        "bc_emu_allreduce": (i, [vp, ll, P(vp), ll, i, i, f, i, i, vp, i, P(vp), P(C.c_ulonglong), vp]),
-        "bc_emu_fused_step": (i, [vp, ll, ll, i, P(vp), P(vp), P(vp), P(vp), P(OptHyper), f, i, vp]),
+        "bc_emu_allreduce": (i, [vp, ll, P(vp), ll, i, i, f, i, i, vp, i, P(vp), P(C.c_ulonglong), vp, i]),
+        "bc_emu_fused_step": (i, [vp, ll, ll, i, P(vp), P(vp), P(vp), P(vp), P(OptHyper), f, i, vp, i]),
         "bc_emu_allgatherv": (i, [vp, P(vp), P(C.c_ulonglong), P(C.c_ulonglong), i, vp]),
         "bc_emu_barrier_probe": (i, [vp, i, d, vp]),
         "bc_max_emulated_blocks": (i, [i, i]),

@@ -126,9 +126,13 @@ long long bc_emu_damaged_guard_bytes(void* g);
  * path). `places` (or NULL): per rank the offset it claims to reduce in place; ranks that disagree set status
  * bit 0x20000000. `prof` (or NULL): device array of 5 uint64 time stamps, see bc_set_allreduce_profile(). */
 int bc_emu_allreduce(void* g, long long off, void* const* outs, long long count, int dtype, int algo, float scale, int idiv,
-                     int blocks, void* stream, int reduce_op, const void* const* srcs, const unsigned long long* places, void* prof);
+                     int blocks, void* stream, int reduce_op, const void* const* srcs, const unsigned long long* places, void* prof,
+                     int phase1_blocks);
+/* `phase1_blocks` > 0 (both calls above and below): a mixed grid, in which only that many blocks of every rank run the
+ * cross-rank phase and the rank's blocks meet at two local barriers (what real groups use for NVLS launches). */
 int bc_emu_fused_step(void* g, long long off, long long count, int dtype, void* const* params, float* const* masters,
-                      float* const* s1, float* const* s2, const bc_opt_hyper* h, float scale, int blocks, void* stream);
+                      float* const* s1, float* const* s2, const bc_opt_hyper* h, float scale, int blocks, void* stream,
+                      int phase1_blocks);
 int bc_emu_allgatherv(void* g, const void* const* ins, const unsigned long long* bytes, const unsigned long long* out_offs,
                       int blocks, void* stream);
 int bc_emu_barrier_probe(void* g, int absent, double timeout_s, void* stream);

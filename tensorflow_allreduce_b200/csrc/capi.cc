@@ -430,23 +430,26 @@ unsigned bc_emu_status(void* g) { API_BEGIN return ((gpu::EmuGroup*)g)->status()
 int bc_emu_clear_status(void* g) { API_BEGIN ((gpu::EmuGroup*)g)->clear_status(); return 0; API_END(-1) }
 
 int bc_emu_allreduce(void* g, long long off, void* const* outs, long long count, int dtype, int algo, float scale, int idiv,
-                     int blocks, void* stream, int reduce_op, const void* const* srcs, const unsigned long long* places, void* prof) {
+                     int blocks, void* stream, int reduce_op, const void* const* srcs, const unsigned long long* places, void* prof,
+                     int phase1_blocks) {
   API_BEGIN
   if (reduce_op < 0 || reduce_op > (int)ReduceOp::MAX) throw Error("unknown reduction");
   check_cuda(((gpu::EmuGroup*)g)->allreduce((size_t)off, outs, (size_t)count, (DType)dtype, (gpu::Algo)algo, scale, idiv, blocks,
-                                            (cudaStream_t)stream, (ReduceOp)reduce_op, srcs, places, (unsigned long long*)prof),
+                                            (cudaStream_t)stream, (ReduceOp)reduce_op, srcs, places, (unsigned long long*)prof,
+                                            phase1_blocks),
              "emulated allreduce launch");
   return 0;
   API_END(-1)
 }
 
 int bc_emu_fused_step(void* g, long long off, long long count, int dtype, void* const* params, float* const* masters,
-                      float* const* s1, float* const* s2, const bc_opt_hyper* h, float scale, int blocks, void* stream) {
+                      float* const* s1, float* const* s2, const bc_opt_hyper* h, float scale, int blocks, void* stream,
+                      int phase1_blocks) {
   API_BEGIN
   gpu::OptHyper hh;
   memcpy(&hh, h, sizeof(hh));
   check_cuda(((gpu::EmuGroup*)g)->fused_step((size_t)off, (size_t)count, (DType)dtype, params, masters, s1, s2, hh, scale, blocks,
-                                             (cudaStream_t)stream), "emulated fused step launch");
+                                             (cudaStream_t)stream, phase1_blocks), "emulated fused step launch");
   return 0;
   API_END(-1)
 }

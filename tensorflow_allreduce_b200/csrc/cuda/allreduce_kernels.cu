@@ -316,8 +316,18 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
   }
   if (R.place && blockIdx.x == 0 && (int)threadIdx.x < P) c.meta[threadIdx.x][(size_t)me * 2] = R.place;
 
+  // Mixed grids (two-phase algorithms only): all blocks copy in and run the local epilogue, the
+  // first phase1_blocks alone talk to the peers. Two barriers among this rank's blocks replace
+  // the "block b only touches what block b produced" rule: every block's copy-in is complete
+  // before any block signals a peer, and every peer's results are complete before any block
+  // starts the epilogue.
+  const bool mixed = ALGO != ALGO_ONE && a.phase1_blocks > 0 && a.phase1_blocks < (int)gridDim.x;
+  const bool in_p1 = !mixed || (int)blockIdx.x < a.phase1_blocks;
+  const size_t stride1 = mixed ? (size_t)a.phase1_blocks * blockDim.x : stride;
+  if (mixed && !local_barrier(c, c.local_base + gridDim.x, true)) return;
+
   uint32_t epoch = load_epoch(c);
-  if (!peer_barrier(c, epoch)) { store_epoch(c, epoch); return; }
+  if (in_p1 && !peer_barrier(c, epoch)) { store_epoch(c, epoch); return; }
   stamp(a, 1);
   if (R.place && blockIdx.x == 0 && (int)threadIdx.x < P) {
     // In place on symmetric memory: every rank must have passed the same offset, or the peers'
@@ -345,6 +355,7 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
   } else {
     // Phase 1: reduce this rank's slice and store the result into every rank's buffer.
     const size_t sbeg = npacks * (size_t)me / P, send = npacks * (size_t)(me + 1) / P;
+    if (in_p1) {
     if constexpr (ALGO == ALGO_NVLS && IsFloatGrad<T>::value) {
       // Software pipeline of batches of kNvlsUnroll packs: the reductions of batch k+1 are issued
       // before the stores of batch k. The reduction keeps this GPU's outbound links busy (every
@@ -355,14 +366,14 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
       auto load_batch = [&](size_t i0, uint4* r) {
 #pragma unroll
         for (int u = 0; u < kNvlsUnroll; u++) {
-          const size_t i = i0 + (size_t)u * stride;
+          const size_t i = i0 + (size_t)u * stride1;
           if (i < send && in_bounds(c, i < npacks)) r[u] = nvls_reduce<T>(R.mc_in + i * 16);
         }
       };
       auto store_batch = [&](size_t i0, uint4* r) {
 #pragma unroll
         for (int u = 0; u < kNvlsUnroll; u++) {
-          const size_t i = i0 + (size_t)u * stride;
+          const size_t i = i0 + (size_t)u * stride1;
           if (i < send && in_bounds(c, i < npacks)) {
             if (a.scale != 1.f) {
               Acc acc[E];
@@ -375,7 +386,7 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
           }
         }
       };
-      const size_t step = stride * kNvlsUnroll;
+      const size_t step = stride1 * kNvlsUnroll;
       uint4 ra[kNvlsUnroll], rb[kNvlsUnroll];
       size_t i0 = sbeg + first;
       if (i0 < send) load_batch(i0, ra);
@@ -390,7 +401,7 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
         i0 = i2;
       }
     } else {
-      reduce_range_any<T, OPT == OPT_RED>(R, P, sbeg, send, first, stride, npacks, a.red, [&](size_t i, Acc* acc) {
+      reduce_range_any<T, OPT == OPT_RED>(R, P, sbeg, send, first, stride1, npacks, a.red, [&](size_t i, Acc* acc) {
 #pragma unroll
         for (int e = 0; e < E; e++) acc[e] = finish<Acc>(acc[e], a.scale, a.idiv);
         const uint4 r = PK::pack(acc);
@@ -406,9 +417,13 @@ __global__ void __launch_bounds__(512, 2) allreduce_kernel(const __grid_constant
         for (int p = 0; p < P; p++) Scalar<T>::st(reinterpret_cast<T*>(R.in[p]) + e, g);
       }
     }
+    }   // in_p1
     stamp(a, 2);
-    if (!peer_barrier(c, epoch)) { store_epoch(c, epoch); return; }
-    store_epoch(c, epoch);
+    if (in_p1) {
+      if (!peer_barrier(c, epoch)) { store_epoch(c, epoch); return; }
+      store_epoch(c, epoch);
+    }
+    if (mixed && !local_barrier(c, c.local_base + gridDim.x + a.phase1_blocks, in_p1)) return;
     stamp(a, 3);
 
     // Phase 2: local epilogue. Block b reads, inside each slice, exactly the packs that block b

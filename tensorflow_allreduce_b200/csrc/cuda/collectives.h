@@ -76,6 +76,9 @@ struct ArArgs {
   float scale;                // applied to floating sums (1/size when averaging)
   int idiv;                   // integer divisor when averaging integer tensors
   int red;                    // ReduceOp; anything but SUM goes with no scale, no update and no NVLS
+  int phase1_blocks;          // two-phase algorithms: 0 = every block takes part in the cross-rank phase; else only
+                              // the first phase1_blocks do (NVLS wants few blocks, the local copy and update
+                              // phases many) and the blocks of a rank meet at local barriers in between
   unsigned long long* prof;   // optional device array of kProfStamps: %globaltimer of block 0 of rank slot 0 at
                               // kernel entry, after barrier 1, after phase 1, after barrier 2, at the end
   OptHyper opt;

@@ -51,8 +51,8 @@ Comm::Comm(int rank, int world, int device, uint64_t job_id, const CommConfig& c
   heap_off_ = staging_off_ + cfg_.staging_bytes;
   cfg_.heap_bytes = align_up(cfg_.heap_bytes, 1u << 20);
   seg0_ = alloc_->alloc(heap_off_ + cfg_.heap_bytes, ag);
-  CUDA_RT(cudaMalloc(&epochs_, sizeof(uint32_t) * kChannels * kMaxBlocks));
-  CUDA_RT(cudaMemset(epochs_, 0, sizeof(uint32_t) * kChannels * kMaxBlocks));
+  CUDA_RT(cudaMalloc(&epochs_, sizeof(uint32_t) * kChannels * (kMaxBlocks + 1)));
+  CUDA_RT(cudaMemset(epochs_, 0, sizeof(uint32_t) * kChannels * (kMaxBlocks + 1)));
   CUDA_RT(cudaHostAlloc(&status_host_, 64, cudaHostAllocMapped));
   memset(status_host_, 0, 64);
   CUDA_RT(cudaHostGetDevicePointer((void**)&status_dev_, status_host_, 0));
@@ -90,6 +90,8 @@ RankCtx Comm::make_ctx(int channel) const {
     c.meta[p] = (uint64_t*)(pad + kFlagBytes);
   }
   c.epochs = epochs_ + (size_t)channel * kMaxBlocks;
+  c.local_ctr = epochs_ + (size_t)kChannels * kMaxBlocks + channel;
+  c.local_base = local_arrivals_[channel];
   c.status = status_dev_;
   c.timeout_ns = to_ns(cfg_.device_timeout_s);
   return c;
@@ -221,9 +223,17 @@ Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType
     a.algo = (int)algo;
     a.count = count;
     cfg.blocks = choose_blocks(bytes, world_, a.algo, false, sm_count_, cfg_.max_blocks);
-    // The copy phases of this kernel want many blocks, its NVLS phase few: 64 is the compromise
-    // (64 MiB on 4 GPUs: 445 GB/s with 64 blocks, 290 with 16, 456 with 128).
-    if (algo == Algo::NVLS && cfg_.max_blocks <= 0) cfg.blocks = choose_blocks(bytes, world_, (int)Algo::TWO_SHOT, false, sm_count_, 64);
+    // The copy phases of this kernel want many blocks, its NVLS phase few: a mixed grid, in which
+    // all blocks copy and the first few alone drive the switch (64 MiB on 4 GPUs with one grid for
+    // all phases: 445 GB/s with 64 blocks, 290 with 16, 456 with 128).
+    if (algo == Algo::NVLS && cfg_.max_blocks <= 0) {
+      const int p1 = cfg.blocks;
+      cfg.blocks = choose_blocks(bytes, world_, (int)Algo::TWO_SHOT, false, sm_count_, 0);
+      if (cfg.blocks > p1) {
+        a.phase1_blocks = p1;
+        a.r[0].ctx.local_base = claim_local_barrier(channel, cfg.blocks, p1);
+      }
+    }
     CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, s));
     last_blocks = cfg.blocks;
     last_launches = 1;
@@ -410,6 +420,16 @@ Algo Comm::fused_step(int channel, void* grad, size_t count, DType dtype, void* 
   LaunchCfg cfg;
   cfg.blocks = choose_blocks(bytes, world_, a.algo, true, sm_count_, beside_compute && cfg_.overlap_blocks > 0 ? cfg_.overlap_blocks : cfg_.max_blocks,
                              beside_compute);
+  if (algo == Algo::NVLS && !beside_compute && cfg_.max_blocks <= 0) {
+    // Nothing else is expected on the GPU: the update phase gets one block per SM (all of them
+    // can be resident whatever else still drains), the switch phase the few blocks that suit it.
+    const int p1 = choose_blocks(bytes, world_, a.algo, false, sm_count_, 0);
+    if (cfg.blocks > sm_count_) cfg.blocks = sm_count_;
+    if (cfg.blocks > p1) {
+      a.phase1_blocks = p1;
+      a.r[0].ctx.local_base = claim_local_barrier(channel, cfg.blocks, p1);
+    }
+  }
   CUDA_RT(launch_allreduce(a, dtype, dtype, cfg, s));
   last_blocks = cfg.blocks;
   return algo;
@@ -432,8 +452,8 @@ EmuGroup::EmuGroup(int device, int nranks, size_t bytes_per_rank) : device_(devi
     pads_[r] = raw + kGuardBytes;
     CUDA_RT(cudaMemset(pads_[r], 0, kPadBytes));
   }
-  CUDA_RT(cudaMalloc(&epochs_, sizeof(uint32_t) * n_ * kChannels * kMaxBlocks));
-  CUDA_RT(cudaMemset(epochs_, 0, sizeof(uint32_t) * n_ * kChannels * kMaxBlocks));
+  CUDA_RT(cudaMalloc(&epochs_, sizeof(uint32_t) * (n_ * kChannels * kMaxBlocks + n_)));
+  CUDA_RT(cudaMemset(epochs_, 0, sizeof(uint32_t) * (n_ * kChannels * kMaxBlocks + n_)));
   CUDA_RT(cudaHostAlloc(&status_host_, 64, cudaHostAllocMapped));
   memset(status_host_, 0, 64);
   CUDA_RT(cudaHostGetDevicePointer((void**)&status_dev_, status_host_, 0));
@@ -478,6 +498,8 @@ RankCtx EmuGroup::ctx(int r, int channel) const {
     c.meta[p] = (uint64_t*)(pad + kFlagBytes);
   }
   c.epochs = epochs_ + ((size_t)r * kChannels + channel) * kMaxBlocks;
+  c.local_ctr = epochs_ + (size_t)n_ * kChannels * kMaxBlocks + r;
+  c.local_base = local_arrivals_;
   c.status = status_dev_;
   c.timeout_ns = to_ns(timeout_s_);
   return c;
@@ -485,7 +507,7 @@ RankCtx EmuGroup::ctx(int r, int channel) const {
 
 cudaError_t EmuGroup::allreduce(size_t off, void* const* outs, size_t count, DType dtype, Algo algo, float scale, int idiv,
                                 int blocks, cudaStream_t s, ReduceOp red, const void* const* srcs, const unsigned long long* places,
-                                unsigned long long* prof) {
+                                unsigned long long* prof, int phase1_blocks) {
   ArArgs a;
   memset(&a, 0, sizeof(a));
   a.nranks_here = n_;
@@ -505,11 +527,16 @@ cudaError_t EmuGroup::allreduce(size_t off, void* const* outs, size_t count, DTy
   LaunchCfg cfg;
   cfg.cooperative = true;
   cfg.blocks = std::min(blocks > 0 ? blocks : 4, max_emulated_blocks(device_, n_, cfg.threads));
+  if (phase1_blocks > 0 && phase1_blocks < cfg.blocks && algo != Algo::ONE_SHOT) {
+    a.phase1_blocks = phase1_blocks;
+    local_arrivals_ += (uint32_t)(cfg.blocks + phase1_blocks);     // every rank's counter advances alike
+  }
   return launch_allreduce(a, dtype, dtype, cfg, s);
 }
 
 cudaError_t EmuGroup::fused_step(size_t off, size_t count, DType dtype, void* const* params, float* const* masters,
-                                 float* const* s1, float* const* s2, const OptHyper& h, float scale, int blocks, cudaStream_t s) {
+                                 float* const* s1, float* const* s2, const OptHyper& h, float scale, int blocks, cudaStream_t s,
+                                 int phase1_blocks) {
   ArArgs a;
   memset(&a, 0, sizeof(a));
   a.nranks_here = n_;
@@ -530,6 +557,10 @@ cudaError_t EmuGroup::fused_step(size_t off, size_t count, DType dtype, void* co
   LaunchCfg cfg;
   cfg.cooperative = true;
   cfg.blocks = std::min(blocks > 0 ? blocks : 4, max_emulated_blocks(device_, n_, cfg.threads));
+  if (phase1_blocks > 0 && phase1_blocks < cfg.blocks) {
+    a.phase1_blocks = phase1_blocks;
+    local_arrivals_ += (uint32_t)(cfg.blocks + phase1_blocks);
+  }
   return launch_allreduce(a, dtype, dtype, cfg, s);
 }
 

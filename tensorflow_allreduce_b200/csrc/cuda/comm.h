@@ -115,7 +115,16 @@ class Comm {
   std::unique_ptr<SymmAllocator> alloc_;
   Segment* seg0_ = nullptr;
   size_t pad_off_ = 0, staging_off_ = 0, heap_off_ = 0;
-  uint32_t* epochs_ = nullptr;        // device-local epoch counters [kChannels][kMaxBlocks]
+  uint32_t* epochs_ = nullptr;        // device-local epoch counters [kChannels][kMaxBlocks], then one arrival counter
+                                      // per channel for the barriers among the blocks of a launch (mixed grids)
+  mutable uint32_t local_arrivals_[dev::kChannels] = {0};   // what those counters will hold once the queued launches have run
+  // Marks the next launch on `channel` as one with a mixed grid of `blocks` blocks of which
+  // `phase1_blocks` talk to the peers: returns the counter value it starts from.
+  uint32_t claim_local_barrier(int channel, int blocks, int phase1_blocks) const {
+    const uint32_t base = local_arrivals_[channel];
+    local_arrivals_[channel] += (uint32_t)(blocks + phase1_blocks);
+    return base;
+  }
   uint32_t* status_host_ = nullptr;   // pinned, mapped
   uint32_t* status_dev_ = nullptr;
   cudaStream_t streams_[dev::kChannels] = {nullptr};
@@ -151,11 +160,13 @@ class EmuGroup {
   // `srcs` (optional): private inputs that the kernel copies into the ranks' buffers first, as the
   // staged path does. `places` (optional): the offsets the ranks claim to have passed (the kernel
   // compares them and sets kStatusLayout on a mismatch).
+  // `phase1_blocks` > 0: mixed grid, only that many blocks of every rank run the cross-rank phase.
   cudaError_t allreduce(size_t off, void* const* outs, size_t count, DType dtype, Algo algo, float scale, int idiv,
                         int blocks, cudaStream_t s, ReduceOp red = ReduceOp::SUM, const void* const* srcs = nullptr,
-                        const unsigned long long* places = nullptr, unsigned long long* prof = nullptr);
+                        const unsigned long long* places = nullptr, unsigned long long* prof = nullptr, int phase1_blocks = 0);
   cudaError_t fused_step(size_t off, size_t count, DType dtype, void* const* params, float* const* masters,
-                         float* const* s1, float* const* s2, const OptHyper& h, float scale, int blocks, cudaStream_t s);
+                         float* const* s1, float* const* s2, const OptHyper& h, float scale, int blocks, cudaStream_t s,
+                         int phase1_blocks = 0);
   cudaError_t allgatherv(const void* const* ins, const unsigned long long* bytes, const unsigned long long* out_offs,
                          int blocks, cudaStream_t s);
   // A barrier-only launch in which rank `absent` (if >= 0) does not take part, so that the
@@ -168,7 +179,8 @@ class EmuGroup {
   size_t bytes_;
   std::vector<char*> bufs_;   // user-visible starts (allocation start + kGuardBytes)
   std::vector<char*> pads_;
-  uint32_t* epochs_ = nullptr;  // [n][kChannels][kMaxBlocks]
+  uint32_t* epochs_ = nullptr;  // [n][kChannels][kMaxBlocks], then one arrival counter per rank (mixed grids)
+  uint32_t local_arrivals_ = 0; // what each rank's counter will hold once the queued launches have run
   uint32_t* status_host_ = nullptr;
   uint32_t* status_dev_ = nullptr;
   double timeout_s_ = 20.0;

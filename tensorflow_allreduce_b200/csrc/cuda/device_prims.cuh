@@ -122,6 +122,34 @@ __device__ __forceinline__ bool peer_barrier(const RankCtx& c, uint32_t& epoch) 
   return __syncthreads_and(ok) != 0;
 }
 
+// Barrier among the blocks of this rank's launch: blocks with `arrive` add one to the rank's
+// counter, every block waits until the counter has reached `target` (arrivals are counted from
+// RankCtx::local_base on, see there). All blocks of the launch must be able to be resident at
+// the same time; the wait is bounded like every other. Returns false in every thread of the
+// block when it ran out.
+__device__ __forceinline__ bool local_barrier(const RankCtx& c, uint32_t target, bool arrive) {
+  __syncthreads();
+  int ok = 1;
+  if (threadIdx.x == 0) {
+    if (arrive) {
+      __threadfence();
+      atomicAdd(c.local_ctr, 1u);
+    }
+    const unsigned long long t0 = global_timer();
+    uint32_t spins = 0, seen;
+    do {
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(c.local_ctr) : "memory");
+      if ((int32_t)(seen - target) >= 0) break;
+      if (((++spins) & 0xff) == 0 && global_timer() - t0 > c.timeout_ns) {
+        ok = 0;
+        atomicOr(c.status, kStatusTimeout | 0x80u | ((uint32_t)c.rank << 8));
+        break;
+      }
+    } while (true);
+  }
+  return __syncthreads_and(ok) != 0;
+}
+
 // Bounds-checked builds (-DBC_DEBUG, `build.build(debug=True)` -> lib/libbcoll_debug.so, loaded
 // when BC_DEBUG_KERNELS=1): every pack index and every allgather destination range is tested
 // before the access; a violation sets kStatusBounds in the status word and the access is

@@ -42,6 +42,11 @@ struct RankCtx {
   uint32_t* epochs;             // this rank's private per-block epoch counters for the channel
   uint32_t* status;             // host-visible status word
   unsigned long long timeout_ns;
+  // Barrier among the blocks of ONE rank's launch (kernels whose phases run on different numbers
+  // of blocks): an arrival counter of this rank and channel in device memory, and its value
+  // before this launch (the host adds up what every launch will contribute).
+  uint32_t* local_ctr;
+  uint32_t local_base;
 };
 
 }  // namespace dev

@@ -69,13 +69,14 @@ class EmulatedGroup:
     def allreduce(self, count: int, dtype: torch.dtype, algo: str = "two_shot", outs: Optional[Sequence[torch.Tensor]] = None,
                   scale: float = 1.0, idiv: int = 1, blocks: int = 4, offset_bytes: int = 0, op: str = "sum",
                   srcs: Optional[Sequence[torch.Tensor]] = None, places: Optional[Sequence[int]] = None,
-                  profile: Optional[torch.Tensor] = None):
+                  profile: Optional[torch.Tensor] = None, phase1_blocks: int = 0):
         """Reduce the first `count` elements (at `offset_bytes`) of all ranks' buffers. `outs`
         defaults to in place (two-shot only). `op`: sum, prod, min or max. `srcs`: private inputs
         that the kernel itself copies into the ranks' buffers first (the staged path of a real
         group). `places`: the offsets that the ranks claim for an in-place reduction; ranks that
         disagree set the layout bit of the status word. `profile`: int64 CUDA tensor of 5 time
-        stamps written by block 0 of rank 0."""
+        stamps written by block 0 of rank 0. `phase1_blocks` > 0 (two-shot): a mixed grid, only
+        that many blocks of every rank run the cross-rank phase, all of them the local phases."""
         n = self.nranks
         arr = (C.c_void_p * n)()
         for r in range(n):
@@ -92,14 +93,16 @@ class EmulatedGroup:
         s = torch.cuda.current_stream(self.device).cuda_stream
         _check(self.lib.bc_emu_allreduce(self._g, offset_bytes, arr, count, _DTYPES[dtype], ALGOS[algo], float(scale), int(idiv),
                                          blocks, C.c_void_p(s), {"sum": 0, "prod": 1, "min": 2, "max": 3}[op], sp, pl,
-                                         C.c_void_p(profile.data_ptr()) if profile is not None else None), "emulated allreduce")
+                                         C.c_void_p(profile.data_ptr()) if profile is not None else None, int(phase1_blocks)),
+               "emulated allreduce")
 
     def clear_status(self):
         self.lib.bc_emu_clear_status(self._g)
 
     def fused_step(self, count: int, dtype: torch.dtype, params: Sequence[torch.Tensor], hyper: "_lib.OptHyper",
                    masters: Optional[Sequence[torch.Tensor]] = None, state1: Optional[Sequence[torch.Tensor]] = None,
-                   state2: Optional[Sequence[torch.Tensor]] = None, scale: float = 1.0, blocks: int = 4, offset_bytes: int = 0):
+                   state2: Optional[Sequence[torch.Tensor]] = None, scale: float = 1.0, blocks: int = 4, offset_bytes: int = 0,
+                   phase1_blocks: int = 0):
         n = self.nranks
 
         def ptrs(ts):
@@ -112,7 +115,8 @@ class EmulatedGroup:
 
         s = torch.cuda.current_stream(self.device).cuda_stream
         _check(self.lib.bc_emu_fused_step(self._g, offset_bytes, count, _DTYPES[dtype], ptrs(params), ptrs(masters), ptrs(state1),
-                                          ptrs(state2), C.byref(hyper), float(scale), blocks, C.c_void_p(s)), "emulated fused step")
+                                          ptrs(state2), C.byref(hyper), float(scale), blocks, C.c_void_p(s), int(phase1_blocks)),
+               "emulated fused step")
 
     def allgatherv(self, ins: Sequence[torch.Tensor], out_offsets: Sequence[int], blocks: int = 2):
         """Each rank r pushes `ins[r]` into every rank's buffer at `out_offsets[that rank]` plus

@@ -319,3 +319,42 @@ def test_profile_stamps_are_ordered(emu):
         t = stamps[:5].tolist()
         assert t[0] > 0 and all(b >= a for a, b in zip(t, t[1:])), t
         assert t[4] - t[0] < 1e9
+
+
+@pytest.mark.parametrize("nranks", [2, 4, 8])
+def test_mixed_grid_runs_the_cross_rank_phase_on_a_few_blocks(emu, nranks):
+    # NVLS launches of real groups use a mixed grid: every block copies in and runs the local
+    # epilogue, only the first few talk to the peers, and the blocks of a rank meet at two local
+    # barriers in between. Same kernel code here with peer loads: staged inputs, separate outputs,
+    # several launches in a row (the barrier counter runs on), then a fused update.
+    g = emu(nranks)
+    for dtype in (torch.float32, torch.bfloat16):
+        e = PACK[dtype]
+        for n, blocks, p1 in (((1 << 18) + 7, 6, 2), (5 * e * nranks + 3, 4, 1), ((1 << 16) + 1, 5, 3), (e - 1, 3, 1)):
+            xs = [_fill(dtype, n, 77 * r + n % 11) for r in range(nranks)]
+            keep = [x.clone() for x in xs]
+            outs = [torch.empty(n, dtype=dtype, device="cuda") for _ in range(nranks)]
+            g.allreduce(n, dtype, "two_shot", outs=outs, blocks=blocks, srcs=xs, phase1_blocks=p1)
+            torch.cuda.synchronize()
+            assert g.status == 0, hex(g.status)
+            want = _reference_sum(keep, dtype)
+            for r in range(nranks):
+                assert torch.equal(outs[r], want), f"rank {r} n={n} {dtype}"
+    # fused momentum-SGD with a mixed grid equals the same step with a plain grid
+    from tensorflow_allreduce_b200.ops import fused_optim as fo
+
+    n = (1 << 17) + 5
+    results = []
+    for p1 in (0, 2):
+        grads = [_fill(torch.float32, n, 5 * r + 1) for r in range(nranks)]
+        for r in range(nranks):
+            g.buffer(r, torch.float32, n).copy_(grads[r])
+        params = [torch.linspace(-1, 1, n, device="cuda") for _ in range(nranks)]
+        mom = [torch.full((n,), 0.25, device="cuda") for _ in range(nranks)]
+        g.fused_step(n, torch.float32, params, fo.sgd_hyper(0.1, momentum=0.9, weight_decay=0.01, zero_grad=True), state1=mom,
+                     scale=1.0 / nranks, blocks=6, phase1_blocks=p1)
+        torch.cuda.synchronize()
+        assert g.status == 0
+        results.append((params[0].clone(), mom[nranks - 1].clone()))
+        assert float(g.buffer(0, torch.float32, n).abs().max()) == 0.0        # gradients zeroed
+    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
