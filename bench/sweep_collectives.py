@@ -321,7 +321,8 @@ def main():
             # results of the timed calls above live in the symmetric heap until they are collected
             torch.cuda.synchronize()
             gc.collect()
-            sym_out = symmetric.try_empty((total // (es * cols), cols), dtype, torch.device("cuda", local))
+            # ordered launches need all ranks on one host
+            sym_out = None if a.fake_hosts > 1 else symmetric.try_empty((total // (es * cols), cols), dtype, torch.device("cuda", local))
             if not all(bc.host_allgather(sym_out is not None)):
                 rows.append(row)
                 if rank == 0:

@@ -239,8 +239,9 @@ Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType
     last_launches = 1;
     return algo;
   }
-  // Chunks of the pipeline below: equal shares of at most one part, in multiples of 256 bytes.
-  const size_t nchunks = (count + part_elems - 1) / part_elems;
+  // Chunks of the pipeline below: equal shares of at most one part, in multiples of 256 bytes,
+  // and at least four of them (with two, nothing is copied while something else is reduced).
+  const size_t nchunks = std::max<size_t>(4, (count + part_elems - 1) / part_elems);
   const size_t chunk_elems = align_up((count + nchunks - 1) / nchunks, 256 / es);
   // A larger tensor goes in chunks of one part through a pipeline on three streams: the
   // reductions (NVLink-bound) alternate between the channel's stream and its second lane, so
