@@ -14,8 +14,9 @@ device->host read of the loss inside the timed region.
 
 After its own numbers an `--impl ours` run measures, in the same process and with the same steps
 and warm-up, torch DistributedDataParallel + NCCL + the plain torch optimizer on the same model:
-once with the same GRU kernels (`ddp_nccl_same_kernels`, which isolates what the collectives
-library is worth) and once with cuDNN's GRU (`ddp_nccl_cudnn`). They go under `comparators` and are
+once with the same model kernels (`ddp_nccl_same_kernels`: the persistent GRU and the fused batch
+norm, which isolates what the collectives library is worth) and once with the stock model
+(`ddp_nccl_cudnn`: cuDNN's GRU and batch norm). They go under `comparators` and are
 labelled as what they are: not the reference. `--no-comparators` skips them.
 
 Other arms: `--impl reference` reports the reference's own build (unavailable on this image);
@@ -44,7 +45,7 @@ def parse():
     ap.add_argument("--model", default="ds2", choices=["ds2", "gpt2", "resnet50"])
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (0 = the configuration's value)")
     ap.add_argument("--rnn", default="auto", choices=["auto", "persistent", "cudnn"],
-                    help="ds2: GRU stack on the library's persistent tcgen05 kernels (auto: ours yes, ddp no) or on cuDNN")
+                    help="ds2: GRU stack and batch norm on the library's kernels (auto: ours yes, ddp no) or the stock cuDNN model")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-comparators", action="store_true",
                     help="skip the torch DDP + NCCL arms that an `--impl ours` run measures after its own numbers")
@@ -62,13 +63,13 @@ def reference_unavailable():
     return 0
 
 
-def build_model(name: str, device, batch: int, persistent_rnn: bool = True):
+def build_model(name: str, device, batch: int, persistent_rnn: bool = True, fused_norm: bool = True):
     import torch
 
     if name == "ds2":
         from tensorflow_allreduce_b200.models import ds2
 
-        cfg = ds2.DS2Config(persistent_rnn=persistent_rnn)
+        cfg = ds2.DS2Config(persistent_rnn=persistent_rnn, fused_norm=fused_norm)
         model = ds2.DeepSpeech2(cfg).to(device)
         model.rnn.flatten_parameters()
         b = batch or 32
@@ -149,7 +150,8 @@ def run_arm(a, impl: str, rnn: str, device, rank: int, world: int, local: int, w
 
     torch.manual_seed(1234)          # same initial weights on every rank, as the reference requires
     persistent = rnn == "persistent"
-    model, base_opt, make, loss_fn, per_gpu_batch, meta = build_model(a.model, device, a.batch, persistent)
+    # "cudnn" is the stock model: cuDNN's GRU and cuDNN's batch norm + a separate clipped ReLU
+    model, base_opt, make, loss_fn, per_gpu_batch, meta = build_model(a.model, device, a.batch, persistent, fused_norm=persistent)
     ddp = None
     fwd = model
     if impl == "ddp":
@@ -299,7 +301,8 @@ def main():
                        "parallelism": f"dp{world}", "optimizer": meta["optimizer"], "params_m": round(r["n_params"] / 1e6, 2),
                        "l2": "256 MB buffer written between steps (L2 flush); working set exceeds L2 anyway",
                        "grad_buckets": r["grad_buckets"], "fused_update": r["fused"],
-                       "rnn": ("persistent tcgen05 kernels" if persistent else "cudnn") if a.model == "ds2" else None},
+                       "rnn": ("persistent tcgen05 kernels" if persistent else "cudnn") if a.model == "ds2" else None,
+                       "norm": ("fused batch norm + clipped ReLU kernels" if persistent else "cudnn") if a.model == "ds2" else None},
             "clocks": {"sm_mhz": clocks.get("sm_mhz"), "sm_max_mhz": clocks.get("sm_max_mhz"), "reasons": clocks.get("reasons", []),
                        "power_w_max": clocks.get("power_w_max"), "samples": clocks.get("samples"), "source": clocks.get("source")},
             "gpu_launches": r["launches"],
