@@ -9,8 +9,9 @@ gradient allreduce kernel of this library. Synthetic data, random-initialised we
 
 Prints ONE JSON line (rank 0). `value` is the whole-job samples/s over the K timed steps, timed
 with CUDA events between barriers, maximum over ranks. `e2e` repeats the measurement through the
-public API with the per-step host->device copy of the inputs from pinned memory and the
-device->host read of the loss inside the timed region.
+public API with the per-step host->device copy of the inputs from pinned memory (on a copy stream,
+issued one step ahead so that it overlaps the previous step's compute; K + 1 copies for K steps,
+all inside the timed region) and the device->host read of the loss inside the timed region.
 
 After its own numbers an `--impl ours` run measures, in the same process and with the same steps
 and warm-up, torch DistributedDataParallel + NCCL + the plain torch optimizer on the same model:
@@ -185,7 +186,13 @@ def run_arm(a, impl: str, rnn: str, device, rank: int, world: int, local: int, w
     for _ in range(a.warmup):
         step(dev_batch)
     torch.cuda.synchronize()
-    launches0 = getattr(opt, "launch_count", 0) + persistent_gru.launch_count
+    from tensorflow_allreduce_b200.ops import bn_clip
+
+    def own_launches():
+        # kernels of this library launched so far: bucket reductions / fused updates, persistent GRU layers, fused batch norms
+        return getattr(opt, "launch_count", 0) + persistent_gru.launch_count + 2 * bn_clip.launch_count
+
+    launches0 = own_launches()
     bc.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clk:
@@ -197,7 +204,7 @@ def run_arm(a, impl: str, rnn: str, device, rank: int, world: int, local: int, w
         torch.cuda.synchronize()
     bc.barrier()
     ms = max_over_ranks(e0.elapsed_time(e1))
-    launches = getattr(opt, "launch_count", 0) + persistent_gru.launch_count - launches0
+    launches = own_launches() - launches0
     persistent_gru.check_status()
     bc.check_device_status()
     res = {
@@ -210,16 +217,33 @@ def run_arm(a, impl: str, rnn: str, device, rank: int, world: int, local: int, w
         pinned = make(True)
         h2d = sum(t.numel() * t.element_size() for t in pinned)
         loss_host = 0.0
+        copy_stream = torch.cuda.Stream(device)
+
+        def fetch():
+            # host -> device copy of one step's inputs from pinned memory, on a stream of its own
+            with torch.cuda.stream(copy_stream):
+                b_ = tuple(t.to(device, non_blocking=True) for t in pinned)
+            ev = torch.cuda.Event()
+            ev.record(copy_stream)
+            return b_, ev
+
         for _ in range(2):
-            step(tuple(t.to(device, non_blocking=True) for t in pinned))
+            b_, ev = fetch()
+            torch.cuda.current_stream().wait_event(ev)
+            step(b_)
         torch.cuda.synchronize()
         bc.barrier()
         t0 = time.perf_counter()
+        nxt = fetch()
         for _ in range(a.steps):
-            batch_ = tuple(t.to(device, non_blocking=True) for t in pinned)
-            loss_host = step(batch_).item()          # device -> host read of the step's result
+            batch_, ev = nxt
+            torch.cuda.current_stream().wait_event(ev)
+            loss = step(batch_)
+            nxt = fetch()                            # the next step's inputs travel while this step computes
+            loss_host = loss.item()                  # device -> host read of the step's result
         torch.cuda.synchronize()
         t1 = time.perf_counter()
+        del nxt
         bc.barrier()
         e2e_s = max_over_ranks(t1 - t0)
         res["e2e"] = {"value": round(world * per_gpu_batch * a.steps / e2e_s, 3), "unit": "samples/s", "h2d_bytes_per_step": h2d,

@@ -14,6 +14,8 @@ Arms:
   ours_staged allreduce of an ordinary tensor through the name-keyed API (negotiation + staging area)
   ours_private the same ordinary tensor with an ordered launch (`allreduce_direct_`): staging without negotiation,
               which is what NCCL's ordered `all_reduce` is comparable with
+  ours_pipeline (not in the default list) ours_private with the staged pipeline kernel switched on: one launch whose
+              copier blocks and reducer blocks work on different chunks of a ring in the staging area
   nccl        torch.distributed.all_reduce / all_gather on the same sizes
   (--fake-hosts H: the ranks report H host names, so ours_staged runs in two levels: NVLink kernels
    inside a "host", pinned memory and socket rings between them)
@@ -136,7 +138,7 @@ def markdown(rows, world, link_measured=764.0, link_nominal=900.0):
             sel = [r for r in rows if r["op"] == op and r["dtype"] == dname]
             if not sel:
                 continue
-            arms = [k[:-6] for k in ("ours_direct_busbw", "ours_symm_busbw", "ours_staged_busbw", "ours_private_busbw", "ours_busbw", "nccl_busbw",
+            arms = [k[:-6] for k in ("ours_direct_busbw", "ours_symm_busbw", "ours_staged_busbw", "ours_private_busbw", "ours_pipeline_busbw", "ours_busbw", "nccl_busbw",
                                       "nccl_padded_busbw", "ref_ring_busbw") if any(k in r for r in sel)]
             out.append(f"\n### {op}, {world} GPUs, {dname}\n")
             head = ["bytes"] + [f"{a_} ms" for a_ in arms if a_.startswith("ours")] + [f"{a_} GB/s" for a_ in arms]
@@ -151,7 +153,7 @@ def markdown(rows, world, link_measured=764.0, link_nominal=900.0):
                 cells += [f'{r[a_ + "_busbw"]:.1f}' if a_ + "_busbw" in r else "-" for a_ in arms]
                 best = max([r[a_ + "_busbw"] for a_ in arms if a_.startswith("ours") and a_ + "_busbw" in r] or [0.0])
                 cells += [f"{best / link_measured:.2f}", f"{best / link_nominal:.2f}"]
-                flags = [k.split("_")[0] + ("=ok" if r[k] else "=WRONG") for k in ("direct_correct", "symm_correct", "staged_correct", "private_correct", "correct") if k in r]
+                flags = [k.split("_")[0] + ("=ok" if r[k] else "=WRONG") for k in ("direct_correct", "symm_correct", "staged_correct", "private_correct", "pipeline_correct", "correct") if k in r]
                 cells.append(" ".join(flags) or "-")
                 if any("direct_phases_us" in x for x in sel):
                     cells.append(" / ".join(f"{v:.1f}" for v in r["direct_phases_us"]) if "direct_phases_us" in r else "-")
@@ -173,6 +175,7 @@ def main():
     ap.add_argument("--no-allreduce", action="store_true")
     ap.add_argument("--phases", action="store_true", help="ours_direct: also record the kernel's phase times (block 0 time stamps)")
     ap.add_argument("--phases-min-kb", type=int, default=1024)
+    ap.add_argument("--pipeline-mode", type=int, default=2, help="arm ours_pipeline: 1 = only where the switch reduces, 2 = always")
     ap.add_argument("--staging-mb", type=int, default=0, help="size of the staging area (0 = the library's default)")
     ap.add_argument("--fake-hosts", type=int, default=1,
                     help="report this many host names (consecutive ranks share one): times the two-level path on one box")
@@ -274,6 +277,27 @@ def main():
                 row["ours_private_ms"] = ms
                 row["ours_private_busbw"] = nbytes / (ms * 1e-3) * factor / 1e9
                 del y
+            if "ours_pipeline" in arms:
+                # the same ordered launch with the staged pipeline kernel switched on for this arm
+                from tensorflow_allreduce_b200 import _lib
+                from tensorflow_allreduce_b200.ops.direct import allreduce_direct_
+                before = cfg.staged_pipeline
+                _lib.lib().bc_set_option(b"staged_pipeline", a.pipeline_mode)
+                y = x.clone()
+                allreduce_direct_(y)
+                ref = x.clone()
+                if use_nccl:
+                    dist.all_reduce(ref)
+                    tol = 1e-5 * P if dtype == torch.float32 else 1e-2 * P
+                    row["pipeline_correct"] = bool(torch.allclose(y.float(), ref.float(), rtol=tol, atol=tol))
+                y.zero_()
+                del ref
+                ms = timed(lambda: allreduce_direct_(y), iters)
+                row["ours_pipeline_ms"] = ms
+                row["ours_pipeline_busbw"] = nbytes / (ms * 1e-3) * factor / 1e9
+                del y
+                _lib.lib().bc_set_option(b"staged_pipeline", before)
+                bc.check_device_status()
             if "nccl" in arms and use_nccl:
                 y = x.clone()
                 ms = timed(lambda: dist.all_reduce(y), iters)

@@ -50,6 +50,13 @@ class Config:
     bucket_mb: float = 32.0            # DistributedOptimizer gradient bucket size
     overlap_blocks: int = 0            # CTAs of a bucket launch that runs beside backward (0 = one per SM left free
                                        # by a 128-SM persistent kernel, at least 8)
+    staged_pipeline: int = 0           # tensors outside symmetric memory from 4 MiB on in one launch whose blocks copy
+                                       # chunks in and out while others reduce: 0 = off, 1 = where the switch
+                                       # reduces (NVLS), 2 = with peer loads and stores as well
+    pipeline_chunk_kb: int = 2048      # largest chunk of that kernel
+    pipeline_slots: int = 16           # chunks that its ring inside the staging slice holds
+    pipeline_copiers: int = 64         # its blocks that copy
+    pipeline_reducers: int = 0         # its blocks that reduce (0 = as an in-place reduction of that size)
     device_timing_every: int = 0       # DistributedOptimizer: time every bucket launch of every Nth step on the device
                                        # (CUDA events; records in stats() carry device_us and bus GB/s); 0 = never
     link_gbs: float = 764.0            # NVLink rate per direction per GPU that stats() reports fractions of
@@ -71,6 +78,11 @@ class Config:
             symm=_env("BC_SYMM", str, cls.symm),
             bucket_mb=_env("BC_BUCKET_MB", float, cls.bucket_mb),
             overlap_blocks=_env("BC_OVERLAP_BLOCKS", int, cls.overlap_blocks),
+            staged_pipeline=_env("BC_STAGED_PIPELINE", int, cls.staged_pipeline),
+            pipeline_chunk_kb=_env("BC_PIPELINE_CHUNK_KB", int, cls.pipeline_chunk_kb),
+            pipeline_slots=_env("BC_PIPELINE_SLOTS", int, cls.pipeline_slots),
+            pipeline_copiers=_env("BC_PIPELINE_COPIERS", int, cls.pipeline_copiers),
+            pipeline_reducers=_env("BC_PIPELINE_REDUCERS", int, cls.pipeline_reducers),
             device_timing_every=_env("BC_DEVICE_TIMING_EVERY", int, cls.device_timing_every),
             link_gbs=_env("BC_LINK_GBS", float, cls.link_gbs),
             fault=_env("BC_FAULT", str, cls.fault),

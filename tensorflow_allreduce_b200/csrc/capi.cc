@@ -141,6 +141,20 @@ int bc_select_algo(int world, long long bytes, int dtype, int in_place_or_fused,
   API_END(-1)
 }
 
+int bc_plan_pipeline(long long bytes, long long slice_bytes, long long chunk_bytes, int slots, long long* out4) {
+  API_BEGIN
+  gpu::CommConfig cfg;
+  if (chunk_bytes > 0) cfg.pipeline_chunk_bytes = (size_t)chunk_bytes;
+  if (slots > 0) cfg.pipeline_slots = slots;
+  const gpu::PipePlan p = gpu::plan_pipeline(cfg, (size_t)bytes, (size_t)slice_bytes);
+  out4[0] = (long long)p.chunk_bytes;
+  out4[1] = p.nchunks;
+  out4[2] = p.slots;
+  out4[3] = p.lag;
+  return 0;
+  API_END(-1)
+}
+
 long long bc_plan_gather_rounds(int world, const unsigned long long* all_bytes, long long staging_bytes, unsigned long long* pieces_out) {
   API_BEGIN
   std::vector<size_t> piece;
@@ -378,6 +392,18 @@ int bc_set_option(const char* key, long long value) {
     rt().set_device_timing(value != 0);
   } else if (k == "overlap_blocks") {
     comm().set_overlap_blocks((int)value);
+  } else if (k == "staged_pipeline") {
+    comm().mutable_config().staged_pipeline = (int)value;
+  } else if (k == "pipeline_min_bytes") {
+    comm().mutable_config().pipeline_min_bytes = (size_t)std::max<long long>(value, 16);
+  } else if (k == "pipeline_chunk_bytes") {
+    comm().mutable_config().pipeline_chunk_bytes = (size_t)std::max<long long>(value, 4096);
+  } else if (k == "pipeline_slots") {
+    comm().mutable_config().pipeline_slots = (int)std::min<long long>(std::max<long long>(value, 2), 1024);
+  } else if (k == "pipeline_copiers") {
+    comm().mutable_config().pipeline_copiers = (int)std::min<long long>(std::max<long long>(value, 1), 200);
+  } else if (k == "pipeline_reducers") {
+    comm().mutable_config().pipeline_reducers = (int)std::min<long long>(std::max<long long>(value, 0), 96);
   } else {
     throw Error("unknown option '" + k + "'");
   }
@@ -450,6 +476,17 @@ int bc_emu_fused_step(void* g, long long off, long long count, int dtype, void* 
   memcpy(&hh, h, sizeof(hh));
   check_cuda(((gpu::EmuGroup*)g)->fused_step((size_t)off, (size_t)count, (DType)dtype, params, masters, s1, s2, hh, scale, blocks,
                                              (cudaStream_t)stream, phase1_blocks), "emulated fused step launch");
+  return 0;
+  API_END(-1)
+}
+
+int bc_emu_staged_pipeline(void* g, long long off, const void* const* srcs, void* const* outs, long long count, int dtype,
+                           float scale, int idiv, long long chunk_bytes, int slots, int lag, int reducers, int copiers,
+                           void* stream) {
+  API_BEGIN
+  check_cuda(((gpu::EmuGroup*)g)->staged_pipeline((size_t)off, srcs, outs, (size_t)count, (DType)dtype, scale, idiv,
+                                                  (size_t)chunk_bytes, slots, lag, reducers, copiers, (cudaStream_t)stream),
+             "emulated staged pipeline launch");
   return 0;
   API_END(-1)
 }

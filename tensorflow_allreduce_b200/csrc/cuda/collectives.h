@@ -85,6 +85,32 @@ struct ArArgs {
   ArRank r[dev::kMaxRanks];
 };
 
+// Per-rank operands of the staged pipeline launch (allreduce of a tensor outside symmetric
+// memory in one kernel whose copier blocks and reducer blocks work on different chunks).
+struct PipeRank {
+  dev::RankCtx ctx;
+  char* stage[dev::kMaxRanks];      // every rank's staging ring as mapped here
+  char* mc_stage;                   // multicast mapping of the ring (NVLS) or null
+  const char* src;                  // private input (16-byte aligned)
+  char* out;                        // private output (16-byte aligned; may equal src)
+  uint32_t* progress[dev::kMaxRanks];  // progress[p] = the progress words inside rank p's pad: [2][kMaxRanks]
+  uint32_t* local;                  // this rank's arrival counters, zeroed before the launch: [2][nchunks]
+};
+
+struct PipeArgs {
+  int nranks_here;            // 1, or the number of emulated ranks (grid.y)
+  size_t npacks;              // 16-byte packs to reduce
+  size_t chunk_packs;         // packs per chunk (the last chunk may be shorter)
+  int nchunks;
+  int slots;                  // chunks that the staging ring holds
+  int lag;                    // chunks by which the copy-out trails the copy-in (< slots unless everything fits)
+  int reducers;               // the first `reducers` blocks of a rank reduce, the others copy
+  uint32_t base;              // value of the progress words before this launch
+  float scale;
+  int idiv;
+  PipeRank r[dev::kMaxRanks];
+};
+
 // Per-rank operands of a variable-length allgather launch.
 struct AgRank {
   dev::RankCtx ctx;
@@ -113,6 +139,8 @@ struct LaunchCfg {
 // Launch the reduction. `param_dtype` is F32, or equal to `dtype` for 16-bit parameters.
 cudaError_t launch_allreduce(const ArArgs& a, DType dtype, DType param_dtype, const LaunchCfg& cfg, cudaStream_t s);
 cudaError_t launch_allgatherv(const AgArgs& a, const LaunchCfg& cfg, cudaStream_t s);
+// Sum (scaled) of private tensors through the staging rings; `nvls` needs a float type.
+cudaError_t launch_staged_pipeline(const PipeArgs& a, DType dtype, bool nvls, const LaunchCfg& cfg, cudaStream_t s);
 // Plain device copy kernel (staging of tensors that are not in symmetric memory).
 cudaError_t launch_copy(void* dst, const void* src, size_t bytes, cudaStream_t s);
 

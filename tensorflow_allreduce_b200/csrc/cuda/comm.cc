@@ -53,6 +53,7 @@ Comm::Comm(int rank, int world, int device, uint64_t job_id, const CommConfig& c
   seg0_ = alloc_->alloc(heap_off_ + cfg_.heap_bytes, ag);
   CUDA_RT(cudaMalloc(&epochs_, sizeof(uint32_t) * kChannels * (kMaxBlocks + 1)));
   CUDA_RT(cudaMemset(epochs_, 0, sizeof(uint32_t) * kChannels * (kMaxBlocks + 1)));
+  CUDA_RT(cudaMalloc(&pipe_local_, sizeof(uint32_t) * kUserChannels * 2 * kPipeMaxChunks));
   CUDA_RT(cudaHostAlloc(&status_host_, 64, cudaHostAllocMapped));
   memset(status_host_, 0, 64);
   CUDA_RT(cudaHostGetDevicePointer((void**)&status_dev_, status_host_, 0));
@@ -65,6 +66,7 @@ Comm::~Comm() {
   cudaDeviceSynchronize();
   alloc_.reset();
   if (epochs_) cudaFree(epochs_);
+  if (pipe_local_) cudaFree(pipe_local_);
   if (status_host_) cudaFreeHost(status_host_);
   for (int c = 0; c < kChannels; c++)
     if (streams_[c]) cudaStreamDestroy(streams_[c]);
@@ -125,6 +127,64 @@ Algo select_algo(const CommConfig& cfg, int world, size_t bytes, DType dtype, bo
   // and measured slower than plain peer loads and stores; it pays from four ranks on.
   if (has_mc && cfg.use_nvls && is_float && world >= 4 && bytes >= cfg.nvls_min_bytes) return Algo::NVLS;
   return Algo::TWO_SHOT;
+}
+
+PipePlan plan_pipeline(const CommConfig& cfg, size_t bytes, size_t slice_bytes) {
+  PipePlan p;
+  const int slots = std::max(2, cfg.pipeline_slots);
+  // at least eight chunks, each a multiple of 4 KiB, `slots` of them inside the slice
+  size_t chunk = std::min(cfg.pipeline_chunk_bytes, std::max<size_t>(bytes / 8, 64u << 10));
+  chunk = std::min(chunk, slice_bytes / (size_t)slots);
+  chunk = std::max<size_t>(chunk / 4096 * 4096, 4096);
+  p.chunk_bytes = chunk;
+  const size_t n = (bytes + chunk - 1) / chunk;
+  p.nchunks = (int)std::min<size_t>(n, (size_t)kPipeMaxChunks);   // the caller launches again for the rest
+  p.slots = std::min(slots, p.nchunks);
+  p.lag = std::max(1, p.slots / 2);
+  if (p.nchunks <= p.slots) p.lag = std::min(p.lag, p.nchunks);
+  return p;
+}
+
+void Comm::launch_pipeline(int channel, const char* in, char* out, size_t packs, DType dtype, float scale, int idiv, bool nvls,
+                           const PipePlan& plan) {
+  cudaStream_t s = streams_[channel];
+  const size_t chunk_packs = plan.chunk_bytes / 16;
+  for (size_t done = 0; done < packs;) {
+    const size_t n = std::min(packs - done, chunk_packs * (size_t)kPipeMaxChunks);
+    PipeArgs a;
+    memset(&a, 0, sizeof(a));
+    a.nranks_here = 1;
+    a.npacks = n;
+    a.chunk_packs = chunk_packs;
+    a.nchunks = (int)((n + chunk_packs - 1) / chunk_packs);
+    a.slots = std::min(plan.slots, a.nchunks);
+    a.lag = std::min(plan.lag, a.nchunks);
+    a.base = pipe_base_[channel];
+    a.scale = scale;
+    a.idiv = idiv;
+    const size_t bytes = n * 16;
+    a.reducers = cfg_.pipeline_reducers > 0 ? cfg_.pipeline_reducers
+                 : nvls                     ? choose_blocks(bytes, world_, (int)Algo::NVLS, false, sm_count_, 0)
+                                            : 48;
+    PipeRank& r = a.r[0];
+    r.ctx = make_ctx(channel);
+    for (int p = 0; p < world_; p++) {
+      r.stage[p] = seg0_->peer[p] + staging_offset(channel);
+      r.progress[p] = (uint32_t*)(seg0_->peer[p] + pad_off_ + (size_t)channel * kChannelBytes + kFlagBytes + kMetaBytes);
+    }
+    r.mc_stage = seg0_->mc ? seg0_->mc + staging_offset(channel) : nullptr;
+    r.src = in + done * 16;
+    r.out = out + done * 16;
+    r.local = pipe_local_ + (size_t)channel * 2 * kPipeMaxChunks;
+    CUDA_RT(cudaMemsetAsync(r.local, 0, sizeof(uint32_t) * 2 * (size_t)a.nchunks, s));
+    LaunchCfg cfg;
+    cfg.blocks = a.reducers + std::max(1, cfg_.pipeline_copiers);
+    CUDA_RT(launch_staged_pipeline(a, dtype, nvls, cfg, s));
+    pipe_base_[channel] += (uint32_t)a.nchunks;
+    last_blocks = cfg.blocks;
+    last_launches++;
+    done += n;
+  }
 }
 
 Algo Comm::choose_algo(size_t bytes, DType dtype, bool in_place_or_fused, bool has_mc) const {
@@ -209,6 +269,27 @@ Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType
     last_blocks = cfg.blocks;
     last_launches = 1;
     return Algo::ONE_SHOT;
+  }
+
+  // Staged, large enough for the pipeline kernel: copier blocks and reducer blocks of ONE launch
+  // work on different chunks of a ring inside the channel's slice (staged_pipeline.cu).
+  if (cfg_.staged_pipeline > 0 && red == ReduceOp::SUM && bytes >= cfg_.pipeline_min_bytes && bytes >= 16) {
+    const Algo inplace = pick(bytes, true, seg0_->mc != nullptr);
+    const bool nvls = inplace == Algo::NVLS;
+    if (nvls || cfg_.staged_pipeline > 1) {
+      const size_t packs = bytes / 16;
+      launch_pipeline(channel, (const char*)in, (char*)out, packs, dtype, scale, idiv, nvls,
+                      plan_pipeline(cfg_, packs * 16, staging_slice_bytes()));
+      const size_t head = packs * (16 / es);
+      if (head < count) {
+        // the last few elements (less than one pack) take the small-tensor path
+        const int launches = last_launches, blocks = last_blocks;
+        allreduce(channel, (const char*)in + head * es, (char*)out + head * es, count - head, dtype, scale, idiv, false, red, false);
+        last_launches += launches;
+        last_blocks = blocks;
+      }
+      return nvls ? Algo::NVLS : Algo::TWO_SHOT;
+    }
   }
 
   // Staged. A tensor of at most one part (a quarter) of the channel's slice: ONE kernel copies
@@ -455,6 +536,7 @@ EmuGroup::EmuGroup(int device, int nranks, size_t bytes_per_rank) : device_(devi
   }
   CUDA_RT(cudaMalloc(&epochs_, sizeof(uint32_t) * (n_ * kChannels * kMaxBlocks + n_)));
   CUDA_RT(cudaMemset(epochs_, 0, sizeof(uint32_t) * (n_ * kChannels * kMaxBlocks + n_)));
+  CUDA_RT(cudaMalloc(&pipe_local_, sizeof(uint32_t) * n_ * 2 * kPipeMaxChunks));
   CUDA_RT(cudaHostAlloc(&status_host_, 64, cudaHostAllocMapped));
   memset(status_host_, 0, 64);
   CUDA_RT(cudaHostGetDevicePointer((void**)&status_dev_, status_host_, 0));
@@ -467,6 +549,7 @@ EmuGroup::~EmuGroup() {
   for (char* p : bufs_) if (p) cudaFree(p - kGuardBytes);
   for (char* p : pads_) if (p) cudaFree(p - kGuardBytes);
   if (epochs_) cudaFree(epochs_);
+  if (pipe_local_) cudaFree(pipe_local_);
   if (status_host_) cudaFreeHost(status_host_);
 }
 
@@ -582,6 +665,49 @@ cudaError_t EmuGroup::allgatherv(const void* const* ins, const unsigned long lon
   cfg.cooperative = true;
   cfg.blocks = std::min(std::min(blocks > 0 ? blocks : 2, (int)kMetaBlocks), max_emulated_blocks(device_, n_, cfg.threads));
   return launch_allgatherv(a, cfg, s);
+}
+
+cudaError_t EmuGroup::staged_pipeline(size_t off, const void* const* srcs, void* const* outs, size_t count, DType dtype,
+                                      float scale, int idiv, size_t chunk_bytes, int slots, int lag, int reducers, int copiers,
+                                      cudaStream_t s) {
+  const size_t bytes = count * dtype_size(dtype);
+  if (bytes == 0 || bytes % 16 || chunk_bytes == 0 || chunk_bytes % 16 || slots < 1 || reducers < 1 || copiers < 1)
+    return cudaErrorInvalidValue;
+  if (off + (size_t)slots * chunk_bytes > bytes_) return cudaErrorInvalidValue;
+  PipeArgs a;
+  memset(&a, 0, sizeof(a));
+  a.nranks_here = n_;
+  a.npacks = bytes / 16;
+  a.chunk_packs = chunk_bytes / 16;
+  const size_t nchunks = (a.npacks + a.chunk_packs - 1) / a.chunk_packs;
+  if (nchunks > (size_t)kPipeMaxChunks) return cudaErrorInvalidValue;
+  a.nchunks = (int)nchunks;
+  a.slots = std::min(slots, a.nchunks);
+  a.lag = lag;
+  a.reducers = reducers;
+  a.base = pipe_base_;
+  a.scale = scale;
+  a.idiv = idiv;
+  for (int r = 0; r < n_; r++) {
+    PipeRank& R = a.r[r];
+    R.ctx = ctx(r, 3);
+    for (int p = 0; p < n_; p++) {
+      R.stage[p] = bufs_[p] + off;
+      R.progress[p] = (uint32_t*)(pads_[p] + 3 * kChannelBytes + kFlagBytes + kMetaBytes);
+    }
+    R.src = (const char*)srcs[r];
+    R.out = (char*)outs[r];
+    R.local = pipe_local_ + (size_t)r * 2 * kPipeMaxChunks;
+  }
+  cudaError_t e = cudaMemsetAsync(pipe_local_, 0, sizeof(uint32_t) * n_ * 2 * kPipeMaxChunks, s);
+  if (e != cudaSuccess) return e;
+  LaunchCfg cfg;
+  cfg.cooperative = true;
+  cfg.blocks = reducers + copiers;
+  if (cfg.blocks > max_emulated_blocks(device_, n_, cfg.threads)) return cudaErrorInvalidConfiguration;
+  e = launch_staged_pipeline(a, dtype, false, cfg, s);
+  if (e == cudaSuccess) pipe_base_ += (uint32_t)a.nchunks;
+  return e;
 }
 
 cudaError_t EmuGroup::barrier_probe(int absent, double timeout_s, cudaStream_t s) {

@@ -30,8 +30,24 @@ struct CommConfig {
   int max_blocks = 0;                   // 0 = heuristic
   int overlap_blocks = 0;               // grid cap of launches that run beside the backward pass (0 = one per SM that a
                                         // 128-SM persistent kernel leaves free, at least 8)
+  // Tensors outside symmetric memory in one launch whose blocks have roles (staged_pipeline.cu):
+  // 0 = off, 1 = where the switch reduces (NVLS), 2 = also with peer loads and stores.
+  int staged_pipeline = 0;
+  size_t pipeline_min_bytes = 4u << 20;
+  size_t pipeline_chunk_bytes = 2u << 20;   // upper bound; a tensor is cut into at least eight chunks
+  int pipeline_slots = 16;                  // chunks that the staging ring holds
+  int pipeline_copiers = 64;                // blocks that copy in and out
+  int pipeline_reducers = 0;                // 0 = the grid of an in-place reduction of that size (peer variant: 48)
   SymmAllocator::Mode symm_mode = SymmAllocator::Mode::AUTO;
 };
+
+// How the staged pipeline kernel cuts a tensor of `bytes` bytes whose staging slice has
+// `slice_bytes`: a pure function, the same on every rank.
+struct PipePlan {
+  size_t chunk_bytes;
+  int nchunks, slots, lag;
+};
+PipePlan plan_pipeline(const CommConfig& cfg, size_t bytes, size_t slice_bytes);
 
 // The algorithm for a reduction of `bytes` bytes in a group of `world` ranks: a pure function of
 // its arguments, so every rank computes the same answer (and it can be checked without a GPU).
@@ -62,6 +78,7 @@ class Comm {
   uint32_t device_status() const { return status_host_ ? *(volatile uint32_t*)status_host_ : 0; }
   void set_device_timeout(double s) { cfg_.device_timeout_s = s; }
   void set_overlap_blocks(int n) { cfg_.overlap_blocks = n; }
+  CommConfig& mutable_config() { return cfg_; }
 
   // Algorithm for a reduction of `bytes` bytes (all ranks compute the same answer).
   Algo choose_algo(size_t bytes, DType dtype, bool in_place_or_fused, bool has_mc) const;
@@ -127,6 +144,14 @@ class Comm {
   }
   uint32_t* status_host_ = nullptr;   // pinned, mapped
   uint32_t* status_dev_ = nullptr;
+  // Staged pipeline kernel: arrival counters per user channel ([2][kPipeMaxChunks], zeroed on the
+  // stream before each launch) and the value that the channel's progress words hold once the
+  // queued launches have run.
+  uint32_t* pipe_local_ = nullptr;
+  uint32_t pipe_base_[dev::kUserChannels] = {0};
+  // Reduces the first `packs` 16-byte packs of a private tensor with the staged pipeline kernel.
+  void launch_pipeline(int channel, const char* in, char* out, size_t packs, DType dtype, float scale, int idiv, bool nvls,
+                       const PipePlan& plan);
   cudaStream_t streams_[dev::kChannels] = {nullptr};
   // Events of the pipeline that carries a large staged tensor (Comm::allreduce).
   static constexpr int kStageBuffers = 4;                      // parts of a channel's staging slice in rotation
@@ -169,6 +194,11 @@ class EmuGroup {
                          int phase1_blocks = 0);
   cudaError_t allgatherv(const void* const* ins, const unsigned long long* bytes, const unsigned long long* out_offs,
                          int blocks, cudaStream_t s);
+  // The staged pipeline kernel (peer loads and stores) on private tensors srcs[r] -> outs[r] of
+  // `count` elements (a multiple of 16 bytes), through rings of `slots` chunks of `chunk_bytes`
+  // at `off` of the ranks' buffers; `reducers` + `copiers` blocks per rank.
+  cudaError_t staged_pipeline(size_t off, const void* const* srcs, void* const* outs, size_t count, DType dtype, float scale,
+                              int idiv, size_t chunk_bytes, int slots, int lag, int reducers, int copiers, cudaStream_t s);
   // A barrier-only launch in which rank `absent` (if >= 0) does not take part, so that the
   // others run into the bounded wait. `timeout_s` bounds it.
   cudaError_t barrier_probe(int absent, double timeout_s, cudaStream_t s);
@@ -181,6 +211,8 @@ class EmuGroup {
   std::vector<char*> pads_;
   uint32_t* epochs_ = nullptr;  // [n][kChannels][kMaxBlocks], then one arrival counter per rank (mixed grids)
   uint32_t local_arrivals_ = 0; // what each rank's counter will hold once the queued launches have run
+  uint32_t* pipe_local_ = nullptr;  // [n][2][kPipeMaxChunks] arrival counters of the staged pipeline kernel
+  uint32_t pipe_base_ = 0;          // what the progress words hold once the queued launches have run
   uint32_t* status_host_ = nullptr;
   uint32_t* status_dev_ = nullptr;
   double timeout_s_ = 20.0;

@@ -118,6 +118,25 @@ class EmulatedGroup:
                                           ptrs(state2), C.byref(hyper), float(scale), blocks, C.c_void_p(s), int(phase1_blocks)),
                "emulated fused step")
 
+    def staged_pipeline(self, srcs: Sequence[torch.Tensor], outs: Sequence[torch.Tensor], scale: float = 1.0, idiv: int = 1,
+                        chunk_bytes: int = 64 << 10, slots: int = 4, lag: int = 2, reducers: int = 2, copiers: int = 3,
+                        offset_bytes: int = 0):
+        """Allreduce of the private tensors `srcs[r]` into `outs[r]` (may be the same tensors) with
+        the staged pipeline kernel: `copiers` blocks of every rank copy chunks into a ring of
+        `slots` chunks inside the rank's buffer and finished chunks out again, `reducers` blocks
+        reduce chunk after chunk with peer loads and stores. The tensors' size must be a
+        multiple of 16 bytes."""
+        n = self.nranks
+        sp = (C.c_void_p * n)()
+        op = (C.c_void_p * n)()
+        for r in range(n):
+            sp[r] = srcs[r].data_ptr()
+            op[r] = outs[r].data_ptr()
+        s = torch.cuda.current_stream(self.device).cuda_stream
+        _check(self.lib.bc_emu_staged_pipeline(self._g, offset_bytes, sp, op, srcs[0].numel(), _DTYPES[srcs[0].dtype], float(scale),
+                                               int(idiv), int(chunk_bytes), int(slots), int(lag), int(reducers), int(copiers),
+                                               C.c_void_p(s)), "emulated staged pipeline")
+
     def allgatherv(self, ins: Sequence[torch.Tensor], out_offsets: Sequence[int], blocks: int = 2):
         """Each rank r pushes `ins[r]` into every rank's buffer at `out_offsets[that rank]` plus
         the displacement of r's slab (computed on the device)."""
