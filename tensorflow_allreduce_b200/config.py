@@ -53,10 +53,12 @@ class Config:
     staged_pipeline: int = 0           # tensors outside symmetric memory from 4 MiB on in one launch whose blocks copy
                                        # chunks in and out while others reduce: 0 = off, 1 = where the switch
                                        # reduces (NVLS), 2 = with peer loads and stores as well
-    pipeline_chunk_kb: int = 2048      # largest chunk of that kernel
+    pipeline_chunk_kb: int = 4096      # largest chunk of that kernel
     pipeline_slots: int = 16           # chunks that its ring inside the staging slice holds
     pipeline_copiers: int = 64         # its blocks that copy
-    pipeline_reducers: int = 0         # its blocks that reduce (0 = as an in-place reduction of that size)
+    pipeline_reducers: int = 0         # its blocks that reduce (0 = 32 where the switch reduces, else 48)
+    pipeline_rgroups: int = 8          # groups of reducer blocks; group g takes the chunks c with c % groups == g
+    pipeline_cgroups: int = 8          # groups of copier blocks
     device_timing_every: int = 0       # DistributedOptimizer: time every bucket launch of every Nth step on the device
                                        # (CUDA events; records in stats() carry device_us and bus GB/s); 0 = never
     link_gbs: float = 764.0            # NVLink rate per direction per GPU that stats() reports fractions of
@@ -83,6 +85,8 @@ class Config:
             pipeline_slots=_env("BC_PIPELINE_SLOTS", int, cls.pipeline_slots),
             pipeline_copiers=_env("BC_PIPELINE_COPIERS", int, cls.pipeline_copiers),
             pipeline_reducers=_env("BC_PIPELINE_REDUCERS", int, cls.pipeline_reducers),
+            pipeline_rgroups=_env("BC_PIPELINE_RGROUPS", int, cls.pipeline_rgroups),
+            pipeline_cgroups=_env("BC_PIPELINE_CGROUPS", int, cls.pipeline_cgroups),
             device_timing_every=_env("BC_DEVICE_TIMING_EVERY", int, cls.device_timing_every),
             link_gbs=_env("BC_LINK_GBS", float, cls.link_gbs),
             fault=_env("BC_FAULT", str, cls.fault),

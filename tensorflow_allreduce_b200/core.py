@@ -144,7 +144,8 @@ def init(device=None, config: Optional[Config] = None, rank: Optional[int] = Non
     if dev_index >= 0:
         for key, value in (("staged_pipeline", cfg.staged_pipeline), ("pipeline_chunk_bytes", cfg.pipeline_chunk_kb << 10),
                            ("pipeline_slots", cfg.pipeline_slots), ("pipeline_copiers", cfg.pipeline_copiers),
-                           ("pipeline_reducers", cfg.pipeline_reducers)):
+                           ("pipeline_reducers", cfg.pipeline_reducers), ("pipeline_rgroups", cfg.pipeline_rgroups),
+                           ("pipeline_cgroups", cfg.pipeline_cgroups)):
             _call(lib.bc_set_option(key.encode(), int(value)), "bc_set_option")
     for k in _counters:
         _counters[k] = itertools.count()

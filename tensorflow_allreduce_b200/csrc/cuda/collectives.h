@@ -93,7 +93,7 @@ struct PipeRank {
   char* mc_stage;                   // multicast mapping of the ring (NVLS) or null
   const char* src;                  // private input (16-byte aligned)
   char* out;                        // private output (16-byte aligned; may equal src)
-  uint32_t* progress[dev::kMaxRanks];  // progress[p] = the progress words inside rank p's pad: [2][kMaxRanks]
+  uint32_t* progress[dev::kMaxRanks];  // progress[p] = the progress words inside rank p's pad: [2][kPipeMaxGroups][kMaxRanks]
   uint32_t* local;                  // this rank's arrival counters, zeroed before the launch: [2][nchunks]
 };
 
@@ -103,9 +103,12 @@ struct PipeArgs {
   size_t chunk_packs;         // packs per chunk (the last chunk may be shorter)
   int nchunks;
   int slots;                  // chunks that the staging ring holds
-  int lag;                    // chunks by which the copy-out trails the copy-in (< slots unless everything fits)
+  int lag;                    // chunks by which the copy-out trails the copy-in (< slots unless everything fits;
+                              // a multiple of cgroups)
   int reducers;               // the first `reducers` blocks of a rank reduce, the others copy
-  uint32_t base;              // value of the progress words before this launch
+  int rgroups, cgroups;       // groups of reducer / copier blocks; group g takes the chunks c with c % groups == g
+  uint32_t base;              // value of the progress words before this launch (a launch adds at most
+                              // ceil(nchunks / groups) to a word)
   float scale;
   int idiv;
   PipeRank r[dev::kMaxRanks];

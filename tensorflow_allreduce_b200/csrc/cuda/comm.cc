@@ -131,7 +131,8 @@ Algo select_algo(const CommConfig& cfg, int world, size_t bytes, DType dtype, bo
 
 PipePlan plan_pipeline(const CommConfig& cfg, size_t bytes, size_t slice_bytes) {
   PipePlan p;
-  const int slots = std::max(2, cfg.pipeline_slots);
+  const int gc = std::min(std::max(cfg.pipeline_cgroups, 1), (int)kPipeMaxGroups);
+  const int slots = std::max(2 * gc, cfg.pipeline_slots / gc * gc);
   // at least eight chunks, each a multiple of 4 KiB, `slots` of them inside the slice
   size_t chunk = std::min(cfg.pipeline_chunk_bytes, std::max<size_t>(bytes / 8, 64u << 10));
   chunk = std::min(chunk, slice_bytes / (size_t)slots);
@@ -139,9 +140,8 @@ PipePlan plan_pipeline(const CommConfig& cfg, size_t bytes, size_t slice_bytes) 
   p.chunk_bytes = chunk;
   const size_t n = (bytes + chunk - 1) / chunk;
   p.nchunks = (int)std::min<size_t>(n, (size_t)kPipeMaxChunks);   // the caller launches again for the rest
-  p.slots = std::min(slots, p.nchunks);
-  p.lag = std::max(1, p.slots / 2);
-  if (p.nchunks <= p.slots) p.lag = std::min(p.lag, p.nchunks);
+  p.slots = std::min(slots, p.nchunks);   // fewer chunks than slots: the ring does not wrap
+  p.lag = std::max(gc, slots / 2 / gc * gc);
   return p;
 }
 
@@ -158,14 +158,14 @@ void Comm::launch_pipeline(int channel, const char* in, char* out, size_t packs,
     a.chunk_packs = chunk_packs;
     a.nchunks = (int)((n + chunk_packs - 1) / chunk_packs);
     a.slots = std::min(plan.slots, a.nchunks);
-    a.lag = std::min(plan.lag, a.nchunks);
+    a.lag = plan.lag;
     a.base = pipe_base_[channel];
     a.scale = scale;
     a.idiv = idiv;
-    const size_t bytes = n * 16;
-    a.reducers = cfg_.pipeline_reducers > 0 ? cfg_.pipeline_reducers
-                 : nvls                     ? choose_blocks(bytes, world_, (int)Algo::NVLS, false, sm_count_, 0)
-                                            : 48;
+    a.rgroups = std::min(std::max(cfg_.pipeline_rgroups, 1), (int)kPipeMaxGroups);
+    a.cgroups = std::min(std::max(cfg_.pipeline_cgroups, 1), (int)kPipeMaxGroups);
+    a.reducers = cfg_.pipeline_reducers > 0 ? cfg_.pipeline_reducers : nvls ? 32 : 48;
+    a.reducers = (a.reducers + a.rgroups - 1) / a.rgroups * a.rgroups;
     PipeRank& r = a.r[0];
     r.ctx = make_ctx(channel);
     for (int p = 0; p < world_; p++) {
@@ -178,7 +178,7 @@ void Comm::launch_pipeline(int channel, const char* in, char* out, size_t packs,
     r.local = pipe_local_ + (size_t)channel * 2 * kPipeMaxChunks;
     CUDA_RT(cudaMemsetAsync(r.local, 0, sizeof(uint32_t) * 2 * (size_t)a.nchunks, s));
     LaunchCfg cfg;
-    cfg.blocks = a.reducers + std::max(1, cfg_.pipeline_copiers);
+    cfg.blocks = a.reducers + (std::max(1, cfg_.pipeline_copiers) + a.cgroups - 1) / a.cgroups * a.cgroups;
     CUDA_RT(launch_staged_pipeline(a, dtype, nvls, cfg, s));
     pipe_base_[channel] += (uint32_t)a.nchunks;
     last_blocks = cfg.blocks;
@@ -669,7 +669,7 @@ cudaError_t EmuGroup::allgatherv(const void* const* ins, const unsigned long lon
 
 cudaError_t EmuGroup::staged_pipeline(size_t off, const void* const* srcs, void* const* outs, size_t count, DType dtype,
                                       float scale, int idiv, size_t chunk_bytes, int slots, int lag, int reducers, int copiers,
-                                      cudaStream_t s) {
+                                      int rgroups, int cgroups, cudaStream_t s) {
   const size_t bytes = count * dtype_size(dtype);
   if (bytes == 0 || bytes % 16 || chunk_bytes == 0 || chunk_bytes % 16 || slots < 1 || reducers < 1 || copiers < 1)
     return cudaErrorInvalidValue;
@@ -685,6 +685,8 @@ cudaError_t EmuGroup::staged_pipeline(size_t off, const void* const* srcs, void*
   a.slots = std::min(slots, a.nchunks);
   a.lag = lag;
   a.reducers = reducers;
+  a.rgroups = rgroups;
+  a.cgroups = cgroups;
   a.base = pipe_base_;
   a.scale = scale;
   a.idiv = idiv;

@@ -34,10 +34,12 @@ struct CommConfig {
   // 0 = off, 1 = where the switch reduces (NVLS), 2 = also with peer loads and stores.
   int staged_pipeline = 0;
   size_t pipeline_min_bytes = 4u << 20;
-  size_t pipeline_chunk_bytes = 2u << 20;   // upper bound; a tensor is cut into at least eight chunks
+  size_t pipeline_chunk_bytes = 4u << 20;   // upper bound; a tensor is cut into at least eight chunks
   int pipeline_slots = 16;                  // chunks that the staging ring holds
   int pipeline_copiers = 64;                // blocks that copy in and out
-  int pipeline_reducers = 0;                // 0 = the grid of an in-place reduction of that size (peer variant: 48)
+  int pipeline_reducers = 0;                // blocks that reduce; 0 = 32 where the switch reduces, else 48
+  int pipeline_rgroups = 8;                 // groups of reducer blocks (one chunk each at a time)
+  int pipeline_cgroups = 8;                 // groups of copier blocks
   SymmAllocator::Mode symm_mode = SymmAllocator::Mode::AUTO;
 };
 
@@ -45,7 +47,7 @@ struct CommConfig {
 // `slice_bytes`: a pure function, the same on every rank.
 struct PipePlan {
   size_t chunk_bytes;
-  int nchunks, slots, lag;
+  int nchunks, slots, lag;   // slots and lag are multiples of the number of copier groups when the ring wraps
 };
 PipePlan plan_pipeline(const CommConfig& cfg, size_t bytes, size_t slice_bytes);
 
@@ -198,7 +200,8 @@ class EmuGroup {
   // `count` elements (a multiple of 16 bytes), through rings of `slots` chunks of `chunk_bytes`
   // at `off` of the ranks' buffers; `reducers` + `copiers` blocks per rank.
   cudaError_t staged_pipeline(size_t off, const void* const* srcs, void* const* outs, size_t count, DType dtype, float scale,
-                              int idiv, size_t chunk_bytes, int slots, int lag, int reducers, int copiers, cudaStream_t s);
+                              int idiv, size_t chunk_bytes, int slots, int lag, int reducers, int copiers, int rgroups,
+                              int cgroups, cudaStream_t s);
   // A barrier-only launch in which rank `absent` (if >= 0) does not take part, so that the
   // others run into the bounded wait. `timeout_s` bounds it.
   cudaError_t barrier_probe(int absent, double timeout_s, cudaStream_t s);

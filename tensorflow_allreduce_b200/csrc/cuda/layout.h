@@ -21,13 +21,14 @@ constexpr int kChannels = 3 * kUserChannels;
 // Layout of one channel inside a rank's signal pad (all offsets in bytes).
 constexpr size_t kFlagBytes = (size_t)kMaxBlocks * kMaxRanks * sizeof(uint32_t);          // 16 KiB
 constexpr size_t kMetaBytes = (size_t)kMetaBlocks * kMaxRanks * 2 * sizeof(uint64_t);     // 16 KiB
-// Progress words of the staged pipeline kernel: per peer one "chunks staged" and one "chunks
-// reduced" counter, which only grow.
-constexpr size_t kProgressBytes = 256;
+// Progress words of the staged pipeline kernel: per peer and group of blocks one "chunks staged"
+// and one "chunks reduced" counter, which only grow.
+constexpr int kPipeMaxGroups = 8;
+constexpr size_t kProgressBytes = 512;
 constexpr size_t kChannelBytes = kFlagBytes + kMetaBytes + kProgressBytes;
-constexpr size_t kPadBytes = kChannels * kChannelBytes;                                  // 387 KiB
+constexpr size_t kPadBytes = kChannels * kChannelBytes;                                  // 390 KiB
 constexpr int kPipeMaxChunks = 2048;   // chunks of one staged pipeline launch (local arrival counters: two per chunk)
-static_assert(2 * kMaxRanks * sizeof(uint32_t) <= kProgressBytes, "progress words do not fit");
+static_assert(2 * kPipeMaxGroups * kMaxRanks * sizeof(uint32_t) <= kProgressBytes, "progress words do not fit");
 
 // Status word written by a block whose wait ran out (host-mapped memory).
 constexpr uint32_t kStatusTimeout = 0x80000000u;

@@ -10,11 +10,11 @@
 // (tensorflow/contrib/mpi_collectives/ring.h:136-228, ring.cu.cc:41-66): one D2D copy, then N-1
 // send / receive / accumulate steps with a stream synchronise each.
 //
-// Synchronisation. Per rank two progress words per peer live in every rank's signal pad:
+// Synchronisation. Progress words live in every rank's signal pad, per peer q and group:
 //   staged[q]  = chunks that rank q has copied into its staging buffer,
 //   reduced[q] = chunks of which rank q has reduced its share,
-// counted from `base` on (the host adds up the chunks of all launches of a channel, so the words
-// only grow and need no reset). The last copier block that finishes chunk c on a rank (a local
+// counted from `base` on (the host adds up what all launches of a channel contribute, so the
+// words only grow and need no reset). The last copier block that finishes chunk c on a rank (a local
 // arrival counter tells) publishes staged = base + c + 1 into every rank's pad with
 // st.release.sys; reducers wait until all P staged words have reached their chunk; the last
 // reducer block that finishes chunk c publishes reduced the same way; copiers wait for all P
@@ -61,25 +61,32 @@ __device__ __forceinline__ bool wait_words(const RankCtx& c, const uint32_t* wor
 
 // The block has finished its part of a chunk: count it, and if it is the last of `nblocks`,
 // tell every rank (this rank's word of the given kind in each pad).
-__device__ __forceinline__ void arrive_and_publish(const PipeRank& R, uint32_t* counter, int nblocks, int kind, uint32_t value) {
+// ONE system-scope fence, then plain stores: a st.release per peer waits for the previous
+// peer's store to be acknowledged over NVLink before the next one leaves (measured on 4 GPUs,
+// 1 GiB in 2 MiB chunks and four groups: 3.93 ms with a release per peer, 3.16 ms like this).
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void arrive_and_publish(const PipeRank& R, uint32_t* counter, int nblocks, int word, uint32_t value) {
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence();
+    // the release half of the atomic orders this block's stores (bar.sync above) before the count
     if (atom_add_acq_rel_gpu(counter, 1u) == (uint32_t)nblocks - 1) {
-      for (int p = 0; p < R.ctx.world; p++) st_release_sys(R.progress[p] + kind * kMaxRanks + R.ctx.rank, value);
+      __threadfence_system();
+      for (int p = 0; p < R.ctx.world; p++) st_relaxed_sys(R.progress[p] + word * kMaxRanks + R.ctx.rank, value);
     }
   }
 }
 
 __device__ __forceinline__ void copy_run(char* dst, const char* src, size_t begin, size_t end, size_t first, size_t stride) {
+  constexpr int U = 8;   // loads in flight per thread
   size_t i = begin + first;
-  for (; i + 3 * stride < end; i += 4 * stride) {
-    const uint4 v0 = ld_stream16(src + i * 16), v1 = ld_stream16(src + (i + stride) * 16);
-    const uint4 v2 = ld_stream16(src + (i + 2 * stride) * 16), v3 = ld_stream16(src + (i + 3 * stride) * 16);
-    st_local16(dst + i * 16, v0);
-    st_local16(dst + (i + stride) * 16, v1);
-    st_local16(dst + (i + 2 * stride) * 16, v2);
-    st_local16(dst + (i + 3 * stride) * 16, v3);
+  for (; i + (U - 1) * stride < end; i += U * stride) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) v[u] = ld_stream16(src + (i + u * stride) * 16);
+#pragma unroll
+    for (int u = 0; u < U; u++) st_local16(dst + (i + u * stride) * 16, v[u]);
   }
   for (; i < end; i += stride) st_local16(dst + i * 16, ld_stream16(src + i * 16));
 }
@@ -98,7 +105,7 @@ template <> struct SwitchAdds<__half> { static constexpr bool value = true; };
 
 
 template <typename T, bool NVLS>
-__global__ void __launch_bounds__(512, 2) staged_pipeline_kernel(const __grid_constant__ PipeArgs a) {
+__global__ void __launch_bounds__(512, 1) staged_pipeline_kernel(const __grid_constant__ PipeArgs a) {
   using PK = Pack<T>;
   using Acc = typename PK::Acc;
   constexpr int E = PK::kElems;
@@ -106,14 +113,16 @@ __global__ void __launch_bounds__(512, 2) staged_pipeline_kernel(const __grid_co
   const RankCtx& c = R.ctx;
   const int P = c.world, me = c.rank;
   const int NB = a.reducers, NC = (int)gridDim.x - NB;
-  const uint32_t* staged = R.progress[me];                  // what the ranks have told THIS rank
-  const uint32_t* reduced = R.progress[me] + kMaxRanks;
+  const int GR = a.rgroups, GC = a.cgroups;
+  // what the ranks have told THIS rank: word (kind * kPipeMaxGroups + group) * kMaxRanks + rank
+  const uint32_t* words = R.progress[me];
 
   if ((int)blockIdx.x < NB) {
-    // ---- reducer ----
-    const size_t first = (size_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (size_t)NB * blockDim.x;
-    for (int ch = 0; ch < a.nchunks; ch++) {
-      if (!wait_words(c, staged, a.base + (uint32_t)ch + 1, 0x10000u)) return;
+    // ---- reducer of group blockIdx.x % GR ----
+    const int grp = (int)blockIdx.x % GR, nb = NB / GR;
+    const size_t first = (size_t)((int)blockIdx.x / GR) * blockDim.x + threadIdx.x, stride = (size_t)nb * blockDim.x;
+    for (int ch = grp; ch < a.nchunks; ch += GR) {
+      if (!wait_words(c, words + (ch % GC) * kMaxRanks, a.base + (uint32_t)(ch / GC) + 1, 0x10000u)) return;
       const size_t cb = (size_t)ch * a.chunk_packs, ce = cb + a.chunk_packs < a.npacks ? cb + a.chunk_packs : a.npacks;
       const size_t n = ce - cb;
       // this rank's share of the chunk, as pack offsets into the ring
@@ -176,22 +185,23 @@ __global__ void __launch_bounds__(512, 2) staged_pipeline_kernel(const __grid_co
           for (int p = 0; p < P; p++) st16(R.stage[p] + i * 16, r);
         }
       }
-      arrive_and_publish(R, R.local + a.nchunks + ch, NB, 1, a.base + (uint32_t)ch + 1);
+      arrive_and_publish(R, R.local + a.nchunks + ch, nb, kPipeMaxGroups + grp, a.base + (uint32_t)(ch / GR) + 1);
     }
     return;
   }
 
-  // ---- copier ----
-  const size_t first = (size_t)((int)blockIdx.x - NB) * blockDim.x + threadIdx.x, stride = (size_t)NC * blockDim.x;
-  for (int ch = 0; ch < a.nchunks + a.lag; ch++) {
+  // ---- copier of group (blockIdx.x - NB) % GC ----
+  const int cid = (int)blockIdx.x - NB, grp = cid % GC, nc = NC / GC;
+  const size_t first = (size_t)(cid / GC) * blockDim.x + threadIdx.x, stride = (size_t)nc * blockDim.x;
+  for (int ch = grp; ch < a.nchunks + a.lag; ch += GC) {
     if (ch < a.nchunks) {
       const size_t cb = (size_t)ch * a.chunk_packs, ce = cb + a.chunk_packs < a.npacks ? cb + a.chunk_packs : a.npacks;
       copy_run(R.stage[me] + (size_t)(ch % a.slots) * a.chunk_packs * 16, R.src + cb * 16, 0, ce - cb, first, stride);
-      arrive_and_publish(R, R.local + ch, NC, 0, a.base + (uint32_t)ch + 1);
+      arrive_and_publish(R, R.local + ch, nc, grp, a.base + (uint32_t)(ch / GC) + 1);
     }
-    const int o = ch - a.lag;
+    const int o = ch - a.lag;          // a chunk of this group as well: the lag is a multiple of GC
     if (o >= 0) {
-      if (!wait_words(c, reduced, a.base + (uint32_t)o + 1, 0x20000u)) return;
+      if (!wait_words(c, words + (kPipeMaxGroups + o % GR) * kMaxRanks, a.base + (uint32_t)(o / GR) + 1, 0x20000u)) return;
       const size_t ob = (size_t)o * a.chunk_packs, oe = ob + a.chunk_packs < a.npacks ? ob + a.chunk_packs : a.npacks;
       copy_run(R.out + ob * 16, R.stage[me] + (size_t)(o % a.slots) * a.chunk_packs * 16, 0, oe - ob, first, stride);
     }
@@ -211,8 +221,11 @@ cudaError_t launch_typed(const PipeArgs& a, bool nvls, const LaunchCfg& cfg, cud
 
 cudaError_t launch_staged_pipeline(const PipeArgs& a, DType dtype, bool nvls, const LaunchCfg& cfg, cudaStream_t s) {
   if (a.nchunks < 1 || a.nchunks > kPipeMaxChunks || a.reducers < 1 || cfg.blocks <= a.reducers || cfg.threads != 512) return cudaErrorInvalidConfiguration;
-  if (a.chunk_packs == 0 || (size_t)a.nchunks * a.chunk_packs < a.npacks || a.slots < 1 || a.lag < 0 || (a.lag >= a.slots && a.nchunks > a.slots))
-    return cudaErrorInvalidValue;
+  if (a.rgroups < 1 || a.rgroups > kPipeMaxGroups || a.cgroups < 1 || a.cgroups > kPipeMaxGroups) return cudaErrorInvalidConfiguration;
+  if (a.reducers % a.rgroups || (cfg.blocks - a.reducers) % a.cgroups) return cudaErrorInvalidConfiguration;
+  if (a.chunk_packs == 0 || (size_t)a.nchunks * a.chunk_packs < a.npacks || a.slots < 1 || a.lag < 0 || a.lag % a.cgroups) return cudaErrorInvalidValue;
+  // a ring that wraps: the copy-out stays fewer chunks behind than the ring holds, and a slot keeps its group
+  if (a.nchunks > a.slots && (a.lag >= a.slots || a.slots % a.cgroups)) return cudaErrorInvalidValue;
   switch (dtype) {
     case DType::F32: return launch_typed<float>(a, nvls, cfg, s);
     case DType::BF16: return launch_typed<__nv_bfloat16>(a, nvls, cfg, s);

@@ -366,28 +366,32 @@ def test_staged_pipeline_kernel_with_copier_and_reducer_blocks(emu, nranks):
     # chunks into a ring inside the staging area and finished chunks out again, reducers reduce
     # chunk after chunk, and progress words (not barriers) order them. Same kernel here with peer
     # loads: one chunk, a ring that is exactly full, a ring that wraps several times with a ragged
-    # last chunk, in place and into separate outputs, launches in a row (the words run on).
+    # last chunk, in place and into separate outputs, launches in a row (the words run on), one
+    # group of blocks per role or several that take every groups-th chunk each.
     g = emu(nranks)
     chunk = 4096
     packs_per_chunk = chunk // 16
     for dtype in (torch.float32, torch.bfloat16, torch.int32):
         e = PACK[dtype]
-        for packs, slots, lag, red, cop in ((1, 4, 2, 2, 3), (packs_per_chunk - 1, 4, 2, 1, 1), (4 * packs_per_chunk, 4, 2, 2, 3),
-                                            (11 * packs_per_chunk + 37, 4, 2, 3, 2), (7 * packs_per_chunk + 1, 2, 1, 2, 4),
-                                            (3 * packs_per_chunk, 8, 5, 2, 2)):
+        for packs, slots, lag, red, cop, gr, gc in ((1, 4, 2, 2, 3, 1, 1), (packs_per_chunk - 1, 4, 2, 1, 1, 1, 1),
+                                                    (4 * packs_per_chunk, 4, 2, 2, 3, 1, 1), (11 * packs_per_chunk + 37, 4, 2, 3, 2, 3, 2),
+                                                    (7 * packs_per_chunk + 1, 2, 1, 2, 4, 2, 1), (3 * packs_per_chunk, 8, 5, 2, 2, 1, 1),
+                                                    (29 * packs_per_chunk + 5, 8, 4, 4, 8, 4, 4), (2 * packs_per_chunk, 6, 3, 4, 6, 2, 3),
+                                                    (13 * packs_per_chunk, 6, 3, 2, 3, 2, 3)):
             n = packs * e
             xs = [_fill(dtype, n, 31 * r + packs % 13) for r in range(nranks)]
             keep = [x.clone() for x in xs]
             scale, idiv = (1.0 / nranks, 1) if dtype.is_floating_point else (1.0, 1)
             want = _reference_sum(keep, dtype, scale=scale, idiv=idiv)
             outs = [torch.full((n,), 3, dtype=dtype, device="cuda") for _ in range(nranks)]
-            g.staged_pipeline(xs, outs, scale=scale, idiv=idiv, chunk_bytes=chunk, slots=slots, lag=lag, reducers=red, copiers=cop)
+            kw = dict(scale=scale, idiv=idiv, chunk_bytes=chunk, slots=slots, lag=lag, reducers=red, copiers=cop, rgroups=gr, cgroups=gc)
+            g.staged_pipeline(xs, outs, **kw)
             torch.cuda.synchronize()
             assert g.status == 0, hex(g.status)
             for r in range(nranks):
                 assert torch.equal(outs[r], want), f"rank {r} packs={packs} {dtype}"
                 assert torch.equal(xs[r], keep[r])
-            g.staged_pipeline(xs, xs, scale=scale, idiv=idiv, chunk_bytes=chunk, slots=slots, lag=lag, reducers=red, copiers=cop)
+            g.staged_pipeline(xs, xs, **kw)
             torch.cuda.synchronize()
             assert g.status == 0, hex(g.status)
             for r in range(nranks):
@@ -396,3 +400,5 @@ def test_staged_pipeline_kernel_with_copier_and_reducer_blocks(emu, nranks):
     xs = [_fill(torch.float32, 64 * packs_per_chunk, r) for r in range(nranks)]
     with pytest.raises(RuntimeError):
         g.staged_pipeline(xs, xs, chunk_bytes=chunk, slots=2, lag=2)
+    with pytest.raises(RuntimeError):                       # a slot would change hands between groups of copiers
+        g.staged_pipeline(xs, xs, chunk_bytes=chunk, slots=5, lag=2, copiers=4, cgroups=2)
