@@ -567,7 +567,11 @@ int choose_blocks(size_t bytes, int world, int algo, bool fused_opt, int sm_coun
   //              on 4 GPUs in place, 64 MiB runs at 618 GB/s bus bandwidth with 16 blocks, 607
   //              with 32, 589 with 64, 545 with 128 (16 MiB: 488 / 462 / 402 / 405), and only
   //              from 512 MiB on 32 blocks are ahead of 16 (682 against 679). One block per
-  //              64 KiB, up to 16, and up to 32 above 256 MiB.
+  //              64 KiB, up to 16, and up to 32 above 256 MiB. On 8 GPUs a rank's share of the
+  //              switch traffic is spread over more, shorter requests and 64 blocks measured
+  //              best or within 2 % of it at every size (16 MiB: 300 GB/s with 32 blocks, 348
+  //              with 64, 327-344 with 128; 256 MiB: 638 / 671 / 641-672; 512 MiB: 731 / 750 /
+  //              738-753; fewer than 32 were not measured there): more than 4 ranks, up to 64.
   //   fused update: the second phase streams the parameters and the optimizer state through
   //              HBM (6 to 9 times the gradient bytes) and wants every SM: two blocks per SM.
   //   beside compute: gradient buckets that go out while backward runs share the GPU with
@@ -584,7 +588,7 @@ int choose_blocks(size_t bytes, int world, int algo, bool fused_opt, int sm_coun
   int cap = 128;
   if (algo == (int)Algo::NVLS) {
     per_block = 64u << 10;
-    cap = bytes <= (256u << 20) ? 16 : 32;
+    cap = world > 4 ? 64 : bytes <= (256u << 20) ? 16 : 32;
   } else if (world == 2) {
     cap = sm_count;
   }

@@ -371,9 +371,12 @@ def test_algorithm_selector_table(native_lib):
     assert blocks(1, 8, TWO, 0, 148, 0, 0) == 1 and blocks(32 << 10, 8, TWO, 0, 148, 0, 0) == 1 and blocks((32 << 10) + 1, 8, TWO, 0, 148, 0, 0) == 2
     assert blocks(1 << 30, 8, TWO, 0, 148, 0, 0) == 128 and blocks(1 << 30, 4, TWO, 0, 148, 0, 0) == 128 and blocks(1 << 30, 2, TWO, 0, 148, 0, 0) == 148
     assert blocks(256 << 10, 8, ONE, 0, 148, 0, 0) == 8 and blocks(64 << 20, 2, ONE, 0, 148, 0, 0) == 148
-    # NVLS: one block per 64 KiB, at most 16 up to 256 MiB and 32 above (the switch does the work; few blocks issue it best)
-    assert blocks(512 << 10, 8, NVLS, 0, 148, 0, 0) == 8 and blocks(1 << 20, 8, NVLS, 0, 148, 0, 0) == 16
-    assert blocks(256 << 20, 8, NVLS, 0, 148, 0, 0) == 16 and blocks(512 << 20, 8, NVLS, 0, 148, 0, 0) == 32
+    # NVLS: one block per 64 KiB, at most 16 up to 256 MiB and 32 above (the switch does the work; few blocks issue it
+    # best), with more than 4 ranks at most 64
+    assert blocks(512 << 10, 4, NVLS, 0, 148, 0, 0) == 8 and blocks(1 << 20, 4, NVLS, 0, 148, 0, 0) == 16
+    assert blocks(256 << 20, 4, NVLS, 0, 148, 0, 0) == 16 and blocks(512 << 20, 4, NVLS, 0, 148, 0, 0) == 32
+    assert blocks(512 << 10, 8, NVLS, 0, 148, 0, 0) == 8 and blocks(2 << 20, 8, NVLS, 0, 148, 0, 0) == 32
+    assert blocks(256 << 20, 8, NVLS, 0, 148, 0, 0) == 64 and blocks(1 << 30, 8, NVLS, 0, 148, 0, 0) == 64
     # a fused update wants every SM twice; beside the backward pass only what a 128-SM kernel leaves free
     assert blocks(1 << 30, 8, NVLS, 1, 148, 0, 0) == 296 and blocks(1 << 30, 8, NVLS, 1, 148, 0, 1) == 20
     assert blocks(1 << 30, 8, NVLS, 1, 132, 0, 1) == 8 and blocks(64 << 10, 8, TWO, 1, 148, 0, 1) == 2
