@@ -14,8 +14,11 @@ Arms:
   ours_staged allreduce of an ordinary tensor through the name-keyed API (negotiation + staging area)
   ours_private the same ordinary tensor with an ordered launch (`allreduce_direct_`): staging without negotiation,
               which is what NCCL's ordered `all_reduce` is comparable with
-  ours_pipeline (not in the default list) ours_private with the staged pipeline kernel switched on: one launch whose
-              copier blocks and reducer blocks work on different chunks of a ring in the staging area
+  ours_pipeline (not in the default list) ours_private with the staged pipeline kernel forced from 4 MiB on (the
+              library uses it from 48 MiB): one launch whose copier blocks and reducer blocks work on different
+              chunks of a ring in the staging area
+  ours_nopipeline (not in the default list) ours_private with that kernel switched off: one kernel that copies in,
+              reduces and copies out up to a quarter of the staging slice, a pipeline of kernels on three streams above
   nccl        torch.distributed.all_reduce / all_gather on the same sizes
   (--fake-hosts H: the ranks report H host names, so ours_staged runs in two levels: NVLink kernels
    inside a "host", pinned memory and socket rings between them)
@@ -138,7 +141,7 @@ def markdown(rows, world, link_measured=764.0, link_nominal=900.0):
             sel = [r for r in rows if r["op"] == op and r["dtype"] == dname]
             if not sel:
                 continue
-            arms = [k[:-6] for k in ("ours_direct_busbw", "ours_symm_busbw", "ours_staged_busbw", "ours_private_busbw", "ours_pipeline_busbw", "ours_busbw", "nccl_busbw",
+            arms = [k[:-6] for k in ("ours_direct_busbw", "ours_symm_busbw", "ours_staged_busbw", "ours_private_busbw", "ours_pipeline_busbw", "ours_nopipeline_busbw", "ours_busbw", "nccl_busbw",
                                       "nccl_padded_busbw", "ref_ring_busbw") if any(k in r for r in sel)]
             out.append(f"\n### {op}, {world} GPUs, {dname}\n")
             head = ["bytes"] + [f"{a_} ms" for a_ in arms if a_.startswith("ours")] + [f"{a_} GB/s" for a_ in arms]
@@ -153,7 +156,7 @@ def markdown(rows, world, link_measured=764.0, link_nominal=900.0):
                 cells += [f'{r[a_ + "_busbw"]:.1f}' if a_ + "_busbw" in r else "-" for a_ in arms]
                 best = max([r[a_ + "_busbw"] for a_ in arms if a_.startswith("ours") and a_ + "_busbw" in r] or [0.0])
                 cells += [f"{best / link_measured:.2f}", f"{best / link_nominal:.2f}"]
-                flags = [k.split("_")[0] + ("=ok" if r[k] else "=WRONG") for k in ("direct_correct", "symm_correct", "staged_correct", "private_correct", "pipeline_correct", "correct") if k in r]
+                flags = [k.split("_")[0] + ("=ok" if r[k] else "=WRONG") for k in ("direct_correct", "symm_correct", "staged_correct", "private_correct", "pipeline_correct", "nopipeline_correct", "correct") if k in r]
                 cells.append(" ".join(flags) or "-")
                 if any("direct_phases_us" in x for x in sel):
                     cells.append(" / ".join(f"{v:.1f}" for v in r["direct_phases_us"]) if "direct_phases_us" in r else "-")
@@ -277,26 +280,29 @@ def main():
                 row["ours_private_ms"] = ms
                 row["ours_private_busbw"] = nbytes / (ms * 1e-3) * factor / 1e9
                 del y
-            if "ours_pipeline" in arms:
-                # the same ordered launch with the staged pipeline kernel switched on for this arm
+            for arm, mode, min_mb in (("ours_pipeline", a.pipeline_mode, 4), ("ours_nopipeline", 0, 0)):
+                # the same ordered launch with the staged pipeline kernel forced from 4 MiB on / switched off for this arm
+                if arm not in arms:
+                    continue
                 from tensorflow_allreduce_b200 import _lib
                 from tensorflow_allreduce_b200.ops.direct import allreduce_direct_
-                before = cfg.staged_pipeline
-                _lib.lib().bc_set_option(b"staged_pipeline", a.pipeline_mode)
+                _lib.lib().bc_set_option(b"staged_pipeline", mode)
+                _lib.lib().bc_set_option(b"pipeline_min_bytes", max(min_mb, 1) << 20)
                 y = x.clone()
                 allreduce_direct_(y)
                 ref = x.clone()
                 if use_nccl:
                     dist.all_reduce(ref)
                     tol = 1e-5 * P if dtype == torch.float32 else 1e-2 * P
-                    row["pipeline_correct"] = bool(torch.allclose(y.float(), ref.float(), rtol=tol, atol=tol))
+                    row[arm[5:] + "_correct"] = bool(torch.allclose(y.float(), ref.float(), rtol=tol, atol=tol))
                 y.zero_()
                 del ref
                 ms = timed(lambda: allreduce_direct_(y), iters)
-                row["ours_pipeline_ms"] = ms
-                row["ours_pipeline_busbw"] = nbytes / (ms * 1e-3) * factor / 1e9
+                row[arm + "_ms"] = ms
+                row[arm + "_busbw"] = nbytes / (ms * 1e-3) * factor / 1e9
                 del y
-                _lib.lib().bc_set_option(b"staged_pipeline", before)
+                _lib.lib().bc_set_option(b"staged_pipeline", cfg.staged_pipeline)
+                _lib.lib().bc_set_option(b"pipeline_min_bytes", cfg.pipeline_min_mb << 20)
                 bc.check_device_status()
             if "nccl" in arms and use_nccl:
                 y = x.clone()

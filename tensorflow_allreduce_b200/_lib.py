@@ -62,7 +62,7 @@ def _declare(lib):
         "bc_two_level_allreduce_host": (i, [vp, ll, i, i, i]),
         "bc_select_algo": (i, [i, ll, i, i, i, i, ll, ll, i]),
         "bc_choose_blocks": (i, [ll, i, i, i, i, i, i]),
-        "bc_plan_pipeline": (i, [ll, ll, ll, i, i, P(ll)]),
+        "bc_plan_pipeline": (i, [ll, ll, ll, i, i, ll, P(ll)]),
         "bc_plan_gather_rounds": (ll, [i, P(C.c_ulonglong), ll, P(C.c_ulonglong)]),
         "bc_allreduce_async": (ll, [cp, vp, vp, i, i, P(ll), i, i, i, vp, i]),
         "bc_allgather_async": (ll, [cp, vp, i, i, P(ll), i, ALLOC_FN, vp, vp]),
@@ -97,7 +97,7 @@ def _declare(lib):
         "bc_emu_damaged_guard_bytes": (ll, [vp]),
         "bc_emu_allreduce": (i, [vp, ll, P(vp), ll, i, i, f, i, i, vp, i, P(vp), P(C.c_ulonglong), vp, i]),
         "bc_emu_fused_step": (i, [vp, ll, ll, i, P(vp), P(vp), P(vp), P(vp), P(OptHyper), f, i, vp, i]),
-        "bc_emu_staged_pipeline": (i, [vp, ll, P(vp), P(vp), ll, i, f, i, ll, i, i, i, i, i, i, vp]),
+        "bc_emu_staged_pipeline": (i, [vp, ll, P(vp), P(vp), ll, i, f, i, ll, i, i, i, i, i, i, i, vp]),
         "bc_emu_allgatherv": (i, [vp, P(vp), P(C.c_ulonglong), P(C.c_ulonglong), i, vp]),
         "bc_emu_barrier_probe": (i, [vp, i, d, vp]),
         "bc_max_emulated_blocks": (i, [i, i]),

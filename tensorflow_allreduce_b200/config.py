@@ -50,15 +50,17 @@ class Config:
     bucket_mb: float = 32.0            # DistributedOptimizer gradient bucket size
     overlap_blocks: int = 0            # CTAs of a bucket launch that runs beside backward (0 = one per SM left free
                                        # by a 128-SM persistent kernel, at least 8)
-    staged_pipeline: int = 0           # tensors outside symmetric memory from 4 MiB on in one launch whose blocks copy
-                                       # chunks in and out while others reduce: 0 = off, 1 = where the switch
-                                       # reduces (NVLS), 2 = with peer loads and stores as well
-    pipeline_chunk_kb: int = 4096      # largest chunk of that kernel
+    staged_pipeline: int = 1           # large tensors outside symmetric memory in one launch whose blocks copy chunks
+                                       # in and out while others reduce: 0 = off, 1 = where the switch reduces
+                                       # (NVLS), 2 = with peer loads and stores as well
+    pipeline_min_mb: int = 48          # ... from this size on
+    pipeline_chunk_kb: int = 8192      # largest chunk of that kernel
     pipeline_slots: int = 16           # chunks that its ring inside the staging slice holds
-    pipeline_copiers: int = 64         # its blocks that copy
+    pipeline_copiers: int = 128        # its blocks that copy
     pipeline_reducers: int = 0         # its blocks that reduce (0 = 32 where the switch reduces, else 48)
+    pipeline_streaming: bool = True    # its reducer blocks never drain between chunks (one warp waits and publishes)
     pipeline_rgroups: int = 8          # groups of reducer blocks; group g takes the chunks c with c % groups == g
-    pipeline_cgroups: int = 8          # groups of copier blocks
+    pipeline_cgroups: int = 4          # groups of copier blocks
     device_timing_every: int = 0       # DistributedOptimizer: time every bucket launch of every Nth step on the device
                                        # (CUDA events; records in stats() carry device_us and bus GB/s); 0 = never
     link_gbs: float = 764.0            # NVLink rate per direction per GPU that stats() reports fractions of
@@ -81,10 +83,12 @@ class Config:
             bucket_mb=_env("BC_BUCKET_MB", float, cls.bucket_mb),
             overlap_blocks=_env("BC_OVERLAP_BLOCKS", int, cls.overlap_blocks),
             staged_pipeline=_env("BC_STAGED_PIPELINE", int, cls.staged_pipeline),
+            pipeline_min_mb=_env("BC_PIPELINE_MIN_MB", int, cls.pipeline_min_mb),
             pipeline_chunk_kb=_env("BC_PIPELINE_CHUNK_KB", int, cls.pipeline_chunk_kb),
             pipeline_slots=_env("BC_PIPELINE_SLOTS", int, cls.pipeline_slots),
             pipeline_copiers=_env("BC_PIPELINE_COPIERS", int, cls.pipeline_copiers),
             pipeline_reducers=_env("BC_PIPELINE_REDUCERS", int, cls.pipeline_reducers),
+            pipeline_streaming=_env("BC_PIPELINE_STREAMING", _flag, cls.pipeline_streaming),
             pipeline_rgroups=_env("BC_PIPELINE_RGROUPS", int, cls.pipeline_rgroups),
             pipeline_cgroups=_env("BC_PIPELINE_CGROUPS", int, cls.pipeline_cgroups),
             device_timing_every=_env("BC_DEVICE_TIMING_EVERY", int, cls.device_timing_every),

@@ -142,9 +142,10 @@ def init(device=None, config: Optional[Config] = None, rank: Optional[int] = Non
     if dev_index >= 0 and cfg.overlap_blocks > 0:
         _call(lib.bc_set_option(b"overlap_blocks", cfg.overlap_blocks), "bc_set_option")
     if dev_index >= 0:
-        for key, value in (("staged_pipeline", cfg.staged_pipeline), ("pipeline_chunk_bytes", cfg.pipeline_chunk_kb << 10),
+        for key, value in (("staged_pipeline", cfg.staged_pipeline), ("pipeline_min_bytes", cfg.pipeline_min_mb << 20), ("pipeline_chunk_bytes", cfg.pipeline_chunk_kb << 10),
                            ("pipeline_slots", cfg.pipeline_slots), ("pipeline_copiers", cfg.pipeline_copiers),
                            ("pipeline_reducers", cfg.pipeline_reducers), ("pipeline_rgroups", cfg.pipeline_rgroups),
+                           ("pipeline_streaming", int(cfg.pipeline_streaming)),
                            ("pipeline_cgroups", cfg.pipeline_cgroups)):
             _call(lib.bc_set_option(key.encode(), int(value)), "bc_set_option")
     for k in _counters:

@@ -46,8 +46,10 @@ int bc_select_algo(int world, long long bytes, int dtype, int in_place_or_fused,
                    long long one_shot_max_bytes, long long nvls_min_bytes, int use_nvls);
 int bc_choose_blocks(long long bytes, int world, int algo, int fused_update, int sm_count, int cap_override, int beside_compute);
 /* How the staged pipeline kernel cuts a tensor (pure function): out4 = chunk bytes, chunks of
- * one launch, ring slots, lag of the copy-out. chunk_bytes / slots / cgroups <= 0: the defaults. */
-int bc_plan_pipeline(long long bytes, long long slice_bytes, long long chunk_bytes, int slots, int cgroups, long long* out4);
+ * one launch, ring slots, lag of the copy-out. chunk_bytes / slots / cgroups <= 0: the defaults;
+ * unit_bytes > 0: chunks are multiples of it instead of 4 KiB. */
+int bc_plan_pipeline(long long bytes, long long slice_bytes, long long chunk_bytes, int slots, int cgroups, long long unit_bytes,
+                     long long* out4);
 /* How a gathered result larger than the staging area is cut into rounds (pure function): returns
  * the number of rounds and writes every rank's piece size per round. */
 long long bc_plan_gather_rounds(int world, const unsigned long long* all_bytes, long long staging_bytes, unsigned long long* pieces_out);
@@ -140,7 +142,7 @@ int bc_emu_fused_step(void* g, long long off, long long count, int dtype, void* 
  * private tensors; the rings of `slots` chunks of `chunk_bytes` start at `off` of the buffers. */
 int bc_emu_staged_pipeline(void* g, long long off, const void* const* srcs, void* const* outs, long long count, int dtype,
                            float scale, int idiv, long long chunk_bytes, int slots, int lag, int reducers, int copiers,
-                           int rgroups, int cgroups, void* stream);
+                           int rgroups, int cgroups, int streaming, void* stream);
 int bc_emu_allgatherv(void* g, const void* const* ins, const unsigned long long* bytes, const unsigned long long* out_offs,
                       int blocks, void* stream);
 int bc_emu_barrier_probe(void* g, int absent, double timeout_s, void* stream);

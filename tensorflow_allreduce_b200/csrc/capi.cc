@@ -141,13 +141,14 @@ int bc_select_algo(int world, long long bytes, int dtype, int in_place_or_fused,
   API_END(-1)
 }
 
-int bc_plan_pipeline(long long bytes, long long slice_bytes, long long chunk_bytes, int slots, int cgroups, long long* out4) {
+int bc_plan_pipeline(long long bytes, long long slice_bytes, long long chunk_bytes, int slots, int cgroups, long long unit_bytes,
+                     long long* out4) {
   API_BEGIN
   gpu::CommConfig cfg;
   if (cgroups > 0) cfg.pipeline_cgroups = cgroups;
   if (chunk_bytes > 0) cfg.pipeline_chunk_bytes = (size_t)chunk_bytes;
   if (slots > 0) cfg.pipeline_slots = slots;
-  const gpu::PipePlan p = gpu::plan_pipeline(cfg, (size_t)bytes, (size_t)slice_bytes);
+  const gpu::PipePlan p = gpu::plan_pipeline(cfg, (size_t)bytes, (size_t)slice_bytes, (size_t)std::max<long long>(unit_bytes, 0));
   out4[0] = (long long)p.chunk_bytes;
   out4[1] = p.nchunks;
   out4[2] = p.slots;
@@ -403,6 +404,8 @@ int bc_set_option(const char* key, long long value) {
     comm().mutable_config().pipeline_slots = (int)std::min<long long>(std::max<long long>(value, 2), 1024);
   } else if (k == "pipeline_copiers") {
     comm().mutable_config().pipeline_copiers = (int)std::min<long long>(std::max<long long>(value, 1), 200);
+  } else if (k == "pipeline_streaming") {
+    comm().mutable_config().pipeline_streaming = value != 0;
   } else if (k == "pipeline_rgroups") {
     comm().mutable_config().pipeline_rgroups = (int)std::min<long long>(std::max<long long>(value, 1), dev::kPipeMaxGroups);
   } else if (k == "pipeline_cgroups") {
@@ -487,11 +490,11 @@ int bc_emu_fused_step(void* g, long long off, long long count, int dtype, void* 
 
 int bc_emu_staged_pipeline(void* g, long long off, const void* const* srcs, void* const* outs, long long count, int dtype,
                            float scale, int idiv, long long chunk_bytes, int slots, int lag, int reducers, int copiers,
-                           int rgroups, int cgroups, void* stream) {
+                           int rgroups, int cgroups, int streaming, void* stream) {
   API_BEGIN
   check_cuda(((gpu::EmuGroup*)g)->staged_pipeline((size_t)off, srcs, outs, (size_t)count, (DType)dtype, scale, idiv,
                                                   (size_t)chunk_bytes, slots, lag, reducers, copiers, rgroups, cgroups,
-                                                  (cudaStream_t)stream),
+                                                  streaming != 0, (cudaStream_t)stream),
              "emulated staged pipeline launch");
   return 0;
   API_END(-1)

@@ -107,6 +107,8 @@ struct PipeArgs {
                               // a multiple of cgroups)
   int reducers;               // the first `reducers` blocks of a rank reduce, the others copy
   int rgroups, cgroups;       // groups of reducer / copier blocks; group g takes the chunks c with c % groups == g
+  int streaming;              // reducer blocks never drain between chunks: 15 warps move data, one warp watches
+                              // the progress words and publishes finished chunks
   uint32_t base;              // value of the progress words before this launch (a launch adds at most
                               // ceil(nchunks / groups) to a word)
   float scale;
@@ -142,6 +144,12 @@ struct LaunchCfg {
 // Launch the reduction. `param_dtype` is F32, or equal to `dtype` for 16-bit parameters.
 cudaError_t launch_allreduce(const ArArgs& a, DType dtype, DType param_dtype, const LaunchCfg& cfg, cudaStream_t s);
 cudaError_t launch_allgatherv(const AgArgs& a, const LaunchCfg& cfg, cudaStream_t s);
+// A streaming reducer block (544 threads: 16 warps that move data, one that waits and publishes)
+// moves kPipeDataThreads x batch packs per step; a chunk whose share per rank is a multiple of
+// that keeps every lane busy in every batch.
+constexpr int kPipeDataThreads = 512;
+constexpr int kPipeStreamingThreads = kPipeDataThreads + 32;
+constexpr int kPipeSwitchBatch = 4, kPipePeerBatch = 2;
 // Sum (scaled) of private tensors through the staging rings; `nvls` needs a float type.
 cudaError_t launch_staged_pipeline(const PipeArgs& a, DType dtype, bool nvls, const LaunchCfg& cfg, cudaStream_t s);
 // Plain device copy kernel (staging of tensors that are not in symmetric memory).

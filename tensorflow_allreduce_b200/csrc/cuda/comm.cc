@@ -129,25 +129,53 @@ Algo select_algo(const CommConfig& cfg, int world, size_t bytes, DType dtype, bo
   return Algo::TWO_SHOT;
 }
 
-PipePlan plan_pipeline(const CommConfig& cfg, size_t bytes, size_t slice_bytes) {
+PipePlan plan_pipeline(const CommConfig& cfg, size_t bytes, size_t slice_bytes, size_t unit_bytes) {
   PipePlan p;
+  const size_t unit = unit_bytes ? unit_bytes : 4096;
   const int gc = std::min(std::max(cfg.pipeline_cgroups, 1), (int)kPipeMaxGroups);
   const int slots = std::max(2 * gc, cfg.pipeline_slots / gc * gc);
-  // at least eight chunks, each a multiple of 4 KiB, `slots` of them inside the slice
-  size_t chunk = std::min(cfg.pipeline_chunk_bytes, std::max<size_t>(bytes / 8, 64u << 10));
+  // Chunks are multiples of the unit (at least one), `slots` of them inside the slice.
+  // Draining reducers: at least eight chunks of at most 4 MiB. Streaming reducers (their unit is
+  // one step of all ranks' reducer blocks): a 64th of the tensor, at least two steps (with one,
+  // the warp that publishes cannot keep up: 64 MiB on 4 GPUs ran at 440 GB/s against 509), at
+  // most pipeline_chunk_bytes (larger chunks lengthen the fill and the drain of the pipeline:
+  // 7.5 MiB chunks ran 64 MiB at 475 GB/s, but 1 GiB at 654 against 540).
+  size_t chunk = unit_bytes ? std::min(cfg.pipeline_chunk_bytes, std::max<size_t>(bytes / 64, 2 * unit))
+                            : std::min(std::min<size_t>(cfg.pipeline_chunk_bytes, 4u << 20), std::max<size_t>(bytes / 8, 64u << 10));
   chunk = std::min(chunk, slice_bytes / (size_t)slots);
-  chunk = std::max<size_t>(chunk / 4096 * 4096, 4096);
+  chunk = std::max<size_t>(chunk / unit * unit, unit);
   p.chunk_bytes = chunk;
   const size_t n = (bytes + chunk - 1) / chunk;
   p.nchunks = (int)std::min<size_t>(n, (size_t)kPipeMaxChunks);   // the caller launches again for the rest
   p.slots = std::min(slots, p.nchunks);   // fewer chunks than slots: the ring does not wrap
   p.lag = std::max(gc, slots / 2 / gc * gc);
+  // A slice too small for the ring (one unit per slot can be megabytes): no plan, the caller
+  // takes another path.
+  if ((size_t)p.slots * chunk > slice_bytes) p.nchunks = 0;
   return p;
 }
 
-void Comm::launch_pipeline(int channel, const char* in, char* out, size_t packs, DType dtype, float scale, int idiv, bool nvls,
-                           const PipePlan& plan) {
+bool Comm::launch_pipeline(int channel, const char* in, char* out, size_t packs, DType dtype, float scale, int idiv, bool nvls) {
   cudaStream_t s = streams_[channel];
+  const bool streaming = cfg_.pipeline_streaming;
+  const int rgroups = streaming ? 1 : std::min(std::max(cfg_.pipeline_rgroups, 1), (int)kPipeMaxGroups);
+  // Streaming reducers where the switch reduces: 16 blocks at every size (4 GPUs: 32 blocks ran
+  // 128 MiB at 498 GB/s against 577); larger groups spread a rank's traffic over more, shorter
+  // requests (as the in-place kernel: choose_blocks), 32.
+  int reducers = cfg_.pipeline_reducers > 0 ? cfg_.pipeline_reducers
+                 : !streaming               ? (nvls ? 32 : 48)
+                 : nvls                     ? (world_ > 4 ? 32 : 16)
+                                            : 32;
+  reducers = (reducers + rgroups - 1) / rgroups * rgroups;
+  // every block of the launch needs an SM of its own
+  const int cgroups = std::min(std::max(cfg_.pipeline_cgroups, 1), (int)kPipeMaxGroups);
+  int copiers = std::min(std::max(cgroups, cfg_.pipeline_copiers), sm_count_ - reducers) / cgroups * cgroups;
+  BC_CHECK(copiers >= cgroups, "the staged pipeline kernel needs more SMs than the device has");
+  // streaming: one step of a rank's reducers is blocks x 512 data threads x batch packs; a chunk is a
+  // whole number of steps of every rank
+  const size_t unit = streaming ? (size_t)world_ * (reducers / rgroups) * kPipeDataThreads * (nvls ? kPipeSwitchBatch : kPipePeerBatch) * 16 : 0;
+  const PipePlan plan = plan_pipeline(cfg_, packs * 16, staging_slice_bytes(), unit);
+  if (plan.nchunks == 0) return false;
   const size_t chunk_packs = plan.chunk_bytes / 16;
   for (size_t done = 0; done < packs;) {
     const size_t n = std::min(packs - done, chunk_packs * (size_t)kPipeMaxChunks);
@@ -162,10 +190,10 @@ void Comm::launch_pipeline(int channel, const char* in, char* out, size_t packs,
     a.base = pipe_base_[channel];
     a.scale = scale;
     a.idiv = idiv;
-    a.rgroups = std::min(std::max(cfg_.pipeline_rgroups, 1), (int)kPipeMaxGroups);
-    a.cgroups = std::min(std::max(cfg_.pipeline_cgroups, 1), (int)kPipeMaxGroups);
-    a.reducers = cfg_.pipeline_reducers > 0 ? cfg_.pipeline_reducers : nvls ? 32 : 48;
-    a.reducers = (a.reducers + a.rgroups - 1) / a.rgroups * a.rgroups;
+    a.rgroups = rgroups;
+    a.cgroups = cgroups;
+    a.reducers = reducers;
+    a.streaming = streaming ? 1 : 0;
     PipeRank& r = a.r[0];
     r.ctx = make_ctx(channel);
     for (int p = 0; p < world_; p++) {
@@ -178,13 +206,15 @@ void Comm::launch_pipeline(int channel, const char* in, char* out, size_t packs,
     r.local = pipe_local_ + (size_t)channel * 2 * kPipeMaxChunks;
     CUDA_RT(cudaMemsetAsync(r.local, 0, sizeof(uint32_t) * 2 * (size_t)a.nchunks, s));
     LaunchCfg cfg;
-    cfg.blocks = a.reducers + (std::max(1, cfg_.pipeline_copiers) + a.cgroups - 1) / a.cgroups * a.cgroups;
+    if (streaming) cfg.threads = kPipeStreamingThreads;
+    cfg.blocks = a.reducers + copiers;
     CUDA_RT(launch_staged_pipeline(a, dtype, nvls, cfg, s));
     pipe_base_[channel] += (uint32_t)a.nchunks;
     last_blocks = cfg.blocks;
     last_launches++;
     done += n;
   }
+  return true;
 }
 
 Algo Comm::choose_algo(size_t bytes, DType dtype, bool in_place_or_fused, bool has_mc) const {
@@ -276,10 +306,8 @@ Algo Comm::allreduce(int channel, const void* in, void* out, size_t count, DType
   if (cfg_.staged_pipeline > 0 && red == ReduceOp::SUM && bytes >= cfg_.pipeline_min_bytes && bytes >= 16) {
     const Algo inplace = pick(bytes, true, seg0_->mc != nullptr);
     const bool nvls = inplace == Algo::NVLS;
-    if (nvls || cfg_.staged_pipeline > 1) {
-      const size_t packs = bytes / 16;
-      launch_pipeline(channel, (const char*)in, (char*)out, packs, dtype, scale, idiv, nvls,
-                      plan_pipeline(cfg_, packs * 16, staging_slice_bytes()));
+    const size_t packs = bytes / 16;
+    if ((nvls || cfg_.staged_pipeline > 1) && launch_pipeline(channel, (const char*)in, (char*)out, packs, dtype, scale, idiv, nvls)) {
       const size_t head = packs * (16 / es);
       if (head < count) {
         // the last few elements (less than one pack) take the small-tensor path
@@ -669,7 +697,7 @@ cudaError_t EmuGroup::allgatherv(const void* const* ins, const unsigned long lon
 
 cudaError_t EmuGroup::staged_pipeline(size_t off, const void* const* srcs, void* const* outs, size_t count, DType dtype,
                                       float scale, int idiv, size_t chunk_bytes, int slots, int lag, int reducers, int copiers,
-                                      int rgroups, int cgroups, cudaStream_t s) {
+                                      int rgroups, int cgroups, bool streaming, cudaStream_t s) {
   const size_t bytes = count * dtype_size(dtype);
   if (bytes == 0 || bytes % 16 || chunk_bytes == 0 || chunk_bytes % 16 || slots < 1 || reducers < 1 || copiers < 1)
     return cudaErrorInvalidValue;
@@ -687,6 +715,7 @@ cudaError_t EmuGroup::staged_pipeline(size_t off, const void* const* srcs, void*
   a.reducers = reducers;
   a.rgroups = rgroups;
   a.cgroups = cgroups;
+  a.streaming = streaming ? 1 : 0;
   a.base = pipe_base_;
   a.scale = scale;
   a.idiv = idiv;

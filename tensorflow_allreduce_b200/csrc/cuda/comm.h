@@ -32,14 +32,15 @@ struct CommConfig {
                                         // 128-SM persistent kernel leaves free, at least 8)
   // Tensors outside symmetric memory in one launch whose blocks have roles (staged_pipeline.cu):
   // 0 = off, 1 = where the switch reduces (NVLS), 2 = also with peer loads and stores.
-  int staged_pipeline = 0;
-  size_t pipeline_min_bytes = 4u << 20;
-  size_t pipeline_chunk_bytes = 4u << 20;   // upper bound; a tensor is cut into at least eight chunks
+  int staged_pipeline = 1;
+  size_t pipeline_min_bytes = 48u << 20;
+  size_t pipeline_chunk_bytes = 8u << 20;   // upper bound of a chunk (see plan_pipeline)
   int pipeline_slots = 16;                  // chunks that the staging ring holds
-  int pipeline_copiers = 64;                // blocks that copy in and out
+  int pipeline_copiers = 128;               // blocks that copy in and out (at most the SMs that the reducers leave)
   int pipeline_reducers = 0;                // blocks that reduce; 0 = 32 where the switch reduces, else 48
-  int pipeline_rgroups = 8;                 // groups of reducer blocks (one chunk each at a time)
-  int pipeline_cgroups = 8;                 // groups of copier blocks
+  int pipeline_rgroups = 8;                 // groups of reducer blocks (one chunk each at a time); streaming: 1
+  bool pipeline_streaming = true;           // reducer blocks that never drain between chunks (staged_pipeline.cu)
+  int pipeline_cgroups = 4;                 // groups of copier blocks
   SymmAllocator::Mode symm_mode = SymmAllocator::Mode::AUTO;
 };
 
@@ -47,9 +48,11 @@ struct CommConfig {
 // `slice_bytes`: a pure function, the same on every rank.
 struct PipePlan {
   size_t chunk_bytes;
-  int nchunks, slots, lag;   // slots and lag are multiples of the number of copier groups when the ring wraps
+  int nchunks, slots, lag;   // slots and lag are multiples of the number of copier groups when the ring wraps;
+                             // nchunks == 0: the slice cannot hold the ring
 };
-PipePlan plan_pipeline(const CommConfig& cfg, size_t bytes, size_t slice_bytes);
+// `unit_bytes` (0 = 4 KiB): chunks are multiples of it.
+PipePlan plan_pipeline(const CommConfig& cfg, size_t bytes, size_t slice_bytes, size_t unit_bytes = 0);
 
 // The algorithm for a reduction of `bytes` bytes in a group of `world` ranks: a pure function of
 // its arguments, so every rank computes the same answer (and it can be checked without a GPU).
@@ -151,9 +154,9 @@ class Comm {
   // queued launches have run.
   uint32_t* pipe_local_ = nullptr;
   uint32_t pipe_base_[dev::kUserChannels] = {0};
-  // Reduces the first `packs` 16-byte packs of a private tensor with the staged pipeline kernel.
-  void launch_pipeline(int channel, const char* in, char* out, size_t packs, DType dtype, float scale, int idiv, bool nvls,
-                       const PipePlan& plan);
+  // Reduces the first `packs` 16-byte packs of a private tensor with the staged pipeline kernel;
+  // false (nothing launched) when the channel's staging slice is too small for its ring.
+  bool launch_pipeline(int channel, const char* in, char* out, size_t packs, DType dtype, float scale, int idiv, bool nvls);
   cudaStream_t streams_[dev::kChannels] = {nullptr};
   // Events of the pipeline that carries a large staged tensor (Comm::allreduce).
   static constexpr int kStageBuffers = 4;                      // parts of a channel's staging slice in rotation
@@ -201,7 +204,7 @@ class EmuGroup {
   // at `off` of the ranks' buffers; `reducers` + `copiers` blocks per rank.
   cudaError_t staged_pipeline(size_t off, const void* const* srcs, void* const* outs, size_t count, DType dtype, float scale,
                               int idiv, size_t chunk_bytes, int slots, int lag, int reducers, int copiers, int rgroups,
-                              int cgroups, cudaStream_t s);
+                              int cgroups, bool streaming, cudaStream_t s);
   // A barrier-only launch in which rank `absent` (if >= 0) does not take part, so that the
   // others run into the bounded wait. `timeout_s` bounds it.
   cudaError_t barrier_probe(int absent, double timeout_s, cudaStream_t s);

@@ -104,8 +104,273 @@ template <> struct SwitchAdds<__nv_bfloat16> { static constexpr bool value = tru
 template <> struct SwitchAdds<__half> { static constexpr bool value = true; };
 
 
+
+// ---- streaming reducer ---------------------------------------------------------------------------
+// A reducer block that waits for a chunk, reduces it and publishes it drains twice per chunk: its
+// last stores must be acknowledged before it may tell the peers, and the first loads of the next
+// chunk start from an empty pipeline. Here the block splits the work by warp instead. All warps
+// but the last move data and never wait for memory they do not need: a warp walks through the batches
+// of all its chunks in ONE software pipeline (the loads of the next batch, which may belong to
+// the next chunk, are issued before the stores of the current one), reads "chunks staged so
+// far" from shared memory before it enters a chunk, and adds one to a counter in shared memory
+// when it has issued its last store of a chunk. The last warp does the waiting: it polls the progress
+// words of the copiers (ld.acquire.sys) and raises the shared "staged" count, and when all data
+// warps have counted a chunk it fences, counts the block in (the global arrival counter of the
+// chunk) and, as the last block, publishes the chunk to every rank. The counters in shared
+// memory are written with release and read with acquire semantics at CTA scope, so the fence of
+// the last warp covers the data warps' stores (the same chain as bar.sync + fence in a plain block).
+// Every wait is a bounded poll; a warp that gives up raises the shared error word, which ends
+// all warps of the block.
+constexpr int kDoneRing = 8;   // chunks that the data warps may be ahead of the publisher
+
+struct StreamShared {
+  uint32_t staged;             // chunks ch < staged are staged on every rank
+  uint32_t published;          // how many of this block's chunks the last warp has retired
+  uint32_t error;
+  uint32_t done[kDoneRing];    // data warps that have finished chunk number k (slot k % kDoneRing)
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_cta_shared(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"((uint32_t)__cvta_generic_to_shared(p)) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_cta_shared(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_cta_shared_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.cta.shared.add.u32 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(p)), "r"(v) : "memory");
+}
+
+// Polls shared memory until pred() holds; false when the block has failed or the wait ran out.
+template <typename Pred>
+__device__ __forceinline__ bool poll_shared(StreamShared& sh, const RankCtx& c, uint32_t what, Pred pred) {
+  if (pred()) return true;
+  const unsigned long long t0 = global_timer();
+  uint32_t spins = 0;
+  while (true) {
+    if (pred()) return true;
+    if (ld_acquire_cta_shared(&sh.error)) return false;
+    if (((++spins) & 0x3ff) == 0 && global_timer() - t0 > c.timeout_ns) {
+      atomicOr(c.status, kStatusTimeout | what | ((uint32_t)c.rank << 8));
+      st_release_cta_shared(&sh.error, 1u);
+      return false;
+    }
+  }
+}
+
 template <typename T, bool NVLS>
-__global__ void __launch_bounds__(512, 1) staged_pipeline_kernel(const __grid_constant__ PipeArgs a) {
+__device__ void reduce_streaming(const PipeArgs& a, const PipeRank& R, StreamShared& sh) {
+  using PK = Pack<T>;
+  using Acc = typename PK::Acc;
+  constexpr int E = PK::kElems;
+  constexpr bool kSwitch = NVLS && SwitchAdds<T>::value;
+  constexpr int U = kSwitch ? 4 : 2;   // packs per batch (peer variant: P loads per pack)
+  const RankCtx& c = R.ctx;
+  const int P = c.world, me = c.rank;
+  const int GR = a.rgroups, GC = a.cgroups;
+  const int grp = (int)blockIdx.x % GR, nb = a.reducers / GR;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kDataWarps = (int)(blockDim.x >> 5) - 1;   // 16 in a launch of 544 threads, 15 in one of 512
+  const uint32_t* words = R.progress[me];
+  const int mine = a.nchunks > grp ? (a.nchunks - grp + GR - 1) / GR : 0;   // chunks of this block's group
+
+  if (threadIdx.x == 0) {
+    sh.staged = 0;
+    sh.published = 0;
+    sh.error = 0;
+    for (int i = 0; i < kDoneRing; i++) sh.done[i] = 0;
+  }
+  __syncthreads();
+
+  if (warp == kDataWarps) {
+    // ---- the warp that waits ----
+    uint32_t staged = 0;       // chunks [0, staged) are staged everywhere
+    int retired = 0;           // chunks of this group that are published
+    unsigned long long t_progress = global_timer();
+    while (retired < mine) {
+      bool moved = false;
+      // (a) has every rank staged the next chunk?
+      if ((int)staged < a.nchunks) {
+        int ok = 1;
+        if (lane < P) ok = (int32_t)(ld_acquire_sys(words + ((int)staged % GC) * kMaxRanks + lane) - (a.base + staged / GC + 1)) >= 0;
+        if (__all_sync(0xffffffffu, ok)) {
+          staged++;
+          if (lane == 0) st_release_cta_shared(&sh.staged, staged);
+          moved = true;
+        }
+      }
+      // (b) have all data warps issued the last store of the oldest unpublished chunk?
+      uint32_t cnt = 0;
+      if (lane == 0) cnt = ld_acquire_cta_shared(&sh.done[retired % kDoneRing]);
+      cnt = __shfl_sync(0xffffffffu, cnt, 0);
+      if (cnt == (uint32_t)kDataWarps) {
+        const int ch = grp + retired * GR;
+        if (lane == 0) {
+          sh.done[retired % kDoneRing] = 0;
+          // acq_rel: the data warps' stores (acquired above) are ordered before the count
+          if (atom_add_acq_rel_gpu(R.local + a.nchunks + ch, 1u) == (uint32_t)nb - 1) {
+            __threadfence_system();
+            for (int p = 0; p < P; p++) st_relaxed_sys(R.progress[p] + (kPipeMaxGroups + grp) * kMaxRanks + me, a.base + (uint32_t)(ch / GR) + 1);
+          }
+          st_release_cta_shared(&sh.published, (uint32_t)retired + 1);
+        }
+        retired++;
+        moved = true;
+      }
+      if (moved) {
+        t_progress = global_timer();
+      } else {
+        int bad = ld_acquire_cta_shared(&sh.error) != 0;
+        if (!bad && global_timer() - t_progress > c.timeout_ns) {
+          bad = 1;
+          if (lane == 0) {
+            atomicOr(c.status, kStatusTimeout | 0x10000u | ((uint32_t)c.rank << 8));
+            st_release_cta_shared(&sh.error, 1u);
+          }
+        }
+        if (__any_sync(0xffffffffu, bad)) return;
+      }
+    }
+    return;
+  }
+
+  // ---- data warps ----
+  const size_t tid = (size_t)((int)blockIdx.x / GR) * (kDataWarps * 32) + threadIdx.x;
+  const size_t stride = (size_t)nb * (kDataWarps * 32), step = stride * U;
+  // position of a batch: chunk number k of this group (chunk grp + k * GR), first pack i0, end of the share
+  struct Pos { int k; size_t i0, se; };
+  auto enter = [&](int k, Pos& p) {   // first batch of chunk k of this thread (may be empty: i0 >= se)
+    const int ch = grp + k * GR;
+    const size_t cb = (size_t)ch * a.chunk_packs, ce = cb + a.chunk_packs < a.npacks ? cb + a.chunk_packs : a.npacks;
+    const size_t n = ce - cb, slot0 = (size_t)(ch % a.slots) * a.chunk_packs;
+    p.k = k;
+    p.i0 = slot0 + n * (size_t)me / P + tid;
+    p.se = slot0 + n * (size_t)(me + 1) / P;
+  };
+  // May the warp touch chunk k? (staged everywhere, and its slot of the done ring is free)
+  // Lane 0 polls for the warp, so that all lanes get the same answer.
+  auto admit = [&](int k) {
+    const uint32_t ch = (uint32_t)(grp + k * GR);
+    int ok = 1;
+    if (lane == 0)
+      ok = poll_shared(sh, c, 0x40000u, [&] {
+        return ld_acquire_cta_shared(&sh.staged) > ch && (uint32_t)k - ld_acquire_cta_shared(&sh.published) < (uint32_t)kDoneRing;
+      });
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    __syncwarp();
+    return ok != 0;
+  };
+  auto load_batch = [&](const Pos& p, uint4* r) {
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const size_t i = p.i0 + (size_t)u * stride;
+      if (i < p.se) {
+        if constexpr (kSwitch) {
+          r[u] = switch_reduce<T>(R.mc_stage + i * 16);
+        } else {
+          Acc acc[E];
+          PK::unpack(ld_stream16(R.stage[0] + i * 16), acc);
+          for (int q = 1; q < P; q++) {
+            Acc tmp[E];
+            PK::unpack(ld_stream16(R.stage[q] + i * 16), tmp);
+#pragma unroll
+            for (int e = 0; e < E; e++) acc[e] = acc[e] + tmp[e];
+          }
+#pragma unroll
+          for (int e = 0; e < E; e++) acc[e] = finish<Acc>(acc[e], a.scale, a.idiv);
+          r[u] = PK::pack(acc);
+        }
+      }
+    }
+  };
+  auto store_batch = [&](const Pos& p, uint4* r) {
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const size_t i = p.i0 + (size_t)u * stride;
+      if (i < p.se) {
+        if constexpr (kSwitch) {
+          if (a.scale != 1.f) {
+            Acc acc[E];
+            PK::unpack(r[u], acc);
+#pragma unroll
+            for (int e = 0; e < E; e++) acc[e] = finish<Acc>(acc[e], a.scale, a.idiv);
+            r[u] = PK::pack(acc);
+          }
+          multimem_st16(R.mc_stage + i * 16, r[u]);
+        } else {
+          for (int q = 0; q < P; q++) st16(R.stage[q] + i * 16, r[u]);
+        }
+      }
+    }
+  };
+  if (mine == 0) return;
+  // Where is the batch after `cur`? The next one of the same chunk, or the first one of the
+  // group's next chunk if the warp may enter it already (kNext: its loads go out before the
+  // stores of `cur`, across the chunk boundary). If that chunk is not staged yet (kWait) the warp
+  // first finishes `cur`, so that nobody waits for this chunk longer than necessary, and then
+  // waits. The lanes of a warp cross chunk boundaries together: lane 0, which holds the warp's
+  // lowest pack, decides.
+  enum { kNext, kEnd, kWait };
+  auto advance = [&](const Pos& cur, Pos& nx, bool& last_of_chunk) {
+    last_of_chunk = false;
+    nx = cur;
+    const size_t lane0_next = __shfl_sync(0xffffffffu, cur.i0, 0) + step;
+    if (lane0_next < cur.se) {
+      nx.i0 = cur.i0 + step;
+      return (int)kNext;
+    }
+    last_of_chunk = true;
+    if (cur.k + 1 >= mine) return (int)kEnd;
+    int open = 0;
+    if (lane == 0) {
+      const uint32_t ch = (uint32_t)(grp + (cur.k + 1) * GR);
+      open = ld_acquire_cta_shared(&sh.staged) > ch && (uint32_t)(cur.k + 1) - ld_acquire_cta_shared(&sh.published) < (uint32_t)kDoneRing;
+    }
+    open = __shfl_sync(0xffffffffu, open, 0);
+    __syncwarp();
+    if (!open) return (int)kWait;
+    enter(cur.k + 1, nx);
+    return (int)kNext;
+  };
+  auto chunk_done = [&](int k) {
+    __syncwarp();
+    if (lane == 0) red_release_cta_shared_add(&sh.done[k % kDoneRing], 1u);
+  };
+  Pos cur, nx;
+  bool last_of_chunk;
+  uint4 ra[U], rb[U];
+  if (!admit(0)) return;
+  enter(0, cur);
+  load_batch(cur, ra);
+  while (true) {
+    int st = advance(cur, nx, last_of_chunk);
+    if (st == kNext) load_batch(nx, rb);
+    store_batch(cur, ra);
+    if (last_of_chunk) chunk_done(cur.k);
+    if (st == kEnd) break;
+    if (st == kWait) {
+      if (!admit(cur.k + 1)) return;
+      enter(cur.k + 1, nx);
+      load_batch(nx, rb);
+    }
+    cur = nx;
+    st = advance(cur, nx, last_of_chunk);
+    if (st == kNext) load_batch(nx, ra);
+    store_batch(cur, rb);
+    if (last_of_chunk) chunk_done(cur.k);
+    if (st == kEnd) break;
+    if (st == kWait) {
+      if (!admit(cur.k + 1)) return;
+      enter(cur.k + 1, nx);
+      load_batch(nx, ra);
+    }
+    cur = nx;
+  }
+}
+
+template <typename T, bool NVLS>
+__global__ void __launch_bounds__(544, 1) staged_pipeline_kernel(const __grid_constant__ PipeArgs a) {
   using PK = Pack<T>;
   using Acc = typename PK::Acc;
   constexpr int E = PK::kElems;
@@ -117,6 +382,11 @@ __global__ void __launch_bounds__(512, 1) staged_pipeline_kernel(const __grid_co
   // what the ranks have told THIS rank: word (kind * kPipeMaxGroups + group) * kMaxRanks + rank
   const uint32_t* words = R.progress[me];
 
+  __shared__ StreamShared sh;
+  if ((int)blockIdx.x < NB && a.streaming) {
+    reduce_streaming<T, NVLS>(a, R, sh);
+    return;
+  }
   if ((int)blockIdx.x < NB) {
     // ---- reducer of group blockIdx.x % GR ----
     const int grp = (int)blockIdx.x % GR, nb = NB / GR;
@@ -220,7 +490,7 @@ cudaError_t launch_typed(const PipeArgs& a, bool nvls, const LaunchCfg& cfg, cud
 }  // namespace
 
 cudaError_t launch_staged_pipeline(const PipeArgs& a, DType dtype, bool nvls, const LaunchCfg& cfg, cudaStream_t s) {
-  if (a.nchunks < 1 || a.nchunks > kPipeMaxChunks || a.reducers < 1 || cfg.blocks <= a.reducers || cfg.threads != 512) return cudaErrorInvalidConfiguration;
+  if (a.nchunks < 1 || a.nchunks > kPipeMaxChunks || a.reducers < 1 || cfg.blocks <= a.reducers || (cfg.threads != 512 && cfg.threads != 544)) return cudaErrorInvalidConfiguration;
   if (a.rgroups < 1 || a.rgroups > kPipeMaxGroups || a.cgroups < 1 || a.cgroups > kPipeMaxGroups) return cudaErrorInvalidConfiguration;
   if (a.reducers % a.rgroups || (cfg.blocks - a.reducers) % a.cgroups) return cudaErrorInvalidConfiguration;
   if (a.chunk_packs == 0 || (size_t)a.nchunks * a.chunk_packs < a.npacks || a.slots < 1 || a.lag < 0 || a.lag % a.cgroups) return cudaErrorInvalidValue;

@@ -120,14 +120,15 @@ class EmulatedGroup:
 
     def staged_pipeline(self, srcs: Sequence[torch.Tensor], outs: Sequence[torch.Tensor], scale: float = 1.0, idiv: int = 1,
                         chunk_bytes: int = 64 << 10, slots: int = 4, lag: int = 2, reducers: int = 2, copiers: int = 3,
-                        rgroups: int = 1, cgroups: int = 1, offset_bytes: int = 0):
+                        rgroups: int = 1, cgroups: int = 1, streaming: bool = False, offset_bytes: int = 0):
         """Allreduce of the private tensors `srcs[r]` into `outs[r]` (may be the same tensors) with
         the staged pipeline kernel: `copiers` blocks of every rank copy chunks into a ring of
         `slots` chunks inside the rank's buffer and finished chunks out again, `reducers` blocks
         reduce chunk after chunk with peer loads and stores; the reducers form `rgroups` groups
         and the copiers `cgroups` groups that take every groups-th chunk each (`lag`, and `slots`
-        when the ring wraps, must be multiples of `cgroups`). The tensors' size must be a
-        multiple of 16 bytes."""
+        when the ring wraps, must be multiples of `cgroups`). `streaming`: reducer blocks whose
+        warps split into 15 that move data without ever draining and one that waits and
+        publishes. The tensors' size must be a multiple of 16 bytes."""
         n = self.nranks
         sp = (C.c_void_p * n)()
         op = (C.c_void_p * n)()
@@ -137,7 +138,7 @@ class EmulatedGroup:
         s = torch.cuda.current_stream(self.device).cuda_stream
         _check(self.lib.bc_emu_staged_pipeline(self._g, offset_bytes, sp, op, srcs[0].numel(), _DTYPES[srcs[0].dtype], float(scale),
                                                int(idiv), int(chunk_bytes), int(slots), int(lag), int(reducers), int(copiers),
-                                               int(rgroups), int(cgroups), C.c_void_p(s)), "emulated staged pipeline")
+                                               int(rgroups), int(cgroups), int(streaming), C.c_void_p(s)), "emulated staged pipeline")
 
     def allgatherv(self, ins: Sequence[torch.Tensor], out_offsets: Sequence[int], blocks: int = 2):
         """Each rank r pushes `ins[r]` into every rank's buffer at `out_offsets[that rank]` plus

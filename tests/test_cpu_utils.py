@@ -421,27 +421,38 @@ def test_pipeline_plan_keeps_the_ring_inside_the_slice_and_the_copy_out_behind_t
            st.sampled_from([0, 64 << 10, 1 << 20, 8 << 20]), st.sampled_from([0, 2, 4, 16, 64]), st.integers(min_value=1, max_value=4))
     def check(nbytes, slice_log2, chunk, slots, groups):
         out = (C.c_longlong * 4)()
-        assert native_lib.bc_plan_pipeline(nbytes, 1 << slice_log2, chunk, slots, groups, out) == 0
+        assert native_lib.bc_plan_pipeline(nbytes, 1 << slice_log2, chunk, slots, groups, 0, out) == 0
         chunk_bytes, nchunks, nslots, lag = out[0], out[1], out[2], out[3]
         ring = max((slots or 16) // groups * groups, 2 * groups)             # slots asked for, in whole groups
-        assert chunk_bytes >= 4096 and chunk_bytes % 4096 == 0 and chunk_bytes <= (chunk or 4 << 20)
+        assert chunk_bytes >= 4096 and chunk_bytes % 4096 == 0 and chunk_bytes <= min(chunk or 8 << 20, 4 << 20)
         assert 1 <= nchunks <= 2048 and 1 <= nslots <= ring and nslots <= nchunks
         assert nslots * chunk_bytes <= 1 << slice_log2
         assert nchunks * chunk_bytes >= nbytes or nchunks == 2048          # one launch covers it, or the caller launches again
         assert lag >= groups and lag % groups == 0
         if nchunks > nslots:                                               # the ring wraps: a slot keeps its group of copiers
             assert nslots % groups == 0 and lag < nslots
-        if nbytes >= 8 * (64 << 10) and (chunk or 4 << 20) >= 64 << 10 and nbytes // 8 <= (1 << slice_log2) // ring:
+        if nbytes >= 8 * (64 << 10) and min(chunk or 8 << 20, 4 << 20) >= 64 << 10 and nbytes // 8 <= (1 << slice_log2) // ring:
             assert nchunks >= 8
 
     check()
     out = (C.c_longlong * 4)()
-    native_lib.bc_plan_pipeline(64 << 20, 256 << 20, 0, 0, 0, out)
+    native_lib.bc_plan_pipeline(64 << 20, 256 << 20, 0, 0, 0, 0, out)
     assert list(out) == [4 << 20, 16, 16, 8]
-    native_lib.bc_plan_pipeline(1 << 30, 256 << 20, 0, 0, 0, out)
+    native_lib.bc_plan_pipeline(1 << 30, 256 << 20, 0, 0, 0, 0, out)
     assert list(out) == [4 << 20, 256, 16, 8]
-    native_lib.bc_plan_pipeline(4 << 20, 256 << 20, 0, 0, 0, out)
+    native_lib.bc_plan_pipeline(4 << 20, 256 << 20, 0, 0, 0, 0, out)
     assert list(out) == [512 << 10, 8, 8, 8]
+    # streaming reducers: chunks are whole steps of all ranks' reducer blocks (4 ranks x 16 blocks x 512 threads x
+    # 4 packs = 2 MiB): a 64th of the tensor, at least two steps, at most 8 MiB
+    unit = 4 * 16 * 512 * 4 * 16
+    native_lib.bc_plan_pipeline(1 << 30, 256 << 20, 0, 0, 0, unit, out)
+    assert list(out) == [8 << 20, 128, 16, 8]
+    native_lib.bc_plan_pipeline(256 << 20, 256 << 20, 0, 0, 0, unit, out)
+    assert list(out) == [4 << 20, 64, 16, 8]
+    native_lib.bc_plan_pipeline(64 << 20, 256 << 20, 0, 0, 0, unit, out)
+    assert list(out) == [4 << 20, 16, 16, 8]
+    native_lib.bc_plan_pipeline(4 << 20, 256 << 20, 0, 0, 0, unit, out)
+    assert list(out) == [4 << 20, 1, 1, 8]
 
 
 def test_static_allreduce_refuses_bad_requests_before_touching_a_device(native_lib):

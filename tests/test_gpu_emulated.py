@@ -367,7 +367,10 @@ def test_staged_pipeline_kernel_with_copier_and_reducer_blocks(emu, nranks):
     # chunk after chunk, and progress words (not barriers) order them. Same kernel here with peer
     # loads: one chunk, a ring that is exactly full, a ring that wraps several times with a ragged
     # last chunk, in place and into separate outputs, launches in a row (the words run on), one
-    # group of blocks per role or several that take every groups-th chunk each.
+    # group of blocks per role or several that take every groups-th chunk each; reducer blocks that
+    # drain after every chunk, and streaming ones (15 warps move data through ONE software pipeline
+    # over all chunks, one warp polls the progress words and publishes; a group of 40 chunks takes
+    # the block's ring of "done" counters around five times).
     g = emu(nranks)
     chunk = 4096
     packs_per_chunk = chunk // 16
@@ -377,7 +380,7 @@ def test_staged_pipeline_kernel_with_copier_and_reducer_blocks(emu, nranks):
                                                     (4 * packs_per_chunk, 4, 2, 2, 3, 1, 1), (11 * packs_per_chunk + 37, 4, 2, 3, 2, 3, 2),
                                                     (7 * packs_per_chunk + 1, 2, 1, 2, 4, 2, 1), (3 * packs_per_chunk, 8, 5, 2, 2, 1, 1),
                                                     (29 * packs_per_chunk + 5, 8, 4, 4, 8, 4, 4), (2 * packs_per_chunk, 6, 3, 4, 6, 2, 3),
-                                                    (13 * packs_per_chunk, 6, 3, 2, 3, 2, 3)):
+                                                    (13 * packs_per_chunk, 6, 3, 2, 3, 2, 3), (40 * packs_per_chunk - 9, 8, 4, 2, 4, 1, 4)):
             n = packs * e
             xs = [_fill(dtype, n, 31 * r + packs % 13) for r in range(nranks)]
             keep = [x.clone() for x in xs]
@@ -385,13 +388,15 @@ def test_staged_pipeline_kernel_with_copier_and_reducer_blocks(emu, nranks):
             want = _reference_sum(keep, dtype, scale=scale, idiv=idiv)
             outs = [torch.full((n,), 3, dtype=dtype, device="cuda") for _ in range(nranks)]
             kw = dict(scale=scale, idiv=idiv, chunk_bytes=chunk, slots=slots, lag=lag, reducers=red, copiers=cop, rgroups=gr, cgroups=gc)
-            g.staged_pipeline(xs, outs, **kw)
-            torch.cuda.synchronize()
-            assert g.status == 0, hex(g.status)
-            for r in range(nranks):
-                assert torch.equal(outs[r], want), f"rank {r} packs={packs} {dtype}"
-                assert torch.equal(xs[r], keep[r])
-            g.staged_pipeline(xs, xs, **kw)
+            for streaming in (False, True):
+                outs = [torch.full((n,), 3, dtype=dtype, device="cuda") for _ in range(nranks)]
+                g.staged_pipeline(xs, outs, streaming=streaming, **kw)
+                torch.cuda.synchronize()
+                assert g.status == 0, hex(g.status)
+                for r in range(nranks):
+                    assert torch.equal(outs[r], want), f"rank {r} packs={packs} {dtype} streaming={streaming}"
+                    assert torch.equal(xs[r], keep[r])
+            g.staged_pipeline(xs, xs, streaming=True, **kw)
             torch.cuda.synchronize()
             assert g.status == 0, hex(g.status)
             for r in range(nranks):

@@ -470,3 +470,44 @@ def test_large_private_tensors_go_through_both_lanes(world):
     """, nranks=world, gpus=True, timeout=300, env={"BC_STAGING_MB": "8"})
     for _, rec in res:
         assert rec["bad"] == [], rec
+
+
+@pytest.mark.skipif(_ngpu() < 4, reason="the switch reduces only in groups of four or more GPUs")
+def test_large_private_tensors_go_through_the_staged_pipeline_kernel():
+    # From 48 MiB on an ordinary tensor is reduced by ONE launch whose copier blocks and reducer
+    # blocks work on different chunks of a ring in the staging slice. Integer-valued floats make
+    # the sums exact: odd element counts (a tail below 16 bytes), fp32 and bf16, sum and average,
+    # several calls in a row (the progress words run on), and the same tensors with that kernel
+    # switched off must give bit-identical results.
+    world = 4 if _ngpu() < 8 else 8
+    res = run("""
+    from tensorflow_allreduce_b200 import _lib
+    bc.init()
+    bad = []
+    launches = []
+    for dtype, n in ((torch.float32, (13 << 20) + 3), (torch.bfloat16, (40 << 20) + 5), (torch.float32, (96 << 20) + 1)):
+        g = torch.Generator(device="cuda").manual_seed(11)
+        base = torch.randint(-20, 20, (n,), generator=g, device="cuda", dtype=torch.int32)
+        x = (base + RANK).to(dtype)
+        want = (base * SIZE + SIZE * (SIZE - 1) // 2).to(dtype)
+        outs = []
+        for mode in (1, 0, 1):
+            _lib.lib().bc_set_option(b"staged_pipeline", mode)
+            got = bc.allreduce(x, average=False)
+            if not torch.equal(got, want): bad.append([str(dtype), n, mode, (got.float() - want.float()).abs().max().item()])
+            rec = [e for e in bc.stats() if e["device"] == 1][-1]
+            launches.append([mode, rec["algo"], rec.get("launches", -1)])
+            outs.append(got)
+        if not (torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])): bad.append(["differs", str(dtype), n])
+        y = x.clone()
+        bc.allreduce_(y, average=True)
+        if not torch.allclose(y.float(), want.float() / SIZE, rtol=1e-2, atol=1e-2): bad.append(["avg", str(dtype), n])
+        del x, y, outs, got, want, base
+    torch.cuda.synchronize()
+    bc.check_device_status()
+    emit(bad=bad, launches=launches)
+    bc.shutdown()
+    """, nranks=world, gpus=True, timeout=300)
+    for _, rec in res:
+        assert rec["bad"] == [], rec
+        assert all(algo == "nvls" for _, algo, _ in rec["launches"]), rec
