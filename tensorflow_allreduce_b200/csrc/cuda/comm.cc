@@ -136,11 +136,11 @@ PipePlan plan_pipeline(const CommConfig& cfg, size_t bytes, size_t slice_bytes, 
   const int slots = std::max(2 * gc, cfg.pipeline_slots / gc * gc);
   // Chunks are multiples of the unit (at least one), `slots` of them inside the slice.
   // Draining reducers: at least eight chunks of at most 4 MiB. Streaming reducers (their unit is
-  // one step of all ranks' reducer blocks): a 64th of the tensor, at least two steps (with one,
-  // the warp that publishes cannot keep up: 64 MiB on 4 GPUs ran at 440 GB/s against 509), at
-  // most pipeline_chunk_bytes (larger chunks lengthen the fill and the drain of the pipeline:
-  // 7.5 MiB chunks ran 64 MiB at 475 GB/s, but 1 GiB at 654 against 540).
-  size_t chunk = unit_bytes ? std::min(cfg.pipeline_chunk_bytes, std::max<size_t>(bytes / 64, 2 * unit))
+  // one step of all ranks' reducer blocks): a 64th of the tensor, at most pipeline_chunk_bytes
+  // (larger chunks lengthen the fill and the drain of the pipeline: 7.5 MiB chunks ran 64 MiB at
+  // 475 GB/s, but 1 GiB at 654 against 540), but at least two steps (with one, the warp that
+  // publishes cannot keep up: 64 MiB on 4 GPUs ran at 440 GB/s against 509).
+  size_t chunk = unit_bytes ? std::max<size_t>(std::min(cfg.pipeline_chunk_bytes, bytes / 64), 2 * unit)
                             : std::min(std::min<size_t>(cfg.pipeline_chunk_bytes, 4u << 20), std::max<size_t>(bytes / 8, 64u << 10));
   chunk = std::min(chunk, slice_bytes / (size_t)slots);
   chunk = std::max<size_t>(chunk / unit * unit, unit);
@@ -160,11 +160,11 @@ bool Comm::launch_pipeline(int channel, const char* in, char* out, size_t packs,
   const bool streaming = cfg_.pipeline_streaming;
   const int rgroups = streaming ? 1 : std::min(std::max(cfg_.pipeline_rgroups, 1), (int)kPipeMaxGroups);
   // Streaming reducers where the switch reduces: 16 blocks at every size (4 GPUs: 32 blocks ran
-  // 128 MiB at 498 GB/s against 577); larger groups spread a rank's traffic over more, shorter
-  // requests (as the in-place kernel: choose_blocks), 32.
+  // 128 MiB at 498 GB/s against 577). Larger groups have not been measured with this kernel;
+  // they use the same 16, which keeps a chunk (two steps of all ranks' reducers) at 8 MiB for 8 ranks.
   int reducers = cfg_.pipeline_reducers > 0 ? cfg_.pipeline_reducers
                  : !streaming               ? (nvls ? 32 : 48)
-                 : nvls                     ? (world_ > 4 ? 32 : 16)
+                 : nvls                     ? 16
                                             : 32;
   reducers = (reducers + rgroups - 1) / rgroups * rgroups;
   // every block of the launch needs an SM of its own

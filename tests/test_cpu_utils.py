@@ -453,6 +453,10 @@ def test_pipeline_plan_keeps_the_ring_inside_the_slice_and_the_copy_out_behind_t
     assert list(out) == [4 << 20, 16, 16, 8]
     native_lib.bc_plan_pipeline(4 << 20, 256 << 20, 0, 0, 0, unit, out)
     assert list(out) == [4 << 20, 1, 1, 8]
+    native_lib.bc_plan_pipeline(1 << 30, 256 << 20, 0, 0, 0, 4 * unit, out)      # two steps win over the 8 MiB cap
+    assert list(out) == [16 << 20, 64, 16, 8]
+    native_lib.bc_plan_pipeline(1 << 30, 8 << 20, 0, 0, 0, unit, out)            # a slice that cannot hold the ring: no plan
+    assert out[1] == 0
 
 
 def test_static_allreduce_refuses_bad_requests_before_touching_a_device(native_lib):
