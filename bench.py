@@ -133,10 +133,10 @@ def build_model(name: str, device, batch: int, persistent_rnn: bool = True, fuse
     return model, opt, make, loss_fn, b, meta
 
 
-# Same-box comparators recorded in BASELINE.md section 4 (torch DDP + NCCL + torch.optim.SGD + cuDNN GRU on the
-# DeepSpeech2-style configuration, samples/s by number of GPUs). They are NOT the reference's own build, which cannot
-# be installed on this image; they are the only published figures that `vs_baseline` can be taken against.
-BASELINE_MD_DS2_DDP_CUDNN = {1: 376.1, 2: 698.6, 4: 1285.4}
+# Recorded same-box comparators (torch DDP + NCCL + torch.optim.SGD + cuDNN GRU on the DeepSpeech2-style
+# configuration, samples/s by number of GPUs, on this pool's B200 boxes). They are NOT the reference's own build,
+# which cannot be installed on this image; they are the only recorded figures that `vs_baseline` can be taken against.
+RECORDED_DS2_DDP_CUDNN = {1: 376.1, 2: 698.6, 4: 1285.4}
 
 
 def run_arm(a, impl: str, rnn: str, device, rank: int, world: int, local: int, with_e2e: bool):
@@ -308,7 +308,7 @@ def main():
 
     if rank == 0:
         meta, clocks, ms = r["meta"], r["clocks"], r["ms"]
-        base = BASELINE_MD_DS2_DDP_CUDNN.get(world) if (a.model == "ds2" and not a.batch) else None
+        base = RECORDED_DS2_DDP_CUDNN.get(world) if (a.model == "ds2" and not a.batch) else None
         out = {
             "metric": f"{a.model}_train_samples_per_sec",
             "value": round(r["value"], 3),
@@ -317,7 +317,7 @@ def main():
             "ms_per_step": round(ms / a.steps, 3),
             "higher_is_better": True, "scaling": "weak",
             "vs_baseline": round(r["value"] / base, 4) if base else None,
-            "vs_baseline_of": ("torch DDP + NCCL + torch.optim.SGD + cuDNN GRU on the same B200 boxes (BASELINE.md section 4); "
+            "vs_baseline_of": ("torch DDP + NCCL + torch.optim.SGD + cuDNN GRU recorded earlier on the same B200 boxes; "
                                "the reference publishes no number and its own build is unavailable") if base else None,
             "dtype": meta["dtype"], "data": "synthetic (random inputs and labels, random-init weights)",
             "impl": a.impl,
