@@ -15,7 +15,7 @@ Arms:
   ours_private the same ordinary tensor with an ordered launch (`allreduce_direct_`): staging without negotiation,
               which is what NCCL's ordered `all_reduce` is comparable with
   ours_pipeline (not in the default list) ours_private with the staged pipeline kernel forced from 4 MiB on (the
-              library uses it from 48 MiB): one launch whose copier blocks and reducer blocks work on different
+              library uses it from 96 MiB): one launch whose copier blocks and reducer blocks work on different
               chunks of a ring in the staging area
   ours_nopipeline (not in the default list) ours_private with that kernel switched off: one kernel that copies in,
               reduces and copies out up to a quarter of the staging slice, a pipeline of kernels on three streams above

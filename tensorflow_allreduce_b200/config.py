@@ -53,13 +53,13 @@ class Config:
     staged_pipeline: int = 1           # large tensors outside symmetric memory in one launch whose blocks copy chunks
                                        # in and out while others reduce: 0 = off, 1 = where the switch reduces
                                        # (NVLS), 2 = with peer loads and stores as well
-    pipeline_min_mb: int = 48          # ... from this size on
+    pipeline_min_mb: int = 96          # ... from this size on
     pipeline_chunk_kb: int = 8192      # largest chunk of that kernel
     pipeline_slots: int = 16           # chunks that its ring inside the staging slice holds
-    pipeline_copiers: int = 128        # its blocks that copy
-    pipeline_reducers: int = 0         # its blocks that reduce (0 = 32 where the switch reduces, else 48)
+    pipeline_copiers: int = 0          # its blocks that copy (0 = what half of the SMs leaves beside the reducers)
+    pipeline_reducers: int = 0         # its blocks that reduce (0 = 16 where the switch reduces, else 32; draining: 32 / 48)
     pipeline_streaming: bool = True    # its reducer blocks never drain between chunks (one warp waits and publishes)
-    pipeline_rgroups: int = 8          # groups of reducer blocks; group g takes the chunks c with c % groups == g
+    pipeline_rgroups: int = 8          # draining reducers: groups of blocks; group g takes the chunks c with c % groups == g
     pipeline_cgroups: int = 4          # groups of copier blocks
     device_timing_every: int = 0       # DistributedOptimizer: time every bucket launch of every Nth step on the device
                                        # (CUDA events; records in stats() carry device_us and bus GB/s); 0 = never

@@ -403,7 +403,7 @@ int bc_set_option(const char* key, long long value) {
   } else if (k == "pipeline_slots") {
     comm().mutable_config().pipeline_slots = (int)std::min<long long>(std::max<long long>(value, 2), 1024);
   } else if (k == "pipeline_copiers") {
-    comm().mutable_config().pipeline_copiers = (int)std::min<long long>(std::max<long long>(value, 1), 200);
+    comm().mutable_config().pipeline_copiers = (int)std::min<long long>(std::max<long long>(value, 0), 200);
   } else if (k == "pipeline_streaming") {
     comm().mutable_config().pipeline_streaming = value != 0;
   } else if (k == "pipeline_rgroups") {

@@ -33,11 +33,11 @@ struct CommConfig {
   // Tensors outside symmetric memory in one launch whose blocks have roles (staged_pipeline.cu):
   // 0 = off, 1 = where the switch reduces (NVLS), 2 = also with peer loads and stores.
   int staged_pipeline = 1;
-  size_t pipeline_min_bytes = 48u << 20;
+  size_t pipeline_min_bytes = 96u << 20;
   size_t pipeline_chunk_bytes = 8u << 20;   // upper bound of a chunk (see plan_pipeline)
   int pipeline_slots = 16;                  // chunks that the staging ring holds
-  int pipeline_copiers = 128;               // blocks that copy in and out (at most the SMs that the reducers leave)
-  int pipeline_reducers = 0;                // blocks that reduce; 0 = 32 where the switch reduces, else 48
+  int pipeline_copiers = 0;                 // blocks that copy in and out; 0 = what half of the SMs leaves beside the reducers
+  int pipeline_reducers = 0;                // blocks that reduce; 0 = 16 where the switch reduces, else 32 (draining: 32 / 48)
   int pipeline_rgroups = 8;                 // groups of reducer blocks (one chunk each at a time); streaming: 1
   bool pipeline_streaming = true;           // reducer blocks that never drain between chunks (staged_pipeline.cu)
   int pipeline_cgroups = 4;                 // groups of copier blocks

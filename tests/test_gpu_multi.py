@@ -474,8 +474,8 @@ def test_large_private_tensors_go_through_both_lanes(world):
 
 @pytest.mark.skipif(_ngpu() < 4, reason="the switch reduces only in groups of four or more GPUs")
 def test_large_private_tensors_go_through_the_staged_pipeline_kernel():
-    # From 48 MiB on an ordinary tensor is reduced by ONE launch whose copier blocks and reducer
-    # blocks work on different chunks of a ring in the staging slice. Integer-valued floats make
+    # A large ordinary tensor (by default from 96 MiB; here from 32 MiB) is reduced by ONE launch
+    # whose copier blocks and reducer blocks work on different chunks of a ring in the staging slice. Integer-valued floats make
     # the sums exact: odd element counts (a tail below 16 bytes), fp32 and bf16, sum and average,
     # several calls in a row (the progress words run on), and the same tensors with that kernel
     # switched off must give bit-identical results. Four ranks: the group size at which the kernel
@@ -484,6 +484,7 @@ def test_large_private_tensors_go_through_the_staged_pipeline_kernel():
     res = run("""
     from tensorflow_allreduce_b200 import _lib
     bc.init()
+    _lib.lib().bc_set_option(b"pipeline_min_bytes", 32 << 20)
     bad = []
     launches = []
     for dtype, n in ((torch.float32, (13 << 20) + 3), (torch.bfloat16, (40 << 20) + 5), (torch.float32, (96 << 20) + 1)):
