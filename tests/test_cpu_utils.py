@@ -569,3 +569,26 @@ def test_bucket_plan_of_a_recurrent_stack_follows_the_layers():
             assert layers == {(4 - i // 2, 1 - i % 2)}                   # layer 4 reverse first, layer 0 forward last
             assert (hi - lo) * 4 <= 40 << 20
         assert len(ranges) == (11 if biases_last else 10)
+
+
+def test_settings_come_from_the_environment_and_overrides(monkeypatch):
+    # Every field of Config has a BC_* variable; overrides given in code win over the environment,
+    # None leaves a field alone. The staged pipeline's defaults are the conservative ones: on where
+    # the switch reduces, from 96 MiB, copiers sized by the library (0 = half of the SMs).
+    from tensorflow_allreduce_b200.config import Config
+
+    for name in ("BC_STAGED_PIPELINE", "BC_PIPELINE_MIN_MB", "BC_PIPELINE_COPIERS", "BC_PIPELINE_CGROUPS", "BC_STAGING_MB", "BC_NVLS"):
+        monkeypatch.delenv(name, raising=False)
+    c = Config.from_env()
+    assert (c.staged_pipeline, c.pipeline_min_mb, c.pipeline_copiers, c.pipeline_cgroups, c.pipeline_streaming) == (1, 96, 0, 4, True)
+    assert c.staging_mb == 1024 and c.nvls is True
+    monkeypatch.setenv("BC_STAGED_PIPELINE", "2")
+    monkeypatch.setenv("BC_PIPELINE_COPIERS", "128")
+    monkeypatch.setenv("BC_PIPELINE_MIN_MB", "48")
+    monkeypatch.setenv("BC_PIPELINE_STREAMING", "0")
+    monkeypatch.setenv("BC_STAGING_MB", "64")
+    monkeypatch.setenv("BC_NVLS", "0")
+    c = Config.from_env(staging_mb=None, heap_mb=512)
+    assert (c.staged_pipeline, c.pipeline_copiers, c.pipeline_min_mb, c.pipeline_streaming) == (2, 128, 48, False)
+    assert c.staging_mb == 64 and c.heap_mb == 512 and c.nvls is False
+    assert Config.from_env(staging_mb=8).staging_mb == 8
