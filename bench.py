@@ -238,6 +238,8 @@ def run_arm(a, impl: str, rnn: str, device, rank: int, world: int, local: int, w
         for _ in range(a.steps):
             batch_, ev = nxt
             torch.cuda.current_stream().wait_event(ev)
+            for t in batch_:                          # allocated on the copy stream, read on this one
+                t.record_stream(torch.cuda.current_stream())
             loss = step(batch_)
             nxt = fetch()                            # the next step's inputs travel while this step computes
             loss_host = loss.item()                  # device -> host read of the step's result
