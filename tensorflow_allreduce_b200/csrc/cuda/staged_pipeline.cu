@@ -10,18 +10,37 @@
 // (tensorflow/contrib/mpi_collectives/ring.h:136-228, ring.cu.cc:41-66): one D2D copy, then N-1
 // send / receive / accumulate steps with a stream synchronise each.
 //
-// Synchronisation. Progress words live in every rank's signal pad, per peer q and group:
+// Synchronisation. Progress words live in every rank's signal pad, per peer q and group of blocks:
 //   staged[q]  = chunks that rank q has copied into its staging buffer,
 //   reduced[q] = chunks of which rank q has reduced its share,
 // counted from `base` on (the host adds up what all launches of a channel contribute, so the
-// words only grow and need no reset). The last copier block that finishes chunk c on a rank (a local
-// arrival counter tells) publishes staged = base + c + 1 into every rank's pad with
-// st.release.sys; reducers wait until all P staged words have reached their chunk; the last
-// reducer block that finishes chunk c publishes reduced the same way; copiers wait for all P
-// reduced words before they copy chunk c out. Nobody waits at a barrier: ranks and roles drift
-// apart as far as the data allows. A rank's kernel ends only after its last copy-out, i.e.
+// words only grow and need no reset). The last copier block that finishes chunk c on a rank (a
+// local arrival counter tells) publishes "staged" into every rank's pad: one system-scope fence,
+// then a plain store per peer. Reducers wait until all P staged words have reached their chunk;
+// the last reducer block that finishes chunk c publishes "reduced" the same way; copiers wait for
+// all P reduced words before they copy chunk c out. Nobody waits at a barrier: ranks and roles
+// drift apart as far as the data allows. A rank's kernel ends only after its last copy-out, i.e.
 // after every rank has reduced every chunk, so no peer reads this rank's staging buffer any
 // more when the next launch overwrites it. Every wait is bounded (status word, early return).
+//
+// The staging buffer is a ring of `slots` chunks: chunk c lives in slot c % slots, so one launch
+// takes a tensor of any size through a staging area of a few tens of MiB. A copier thread
+// handles the same offsets of a slot for every chunk (`slots` and the lag of the copy-out are
+// multiples of `cgroups`, so a slot always belongs to the same group of copiers), copies chunk c
+// out before it copies chunk c + slots in (the copy-out trails the copy-in by fewer chunks than
+// the ring has slots), and has by then seen every rank's "reduced" word for chunk c: nothing in
+// a slot is overwritten while anybody still needs it.
+//
+// Groups. The copier blocks form `cgroups` groups; group g takes the chunks c with
+// c % cgroups == g, so that several chunks are on their way at once and the pause of one group
+// between two chunks (publish, wait) is covered by the others. Reducer blocks come in two kinds:
+// draining ones (`streaming` = 0: wait, reduce, publish chunk by chunk, in `rgroups` groups that
+// hide one another's pauses; 4 GPUs, 1 GiB fp32 in 2 MiB chunks: 6.74 ms with one group of 16
+// blocks, 2.74 ms with eight groups of 4) and streaming ones (below: a block never pauses;
+// 2.45 ms), which the library uses.
+//
+// All blocks of a launch must be resident at once (reducers and copiers wait for one another),
+// one block per SM (`__launch_bounds__(544, 1)`); the host sizes the grid accordingly.
 #include "collectives.h"
 #include "device_prims.cuh"
 
