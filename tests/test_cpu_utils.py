@@ -592,3 +592,34 @@ def test_settings_come_from_the_environment_and_overrides(monkeypatch):
     assert (c.staged_pipeline, c.pipeline_copiers, c.pipeline_min_mb, c.pipeline_streaming) == (2, 128, 48, False)
     assert c.staging_mb == 64 and c.heap_mb == 512 and c.nvls is False
     assert Config.from_env(staging_mb=8).staging_mb == 8
+
+
+def test_sweep_tables_show_every_arm_and_the_best_of_this_library():
+    # bench/sweep_collectives.py renders its rows as markdown: one table per operation and dtype,
+    # a time and a bandwidth column per arm that has numbers, the best of this library's arms as a
+    # fraction of the measured and of the nominal link rate, and the correctness flags.
+    import importlib.util
+    import os
+
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench", "sweep_collectives.py")
+    spec = importlib.util.spec_from_file_location("sweep_collectives", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    rows = [
+        {"op": "allreduce", "dtype": "fp32", "bytes": 64 << 20, "ours_direct_ms": 0.1628, "ours_direct_busbw": 618.3,
+         "ours_private_ms": 0.1821, "ours_private_busbw": 552.9, "ours_nopipeline_ms": 0.1929, "ours_nopipeline_busbw": 521.9,
+         "nccl_ms": 0.18, "nccl_busbw": 548.1, "direct_correct": True, "private_correct": True, "nopipeline_correct": False},
+        {"op": "allreduce", "dtype": "fp32", "bytes": 1 << 10, "ours_direct_ms": 0.0173, "ours_direct_busbw": 0.1, "nccl_busbw": 0.1},
+        {"op": "allgather", "dtype": "bf16", "bytes": 255 << 20, "ours_direct_ms": 0.4, "ours_direct_busbw": 501.0, "nccl_padded_busbw": 345.0, "correct": True},
+    ]
+    text = mod.markdown(rows, 4)
+    assert "### allreduce, 4 GPUs, fp32" in text and "### allgather, 4 GPUs, bf16" in text and "### allreduce, 4 GPUs, bf16" not in text
+    head = [l for l in text.splitlines() if l.startswith("| bytes")][0]
+    for col in ("ours_direct ms", "ours_private ms", "ours_nopipeline ms", "ours_direct GB/s", "nccl GB/s", "ours / 764", "ours / 900", "correct"):
+        assert col in head, col
+    assert "ours_staged" not in head                     # no numbers, no column
+    line = [l for l in text.splitlines() if l.startswith("| 64 MiB")][0]
+    assert "618.3" in line and "0.81" in line and "0.69" in line          # best arm / 764 and / 900
+    assert "direct=ok" in line and "nopipeline=WRONG" in line
+    assert [l for l in text.splitlines() if l.startswith("| 1 KiB")][0].count("-") >= 2      # arms without a number show a dash
+    assert mod._size(255 << 20) == "255 MiB" and mod._size(1536) == "1.5 KiB" and mod._size(100) == "100 B"
