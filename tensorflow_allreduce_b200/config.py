@@ -9,7 +9,9 @@ build, `_lib.py`), `BC_GRU_TIMEOUT_S` (`ops/persistent_gru.py`), and by the nati
 `init()`: `BC_SHM` (0 = CPU tensors of ranks on one host use the socket ring instead of shared
 memory), `BC_SHM_SLOT_KB` (chunk per rank in the shared segment, default 512), `BC_NODE_GROUPS`
 (1 = build the node groups and rails of a job over several hosts for a CPU group too),
-`BC_HOSTNAME` (the host name this rank reports), `BC_SPIN_US` (how long the background thread and
+`BC_HOSTNAME` (the host name this rank reports), `BC_TWO_LEVEL_CHUNK_KB` (CPU tensors of a job over
+several hosts: chunk of the pipelined two-level allreduce, default 2048, used from four chunks on; 0 = in
+one piece), `BC_SPIN_US` (how long the background thread and
 a waiting caller keep polling after an event before they sleep; default 100, or 0 = sleep at once
 when the host has fewer than two cores per local rank).
 """

@@ -116,6 +116,7 @@ Runtime::Runtime(const RuntimeOptions& o) : opt_(o) {
   // Polling instead of sleeping pays while every thread has a core of its own (a caller and a
   // background thread per rank); on a machine with fewer cores it only takes time from the peers.
   if (const char* us = getenv("BC_SPIN_US")) spin_s_ = std::max(0, atoi(us)) * 1e-6;
+  if (const char* kb = getenv("BC_TWO_LEVEL_CHUNK_KB")) two_level_chunk_bytes_ = (size_t)std::max(0, atoi(kb)) << 10;
   else if (std::thread::hardware_concurrency() < 2u * (unsigned)std::max(1, t_.local_size)) spin_s_ = 0;
   wake_fd_ = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
   BC_CHECK(wake_fd_ >= 0, "eventfd failed");
@@ -669,9 +670,18 @@ void Runtime::perform_allreduce(OpRecord& r) {
     if (r.in != r.out && count) memcpy(r.out, r.in, count * dtype_size(r.dtype));
     if (shm_ && node_) {
       // several hosts with several ranks each: shared memory inside the host, rails between hosts
-      ShmLocalLevel local(*shm_, r.out, deadline);
-      cpu_staging_.resize(slice_len(count, node_->local_size, 0) * dtype_size(r.dtype) + 16);
-      bc::two_level_allreduce(*node_, local, cpu_staging_.data(), count, r.dtype, scale, idiv, r.red, deadline, r.two_level_s);
+      const size_t es = dtype_size(r.dtype);
+      const size_t chunk_elems = two_level_chunk_bytes_ / es;
+      if (chunk_elems > 0 && count >= 4 * chunk_elems) {
+        // large tensors: chunk by chunk, the step between the hosts on a helper thread beside the steps inside the host
+        cpu_staging_.resize(2 * slice_len(chunk_elems, node_->local_size, 0) * es + 16);
+        bc::two_level_allreduce_pipelined(*node_, *shm_, r.out, cpu_staging_.data(), count, chunk_elems, r.dtype, scale, idiv, r.red,
+                                          deadline, r.two_level_s);
+      } else {
+        ShmLocalLevel local(*shm_, r.out, deadline);
+        cpu_staging_.resize(slice_len(count, node_->local_size, 0) * es + 16);
+        bc::two_level_allreduce(*node_, local, cpu_staging_.data(), count, r.dtype, scale, idiv, r.red, deadline, r.two_level_s);
+      }
     } else {
       cpu_ring_allreduce(t_, r.out, count, r.dtype, scale, idiv, deadline, r.red);
     }

@@ -195,6 +195,8 @@ class Runtime {
 
   std::thread thread_;
   double spin_s_ = 100e-6;            // how long the thread keeps polling after an event before it sleeps (BC_SPIN_US)
+  size_t two_level_chunk_bytes_ = 2u << 20;   // CPU tensors over several hosts: chunk of the pipelined allreduce, used from
+                                              // four chunks on (BC_TWO_LEVEL_CHUNK_KB; 0 = one piece, nothing overlaps)
   double last_event_s_ = 0;
   int wake_fd_ = -1;
   std::mutex mu_;

@@ -2,6 +2,11 @@
 
 #include <string.h>
 
+#include <condition_variable>
+#include <exception>
+#include <mutex>
+#include <thread>
+
 #include "../cpu/ring.h"
 #include "../cpu/shm_group.h"
 
@@ -26,6 +31,97 @@ void two_level_allreduce(NodeGroup& g, LocalLevel& local, void* staging, size_t 
     seconds[1] = t2 - t1;
     seconds[2] = now_s() - t2;
   }
+}
+
+void two_level_allreduce_pipelined(NodeGroup& g, ShmGroup& shm, void* tensor, void* staging, size_t count, size_t chunk_elems,
+                                   DType dtype, double scale, int64_t int_divisor, ReduceOp red, double deadline, double* seconds) {
+  const size_t e = dtype_size(dtype);
+  const int L = g.local_size;
+  BC_CHECK(chunk_elems > 0, "two-level allreduce: empty chunks");
+  const size_t K = (count + chunk_elems - 1) / chunk_elems;
+  char* t = (char*)tensor;
+  char* buf[2] = {(char*)staging, (char*)staging + slice_len(chunk_elems, L, 0) * e};
+  auto chunk_begin = [&](size_t c) { return c * chunk_elems; };
+  auto chunk_len = [&](size_t c) { return std::min(chunk_elems, count - c * chunk_elems); };
+
+  // What the two threads tell each other: how many chunks have been handed to the rail, how many
+  // have come back, and whether either side has given up.
+  struct {
+    std::mutex mu;
+    std::condition_variable cv;
+    size_t fetched = 0, ringed = 0;
+    bool abort = false;
+    std::exception_ptr err;
+  } st;
+
+  std::thread rail([&] {
+    for (size_t c = 0; c < K; c++) {
+      {
+        std::unique_lock<std::mutex> lk(st.mu);
+        st.cv.wait(lk, [&] { return st.fetched > c || st.abort; });
+        if (st.abort) return;
+      }
+      try {
+        // The ranks of one rail hold the same slice of their hosts' sums, so the lengths agree.
+        cpu_ring_allreduce(g.rail, buf[c & 1], slice_len(chunk_len(c), L, g.local_rank), dtype, scale, int_divisor, deadline, red);
+      } catch (...) {
+        std::lock_guard<std::mutex> lk(st.mu);
+        st.err = std::current_exception();
+        st.abort = true;
+        st.cv.notify_all();
+        return;
+      }
+      std::lock_guard<std::mutex> lk(st.mu);
+      st.ringed = c + 1;
+      st.cv.notify_all();
+    }
+  });
+
+  double spent[3] = {0, 0, 0};
+  auto gather = [&](size_t c) {   // wait for chunk c to come back over the rail, then spread it inside the host
+    double t0 = now_s();
+    {
+      std::unique_lock<std::mutex> lk(st.mu);
+      st.cv.wait(lk, [&] { return st.ringed > c || st.abort; });
+      if (st.abort) std::rethrow_exception(st.err ? st.err : std::make_exception_ptr(Error("two-level allreduce was aborted")));
+    }
+    double t1 = now_s();
+    spent[1] += t1 - t0;
+    const size_t n = chunk_len(c);
+    std::vector<int64_t> rows(L);
+    for (int i = 0; i < L; i++) rows[i] = (int64_t)slice_len(n, L, i);     // one "row" per element
+    shm.allgatherv(buf[c & 1], t + chunk_begin(c) * e, rows, e, deadline);
+    spent[2] += now_s() - t1;
+  };
+  try {
+    for (size_t c = 0; c < K; c++) {
+      const double t0 = now_s();
+      const size_t n = chunk_len(c);
+      shm.allreduce(t + chunk_begin(c) * e, n, dtype, 1.0, 1, red, deadline);
+      const size_t len = slice_len(n, L, g.local_rank);
+      // buf[c & 1] last held chunk c - 2, which was gathered in the previous round
+      if (len) memcpy(buf[c & 1], t + (chunk_begin(c) + slice_begin(n, L, g.local_rank)) * e, len * e);
+      spent[0] += now_s() - t0;
+      {
+        std::lock_guard<std::mutex> lk(st.mu);
+        st.fetched = c + 1;
+        st.cv.notify_all();
+      }
+      if (c >= 1) gather(c - 1);
+    }
+    gather(K - 1);
+  } catch (...) {
+    {
+      std::lock_guard<std::mutex> lk(st.mu);
+      st.abort = true;
+      st.cv.notify_all();
+    }
+    rail.join();     // a ring step in flight ends at its deadline at the latest
+    throw;
+  }
+  rail.join();
+  if (seconds)
+    for (int i = 0; i < 3; i++) seconds[i] = spent[i];
 }
 
 namespace {

@@ -46,8 +46,19 @@ inline size_t slice_len(size_t count, int n, int i) { return count / n + ((size_
 void two_level_allreduce(NodeGroup& g, LocalLevel& local, void* staging, size_t count, DType dtype, double scale,
                          int64_t int_divisor, ReduceOp red, double deadline, double* seconds = nullptr);
 
-// The levels inside a host for CPU tensors: the host's shared-memory group.
+// The same three steps for a CPU tensor, chunk by chunk, with the step over the rail on a helper
+// thread: while chunk c travels between the hosts, this thread reduces chunk c + 1 inside the
+// host and gathers chunk c - 1. Every rank of the job runs the same schedule, so the collectives
+// of the shared-memory group and of the rail come in the same order everywhere.
+// `staging` must hold two slices of a chunk: 2 * slice_len(chunk_elems, local_size, 0) elements.
+// `seconds`: time this thread spent inside the host before a chunk could leave, waiting for the
+// rail, and gathering.
 class ShmGroup;
+void two_level_allreduce_pipelined(NodeGroup& g, ShmGroup& shm, void* tensor, void* staging, size_t count, size_t chunk_elems,
+                                   DType dtype, double scale, int64_t int_divisor, ReduceOp red, double deadline,
+                                   double* seconds = nullptr);
+
+// The levels inside a host for CPU tensors: the host's shared-memory group.
 class ShmLocalLevel : public LocalLevel {
  public:
   ShmLocalLevel(ShmGroup& shm, void* tensor, double deadline) : shm_(shm), t_((char*)tensor), deadline_(deadline) {}

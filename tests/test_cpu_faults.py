@@ -163,3 +163,32 @@ def test_fault_specs_are_parsed_or_refused():
     """, nranks=1)
     rec = res[0][1]
     assert rec["s"] == [1.0, 1.0, 1.0] and rec["outcomes"]["ok"] >= 1 and rec["outcomes"]["refused"] >= 1
+
+
+@pytest.mark.parametrize("chunk_kb", ["0", "16"])
+def test_rank_exit_inside_a_two_level_allreduce_is_detected(chunk_kb):
+    # Two hosts of two ranks (one machine, made-up host names). Rank 3 leaves after the go-ahead of
+    # a large allreduce: its neighbour in shared memory notices that the process is gone, its
+    # partner on the rail sees the closed connection, and the failure reaches the remaining rank
+    # through them. With chunks ("16": tensors from 64 KiB on go chunk by chunk, the step between
+    # the hosts on a helper thread) the helper's error must surface on the thread that waits for it,
+    # and a thread that gives up must not leave the helper behind. Well before the 60 s deadline.
+    env = {r: {"BC_HOSTNAME": f"host{r // 2}", "LOCAL_RANK": "-1", "BC_TIMEOUT_S": "60", "BC_TWO_LEVEL_CHUNK_KB": chunk_kb,
+               "BC_FAULT": "exit_in_collective:rank=3:name=doomed"} for r in range(4)}
+    res = run("""
+    import time
+    bc.init(device="cpu")
+    bc.allreduce(torch.ones(50000), name="warm")
+    t0 = time.time()
+    try:
+        bc.allreduce(torch.ones(100000), name="doomed")
+        err = None
+    except bc.CollectiveError as e:
+        err = str(e)
+    emit(err=err, seconds=time.time() - t0, nodes=bc.n_nodes())
+    """, nranks=4, per_rank_env=env, timeout=150, expect_ok=False)
+    assert res[3][0].returncode == 42            # the injected exit
+    for r in (0, 1, 2):
+        rec = res[r][1]
+        assert rec is not None, res[r][0].stderr[-2000:]
+        assert rec["nodes"] == 2 and rec["err"] is not None and rec["seconds"] < 30, rec

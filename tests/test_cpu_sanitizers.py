@@ -20,8 +20,10 @@ def test_host_runtime_is_clean_under_sanitizer(sanitizer, transport):
         if "no C++ compiler" in str(e):
             pytest.skip(str(e))
         raise
-    # CPU tensors through the shared-memory segment (small slots: several chunks) or the socket ring
-    env = dict(os.environ, **({"BC_SHM": "0"} if transport == "ring" else {"BC_SHM_SLOT_KB": "4"}))
+    # CPU tensors through the shared-memory segment (small slots: several chunks) or the socket ring;
+    # with shared memory the two-level pass cuts its tensors into 1 KiB chunks, so that the step
+    # between the hosts runs on its helper thread beside the steps inside the host
+    env = dict(os.environ, **({"BC_SHM": "0"} if transport == "ring" else {"BC_SHM_SLOT_KB": "4", "BC_TWO_LEVEL_CHUNK_KB": "1"}))
     # second port: a second pass with 4 ranks on two host names (node groups, rails, two levels)
     r = subprocess.run([str(exe), "3", str(_free_port()), str(_free_port())], capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-6000:]

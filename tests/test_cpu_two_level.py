@@ -149,22 +149,26 @@ bc.shutdown()
 """
 
 
-@pytest.mark.parametrize("groups", ["default", "off"])
+@pytest.mark.parametrize("groups", ["default", "pipelined", "pipelined_3x2", "off"])
 def test_public_cpu_collectives_over_fake_hosts(groups):
     # 2 hosts x 2 ranks. By default the allreduce runs in two levels (shared memory inside a host,
     # rails between hosts; small slots so that tensors span many chunks); with BC_NODE_GROUPS=0 it
-    # is the single ring over all ranks.
-    env = {r: {"BC_HOSTNAME": f"host{r // 2}", "LOCAL_RANK": "-1", "BC_SHM_SLOT_KB": "4"} for r in range(4)}
-    if groups == "off":
-        for e in env.values():
+    # is the single ring over all ranks. "pipelined": chunks of 1 KiB, so that tensors from 4 KiB
+    # on go chunk by chunk with the step between the hosts on a helper thread (the library's
+    # chunks are 2 MiB); also with three hosts of two ranks.
+    nranks = 6 if groups == "pipelined_3x2" else 4
+    env = {r: {"BC_HOSTNAME": f"host{r // 2}", "LOCAL_RANK": "-1", "BC_SHM_SLOT_KB": "4"} for r in range(nranks)}
+    for e in env.values():
+        if groups == "off":
             e["BC_NODE_GROUPS"] = "0"
-    res = run(PUBLIC, nranks=4, per_rank_env=env, timeout=180)
+        e["BC_TWO_LEVEL_CHUNK_KB"] = "1" if groups.startswith("pipelined") else "0"
+    res = run(PUBLIC, nranks=nranks, per_rank_env=env, timeout=180)
     for _, rec in res:
         assert rec["bad"] == []
-        assert rec["nodes"] == (2 if groups == "default" else 1)
-        assert rec["algos"] == (["cpu_shm"] if groups == "default" else ["cpu_ring"])
+        assert rec["nodes"] == (1 if groups == "off" else nranks // 2)
+        assert rec["algos"] == (["cpu_ring"] if groups == "off" else ["cpu_shm"])
         # the records of a two-level allreduce carry the time of its three steps
-        if groups == "default":
+        if groups != "off":
             assert len(rec["phases"]) == 3 and all(p > 0 for p in rec["phases"])
         else:
             assert rec["phases"] is None
