@@ -6,6 +6,7 @@ data through shared memory; `BC_SHM=0` times the socket ring (loopback TCP) inst
     python -m tensorflow_allreduce_b200.launch --nproc 2 --cpu bench/cpu_ring_bench.py [--max-mb 64]
     BC_SHM=0 python -m tensorflow_allreduce_b200.launch --nproc 2 --cpu bench/cpu_ring_bench.py
     ... bench/cpu_ring_bench.py --gloo        (adds torch.distributed's gloo all_reduce, in place, as a comparator)
+    ... --nproc 4 --cpu bench/cpu_ring_bench.py --fake-hosts 2      (two made-up hosts of two ranks: two levels)
 
 Wall-clock time per call (host timers, maximum over ranks) through the public, name-keyed API, so
 the coordinator round trip is included; `allreduce_inplace_ms` is the same without an output to
@@ -32,7 +33,14 @@ def main():
     ap.add_argument("--max-mb", type=int, default=64)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--gloo", action="store_true", help="also time torch.distributed's gloo backend on the same tensors")
+    ap.add_argument("--fake-hosts", type=int, default=1, help="the ranks report this many host names (equal shares): the allreduce "
+                    "then runs in two levels, shared memory inside a \"host\" and rails between them (BC_TWO_LEVEL_CHUNK_KB=0: in one piece)")
+    ap.add_argument("--min-kb", type=int, default=1)
     a = ap.parse_args()
+    if a.fake_hosts > 1:
+        rank_, world_ = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+        os.environ["BC_HOSTNAME"] = f"host{rank_ // (world_ // a.fake_hosts)}"
+        os.environ["LOCAL_RANK"] = "-1"
     bc.init(device="cpu")
     rank, P = bc.rank(), bc.size()
     if a.gloo:
@@ -40,7 +48,7 @@ def main():
 
         port = bc.host_allgather(__import__("tensorflow_allreduce_b200.utils.spawn", fromlist=["free_port"]).free_port())[0]
         dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=P)
-    s = 1 << 10
+    s = a.min_kb << 10
     while s <= a.max_mb << 20:
         n = s // 4
         x = torch.full((n,), float(rank + 1))
